@@ -1,0 +1,320 @@
+// Memory-bound ops of the step: embedding gather, (residual add +) RMSNorm,
+// per-head q/k RMSNorm + RoPE + cache write, SiLU-mul.  Every kernel is a
+// template over the storage type (float for the true 32-bit path,
+// __nv_bfloat16 for serving) and takes every size as an argument.
+#include "common.cuh"
+
+namespace pih {
+
+// ---------------------------------------------------------------------------
+// embedding: out[t,:] = table[ids[t],:]    (reference: qwen_bf16_primitives.cu:247-262,
+// which skips ids outside the table silently; here they are reported)
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void embedding_kernel(const T* __restrict__ table, const int* __restrict__ ids,
+                                 T* __restrict__ out, int rows, int hidden, int vocab,
+                                 uint32_t* error) {
+  const int t = blockIdx.x;
+  if (t >= rows) return;
+  int id = ids[t];
+  const bool bad = id < 0 || id >= vocab;
+  if (bad) {
+    if (threadIdx.x == 0) publish_error(error, kTokenOutOfVocabulary);
+    id = 0;
+  }
+  const T* src = table + static_cast<size_t>(id) * hidden;
+  T* dst = out + static_cast<size_t>(t) * hidden;
+  const int row_bytes = hidden * static_cast<int>(sizeof(T));
+  if (row_bytes % 16 == 0) {
+    const uint4* s4 = reinterpret_cast<const uint4*>(src);
+    uint4* d4 = reinterpret_cast<uint4*>(dst);
+    for (int i = threadIdx.x; i < row_bytes / 16; i += blockDim.x)
+      d4[i] = bad ? make_uint4(0, 0, 0, 0) : s4[i];
+  } else {
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x)
+      dst[i] = bad ? from_float<T>(0.0f) : src[i];
+  }
+}
+
+// ---------------------------------------------------------------------------
+// (residual add +) RMSNorm, one block per output row.
+//   in place (rows == nullptr): x[r] = round(x[r] + delta[r]) is stored back and normed
+//   gathered (rows != nullptr): out[i] = norm(round(x[rows[i]] + delta[rows[i]])), x untouched
+// y = round( (v * 1/sqrt(mean(v^2) + eps)) * w )      (qwen_bf16_primitives.cu:285-324)
+// ---------------------------------------------------------------------------
+template <typename T, typename W>
+__global__ void rmsnorm_kernel(T* __restrict__ x, const T* __restrict__ delta,
+                               const W* __restrict__ weight, T* __restrict__ out,
+                               const int* __restrict__ rows, int width, float eps) {
+  __shared__ float scratch[33];
+  const int o = blockIdx.x;
+  const size_t r = rows != nullptr ? static_cast<size_t>(rows[o]) : static_cast<size_t>(o);
+  T* xr = x + r * width;
+  const T* dr = delta != nullptr ? delta + r * width : nullptr;
+  const bool write_back = delta != nullptr && rows == nullptr;
+  float ss = 0.0f;
+  for (int c = threadIdx.x; c < width; c += blockDim.x) {
+    float v = to_float<T>(xr[c]);
+    if (dr != nullptr) {
+      v = round_to<T>(v + to_float<T>(dr[c]));
+      if (write_back) xr[c] = from_float<T>(v);
+    }
+    ss += v * v;
+  }
+  ss = block_sum(ss, scratch);
+  const float scale = 1.0f / sqrtf(ss / static_cast<float>(width) + eps);
+  T* yr = out + static_cast<size_t>(o) * width;
+  for (int c = threadIdx.x; c < width; c += blockDim.x) {
+    float v = to_float<T>(xr[c]);                      // after write_back this is the rounded sum
+    if (dr != nullptr && !write_back) v = round_to<T>(v + to_float<T>(dr[c]));
+    yr[c] = from_float<T>((v * scale) * to_float<W>(weight[c]));
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Per-head RMSNorm of q and k, rotate-half RoPE from a (cos, sin) table, and the
+// write of k and v into the paged cache: one warp per (row, head slot).
+//   slot <  heads                      : q head, normed and rotated in place
+//   slot <  heads + kv_heads           : k head, normed, rotated, stored in place and in the cache
+//   slot <  heads + 2 kv_heads         : v head, copied into the cache
+// Rounding as the reference's separate kernels give it: once after the norm,
+// once after the rotation (qwen_bf16_primitives.cu:285-347), cache write is a copy (:468-517).
+// cache layout: [page][2][kv_head][page_size][head_dim]
+// ---------------------------------------------------------------------------
+template <typename T, typename W>
+__global__ void qk_norm_rope_kv_kernel(T* __restrict__ qkv, int row_stride, int rows, int heads,
+                                       int kv_heads, int head_dim, const W* __restrict__ q_w,
+                                       const W* __restrict__ k_w, float eps,
+                                       const float* __restrict__ rope, int rotary_dim, int max_pos,
+                                       const int* __restrict__ positions,
+                                       const int* __restrict__ slot_mapping, T* __restrict__ cache,
+                                       int page_size, int num_pages, int write_kv, uint32_t* error) {
+  extern __shared__ float smem[];
+  const int warps_per_block = blockDim.x >> 5;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int slots = heads + (write_kv ? 2 * kv_heads : 0);
+  const long long item = static_cast<long long>(blockIdx.x) * warps_per_block + warp;
+  if (item >= static_cast<long long>(rows) * slots) return;
+  const int t = static_cast<int>(item / slots);
+  const int slot = static_cast<int>(item % slots);
+  float* buf = smem + warp * head_dim;
+  T* src = qkv + static_cast<size_t>(t) * row_stride + static_cast<size_t>(slot) * head_dim;
+
+  const bool is_q = slot < heads;
+  const bool is_k = !is_q && slot < heads + kv_heads;
+  const bool is_v = !is_q && !is_k;
+  T* dst_cache = nullptr;
+  if (!is_q) {
+    const int m = slot_mapping[t];
+    if (m < 0 || m >= num_pages * page_size) {
+      if (lane == 0) publish_error(error, kRowWithoutPage);
+    } else {
+      const int page = m / page_size, off = m % page_size;
+      const int h = is_k ? slot - heads : slot - heads - kv_heads;
+      dst_cache = cache + ((static_cast<size_t>(page) * 2 + (is_k ? 0 : 1)) * kv_heads + h) *
+                              page_size * head_dim + static_cast<size_t>(off) * head_dim;
+    }
+  }
+  if (is_v) {
+    if (dst_cache != nullptr)
+      for (int c = lane; c < head_dim; c += 32) dst_cache[c] = src[c];
+    return;
+  }
+  const W* w = is_q ? q_w : k_w;
+  // norm
+  float ss = 0.0f;
+  for (int c = lane; c < head_dim; c += 32) {
+    const float v = to_float<T>(src[c]);
+    buf[c] = v;
+    ss += v * v;
+  }
+  if (w != nullptr) {
+    ss = warp_sum(ss);
+    const float scale = 1.0f / sqrtf(ss / static_cast<float>(head_dim) + eps);
+    for (int c = lane; c < head_dim; c += 32)
+      buf[c] = round_to<T>((buf[c] * scale) * to_float<W>(w[c]));
+  }
+  __syncwarp();
+  // rotation
+  const int half = rotary_dim / 2;
+  int pos = positions[t];
+  if (rope != nullptr && (pos < 0 || pos >= max_pos)) {
+    if (lane == 0) publish_error(error, kBadPosition);
+    pos = 0;
+  }
+  const float* cs = rope != nullptr ? rope + static_cast<size_t>(pos) * half * 2 : nullptr;
+  for (int c = lane; c < head_dim; c += 32) {
+    float v = buf[c];
+    if (cs != nullptr && c < rotary_dim) {
+      if (c < half) {
+        v = buf[c] * cs[2 * c] - buf[c + half] * cs[2 * c + 1];
+      } else {
+        const int p = c - half;
+        v = buf[c] * cs[2 * p] + buf[p] * cs[2 * p + 1];
+      }
+    }
+    const T r = from_float<T>(v);
+    src[c] = r;
+    if (dst_cache != nullptr) dst_cache[c] = r;
+  }
+}
+
+// ---------------------------------------------------------------------------
+// SiLU-mul: out[t,i] = round( (g / (1 + exp(-g))) * u ), g = in[t,i], u = in[t,I+i]
+// (qwen_bf16_primitives.cu:274-283)
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ out, long long rows,
+                                int inter) {
+  const long long total = rows * inter;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long t = i / inter;
+    const int c = static_cast<int>(i - t * inter);
+    const float g = to_float<T>(gate_up[t * 2 * inter + c]);
+    const float u = to_float<T>(gate_up[t * 2 * inter + inter + c]);
+    out[i] = from_float<T>((g / (1.0f + expf(-g))) * u);
+  }
+}
+
+// gather rows of a matrix: out[i,:] = in[rows[i],:]
+template <typename T>
+__global__ void gather_rows_kernel(const T* __restrict__ in, const int* __restrict__ rows,
+                                   T* __restrict__ out, int width) {
+  const T* s = in + static_cast<size_t>(rows[blockIdx.x]) * width;
+  T* d = out + static_cast<size_t>(blockIdx.x) * width;
+  for (int c = threadIdx.x; c < width; c += blockDim.x) d[c] = s[c];
+}
+
+}  // namespace pih
+
+using namespace pih;
+
+extern "C" int pih_embedding(int dtype, const void* table, const int* ids, void* out, int rows,
+                             int hidden, int vocab, uint32_t* error, void* stream) {
+  if (rows <= 0) return 0;
+  if (hidden <= 0 || vocab <= 0) return PIH_ERR_BAD_ARGUMENT;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int threads = 128;
+  if (dtype == PIH_F32)
+    embedding_kernel<float><<<rows, threads, 0, s>>>(static_cast<const float*>(table), ids,
+                                                     static_cast<float*>(out), rows, hidden, vocab, error);
+  else if (dtype == PIH_BF16)
+    embedding_kernel<__nv_bfloat16><<<rows, threads, 0, s>>>(
+        static_cast<const __nv_bfloat16*>(table), ids, static_cast<__nv_bfloat16*>(out), rows, hidden,
+        vocab, error);
+  else
+    return PIH_ERR_BAD_ARGUMENT;
+  PIH_LAUNCH_CHECK();
+  return 0;
+}
+
+template <typename T, typename W>
+static int launch_rmsnorm(void* x, const void* delta, const void* weight, void* out, const int* rows,
+                          int out_rows, int width, float eps, cudaStream_t s) {
+  int threads = 256;
+  if (width <= 128) threads = 32;
+  else if (width <= 512) threads = 128;
+  else if (width >= 4096) threads = 512;
+  rmsnorm_kernel<T, W><<<out_rows, threads, 0, s>>>(static_cast<T*>(x), static_cast<const T*>(delta),
+                                                    static_cast<const W*>(weight), static_cast<T*>(out),
+                                                    rows, width, eps);
+  PIH_LAUNCH_CHECK();
+  return 0;
+}
+
+// weight_dtype may be PIH_F32 with a bf16 stream (a norm weight stored in 32-bit stays so)
+extern "C" int pih_rmsnorm(int dtype, int weight_dtype, void* x, const void* delta, const void* weight,
+                           void* out, const int* rows, int out_rows, int width, float eps,
+                           void* stream) {
+  if (out_rows <= 0) return 0;
+  if (width <= 0 || !(eps > 0.0f)) return PIH_ERR_BAD_ARGUMENT;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (dtype == PIH_F32 && weight_dtype == PIH_F32)
+    return launch_rmsnorm<float, float>(x, delta, weight, out, rows, out_rows, width, eps, s);
+  if (dtype == PIH_BF16 && weight_dtype == PIH_BF16)
+    return launch_rmsnorm<__nv_bfloat16, __nv_bfloat16>(x, delta, weight, out, rows, out_rows, width, eps, s);
+  if (dtype == PIH_BF16 && weight_dtype == PIH_F32)
+    return launch_rmsnorm<__nv_bfloat16, float>(x, delta, weight, out, rows, out_rows, width, eps, s);
+  return PIH_ERR_BAD_ARGUMENT;
+}
+
+template <typename T, typename W>
+static int launch_qk(void* qkv, int row_stride, int rows, int heads, int kv_heads, int head_dim,
+                     const void* q_w, const void* k_w, float eps, const float* rope, int rotary_dim,
+                     int max_pos, const int* positions, const int* slot_mapping, void* cache,
+                     int page_size, int num_pages, int write_kv, uint32_t* error, cudaStream_t s) {
+  const int warps = 4;
+  const long long items = static_cast<long long>(rows) * (heads + (write_kv ? 2 * kv_heads : 0));
+  const long long blocks = (items + warps - 1) / warps;
+  const size_t smem = static_cast<size_t>(warps) * head_dim * sizeof(float);
+  qk_norm_rope_kv_kernel<T, W><<<static_cast<unsigned>(blocks), warps * 32, smem, s>>>(
+      static_cast<T*>(qkv), row_stride, rows, heads, kv_heads, head_dim, static_cast<const W*>(q_w),
+      static_cast<const W*>(k_w), eps, rope, rotary_dim, max_pos, positions, slot_mapping,
+      static_cast<T*>(cache), page_size, num_pages, write_kv, error);
+  PIH_LAUNCH_CHECK();
+  return 0;
+}
+
+extern "C" int pih_qk_norm_rope_kv_write(int dtype, int weight_dtype, void* qkv, int row_stride, int rows,
+                                         int heads, int kv_heads, int head_dim, const void* q_w,
+                                         const void* k_w, float eps, const float* rope, int rotary_dim,
+                                         int max_pos, const int* positions, const int* slot_mapping,
+                                         void* cache, int page_size, int num_pages, int write_kv,
+                                         uint32_t* error, void* stream) {
+  if (rows <= 0) return 0;
+  if (heads <= 0 || kv_heads <= 0 || head_dim <= 0 || head_dim > 1024 || rotary_dim < 0 ||
+      rotary_dim > head_dim || (rotary_dim & 1) || page_size <= 0)
+    return PIH_ERR_BAD_ARGUMENT;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (dtype == PIH_F32 && weight_dtype == PIH_F32)
+    return launch_qk<float, float>(qkv, row_stride, rows, heads, kv_heads, head_dim, q_w, k_w, eps, rope,
+                                   rotary_dim, max_pos, positions, slot_mapping, cache, page_size,
+                                   num_pages, write_kv, error, s);
+  if (dtype == PIH_BF16 && weight_dtype == PIH_BF16)
+    return launch_qk<__nv_bfloat16, __nv_bfloat16>(qkv, row_stride, rows, heads, kv_heads, head_dim, q_w,
+                                                   k_w, eps, rope, rotary_dim, max_pos, positions,
+                                                   slot_mapping, cache, page_size, num_pages, write_kv,
+                                                   error, s);
+  if (dtype == PIH_BF16 && weight_dtype == PIH_F32)
+    return launch_qk<__nv_bfloat16, float>(qkv, row_stride, rows, heads, kv_heads, head_dim, q_w, k_w, eps,
+                                           rope, rotary_dim, max_pos, positions, slot_mapping, cache,
+                                           page_size, num_pages, write_kv, error, s);
+  return PIH_ERR_BAD_ARGUMENT;
+}
+
+extern "C" int pih_silu_mul(int dtype, const void* gate_up, void* out, long long rows, int inter,
+                            void* stream) {
+  if (rows <= 0) return 0;
+  if (inter <= 0) return PIH_ERR_BAD_ARGUMENT;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const long long total = rows * inter;
+  const int threads = 256;
+  const unsigned blocks = static_cast<unsigned>(min((total + threads - 1) / threads, 148LL * 16));
+  if (dtype == PIH_F32)
+    silu_mul_kernel<float><<<blocks, threads, 0, s>>>(static_cast<const float*>(gate_up),
+                                                      static_cast<float*>(out), rows, inter);
+  else if (dtype == PIH_BF16)
+    silu_mul_kernel<__nv_bfloat16><<<blocks, threads, 0, s>>>(
+        static_cast<const __nv_bfloat16*>(gate_up), static_cast<__nv_bfloat16*>(out), rows, inter);
+  else
+    return PIH_ERR_BAD_ARGUMENT;
+  PIH_LAUNCH_CHECK();
+  return 0;
+}
+
+extern "C" int pih_gather_rows(int dtype, const void* in, const int* rows, void* out, int out_rows,
+                               int width, void* stream) {
+  if (out_rows <= 0) return 0;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (dtype == PIH_F32)
+    gather_rows_kernel<float><<<out_rows, 128, 0, s>>>(static_cast<const float*>(in), rows,
+                                                       static_cast<float*>(out), width);
+  else if (dtype == PIH_BF16)
+    gather_rows_kernel<__nv_bfloat16><<<out_rows, 128, 0, s>>>(
+        static_cast<const __nv_bfloat16*>(in), rows, static_cast<__nv_bfloat16*>(out), width);
+  else
+    return PIH_ERR_BAD_ARGUMENT;
+  PIH_LAUNCH_CHECK();
+  return 0;
+}

@@ -1,0 +1,188 @@
+"""``CudaOps``: the calls that parts make, bound to the kernel pack through ctypes.
+
+Every method launches hand-written kernels from ``csrc/`` on the current
+CUDA stream.  Matrix products in bfloat16 go to the library (cuBLAS through
+``torch.mm``) where the reference does the same
+(src/backend/cuda/gemm_plan.cpp:192-197 runs every product through
+cuBLASLt); in float32 they run on the pack's own FMA kernel so that no
+reduced-precision mode can slip in.  Nothing here computes on the CPU.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from . import build
+
+_DT = {torch.float32: 0, torch.bfloat16: 1}
+_ERRORS = {1: "a token id is outside the vocabulary", 2: "a row maps to no cache page",
+           3: "logits contain a non-finite value", 4: "a position is outside the rotation table",
+           5: "attention softmax denominator is not positive and finite", 6: "a device wait timed out"}
+
+c_void_p, c_int, c_float, c_ll = ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_longlong
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return c_void_p(0 if t is None else t.data_ptr())
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+class CudaOps:
+    def __init__(self, device=None):
+        if not torch.cuda.is_available():
+            raise RuntimeError("pih_b200 runs on a CUDA device only (there is no CPU path), "
+                               "and torch.cuda.is_available() is False")
+        self.device = torch.device(device if device is not None else "cuda:0")
+        if self.device.type != "cuda":
+            raise RuntimeError(f"pih_b200 runs on a CUDA device only, got {self.device}")
+        major, minor = torch.cuda.get_device_capability(self.device)
+        if major != 10:
+            raise RuntimeError(f"the kernel pack is built for sm_100a; this device is sm_{major}{minor}")
+        path = build.library_path()
+        try:
+            self.lib = ctypes.CDLL(path)
+        except OSError as e:
+            raise RuntimeError(f"pih_b200: the kernel pack {path} could not be loaded: {e}") from None
+        self.library_path = path
+        self._error = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self.launches = 0
+        self._declare()
+
+    # -- plumbing ---------------------------------------------------------------
+    def _declare(self) -> None:
+        lib = self.lib
+        for name in ("pih_embedding", "pih_rmsnorm", "pih_qk_norm_rope_kv_write", "pih_silu_mul",
+                     "pih_gather_rows", "pih_gemm_simt", "pih_paged_attention_generic", "pih_argmax",
+                     "pih_sample"):
+            getattr(lib, name).restype = c_int
+
+    def _stream(self):
+        return c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
+
+    def _check(self, rc: int, what: str) -> None:
+        self.launches += 1
+        if rc == 0:
+            return
+        if rc == -1:
+            raise KernelError(f"{what}: bad argument")
+        if rc == -2:
+            raise KernelError(f"{what}: this size is not supported by the kernel")
+        raise KernelError(f"{what}: CUDA error {rc}")
+
+    def check_errors(self) -> None:
+        """Read the device error word (synchronises); raise if a kernel reported something."""
+        code = int(self._error.item())
+        if code:
+            self._error.zero_()
+            raise KernelError(f"a kernel reported: {_ERRORS.get(code, f'error code {code}')}")
+
+    def _err(self):
+        return c_void_p(self._error.data_ptr())
+
+    # -- ops ----------------------------------------------------------------------
+    def embedding(self, table: torch.Tensor, ids: torch.Tensor) -> torch.Tensor:
+        rows, (vocab, hidden) = ids.shape[0], table.shape
+        out = torch.empty(rows, hidden, dtype=table.dtype, device=table.device)
+        rc = self.lib.pih_embedding(_DT[table.dtype], _ptr(table), _ptr(ids), _ptr(out), rows, hidden, vocab,
+                                    self._err(), self._stream())
+        self._check(rc, "embedding")
+        return out
+
+    def rmsnorm(self, x: torch.Tensor, weight: torch.Tensor, eps: float, delta: Optional[torch.Tensor] = None,
+                rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+        width = x.shape[-1]
+        assert x.is_contiguous() and (delta is None or (delta.is_contiguous() and delta.shape == x.shape))
+        n_out = x.numel() // width if rows is None else rows.shape[0]
+        out = torch.empty((n_out, width) if rows is not None else x.shape, dtype=x.dtype, device=x.device)
+        rc = self.lib.pih_rmsnorm(_DT[x.dtype], _DT[weight.dtype], _ptr(x), _ptr(delta), _ptr(weight), _ptr(out),
+                                  _ptr(rows), n_out, width, c_float(eps), self._stream())
+        self._check(rc, "rmsnorm")
+        return out
+
+    def linear(self, x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+        """``x [M,K] . w [N,K]^T -> [M,N]``; fp32 accumulation; the output is
+        rounded once to ``out_dtype`` (default: the dtype of ``x``)."""
+        M, K = x.shape
+        N = w.shape[0]
+        out_dtype = out_dtype or x.dtype
+        assert w.shape[1] == K and x.dtype == w.dtype and x.stride(1) == 1 and w.stride(1) == 1
+        if x.dtype == torch.float32:
+            out = torch.empty(M, N, dtype=torch.float32, device=x.device)
+            rc = self.lib.pih_gemm_simt(0, 0, _ptr(x), _ptr(w), _ptr(out), M, N, K, c_ll(x.stride(0)),
+                                        c_ll(w.stride(0)), c_ll(N), self._stream())
+            self._check(rc, "gemm_simt")
+            return out
+        if out_dtype == torch.float32:
+            return torch.mm(x, w.t(), out_dtype=torch.float32)
+        return torch.mm(x, w.t())
+
+    def linear_plain(self, x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+        """The pack's FMA product for any supported dtype (plain twin of the tensor-core products)."""
+        M, K = x.shape
+        N = w.shape[0]
+        out_dtype = out_dtype or x.dtype
+        out = torch.empty(M, N, dtype=out_dtype, device=x.device)
+        rc = self.lib.pih_gemm_simt(_DT[x.dtype], _DT[out_dtype], _ptr(x), _ptr(w), _ptr(out), M, N, K,
+                                    c_ll(x.stride(0)), c_ll(w.stride(0)), c_ll(N), self._stream())
+        self._check(rc, "gemm_simt")
+        return out
+
+    def qk_norm_rope_kv_write(self, qkv, *, heads, kv_heads, head_dim, q_norm, k_norm, eps, rope_table,
+                              rotary_dim, positions, slot_mapping, kv_cache, write_kv) -> None:
+        rows = qkv.shape[0]
+        wd = _DT[q_norm.dtype] if q_norm is not None else _DT[qkv.dtype]
+        num_pages, page_size = kv_cache.shape[0], kv_cache.shape[3]
+        max_pos = rope_table.shape[0] if rope_table is not None else 0
+        rc = self.lib.pih_qk_norm_rope_kv_write(
+            _DT[qkv.dtype], wd, _ptr(qkv), qkv.stride(0), rows, heads, kv_heads, head_dim, _ptr(q_norm),
+            _ptr(k_norm), c_float(eps), _ptr(rope_table), rotary_dim, max_pos, _ptr(positions),
+            _ptr(slot_mapping), _ptr(kv_cache), page_size, num_pages, 1 if write_kv else 0, self._err(),
+            self._stream())
+        self._check(rc, "qk_norm_rope_kv_write")
+
+    def paged_attention(self, qkv, *, heads, kv_heads, head_dim, kv_cache, block_table, step, scale,
+                        window) -> torch.Tensor:
+        return self.paged_attention_generic(qkv, heads=heads, kv_heads=kv_heads, head_dim=head_dim,
+                                            kv_cache=kv_cache, block_table=block_table,
+                                            request_of_row=step.request_of_row, positions=step.positions,
+                                            scale=scale, window=window)
+
+    def paged_attention_generic(self, qkv, *, heads, kv_heads, head_dim, kv_cache, block_table,
+                                request_of_row, positions, scale, window) -> torch.Tensor:
+        rows = qkv.shape[0]
+        out = torch.empty(rows, heads * head_dim, dtype=qkv.dtype, device=qkv.device)
+        num_pages, page_size = kv_cache.shape[0], kv_cache.shape[3]
+        rc = self.lib.pih_paged_attention_generic(
+            _DT[qkv.dtype], _ptr(qkv), qkv.stride(0), _ptr(out), _ptr(kv_cache), _ptr(block_table),
+            block_table.shape[1], _ptr(request_of_row), _ptr(positions), rows, heads, kv_heads, head_dim,
+            page_size, num_pages, c_float(scale), int(window), self._err(), self._stream())
+        self._check(rc, "paged_attention_generic")
+        return out
+
+    def silu_mul(self, gate_up: torch.Tensor) -> torch.Tensor:
+        rows, two_i = gate_up.shape
+        inter = two_i // 2
+        out = torch.empty(rows, inter, dtype=gate_up.dtype, device=gate_up.device)
+        rc = self.lib.pih_silu_mul(_DT[gate_up.dtype], _ptr(gate_up), _ptr(out), c_ll(rows), inter, self._stream())
+        self._check(rc, "silu_mul")
+        return out
+
+    def argmax(self, logits: torch.Tensor) -> torch.Tensor:
+        rows, vocab = logits.shape
+        out = torch.empty(rows, dtype=torch.int32, device=logits.device)
+        rc = self.lib.pih_argmax(_ptr(logits), rows, vocab, _ptr(out), self._err(), self._stream())
+        self._check(rc, "argmax")
+        return out
+
+    def sample(self, logits: torch.Tensor, fparams: torch.Tensor, iparams: torch.Tensor) -> torch.Tensor:
+        rows, vocab = logits.shape
+        out = torch.empty(rows, dtype=torch.int32, device=logits.device)
+        rc = self.lib.pih_sample(_ptr(logits), rows, vocab, _ptr(fparams), _ptr(iparams), _ptr(out),
+                                 self._err(), self._stream())
+        self._check(rc, "sample")
+        return out

@@ -1,0 +1,51 @@
+"""The arrangement of parts in a layer.
+
+``prenorm``: ``h += mixer(norm_in(h)); h += ffn(norm_post(h))``
+(plugins/model-qwen3/qwen3_bf16_execution_schedule.cpp:19-39).  The block
+passes on the residual stream ``h`` together with ``delta``, the last
+sub-layer's output that is not yet added, so that the add fuses with the
+next norm wherever that norm lives (the next block's, or the model's final
+norm).
+"""
+from __future__ import annotations
+
+from .registry import Runtime, part_class, register_block
+
+
+def _sub(weights, names, prefix=""):
+    return {rel: weights[prefix + rel] for rel in names}
+
+
+@register_block("prenorm")
+class PreNormBlock:
+    @classmethod
+    def expected_tensors(cls, spec):
+        out = {}
+        n = spec.names
+        for rel, info in part_class("norm", spec.norm_in.kind).expected_tensors(spec.norm_in).items():
+            out[n["norm_in"] + rel] = info
+        for rel, info in part_class("norm", spec.norm_post.kind).expected_tensors(spec.norm_post).items():
+            out[n["norm_post"] + rel] = info
+        out.update(part_class("mixer", spec.mixer.kind).expected_tensors(spec.mixer))
+        out.update(part_class("ffn", spec.ffn.kind).expected_tensors(spec.ffn))
+        return out
+
+    def __init__(self, spec, weights, rt: Runtime):
+        self.spec = spec
+        n = spec.names
+        norm_in_cls = part_class("norm", spec.norm_in.kind)
+        norm_post_cls = part_class("norm", spec.norm_post.kind)
+        mixer_cls = part_class("mixer", spec.mixer.kind)
+        ffn_cls = part_class("ffn", spec.ffn.kind)
+        self.norm_in = norm_in_cls(
+            spec.norm_in, _sub(weights, norm_in_cls.expected_tensors(spec.norm_in), n["norm_in"]), rt)
+        self.norm_post = norm_post_cls(
+            spec.norm_post, _sub(weights, norm_post_cls.expected_tensors(spec.norm_post), n["norm_post"]), rt)
+        self.mixer = mixer_cls(spec.mixer, _sub(weights, mixer_cls.expected_tensors(spec.mixer)), rt)
+        self.ffn = ffn_cls(spec.ffn, _sub(weights, ffn_cls.expected_tensors(spec.ffn)), rt)
+
+    def forward(self, h, delta, step, cache):
+        xn = self.norm_in.add_forward(h, delta)
+        a = self.mixer.forward(xn, step, cache)
+        xn = self.norm_post.add_forward(h, a)
+        return h, self.ffn.forward(xn)

@@ -1,0 +1,5 @@
+"""Sampling: request options and the device sampler."""
+from .params import SamplingParams
+from .sampler import Sampler
+
+__all__ = ["SamplingParams", "Sampler"]

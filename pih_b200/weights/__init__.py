@@ -1,0 +1,7 @@
+"""Weights: safetensors by tensor name, checks, and the random-weights mode."""
+from .loader import WeightError, load_weights
+from .random_init import random_tensors, write_random_model
+from .safetensors_io import SafetensorsError, SafetensorsFile, write_safetensors
+
+__all__ = ["WeightError", "load_weights", "random_tensors", "write_random_model",
+           "SafetensorsError", "SafetensorsFile", "write_safetensors"]

@@ -1,0 +1,108 @@
+"""A torch stand-in for the kernel pack, for tests of HOST-SIDE logic on the CPU.
+
+The product has no CPU path.  This file lets the tests that run without a
+GPU drive the real config, loader, parts, cache manager, batch builder,
+step function and scheduler, so that faults in block tables, slot mappings
+and request bookkeeping show up before a GPU is involved.  It mirrors the
+method names of ``pih_b200.kernels.ops.CudaOps`` and nothing else of it.
+"""
+import torch
+
+
+class FakeOps:
+    launches = 0
+
+    def check_errors(self):
+        pass
+
+    def embedding(self, table, ids):
+        return table[ids.long()].clone()
+
+    def rmsnorm(self, x, weight, eps, delta=None, rows=None):
+        if rows is not None:
+            v = x[rows.long()].float()
+            if delta is not None:
+                v = (v + delta[rows.long()].float()).to(x.dtype).float()
+        else:
+            v = x.float()
+            if delta is not None:
+                v = (v + delta.float()).to(x.dtype).float()
+                x.copy_(v.to(x.dtype))
+        scale = torch.rsqrt((v * v).sum(-1, keepdim=True) / v.shape[-1] + eps)
+        return ((v * scale) * weight.float()).to(x.dtype)
+
+    def linear(self, x, w, out_dtype=None):
+        return (x.float() @ w.float().T).to(out_dtype or x.dtype)
+
+    def qk_norm_rope_kv_write(self, qkv, *, heads, kv_heads, head_dim, q_norm, k_norm, eps, rope_table,
+                              rotary_dim, positions, slot_mapping, kv_cache, write_kv):
+        T = qkv.shape[0]
+        D = head_dim
+        page_size = kv_cache.shape[3]
+
+        def norm_rope(x, w):                      # x [T, n, D]
+            v = x.float()
+            if w is not None:
+                scale = torch.rsqrt((v * v).sum(-1, keepdim=True) / D + eps)
+                v = ((v * scale) * w.float()).to(x.dtype).float()
+            if rope_table is not None:
+                cs = rope_table[positions.long()]        # [T, rot/2, 2]
+                c, s = cs[..., 0][:, None, :], cs[..., 1][:, None, :]
+                half = rotary_dim // 2
+                a, b = v[..., :half], v[..., half:rotary_dim]
+                v = torch.cat([a * c - b * s, b * c + a * s, v[..., rotary_dim:]], dim=-1)
+            return v.to(x.dtype)
+
+        q = qkv[:, :heads * D].reshape(T, heads, D)
+        qkv[:, :heads * D] = norm_rope(q, q_norm).reshape(T, heads * D)
+        if not write_kv:
+            return
+        k = qkv[:, heads * D:(heads + kv_heads) * D].reshape(T, kv_heads, D)
+        v = qkv[:, (heads + kv_heads) * D:].reshape(T, kv_heads, D)
+        k = norm_rope(k, k_norm)
+        qkv[:, heads * D:(heads + kv_heads) * D] = k.reshape(T, kv_heads * D)
+        sm = slot_mapping.long()
+        assert (sm >= 0).all()
+        page, off = sm // page_size, sm % page_size
+        kv_cache[page, 0, :, off, :] = k
+        kv_cache[page, 1, :, off, :] = v
+
+    def paged_attention(self, qkv, *, heads, kv_heads, head_dim, kv_cache, block_table, step, scale, window):
+        T, D = qkv.shape[0], head_dim
+        page_size = kv_cache.shape[3]
+        out = torch.zeros(T, heads, D, dtype=torch.float32)
+        group = heads // kv_heads
+        for t in range(T):
+            r = int(step.request_of_row[t])
+            p = int(step.positions[t])
+            first = max(0, p - window + 1) if window else 0
+            js = torch.arange(first, p + 1)
+            pages = block_table[r, (js // page_size).long()].long()
+            assert (pages >= 0).all(), "attention reads a page that was given back"
+            K = kv_cache[pages, 0, :, (js % page_size).long(), :].float()      # [n, kvh, D]
+            V = kv_cache[pages, 1, :, (js % page_size).long(), :].float()
+            q = qkv[t, :heads * D].reshape(heads, D).float()
+            for h in range(heads):
+                s = (K[:, h // group, :] @ q[h]) * scale
+                out[t, h] = torch.softmax(s, dim=0) @ V[:, h // group, :]
+        return out.reshape(T, heads * D).to(qkv.dtype)
+
+    def silu_mul(self, gate_up):
+        inter = gate_up.shape[1] // 2
+        g, u = gate_up[:, :inter].float(), gate_up[:, inter:].float()
+        return ((g / (1.0 + torch.exp(-g))) * u).to(gate_up.dtype)
+
+    def argmax(self, logits):
+        return torch.argmax(logits, dim=-1).to(torch.int32)
+
+    def sample(self, logits, fparams, iparams):
+        from plain_impl import sample
+        out = []
+        for i in range(logits.shape[0]):
+            ip = [int(v) & 0xFFFFFFFF for v in iparams[i].tolist()]
+            nsup = ip[5]
+            tok, _, _ = sample(logits[i].tolist(), temperature=float(fparams[i, 0]), top_p=float(fparams[i, 1]),
+                               top_k=ip[0] or None, seed=ip[1] | (ip[2] << 32), ordinal=ip[3] | (ip[4] << 32),
+                               suppressed=[int(v) for v in iparams[i, 6:6 + nsup].tolist()])
+            out.append(tok)
+        return torch.tensor(out, dtype=torch.int32)
