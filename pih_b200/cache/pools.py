@@ -26,6 +26,7 @@ class PagePool:
         # most recently freed page is reused first: reuse shows up early in tests
         self._free: List[int] = list(range(num_pages - 1, -1, -1))
         self._owner: List[Hashable] = [None] * num_pages
+        self.pages_handed_out = 0          # over the pool's life; exceeds num_pages once pages are reused
 
     @property
     def num_free(self) -> int:
@@ -41,6 +42,7 @@ class PagePool:
             if self._owner[p] is not None:
                 raise AssertionError(f"page {p} was free and owned by {self._owner[p]!r} at once")
             self._owner[p] = owner
+        self.pages_handed_out += count
         return pages
 
     def free(self, pages, owner: Hashable) -> None:

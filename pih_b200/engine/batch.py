@@ -65,6 +65,7 @@ class BatchBuilder:
         self.device = device
         self._pinned = None
         self._capacity = 0
+        self.last_bytes = 0
 
     def _host(self, n: int) -> torch.Tensor:
         if n > self._capacity:
@@ -111,6 +112,7 @@ class BatchBuilder:
         for off, f in zip(offsets, fields):
             if f:
                 host[off:off + len(f)] = torch.tensor(f, dtype=torch.int32)
+        self.last_bytes = total * 4
         dev = torch.empty(total, dtype=torch.int32, device=self.device)
         dev.copy_(host, non_blocking=True)
         # the pinned buffer is reused by the next build: the copy must have left it

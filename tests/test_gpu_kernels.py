@@ -1,0 +1,310 @@
+"""Each kernel of the pack alone against a plain fp32 torch reference of the
+same op, at sizes other than the engine's tiny configurations: widths and
+vocabularies that are no power of two, head sizes in steps of 16, odd
+numbers of heads and groups, several page sizes, windows."""
+import math
+
+import pytest
+import torch
+
+import plain_impl
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from pih_b200.kernels import get_ops
+    return get_ops(torch.device(DEV))
+
+
+def _tol(dtype):
+    # fp32: accumulation-order noise; bf16: one rounding of the output (2^-9 relative) plus the same noise
+    return dict(rtol=2e-5, atol=2e-6) if dtype == torch.float32 else dict(rtol=8e-3, atol=1e-3)
+
+
+def _rand(shape, dtype, seed, scale=1.0):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(shape, generator=g) * scale).to(dtype).to(DEV)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("vocab,hidden", [(100, 24), (333, 200), (50, 1027)])
+def test_embedding(ops, dtype, vocab, hidden):
+    table = _rand((vocab, hidden), dtype, 0)
+    ids = torch.randint(0, vocab, (37,), dtype=torch.int32, device=DEV)
+    out = ops.embedding(table, ids)
+    assert torch.equal(out, table[ids.long()])
+    ops.check_errors()
+
+
+def test_embedding_reports_a_bad_token(ops):
+    from pih_b200.kernels.ops import KernelError
+    table = _rand((10, 8), torch.float32, 0)
+    ids = torch.tensor([1, 10, 3], dtype=torch.int32, device=DEV)
+    ops.embedding(table, ids)
+    with pytest.raises(KernelError, match="vocabulary"):
+        ops.check_errors()
+    ops.check_errors()          # the word was cleared
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("rows,width,eps", [(5, 24, 1e-6), (33, 200, 1e-5), (7, 1027, 1e-6), (3, 5000, 1e-3)])
+def test_rmsnorm_and_fused_add(ops, dtype, rows, width, eps):
+    x = _rand((rows, width), dtype, 1, 2.0)
+    d = _rand((rows, width), dtype, 2)
+    w = (1 + 0.1 * torch.randn(width)).to(dtype).to(DEV)
+    # plain norm
+    ref = plain_impl.rms_norm(x.cpu().double(), w.cpu().double(), eps)
+    out = ops.rmsnorm(x.clone(), w, eps)
+    torch.testing.assert_close(out.cpu().double(), ref, **_tol(dtype))
+    # fused add: h is updated in place to round(h + d), and that value is normed
+    h = x.clone()
+    out = ops.rmsnorm(h, w, eps, delta=d)
+    s = (x.float() + d.float()).to(dtype)
+    assert torch.equal(h, s)
+    ref = plain_impl.rms_norm(s.cpu().double(), w.cpu().double(), eps)
+    torch.testing.assert_close(out.cpu().double(), ref, **_tol(dtype))
+    # gathered rows, h untouched
+    h = x.clone()
+    pick = torch.tensor([rows - 1, 0, rows // 2], dtype=torch.int32, device=DEV)
+    out = ops.rmsnorm(h, w, eps, delta=d, rows=pick)
+    assert torch.equal(h, x)
+    torch.testing.assert_close(out.cpu().double(), ref[pick.cpu().long()], **_tol(dtype))
+
+
+def test_rmsnorm_keeps_a_32bit_weight_with_a_bf16_stream(ops):
+    x = _rand((4, 96), torch.bfloat16, 1)
+    w = (1 + 0.1 * torch.randn(96)).to(DEV)          # float32
+    out = ops.rmsnorm(x.clone(), w, 1e-6)
+    ref = plain_impl.rms_norm(x.cpu().double(), w.cpu().double(), 1e-6)
+    torch.testing.assert_close(out.cpu().double(), ref, **_tol(torch.bfloat16))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("M,N,K", [(1, 7, 5), (37, 130, 96), (64, 64, 64), (130, 257, 1027), (3, 1000, 33)])
+def test_linear(ops, dtype, M, N, K):
+    x = _rand((M, K), dtype, 3)
+    w = _rand((N, K), dtype, 4, 0.1)
+    ref = x.cpu().double() @ w.cpu().double().T
+    for fn in (ops.linear, ops.linear_plain):
+        out = fn(x, w)
+        assert out.dtype == dtype
+        torch.testing.assert_close(out.cpu().double(), ref, **_tol(dtype))
+        out32 = fn(x, w, out_dtype=torch.float32)
+        assert out32.dtype == torch.float32
+        torch.testing.assert_close(out32.cpu().double(), ref, rtol=2e-5, atol=2e-5)
+
+
+def test_linear_fp32_rows_do_not_depend_on_the_batch(ops):
+    """The 32-bit product gives a row the same bits alone and among others."""
+    x = _rand((77, 300), torch.float32, 5)
+    w = _rand((190, 300), torch.float32, 6)
+    whole = ops.linear(x, w)
+    for lo, hi in [(0, 1), (5, 7), (30, 77)]:
+        assert torch.equal(ops.linear(x[lo:hi].contiguous(), w), whole[lo:hi])
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("rows,inter", [(3, 24), (17, 224), (5, 1031)])
+def test_silu_mul(ops, dtype, rows, inter):
+    gu = _rand((rows, 2 * inter), dtype, 7, 2.0)
+    ref = plain_impl.silu_mul(gu[:, :inter].cpu(), gu[:, inter:].cpu())
+    torch.testing.assert_close(ops.silu_mul(gu).cpu().double(), ref, **_tol(dtype))
+
+
+def _rope_table(max_pos, rotary, theta):
+    cos, sin = plain_impl.rope_angles(range(max_pos), rotary, theta)
+    return torch.stack([cos, sin], dim=-1).float().to(DEV).contiguous()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("heads,kv_heads,D,page", [(4, 2, 16, 16), (6, 1, 32, 8), (5, 5, 48, 4), (16, 8, 128, 16),
+                                                  (3, 1, 80, 32), (8, 2, 256, 16)])
+def test_qk_norm_rope_kv_write(ops, dtype, heads, kv_heads, D, page):
+    T, num_pages, eps, theta = 19, 9, 1e-5, 50000.0
+    width = (heads + 2 * kv_heads) * D
+    qkv = _rand((T, width), dtype, 8)
+    qw = (1 + 0.1 * torch.randn(D)).to(dtype).to(DEV)
+    kw = (1 + 0.1 * torch.randn(D)).to(dtype).to(DEV)
+    positions = torch.randint(0, 300, (T,), dtype=torch.int32, device=DEV)
+    slots = torch.randperm(num_pages * page)[:T].to(torch.int32).to(DEV)
+    cache = torch.zeros(num_pages, 2, kv_heads, page, D, dtype=dtype, device=DEV)
+    table = _rope_table(300, D, theta)
+    rounding = "none" if dtype == torch.float32 else "bf16"
+    x = qkv.cpu()
+    q = x[:, :heads * D].reshape(T, heads, D)
+    k = x[:, heads * D:(heads + kv_heads) * D].reshape(T, kv_heads, D)
+    v = x[:, (heads + kv_heads) * D:].reshape(T, kv_heads, D)
+    cos, sin = plain_impl.rope_angles(positions.cpu().tolist(), D, theta)
+    q_ref = plain_impl.rope_apply(plain_impl.rms_norm(q, qw.cpu(), eps, rounding), cos, sin, rounding)
+    k_ref = plain_impl.rope_apply(plain_impl.rms_norm(k, kw.cpu(), eps, rounding), cos, sin, rounding)
+    ops.qk_norm_rope_kv_write(qkv, heads=heads, kv_heads=kv_heads, head_dim=D, q_norm=qw, k_norm=kw, eps=eps,
+                              rope_table=table, rotary_dim=D, positions=positions, slot_mapping=slots,
+                              kv_cache=cache, write_kv=True)
+    ops.check_errors()
+    tol = _tol(dtype)
+    torch.testing.assert_close(qkv[:, :heads * D].cpu().double().reshape(T, heads, D), q_ref, **tol)
+    got_k = cache[(slots // page).long(), 0, :, (slots % page).long(), :].cpu().double()
+    got_v = cache[(slots // page).long(), 1, :, (slots % page).long(), :].cpu().double()
+    torch.testing.assert_close(got_k, k_ref, **tol)
+    assert torch.equal(got_v, v.double())
+    # nothing else in the cache was touched
+    mask = torch.ones(num_pages * page, dtype=torch.bool)
+    mask[slots.cpu().long()] = False
+    flat = cache.permute(0, 3, 1, 2, 4).reshape(num_pages * page, -1).cpu()
+    assert float(flat[mask].abs().max()) == 0.0
+
+
+def _dense_reference(q, k, v, scale, window):
+    return plain_impl.attention(q, k, v, scale, window)
+
+
+def _paged_setup(dtype, lens, new, heads, kv_heads, D, page, seed, num_pages=None):
+    """Requests with ``lens[r]`` tokens in the cache of which the last ``new[r]`` are this step's rows."""
+    g = torch.Generator().manual_seed(seed)
+    R = len(lens)
+    pages_per = [-(-n // page) for n in lens]
+    num_pages = num_pages or sum(pages_per) + 3
+    perm = torch.randperm(num_pages, generator=g).tolist()
+    width = max(pages_per)
+    table = torch.full((R, width), -1, dtype=torch.int32)
+    cache = torch.zeros(num_pages, 2, kv_heads, page, D, dtype=dtype)
+    ks, vs, qs, req_of_row, positions = [], [], [], [], []
+    for r in range(R):
+        k = (torch.randn(lens[r], kv_heads, D, generator=g)).to(dtype)
+        v = (torch.randn(lens[r], kv_heads, D, generator=g)).to(dtype)
+        q = (torch.randn(new[r], heads, D, generator=g)).to(dtype)
+        ks.append(k), vs.append(v), qs.append(q)
+        for i in range(pages_per[r]):
+            pg = perm.pop()
+            table[r, i] = pg
+            n = min(page, lens[r] - i * page)
+            cache[pg, 0, :, :n, :] = k[i * page:i * page + n].transpose(0, 1)
+            cache[pg, 1, :, :n, :] = v[i * page:i * page + n].transpose(0, 1)
+        req_of_row += [r] * new[r]
+        positions += list(range(lens[r] - new[r], lens[r]))
+    return dict(cache=cache.to(DEV), table=table.to(DEV), ks=ks, vs=vs, qs=qs,
+                q=torch.cat(qs).reshape(sum(new), heads * D).contiguous().to(DEV),
+                req_of_row=torch.tensor(req_of_row, dtype=torch.int32, device=DEV),
+                positions=torch.tensor(positions, dtype=torch.int32, device=DEV))
+
+
+def _attention_reference(setup, lens, new, scale, window):
+    outs = []
+    for r in range(len(lens)):
+        L, n = lens[r], new[r]
+        heads, D = setup["qs"][r].shape[1:]
+        qfull = torch.zeros(L, heads, D, dtype=torch.float64)
+        qfull[L - n:] = setup["qs"][r].double()
+        o = _dense_reference(qfull, setup["ks"][r].double(), setup["vs"][r].double(), scale, window)
+        outs.append(o[L - n:].reshape(n, heads * D))
+    return torch.cat(outs)
+
+
+ATTN_CASES = [
+    # heads, kv_heads, D, page, lens, new, window
+    (4, 2, 16, 16, [5, 40, 17], [5, 1, 17], None),
+    (6, 1, 32, 8, [33, 64, 1, 100], [2, 64, 1, 1], None),
+    (6, 1, 32, 8, [33, 64, 90, 100], [2, 64, 7, 1], 24),
+    (5, 5, 48, 4, [19, 7], [19, 3], 5),
+    (16, 8, 128, 16, [300, 129, 2048], [44, 1, 1], None),
+    (3, 1, 80, 32, [77, 31], [20, 31], 33),
+    (8, 2, 256, 16, [130], [130], None),
+    (14, 2, 64, 16, [257, 90], [1, 90], None),
+]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("case", ATTN_CASES, ids=[f"h{c[0]}kv{c[1]}d{c[2]}p{c[3]}w{c[6]}" for c in ATTN_CASES])
+def test_paged_attention_generic(ops, dtype, case):
+    heads, kv_heads, D, page, lens, new, window = case
+    s = _paged_setup(dtype, lens, new, heads, kv_heads, D, page, seed=9)
+    scale = 1.0 / math.sqrt(D)
+    out = ops.paged_attention_generic(s["q"], heads=heads, kv_heads=kv_heads, head_dim=D, kv_cache=s["cache"],
+                                      block_table=s["table"], request_of_row=s["req_of_row"],
+                                      positions=s["positions"], scale=scale, window=window or 0)
+    ops.check_errors()
+    ref = _attention_reference(s, lens, new, scale, window)
+    torch.testing.assert_close(out.cpu().double(), ref, **_tol(dtype))
+
+
+def test_attention_finds_one_far_key_and_respects_the_window_edge(ops):
+    """Random keys would hide a dropped key among hundreds: make one far key's
+    score dominate, and put it just inside and just outside the window."""
+    heads, kv_heads, D, page, L = 4, 2, 32, 16, 700
+    for dtype in DTYPES:
+        for window, far in [(None, 3), (None, 16 * 20), (64, L - 64), (64, L - 65), (1, L - 1)]:
+            s = _paged_setup(dtype, [L], [1], heads, kv_heads, D, page, seed=10)
+            q = s["qs"][0][0]                                    # [heads, D]
+            # key `far` of kv head 0 points along q head 0, strongly
+            k = s["ks"][0]
+            k[far, 0] = (q[0].float() / q[0].float().norm() * 40.0).to(dtype)
+            pg = int(s["table"][0, far // page])
+            s["cache"][pg, 0, 0, far % page] = k[far, 0].to(DEV)
+            scale = 1.0 / math.sqrt(D)
+            out = ops.paged_attention_generic(s["q"], heads=heads, kv_heads=kv_heads, head_dim=D,
+                                              kv_cache=s["cache"], block_table=s["table"],
+                                              request_of_row=s["req_of_row"], positions=s["positions"],
+                                              scale=scale, window=window or 0)
+            ref = _attention_reference(s, [L], [1], scale, window)
+            torch.testing.assert_close(out.cpu().double(), ref, **_tol(dtype))
+            inside = window is None or far > L - 1 - window
+            v_far = s["vs"][0][far, 0].double()
+            close = float((out[0, :D].cpu().double() - v_far).abs().max())
+            assert (close < 0.05) == inside, (dtype, window, far, close)
+
+
+@pytest.mark.parametrize("vocab", [256, 1000, 151936])
+def test_argmax_ties_go_to_the_lower_id(ops, vocab):
+    logits = _rand((5, vocab), torch.float32, 11)
+    logits[1, 7] = logits[1, vocab - 3] = 50.0
+    logits[2, vocab - 1] = 60.0
+    out = ops.argmax(logits).cpu().tolist()
+    ref = [int(torch.argmax(row)) for row in logits.cpu()]
+    ref[1] = 7
+    assert out == ref
+
+
+def _sample_rows(ops, logits, rows):
+    from pih_b200.sampling import Sampler, SamplingParams
+    sampler = Sampler(ops, logits.shape[1], torch.device(DEV))
+    params = [SamplingParams(temperature=t, top_p=p, top_k=k, seed=s) for (t, p, k, s, o, sup) in rows]
+    return sampler.sample(logits, params, [r[4] for r in rows], [r[5] for r in rows])
+
+
+@pytest.mark.parametrize("vocab", [384, 5000])
+def test_sampler_matches_the_plain_definition(ops, vocab):
+    g = torch.Generator().manual_seed(12)
+    S = 24
+    logits = (torch.randn(S, vocab, generator=g) * 3.0)
+    logits[3, 10] = logits[3, 20] = logits[3, 5] = 9.0          # ties at the top
+    rows = []
+    for i in range(S):
+        t = [0.0, 0.8, 1.0, 2.0][i % 4]
+        p = 1.0 if t == 0.0 else [1.0, 0.9, 0.5, 0.05][(i // 4) % 4]
+        k = None if t == 0.0 else [None, 1, 7, 50, vocab][i % 5]
+        sup = [] if i % 3 else [int(torch.argmax(logits[i])), 3]
+        rows.append((t, p, k, 1234 + i, i * 3, sup))
+    got = _sample_rows(ops, logits.to(DEV), rows)
+    ops.check_errors()
+    for i, (t, p, k, seed, ordinal, sup) in enumerate(rows):
+        ref, _, _ = plain_impl.sample(logits[i].tolist(), temperature=t, top_p=p, top_k=k, seed=seed,
+                                      ordinal=ordinal, suppressed=sup)
+        assert got[i] == ref, (i, rows[i], got[i], ref)
+
+
+def test_sampler_draws_follow_the_distribution(ops):
+    """Many ordinals of one request: frequencies follow softmax(logits / T)."""
+    vocab, n = 12, 4000
+    row = torch.tensor([2.0, 1.0, 0.5, 0.0, -1.0, 3.0, 1.5, -2.0, 0.2, 0.1, 2.5, -0.5])
+    logits = row.repeat(n, 1).to(DEV)
+    got = _sample_rows(ops, logits, [(0.7, 1.0, None, 99, o, []) for o in range(n)])
+    freq = torch.bincount(torch.tensor(got), minlength=vocab).double() / n
+    prob = torch.softmax(row.double() / 0.7, dim=0)
+    assert float((freq - prob).abs().max()) < 0.03
+    # the same (seed, ordinal) gives the same token whatever else is in the batch
+    again = _sample_rows(ops, logits[:7], [(0.7, 1.0, None, 99, o, []) for o in (5, 900, 17, 3, 2500, 0, 41)])
+    assert again == [got[o] for o in (5, 900, 17, 3, 2500, 0, 41)]
