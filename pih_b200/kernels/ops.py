@@ -49,6 +49,10 @@ class CudaOps:
         except OSError as e:
             raise RuntimeError(f"pih_b200: the kernel pack {path} could not be loaded: {e}") from None
         self.library_path = path
+        # library products must accumulate in 32-bit all the way: no bf16 partial sums in split-K
+        # reductions, no TF32
+        torch.backends.cuda.matmul.allow_bf16_reduced_precision_reduction = False
+        torch.backends.cuda.matmul.allow_tf32 = False
         self._error = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.launches = 0
         self._declare()
