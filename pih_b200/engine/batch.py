@@ -20,7 +20,7 @@ Arrays (int32, on the device):
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import Hashable, List, Sequence
+from typing import Hashable, List, Optional, Sequence
 
 import torch
 
@@ -52,6 +52,7 @@ class StepBatch:
     # host copies for planning kernel launches
     host_cu_q: List[int] = field(default_factory=list)
     host_q_start: List[int] = field(default_factory=list)
+    attention_plans: dict = field(default_factory=dict)     # filled by the attention op, per group size
 
 
 def _align(n: int, a: int = 4) -> int:
@@ -74,18 +75,27 @@ class BatchBuilder:
             self._pinned = torch.empty(self._capacity, dtype=torch.int32, pin_memory=pin)
         return self._pinned[:n]
 
-    def build(self, entries: Sequence[StepEntry], cache) -> StepBatch:
-        """``cache``: the CacheManager, after ``append`` was called for every entry."""
+    def build(self, entries: Sequence[StepEntry], cache, width: Optional[int] = None,
+              device_buffer: Optional[torch.Tensor] = None) -> StepBatch:
+        """``cache``: the CacheManager, after ``append`` was called for every entry.
+
+        ``width`` fixes the block tables' row length (default: the longest table of the batch);
+        ``device_buffer`` is an int32 device tensor to fill instead of a fresh one.  The layout is a
+        function of (rows, requests, wanted rows, groups, width) alone, so a step of the same shape
+        written into the same buffer puts every array at the same address — what a captured CUDA
+        graph needs.
+        """
         R = len(entries)
         rids = [e.rid for e in entries]
         counts = [len(e.tokens) for e in entries]
         T = sum(counts)
         starts = [cache.requests[r].num_tokens for r in rids]
         G = len(cache.groups)
-        width = cache.table_width(rids)
+        if width is None:
+            width = cache.table_width(rids)
         token_ids, positions, req_of_row, logit_rows, cu_q = [], [], [], [], [0]
         for r, e in enumerate(entries):
-            token_ids.extend(int(t) for t in e.tokens)
+            token_ids.extend(e.tokens)
             positions.extend(range(starts[r], starts[r] + counts[r]))
             req_of_row.extend([r] * counts[r])
             for w in e.want:
@@ -109,11 +119,17 @@ class BatchBuilder:
             total += _align(max(len(f), 1))
         self.wait_copy()
         host = self._host(total)
+        view = host.numpy()
         for off, f in zip(offsets, fields):
             if f:
-                host[off:off + len(f)] = torch.tensor(f, dtype=torch.int32)
+                view[off:off + len(f)] = f
         self.last_bytes = total * 4
-        dev = torch.empty(total, dtype=torch.int32, device=self.device)
+        if device_buffer is None:
+            dev = torch.empty(total, dtype=torch.int32, device=self.device)
+        else:
+            if device_buffer.numel() < total:
+                raise ValueError("the device buffer is too small for this batch")
+            dev = device_buffer[:total]
         dev.copy_(host, non_blocking=True)
         # the pinned buffer is reused by the next build: the copy must have left it
         if self.device.type == "cuda":
@@ -133,6 +149,14 @@ class BatchBuilder:
             batch.block_tables.append(part(8 + 2 * g, R * width).view(R, width))
             batch.slot_mappings.append(part(9 + 2 * g, T))
         return batch
+
+    @staticmethod
+    def buffer_size(rows: int, requests: int, wanted: int, groups: int, width: int) -> int:
+        """int32 elements that ``build`` needs for a step of this shape."""
+        sizes = [rows, rows, rows, wanted, requests + 1, requests, requests, requests]
+        for _ in range(groups):
+            sizes += [requests * width, rows]
+        return sum(_align(max(n, 1)) for n in sizes)
 
     def wait_copy(self) -> None:
         ev = getattr(self, "_copy_done", None)

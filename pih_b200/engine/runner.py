@@ -21,6 +21,20 @@ from ..cache import CacheManager, OutOfPages
 from .batch import BatchBuilder, StepBatch, StepEntry
 
 
+class _FixedPlans(dict):
+    """Attention plans of a captured step: the same for every group size."""
+
+    def __init__(self, plan):
+        super().__init__()
+        self._plan = plan
+
+    def __contains__(self, key):
+        return True
+
+    def __getitem__(self, key):
+        return self._plan
+
+
 class ModelRunner:
     def __init__(self, model, cache: CacheManager, cuda_graphs: bool = False):
         self.cuda_graphs = cuda_graphs
@@ -30,6 +44,8 @@ class ModelRunner:
         self.builder = BatchBuilder(self.device)
         self.num_entries = len(model.spec.schedule)
         self.steps_run = 0
+        self._graphs = {}
+        self._graph_pool = None
 
     def prepare(self, entries: Sequence[StepEntry]) -> StepBatch:
         """Allocate cache room for every entry (all or none) and pack the batch."""
@@ -62,7 +78,12 @@ class ModelRunner:
 
     def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
         """Run ``entries`` as one batch; returns fp32 logits ``[wanted, vocab]``
-        in the order of the entries and of their ``want`` lists, or None."""
+        in the order of the entries and of their ``want`` lists, or None.
+
+        The returned tensor may be reused by the next step: read it before
+        calling ``step`` again."""
+        if self._graphable(entries):
+            return self._graph_step(entries)
         batch = self.prepare(entries)
         try:
             logits = self.run(batch)
@@ -74,6 +95,93 @@ class ModelRunner:
             self.cache.commit(e.rid)
         self.steps_run += 1
         return logits
+
+    # -- decode steps replayed from CUDA graphs ------------------------------------------
+    # A decode step of B requests is ~10 launches per layer; at small B the launches, not the
+    # kernels, bound the step.  Steps in which every request brings one token and wants its logits
+    # are captured once per (B, block-table width bucket) and replayed: the batch arrays live in
+    # a static device buffer whose layout depends on that key alone.
+    GRAPH_WIDTH_STEP = 64           # block-table widths are rounded up to a multiple of this many pages
+
+    def _graphable(self, entries) -> bool:
+        return (self.cuda_graphs and self.device.type == "cuda" and not self.cache.state_tensors
+                and all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries))
+
+    def _graph_step(self, entries) -> torch.Tensor:
+        for e in entries:
+            if not self.cache.has_request(e.rid):
+                self.cache.add_request(e.rid)
+        done = []
+        try:
+            for e in entries:
+                self.cache.append(e.rid, 1)
+                done.append(e.rid)
+        except OutOfPages:
+            for rid in done:
+                self.cache.rollback(rid)
+            raise
+        B = len(entries)
+        rids = [e.rid for e in entries]
+        step_w = self.GRAPH_WIDTH_STEP
+        width = -(-self.cache.table_width(rids) // step_w) * step_w
+        key = (B, width)
+        state = self._graphs.get(key)
+        try:
+            if state is None:
+                state = self._capture(entries, key)
+            else:
+                self.builder.build(entries, self.cache, width=width, device_buffer=state["buffer"])
+                state["graph"].replay()
+                self._count_launches(state["launches"])
+        except Exception:
+            for rid in rids:
+                self.cache.rollback(rid)
+            raise
+        for rid in rids:
+            self.cache.commit(rid)
+        self.steps_run += 1
+        return state["logits"]
+
+    def _count_launches(self, n: int) -> None:
+        ops = self.model.rt.ops
+        if hasattr(ops, "launches"):
+            ops.launches += n
+
+    def _capture(self, entries, key):
+        B, width = key
+        G = len(self.cache.groups)
+        buffer = torch.empty(self.builder.buffer_size(B, B, B, G, width), dtype=torch.int32, device=self.device)
+        batch = self.builder.build(entries, self.cache, width=width, device_buffer=buffer)
+        # the attention plan of the graph covers every context that fits the table width
+        max_ctx = width * self.cache.page_size
+        batch.attention_plans = _FixedPlans((0, 1, max_ctx))
+        ops = self.model.rt.ops
+        if hasattr(ops, "reserve_attention_scratch"):
+            for block in self.model.blocks:
+                spec = getattr(block.mixer, "spec", None)
+                if spec is not None and hasattr(spec, "heads"):
+                    ops.reserve_attention_scratch(B, 1, spec.heads, spec.head_dim, max_ctx)
+        caches = [self.cache.view(i, batch.block_tables, batch.slot_mappings) for i in range(self.num_entries)]
+        # once eagerly on a side stream (lazy initialisations must not happen under capture) ...
+        side = torch.cuda.Stream(self.device)
+        side.wait_stream(torch.cuda.current_stream(self.device))
+        with torch.cuda.stream(side):
+            self.model.forward(batch, caches)
+        torch.cuda.current_stream(self.device).wait_stream(side)
+        torch.cuda.synchronize(self.device)
+        # ... then captured; the eager run already did this step's work (cache writes are idempotent)
+        graph = torch.cuda.CUDAGraph()
+        before = getattr(ops, "launches", 0)
+        with torch.cuda.graph(graph, pool=self._graph_pool):
+            logits = self.model.forward(batch, caches)
+        launches = getattr(ops, "launches", 0) - before        # the pack's kernels inside the graph
+        if self._graph_pool is None:
+            self._graph_pool = graph.pool()
+        graph.replay()
+        self._count_launches(launches)
+        state = {"graph": graph, "buffer": buffer, "logits": logits, "batch": batch, "launches": launches}
+        self._graphs[key] = state
+        return state
 
     def finish(self, rid: Hashable) -> None:
         """The request has ended: everything it holds goes back to the pools."""

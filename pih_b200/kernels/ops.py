@@ -55,6 +55,10 @@ class CudaOps:
         torch.backends.cuda.matmul.allow_tf32 = False
         self._error = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.launches = 0
+        self._attn_scratch = None          # partials of the split-KV attention kernel, grown on demand
+        self._retired_scratch = []
+        self.attention_split = 128         # keys per split of the decode attention kernel
+        self.tensor_core_attention = True  # False: bf16 attention runs on the generic kernel too
         self._declare()
 
     # -- plumbing ---------------------------------------------------------------
@@ -62,8 +66,9 @@ class CudaOps:
         lib = self.lib
         for name in ("pih_embedding", "pih_rmsnorm", "pih_qk_norm_rope_kv_write", "pih_silu_mul",
                      "pih_gather_rows", "pih_gemm_simt", "pih_paged_attention_generic", "pih_argmax",
-                     "pih_sample"):
+                     "pih_sample", "pih_paged_attention_mma"):
             getattr(lib, name).restype = c_int
+        lib.pih_attention_scratch_floats.restype = c_ll
 
     def _stream(self):
         return c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
@@ -151,10 +156,70 @@ class CudaOps:
 
     def paged_attention(self, qkv, *, heads, kv_heads, head_dim, kv_cache, block_table, step, scale,
                         window) -> torch.Tensor:
+        """Attention of the step's rows over the cache.  bf16 runs on the tensor-core kernels
+        when they have an instance for ``head_dim``; everything else on the generic kernel."""
+        if self.tensor_core_attention and qkv.dtype == torch.bfloat16 and head_dim in self.MMA_HEAD_DIMS:
+            return self.paged_attention_mma(qkv, heads=heads, kv_heads=kv_heads, head_dim=head_dim,
+                                            kv_cache=kv_cache, block_table=block_table, step=step,
+                                            scale=scale, window=window)
         return self.paged_attention_generic(qkv, heads=heads, kv_heads=kv_heads, head_dim=head_dim,
                                             kv_cache=kv_cache, block_table=block_table,
                                             request_of_row=step.request_of_row, positions=step.positions,
                                             scale=scale, window=window)
+
+    MMA_HEAD_DIMS = (16, 32, 64, 80, 96, 128, 256)
+
+    @staticmethod
+    def attention_plan(host_cu_q, host_q_start, group: int):
+        """(tile_max_q, dec_tok_cap, dec_max_ctx): a request is decode-like when it brings at most
+        16 packed rows (rows * heads / kv_heads)."""
+        tile_max_q = dec_cap = dec_ctx = 0
+        for r in range(len(host_q_start)):
+            n = host_cu_q[r + 1] - host_cu_q[r]
+            if n * group <= 16:
+                dec_cap = max(dec_cap, n)
+                dec_ctx = max(dec_ctx, host_q_start[r] + n)
+            else:
+                tile_max_q = max(tile_max_q, n)
+        return tile_max_q, dec_cap, dec_ctx
+
+    def reserve_attention_scratch(self, num_requests, dec_tok_cap, heads, head_dim, max_ctx) -> None:
+        """Make the split kernel's scratch large enough (before a CUDA graph that uses it is
+        captured: an allocation cannot happen under capture).  A buffer that is outgrown is kept
+        alive, because captured graphs hold its address."""
+        need = self.lib.pih_attention_scratch_floats(num_requests, dec_tok_cap, heads, head_dim,
+                                                     -(-max_ctx // self.attention_split))
+        if self._attn_scratch is None or self._attn_scratch.numel() < need:
+            if self._attn_scratch is not None:
+                self._retired_scratch.append(self._attn_scratch)     # captured graphs may still point at it
+            self._attn_scratch = torch.empty(int(need * 1.25) + 1024, dtype=torch.float32, device=self.device)
+
+    def paged_attention_mma(self, qkv, *, heads, kv_heads, head_dim, kv_cache, block_table, step, scale,
+                            window, plan=None) -> torch.Tensor:
+        rows = qkv.shape[0]
+        group = heads // kv_heads
+        plans = getattr(step, "attention_plans", None)
+        if plan is None and plans is not None and group in plans:
+            plan = plans[group]
+        if plan is None:
+            plan = self.attention_plan(step.host_cu_q, step.host_q_start, group)
+            if plans is not None:
+                plans[group] = plan
+        tile_max_q, dec_cap, dec_ctx = plan
+        out = torch.empty(rows, heads * head_dim, dtype=qkv.dtype, device=qkv.device)
+        num_pages, page_size = kv_cache.shape[0], kv_cache.shape[3]
+        split = self.attention_split
+        scratch = None
+        if dec_cap > 0:
+            self.reserve_attention_scratch(step.num_requests, dec_cap, heads, head_dim, dec_ctx)
+            scratch = self._attn_scratch
+        rc = self.lib.pih_paged_attention_mma(
+            _ptr(qkv), qkv.stride(0), _ptr(out), _ptr(kv_cache), _ptr(block_table), block_table.shape[1],
+            _ptr(step.cu_q), _ptr(step.q_start), _ptr(step.request_of_row), _ptr(step.positions), rows,
+            step.num_requests, tile_max_q, dec_cap, dec_ctx, heads, kv_heads, head_dim, page_size, num_pages,
+            c_float(scale), int(window), split, _ptr(scratch), self._err(), self._stream())
+        self._check(rc, "paged_attention_mma")
+        return out
 
     def paged_attention_generic(self, qkv, *, heads, kv_heads, head_dim, kv_cache, block_table,
                                 request_of_row, positions, scale, window) -> torch.Tensor:

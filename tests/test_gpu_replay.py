@@ -24,12 +24,13 @@ FAMILIES = ["whole", "tail_decode", "portions", "mixed"]
 
 # 32-bit: accumulation-order noise only (logits are O(1)).
 TOL_F32 = 2e-5
-# bfloat16: compared with the plain implementation rounding at the same places; two such
-# implementations differ where an accumulation order flips a bf16 rounding.  Measured between
-# two CPU implementations on these configurations: 1.5 % (A) and 2.8 % (B) of the logits'
-# standard deviation at the worst position; the bound is 5 % at the worst position and 0.6 %
-# on average.
-TOL_BF16_MAX, TOL_BF16_MEAN = 0.05, 0.006
+# bfloat16: every op rounds its output to 8 bits of mantissa, so even the plain implementation with
+# the reference's rounding places ("plain-bf16") sits a measurable distance from the unrounded truth,
+# and any two bf16 implementations that differ in one accumulation order decorrelate from each other
+# by about that distance.  The yardstick is therefore measured, per request, inside the test:
+# E = |plain-bf16 - truth|.  The engine must be as close to the truth as plain-bf16 is, within half
+# again (mean and worst position), and within the triangle's reach of plain-bf16 itself.
+BF16_TRUTH_FACTOR, BF16_PLAIN_FACTOR, BF16_FLOOR = 1.5, 2.5, 0.004
 
 _REF = {}
 
@@ -42,21 +43,32 @@ def reference(model_dir, name, requests, rounding):
     return _REF[key]
 
 
-def compare(got, ref, dtype, what):
-    for rid in ref:
-        g, r = got[rid].double(), ref[rid]
+def compare(got, truth, dtype, what, plain_bf16=None):
+    for rid in truth:
+        g, r = got[rid].double(), truth[rid]
         assert g.shape == r.shape, (what, rid, g.shape, r.shape)
         err = (g - r).abs()
         if dtype == "float32":
             worst = int(err.max(dim=1).values.argmax())
             assert float(err.max()) < TOL_F32, f"{what} {rid}: max abs error {float(err.max()):.3e} at position {worst}"
-        else:
-            spread = float(r.std())
-            per_pos = err.max(dim=1).values / spread
-            worst = int(per_pos.argmax())
-            assert float(per_pos.max()) < TOL_BF16_MAX, \
-                f"{what} {rid}: error {float(per_pos.max()):.4f} of the spread at position {worst}"
-            assert float(err.mean()) / spread < TOL_BF16_MEAN, f"{what} {rid}: mean error {float(err.mean()) / spread:.4f}"
+            continue
+        spread = float(r.std())
+        yard = (plain_bf16[rid] - r).abs()
+        worst = int(err.max(dim=1).values.argmax())
+        assert float(err.mean()) <= BF16_TRUTH_FACTOR * float(yard.mean()), \
+            f"{what} {rid}: mean error {float(err.mean()):.5f} vs plain-bf16's own {float(yard.mean()):.5f}"
+        assert float(err.max()) <= BF16_TRUTH_FACTOR * float(yard.max()) + BF16_FLOOR * spread, \
+            f"{what} {rid}: worst error {float(err.max()):.5f} at position {worst} vs plain-bf16's own {float(yard.max()):.5f}"
+        apart = (g - plain_bf16[rid]).abs()
+        assert float(apart.mean()) <= BF16_PLAIN_FACTOR * float(yard.mean()), (what, rid, float(apart.mean()))
+        assert float(apart.max()) <= BF16_PLAIN_FACTOR * float(yard.max()) + BF16_FLOOR * spread, \
+            (what, rid, float(apart.max()))
+
+
+def compare_with_plain(got, model_dir, name, requests, dtype, what):
+    truth = reference(model_dir, name, requests, "none")
+    plain = reference(model_dir, name, requests, "bf16") if dtype == "bfloat16" else None
+    compare(got, truth, dtype, what, plain)
 
 
 @pytest.fixture(scope="module")
@@ -76,8 +88,7 @@ def test_replay_families(model_dirs, requests_of, name, dtype, family):
                                             max_cache_tokens=pool, max_requests=4)
     got = traces.replay(runner, steps)
     model.rt.ops.check_errors()
-    ref = reference(model_dirs[name], name, requests, "none" if dtype == "float32" else "bf16")
-    compare(got, ref, dtype, f"{name} {family}")
+    compare_with_plain(got, model_dirs[name], name, requests, dtype, f"{name} {family}")
     cache.check()
     assert all(f == cache.num_pages for f in cache.num_free_pages())
     if family == "mixed":
@@ -100,7 +111,8 @@ def test_32bit_and_bf16_cuttings_agree_with_each_other(model_dirs, requests_of, 
     for family in FAMILIES[1:]:
         for rid in requests:
             diff = float((outs[family][rid] - outs["whole"][rid]).abs().max())
-            bound = 1e-6 if dtype == "float32" else 0.05 * float(outs["whole"][rid].std())
+            # bf16: different kernels serve different cuttings (tile, split, graph); they may differ by rounding
+            bound = 1e-6 if dtype == "float32" else 0.08 * float(outs["whole"][rid].std())
             assert diff <= bound, (family, rid, diff)
 
 
@@ -132,8 +144,7 @@ def test_trace_run_program(model_dirs, requests_of, tmp_path, dtype):
                 rows.setdefault(e["id"], []).append(torch.from_numpy(data[i].copy()))
                 i += 1
     got = {rid: torch.stack(v) for rid, v in rows.items()}
-    ref = reference(model_dirs[name], name, requests, "none" if dtype == "float32" else "bf16")
-    compare(got, ref, dtype, f"trace_run {dtype}")
+    compare_with_plain(got, model_dirs[name], name, requests, dtype, f"trace_run {dtype}")
 
 
 def test_trace_run_steps_without_wanted_logits_and_pauses(model_dirs, tmp_path):
