@@ -17,12 +17,16 @@
 //   bank conflicts for every head_dim that is a multiple of 16), two stages.
 // * "Tile" kernel (4 warps, 64 packed rows, K/V tiles shared by the warps):
 //   requests that bring more than 16 packed rows.
-// * "Split" kernel (1 warp, 16 packed rows): requests that bring at most 16
+// * "Split" kernel (4 warps, 16 packed rows): requests that bring at most 16
 //   packed rows (decode).  The keys are cut at fixed absolute positions
-//   (multiples of `split`), one CTA per (split, kv head, request), each writing
-//   an unnormalised partial (acc, max, sum) to scratch memory; a combine
-//   kernel merges the partials of a row in ascending order.  The cut does not
-//   depend on the batch.
+//   (multiples of `split`), one CTA per (split, kv head, request).  All tiles
+//   of a split are requested at once (cp.async), the four warps take a
+//   quarter of each tile's keys, merge through shared memory and write an
+//   unnormalised partial (acc, max, sum) to scratch memory.  The CTA that
+//   finishes last for its (request, kv head) — found with one atomic ticket —
+//   merges the partials in ascending split order and writes the output, so
+//   no second launch is needed and the order of the merge is fixed.  The cut
+//   does not depend on the batch.
 //
 // mma.sync.m16n8k16 is used rather than tcgen05: the M dimension of a decode
 // tile is 2..16 rows, far below the 128-row tcgen05 tile, and the kernel is
@@ -51,6 +55,8 @@ struct AttnParams {
   int dec_tok_cap;                     // most rows of one decode-like request
   float* part_o;                       // [R, dec_tok_cap, heads, max_splits, D]
   float* part_ml;                      // [R, dec_tok_cap, heads, max_splits, 2]
+  int* tickets;                        // [R, kv_heads], zero between launches
+  int page_shift;                      // log2(page_size) or -1
   uint32_t* error;
 };
 
@@ -102,12 +108,14 @@ __device__ __forceinline__ void load_kv_tile(const AttnParams& p, const int* tab
     const __nv_bfloat16* vsrc = p.cache;
     int bytes = 0;
     if (j >= kmin && j <= kmax) {
-      const int page = table[j / p.page_size];
+      const int pidx = p.page_shift >= 0 ? (j >> p.page_shift) : (j / p.page_size);
+      const int poff = j - pidx * p.page_size;
+      const int page = table[pidx];
       if (page < 0 || page >= p.num_pages) {
         publish_error(p.error, kRowWithoutPage);
       } else {
         const size_t base = (static_cast<size_t>(page) * 2 * p.kv_heads + g) * head_elems +
-                            static_cast<size_t>(j % p.page_size) * D + ch * 8;
+                            static_cast<size_t>(poff) * D + ch * 8;
         ksrc = p.cache + base;
         vsrc = p.cache + base + static_cast<size_t>(p.kv_heads) * head_elems;
         bytes = 16;
@@ -118,24 +126,24 @@ __device__ __forceinline__ void load_kv_tile(const AttnParams& p, const int* tab
   }
 }
 
-// One warp: 16 packed rows against one tile of BN keys.
-template <int D>
+// One warp: 16 packed rows against NK keys (rows of Ks / Vs), the first of which is key j0.
+template <int D, int NK>
 __device__ __forceinline__ void tile_step(const __nv_bfloat16* Qs /* this warp's 16 rows */,
                                           const __nv_bfloat16* Ks, const __nv_bfloat16* Vs, int j0,
                                           const int (&row_pos)[2], const int (&row_first)[2], float scale_log2,
                                           float (&m)[2], float (&l)[2], float (&o)[D / 8][4]) {
   constexpr int LD = D + 8;
   const int lane = threadIdx.x & 31;
-  float s[BN / 8][4];
+  float s[NK / 8][4];
 #pragma unroll
-  for (int n = 0; n < BN / 8; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.0f;
+  for (int n = 0; n < NK / 8; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.0f;
   // S = Q K^T
 #pragma unroll
   for (int kk = 0; kk < D / 16; ++kk) {
     uint32_t a[4];
     ldmatrix_x4(a, Qs + ((lane & 7) + ((lane >> 3) & 1) * 8) * LD + kk * 16 + (lane >> 4) * 8);
 #pragma unroll
-    for (int nt = 0; nt < BN / 16; ++nt) {
+    for (int nt = 0; nt < NK / 16; ++nt) {
       uint32_t b[4];
       ldmatrix_x4(b, Ks + (nt * 16 + (lane & 7) + (lane >> 4) * 8) * LD + kk * 16 + ((lane >> 3) & 1) * 8);
       mma_bf16(s[2 * nt], a, b[0], b[1]);
@@ -145,7 +153,7 @@ __device__ __forceinline__ void tile_step(const __nv_bfloat16* Qs /* this warp's
   // scale, mask, online softmax (base 2)
   float tile_max[2] = {-INFINITY, -INFINITY};
 #pragma unroll
-  for (int n = 0; n < BN / 8; ++n) {
+  for (int n = 0; n < NK / 8; ++n) {
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
       const int r = e >> 1;
@@ -168,7 +176,7 @@ __device__ __forceinline__ void tile_step(const __nv_bfloat16* Qs /* this warp's
   }
   float tile_sum[2] = {0.0f, 0.0f};
 #pragma unroll
-  for (int n = 0; n < BN / 8; ++n) {
+  for (int n = 0; n < NK / 8; ++n) {
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
       const int r = e >> 1;
@@ -188,7 +196,7 @@ __device__ __forceinline__ void tile_step(const __nv_bfloat16* Qs /* this warp's
   }
   // O += P V
 #pragma unroll
-  for (int kk = 0; kk < BN / 16; ++kk) {
+  for (int kk = 0; kk < NK / 16; ++kk) {
     uint32_t a[4];
     a[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
     a[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
@@ -204,13 +212,13 @@ __device__ __forceinline__ void tile_step(const __nv_bfloat16* Qs /* this warp's
   }
 }
 
-// NWARPS = 4: tile kernel, grid (q tiles, kv_heads, R).  NWARPS = 1: split kernel, grid (splits, kv_heads, R).
-template <int D, int NWARPS, bool SPLIT>
-__global__ void __launch_bounds__(NWARPS * 32)
-attn_mma_kernel(const AttnParams p) {
+// Tile kernel: 4 warps, 64 packed rows, grid (q tiles, kv_heads, R); requests with more than 16 packed rows.
+template <int D>
+__global__ void __launch_bounds__(128)
+attn_tile_kernel(const AttnParams p) {
   constexpr int LD = D + 8;
-  constexpr int BM = NWARPS * 16;
-  constexpr int THREADS = NWARPS * 32;
+  constexpr int BM = 64;
+  constexpr int THREADS = 128;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);
   __nv_bfloat16* Ks0 = Qs + BM * LD;
@@ -221,25 +229,18 @@ attn_mma_kernel(const AttnParams p) {
   const int row0 = p.cu_q[r];
   const int n_tok = p.cu_q[r + 1] - row0;
   const int packed = n_tok * G;
-  const bool decode_like = packed <= 16;
-  if (SPLIT != decode_like) return;
-  const int tile_row0 = SPLIT ? 0 : blockIdx.x * BM;
+  if (packed <= 16) return;                          // decode-like: the split kernel's
+  const int tile_row0 = blockIdx.x * BM;
   if (tile_row0 >= packed) return;
   const int start = p.q_start[r];
   // key range that the rows of this tile can see
   const int tok_lo = tile_row0 / G;
   const int tok_hi = min(packed - 1, tile_row0 + BM - 1) / G;
-  int kmin = p.window > 0 ? max(0, start + tok_lo - p.window + 1) : 0;
-  int kmax = start + tok_hi;
-  if (SPLIT) {
-    kmin = max(kmin, static_cast<int>(blockIdx.x) * p.split);
-    kmax = min(kmax, (static_cast<int>(blockIdx.x) + 1) * p.split - 1);
-    if (kmin > kmax) return;
-  }
+  const int kmin = p.window > 0 ? max(0, start + tok_lo - p.window + 1) : 0;
+  const int kmax = start + tok_hi;
   const int* table = p.block_table + static_cast<size_t>(r) * p.table_width;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
-  // Q tile
   for (int c = threadIdx.x; c < BM * (D / 8); c += THREADS) {
     const int row = c / (D / 8), ch = c % (D / 8);
     const int i = tile_row0 + row;
@@ -283,8 +284,8 @@ attn_mma_kernel(const AttnParams p) {
       cp_async_wait<0>();
     }
     __syncthreads();
-    tile_step<D>(Qs + warp * 16 * LD, Ks0 + buf * BN * LD, Vs0 + buf * BN * LD, t * BN, row_pos, row_first,
-                 scale_log2, m, l, o);
+    tile_step<D, BN>(Qs + warp * 16 * LD, Ks0 + buf * BN * LD, Vs0 + buf * BN * LD, t * BN, row_pos, row_first,
+                     scale_log2, m, l, o);
     __syncthreads();
   }
 #pragma unroll
@@ -297,115 +298,206 @@ attn_mma_kernel(const AttnParams p) {
     const int i = tile_row0 + warp * 16 + (lane >> 2) + h * 8;
     if (i >= packed) continue;
     const int grow = row0 + i / G, head = g * G + i % G;
-    if (SPLIT) {
-      const size_t slot =
-          ((static_cast<size_t>(r) * p.dec_tok_cap + i / G) * p.heads + head) * p.max_splits + blockIdx.x;
-      float* po = p.part_o + slot * D;
+    if (!(l[h] > 0.0f) || !isfinite(l[h])) {
+      publish_error(p.error, kAttentionDenominator);
+      continue;
+    }
+    const float inv = 1.0f / l[h];
+    __nv_bfloat16* orow = p.out + (static_cast<size_t>(grow) * p.heads + head) * D;
 #pragma unroll
-      for (int n = 0; n < D / 8; ++n) {
-        const int d = n * 8 + (lane & 3) * 2;
-        *reinterpret_cast<float2*>(po + d) = make_float2(o[n][2 * h], o[n][2 * h + 1]);
-      }
-      if ((lane & 3) == 0) {
-        p.part_ml[slot * 2] = m[h];
-        p.part_ml[slot * 2 + 1] = l[h];
-      }
-    } else {
-      if (!(l[h] > 0.0f) || !isfinite(l[h])) {
-        publish_error(p.error, kAttentionDenominator);
-        continue;
-      }
-      const float inv = 1.0f / l[h];
-      __nv_bfloat16* orow = p.out + (static_cast<size_t>(grow) * p.heads + head) * D;
-#pragma unroll
-      for (int n = 0; n < D / 8; ++n) {
-        const int d = n * 8 + (lane & 3) * 2;
-        *reinterpret_cast<uint32_t*>(orow + d) = pack_bf16(o[n][2 * h] * inv, o[n][2 * h + 1] * inv);
-      }
+    for (int n = 0; n < D / 8; ++n) {
+      const int d = n * 8 + (lane & 3) * 2;
+      *reinterpret_cast<uint32_t*>(orow + d) = pack_bf16(o[n][2 * h] * inv, o[n][2 * h + 1] * inv);
     }
   }
 }
 
-// Merge the partials of each decode-like row in ascending split order.  One warp per (row, head).
-__global__ void attn_combine_kernel(const AttnParams p, int rows, int head_dim, const int* request_of_row,
-                                    const int* positions) {
-  const int warps = blockDim.x >> 5;
-  const long long item = static_cast<long long>(blockIdx.x) * warps + (threadIdx.x >> 5);
-  if (item >= static_cast<long long>(rows) * p.heads) return;
-  const int lane = threadIdx.x & 31;
-  const int t = static_cast<int>(item / p.heads), h = static_cast<int>(item % p.heads);
-  const int r = request_of_row[t];
-  const int G = p.heads / p.kv_heads;
-  if ((p.cu_q[r + 1] - p.cu_q[r]) * G > 16) return;              // not a decode-like request
-  const int pos = positions[t];
-  const int first = p.window > 0 ? max(0, pos - p.window + 1) : 0;
-  const int s_lo = first / p.split, s_hi = pos / p.split;
-  const size_t base =
-      ((static_cast<size_t>(r) * p.dec_tok_cap + (t - p.cu_q[r])) * p.heads + h) * p.max_splits;
-  float m = -INFINITY;
-  for (int s = s_lo; s <= s_hi; ++s) m = fmaxf(m, p.part_ml[(base + s) * 2]);
-  float l = 0.0f;
-  float acc[8];
-#pragma unroll
-  for (int i = 0; i < 8; ++i) acc[i] = 0.0f;
-  for (int s = s_lo; s <= s_hi; ++s) {
-    const float ms = p.part_ml[(base + s) * 2];
-    if (ms == -INFINITY) continue;
-    const float w = exp2f(ms - m);
-    l += p.part_ml[(base + s) * 2 + 1] * w;
-    const float* po = p.part_o + (base + s) * head_dim;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const int d = lane + 32 * i;
-      if (d < head_dim) acc[i] += po[d] * w;
-    }
-  }
-  if (!(l > 0.0f) || !isfinite(l)) {
-    if (lane == 0) publish_error(p.error, kAttentionDenominator);
-    return;
-  }
-  __nv_bfloat16* orow = p.out + (static_cast<size_t>(t) * p.heads + h) * head_dim;
-#pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    const int d = lane + 32 * i;
-    if (d < head_dim) orow[d] = __float2bfloat16_rn(acc[i] / l);
-  }
-}
+constexpr int kMaxSplitTiles = 4;      // split <= 4 * BN keys
 
-template <int D, int NWARPS, bool SPLIT>
-static int launch_attn(const AttnParams& p, dim3 grid, cudaStream_t s) {
+// Split kernel: 4 warps, at most 16 packed rows, grid (splits, kv_heads, R); decode-like requests.
+template <int D>
+__global__ void __launch_bounds__(128)
+attn_split_kernel(const AttnParams p) {
   constexpr int LD = D + 8;
-  constexpr int BM = NWARPS * 16;
-  const int smem = (BM * LD + 4 * BN * LD) * static_cast<int>(sizeof(__nv_bfloat16));
-  static bool configured = false;            // per template instance
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(attn_mma_kernel<D, NWARPS, SPLIT>,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-    if (e != cudaSuccess) return static_cast<int>(e);
-    configured = true;
+  constexpr int THREADS = 128;
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);
+  __nv_bfloat16* KV = Qs + 16 * LD;                  // per tile: K [BN][LD] then V [BN][LD]
+  __shared__ int s_last;
+
+  const int r = blockIdx.z, g = blockIdx.y, sp = blockIdx.x;
+  const int G = p.heads / p.kv_heads;
+  const int row0 = p.cu_q[r];
+  const int n_tok = p.cu_q[r + 1] - row0;
+  const int packed = n_tok * G;
+  if (packed > 16) return;                           // the tile kernel's
+  const int start = p.q_start[r];
+  // keys that any row of the request sees, and the splits that hold them
+  const int req_kmin = p.window > 0 ? max(0, start - p.window + 1) : 0;
+  const int req_kmax = start + n_tok - 1;
+  const int s_lo = req_kmin / p.split, s_hi = req_kmax / p.split;
+  if (sp < s_lo || sp > s_hi) return;
+  const int kmin = max(req_kmin, sp * p.split);
+  const int kmax = min(req_kmax, (sp + 1) * p.split - 1);
+  const int* table = p.block_table + static_cast<size_t>(r) * p.table_width;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  for (int c = threadIdx.x; c < 16 * (D / 8); c += THREADS) {
+    const int row = c / (D / 8), ch = c % (D / 8);
+    const bool valid = row < packed;
+    const __nv_bfloat16* src = p.q;
+    if (valid)
+      src = p.q + static_cast<size_t>(row0 + row / G) * p.q_stride + static_cast<size_t>(g * G + row % G) * D + ch * 8;
+    cp_async16(Qs + row * LD + ch * 8, src, valid ? 16 : 0);
   }
-  attn_mma_kernel<D, NWARPS, SPLIT><<<grid, NWARPS * 32, smem, s>>>(p);
-  PIH_LAUNCH_CHECK();
-  return 0;
+  // every tile of the split is requested at once: one commit group per tile
+  const int t_first = kmin / BN, t_last = kmax / BN;
+  const int ntiles = t_last - t_first + 1;           // <= split / BN <= kMaxSplitTiles
+  for (int i = 0; i < ntiles; ++i) {
+    load_kv_tile<D, THREADS>(p, table, g, (t_first + i) * BN, kmin, kmax, KV + (2 * i) * BN * LD,
+                             KV + (2 * i + 1) * BN * LD);
+    cp_async_commit();
+  }
+  int row_pos[2], row_first[2];
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const int i = (lane >> 2) + h * 8;
+    if (i < packed) {
+      row_pos[h] = start + i / G;
+      row_first[h] = p.window > 0 ? max(0, row_pos[h] - p.window + 1) : 0;
+    } else {
+      row_pos[h] = -1;
+      row_first[h] = 0;
+    }
+  }
+  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.0f, 0.0f};
+  float o[D / 8][4];
+#pragma unroll
+  for (int n = 0; n < D / 8; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.0f;
+  const float scale_log2 = p.scale * kLog2e;
+
+  for (int i = 0; i < ntiles; ++i) {
+    const int pending = ntiles - 1 - i;              // groups that may still be in flight
+    if (pending >= 3) cp_async_wait<3>();
+    else if (pending == 2) cp_async_wait<2>();
+    else if (pending == 1) cp_async_wait<1>();
+    else cp_async_wait<0>();
+    __syncthreads();
+    // warp w takes keys 16 w .. 16 w + 15 of the tile
+    const __nv_bfloat16* Ks = KV + (2 * i) * BN * LD + warp * 16 * LD;
+    const __nv_bfloat16* Vs = KV + (2 * i + 1) * BN * LD + warp * 16 * LD;
+    tile_step<D, 16>(Qs, Ks, Vs, (t_first + i) * BN + warp * 16, row_pos, row_first, scale_log2, m, l, o);
+  }
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    l[h] += __shfl_xor_sync(0xffffffffu, l[h], 1);
+    l[h] += __shfl_xor_sync(0xffffffffu, l[h], 2);
+  }
+  // merge the four warps through shared memory (the K/V tiles are no longer needed)
+  __syncthreads();
+  float* Ow = reinterpret_cast<float*>(KV);          // [4][16][D]
+  float* Mw = Ow + 4 * 16 * D;                       // [4][16]
+  float* Lw = Mw + 4 * 16;                           // [4][16]
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const int row = (lane >> 2) + h * 8;
+    float* orow = Ow + (warp * 16 + row) * D;
+#pragma unroll
+    for (int n = 0; n < D / 8; ++n) {
+      const int d = n * 8 + (lane & 3) * 2;
+      *reinterpret_cast<float2*>(orow + d) = make_float2(o[n][2 * h], o[n][2 * h + 1]);
+    }
+    if ((lane & 3) == 0) {
+      Mw[warp * 16 + row] = m[h];
+      Lw[warp * 16 + row] = l[h];
+    }
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < packed * D; idx += THREADS) {
+    const int row = idx / D, d = idx % D;
+    float mm = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) mm = fmaxf(mm, Mw[w * 16 + row]);
+    float acc = 0.0f, ll = 0.0f;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      const float mw = Mw[w * 16 + row];
+      if (mw == -INFINITY) continue;
+      const float f = exp2f(mw - mm);
+      acc += Ow[(w * 16 + row) * D + d] * f;
+      ll += Lw[w * 16 + row] * f;
+    }
+    const size_t slot =
+        ((static_cast<size_t>(r) * p.dec_tok_cap + row / G) * p.heads + g * G + row % G) * p.max_splits + sp;
+    p.part_o[slot * D + d] = acc;
+    if (d == 0) {
+      p.part_ml[slot * 2] = mm;
+      p.part_ml[slot * 2 + 1] = ll;
+    }
+  }
+  // one ticket per CTA; the CTA that draws the last one merges the splits
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const int ticket = atomicAdd(&p.tickets[r * p.kv_heads + g], 1);
+    s_last = ticket == (s_hi - s_lo);
+  }
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  for (int idx = threadIdx.x; idx < packed * D; idx += THREADS) {
+    const int row = idx / D, d = idx % D;
+    const size_t base =
+        ((static_cast<size_t>(r) * p.dec_tok_cap + row / G) * p.heads + g * G + row % G) * p.max_splits;
+    float mm = -INFINITY;
+    for (int s = s_lo; s <= s_hi; ++s) mm = fmaxf(mm, __ldcg(p.part_ml + (base + s) * 2));
+    float acc = 0.0f, ll = 0.0f;
+    for (int s = s_lo; s <= s_hi; ++s) {
+      const float ms = __ldcg(p.part_ml + (base + s) * 2);
+      if (ms == -INFINITY) continue;
+      const float f = exp2f(ms - mm);
+      ll += __ldcg(p.part_ml + (base + s) * 2 + 1) * f;
+      acc += __ldcg(p.part_o + (base + s) * D + d) * f;
+    }
+    if (!(ll > 0.0f) || !isfinite(ll)) {
+      publish_error(p.error, kAttentionDenominator);
+      continue;
+    }
+    p.out[(static_cast<size_t>(row0 + row / G) * p.heads + g * G + row % G) * D + d] =
+        __float2bfloat16_rn(acc / ll);
+  }
+  if (threadIdx.x == 0) p.tickets[r * p.kv_heads + g] = 0;     // ready for the next launch
 }
 
 template <int D>
-static int launch_both(const AttnParams& p, int R, int tile_max_q, int rows, const int* request_of_row,
-                       const int* positions, cudaStream_t s) {
+static int launch_both(const AttnParams& p, int R, int tile_max_q, cudaStream_t s) {
+  constexpr int LD = D + 8;
   const int G = p.heads / p.kv_heads;
+  static int tile_smem_set = 0, split_smem_set = 0;   // per head_dim instance
   if (tile_max_q > 0) {
+    const int smem = (64 * LD + 4 * BN * LD) * static_cast<int>(sizeof(__nv_bfloat16));
+    if (tile_smem_set < smem) {
+      cudaError_t e = cudaFuncSetAttribute(attn_tile_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+      if (e != cudaSuccess) return static_cast<int>(e);
+      tile_smem_set = smem;
+    }
     dim3 grid((tile_max_q * G + 63) / 64, p.kv_heads, R);
-    const int rc = launch_attn<D, 4, false>(p, grid, s);
-    if (rc) return rc;
+    attn_tile_kernel<D><<<grid, 128, smem, s>>>(p);
+    PIH_LAUNCH_CHECK();
   }
   if (p.dec_tok_cap > 0) {
+    const int tiles = p.split / BN;
+    int smem = (16 * LD + 2 * tiles * BN * LD) * static_cast<int>(sizeof(__nv_bfloat16));
+    const int merge = 16 * LD * static_cast<int>(sizeof(__nv_bfloat16)) + (4 * 16 * D + 128) * static_cast<int>(sizeof(float));
+    if (merge > smem) smem = merge;
+    if (smem > 227 * 1024) return PIH_ERR_UNSUPPORTED;
+    if (split_smem_set < smem) {
+      cudaError_t e = cudaFuncSetAttribute(attn_split_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+      if (e != cudaSuccess) return static_cast<int>(e);
+      split_smem_set = smem;
+    }
     dim3 grid(p.max_splits, p.kv_heads, R);
-    int rc = launch_attn<D, 1, true>(p, grid, s);
-    if (rc) return rc;
-    const int warps = 4;
-    const long long items = static_cast<long long>(rows) * p.heads;
-    attn_combine_kernel<<<static_cast<unsigned>((items + warps - 1) / warps), warps * 32, 0, s>>>(
-        p, rows, D, request_of_row, positions);
+    attn_split_kernel<D><<<grid, 128, smem, s>>>(p);
     PIH_LAUNCH_CHECK();
   }
   return 0;
@@ -415,30 +507,37 @@ static int launch_both(const AttnParams& p, int R, int tile_max_q, int rows, con
 
 using namespace pih;
 
-// Floats of scratch that the split kernel needs.
-extern "C" long long pih_attention_scratch_floats(int num_requests, int dec_tok_cap, int heads, int head_dim,
-                                                  int max_splits) {
-  return static_cast<long long>(num_requests) * dec_tok_cap * heads * max_splits * (head_dim + 2);
+// Floats (4-byte words) of scratch that the split kernel needs: tickets first, then the partials.
+// The first pih_attention_ticket_words(...) words must be zero before the first launch; the kernel
+// leaves them zero.
+extern "C" long long pih_attention_ticket_words(int num_requests, int kv_heads) {
+  return (static_cast<long long>(num_requests) * kv_heads + 63) / 64 * 64;
+}
+extern "C" long long pih_attention_scratch_floats(int num_requests, int dec_tok_cap, int heads, int kv_heads,
+                                                  int head_dim, int max_splits) {
+  return pih_attention_ticket_words(num_requests, kv_heads) +
+         static_cast<long long>(num_requests) * dec_tok_cap * heads * max_splits * (head_dim + 2);
 }
 
 // A request is "decode-like" when it brings at most 16 packed rows (rows * heads / kv_heads <= 16).
 //   tile_max_q   the most rows of a request that is NOT decode-like (0: there is none)
 //   dec_tok_cap  the most rows of a decode-like request (0: there is none)
 //   dec_max_ctx  the longest context (after the step) of a decode-like request
-// scratch holds pih_attention_scratch_floats(num_requests, dec_tok_cap, heads, head_dim,
-// ceil(dec_max_ctx / split)) floats.  Returns PIH_ERR_UNSUPPORTED for a head_dim that has no
+// scratch holds pih_attention_scratch_floats(num_requests, dec_tok_cap, heads, kv_heads, head_dim,
+// ceil(dec_max_ctx / split)) words, the leading ticket words zero.  Launches that share the scratch
+// must not overlap on the device.  Returns PIH_ERR_UNSUPPORTED for a head_dim that has no
 // tensor-core instance (the caller then uses the generic kernel).
 extern "C" int pih_paged_attention_mma(const void* q, int q_stride, void* out, const void* cache,
                                        const int* block_table, int table_width, const int* cu_q,
-                                       const int* q_start, const int* request_of_row, const int* positions,
-                                       int rows, int num_requests, int tile_max_q, int dec_tok_cap,
-                                       int dec_max_ctx, int heads, int kv_heads, int head_dim, int page_size,
-                                       int num_pages, float scale, int window, int split, float* scratch,
-                                       uint32_t* error, void* stream) {
+                                       const int* q_start, int rows, int num_requests, int tile_max_q,
+                                       int dec_tok_cap, int dec_max_ctx, int heads, int kv_heads, int head_dim,
+                                       int page_size, int num_pages, float scale, int window, int split,
+                                       float* scratch, uint32_t* error, void* stream) {
   if (rows <= 0) return 0;
   if (heads <= 0 || kv_heads <= 0 || heads % kv_heads || page_size <= 0 || table_width <= 0 || window < 0 ||
-      split <= 0 || split % BN || num_requests <= 0 || num_requests > 65535 || kv_heads > 65535 ||
-      q_stride % 8 || tile_max_q < 0 || dec_tok_cap < 0 || (dec_tok_cap > 0 && (dec_max_ctx <= 0 || !scratch)))
+      split <= 0 || split % BN || split / BN > kMaxSplitTiles || num_requests <= 0 || num_requests > 65535 ||
+      kv_heads > 65535 || q_stride % 8 || tile_max_q < 0 || dec_tok_cap < 0 ||
+      (dec_tok_cap > 0 && (dec_max_ctx <= 0 || !scratch)))
     return PIH_ERR_BAD_ARGUMENT;
   AttnParams p;
   p.q = static_cast<const __nv_bfloat16*>(q);
@@ -458,18 +557,23 @@ extern "C" int pih_paged_attention_mma(const void* q, int q_stride, void* out, c
   p.split = split;
   p.max_splits = dec_tok_cap > 0 ? (dec_max_ctx + split - 1) / split : 0;
   p.dec_tok_cap = dec_tok_cap;
-  p.part_o = scratch;
-  p.part_ml = scratch + static_cast<size_t>(num_requests) * dec_tok_cap * heads * p.max_splits * head_dim;
+  p.page_shift = -1;
+  for (int sft = 0; sft < 20; ++sft)
+    if ((1 << sft) == page_size) p.page_shift = sft;
+  const long long tickets = pih_attention_ticket_words(num_requests, kv_heads);
+  p.tickets = reinterpret_cast<int*>(scratch);
+  p.part_o = scratch + tickets;
+  p.part_ml = p.part_o + static_cast<size_t>(num_requests) * dec_tok_cap * heads * p.max_splits * head_dim;
   p.error = error;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   switch (head_dim) {
-    case 16: return launch_both<16>(p, num_requests, tile_max_q, rows, request_of_row, positions, s);
-    case 32: return launch_both<32>(p, num_requests, tile_max_q, rows, request_of_row, positions, s);
-    case 64: return launch_both<64>(p, num_requests, tile_max_q, rows, request_of_row, positions, s);
-    case 80: return launch_both<80>(p, num_requests, tile_max_q, rows, request_of_row, positions, s);
-    case 96: return launch_both<96>(p, num_requests, tile_max_q, rows, request_of_row, positions, s);
-    case 128: return launch_both<128>(p, num_requests, tile_max_q, rows, request_of_row, positions, s);
-    case 256: return launch_both<256>(p, num_requests, tile_max_q, rows, request_of_row, positions, s);
+    case 16: return launch_both<16>(p, num_requests, tile_max_q, s);
+    case 32: return launch_both<32>(p, num_requests, tile_max_q, s);
+    case 64: return launch_both<64>(p, num_requests, tile_max_q, s);
+    case 80: return launch_both<80>(p, num_requests, tile_max_q, s);
+    case 96: return launch_both<96>(p, num_requests, tile_max_q, s);
+    case 128: return launch_both<128>(p, num_requests, tile_max_q, s);
+    case 256: return launch_both<256>(p, num_requests, tile_max_q, s);
     default: return PIH_ERR_UNSUPPORTED;
   }
 }

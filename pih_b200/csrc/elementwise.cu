@@ -159,6 +159,85 @@ __global__ void qk_norm_rope_kv_kernel(T* __restrict__ qkv, int row_stride, int 
   }
 }
 
+// Fast path of the kernel above for head_dim = 32 * EPL with EPL in {2, 4, 8} and a rotation over
+// the whole head: a lane keeps EPL contiguous elements in registers; its rotation partner (i +- D/2)
+// sits in lane ^ 16.  Same arithmetic and roundings as the general kernel.
+template <typename T, typename W, int EPL>
+__global__ void qk_norm_rope_kv_fast_kernel(T* __restrict__ qkv, int row_stride, int rows, int heads,
+                                            int kv_heads, const W* __restrict__ q_w,
+                                            const W* __restrict__ k_w, float eps,
+                                            const float* __restrict__ rope, int max_pos,
+                                            const int* __restrict__ positions,
+                                            const int* __restrict__ slot_mapping, T* __restrict__ cache,
+                                            int page_size, int num_pages, int write_kv, uint32_t* error) {
+  constexpr int D = 32 * EPL;
+  constexpr int HALF = D / 2;
+  const int warps_per_block = blockDim.x >> 5;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int slots = heads + (write_kv ? 2 * kv_heads : 0);
+  const long long item = static_cast<long long>(blockIdx.x) * warps_per_block + warp;
+  if (item >= static_cast<long long>(rows) * slots) return;
+  const int t = static_cast<int>(item / slots);
+  const int slot = static_cast<int>(item % slots);
+  T* src = qkv + static_cast<size_t>(t) * row_stride + static_cast<size_t>(slot) * D + lane * EPL;
+  const bool is_q = slot < heads;
+  const bool is_k = !is_q && slot < heads + kv_heads;
+  T* dst_cache = nullptr;
+  if (!is_q) {
+    const int m = slot_mapping[t];
+    if (m < 0 || m >= num_pages * page_size) {
+      if (lane == 0) publish_error(error, kRowWithoutPage);
+    } else {
+      const int page = m / page_size, off = m % page_size;
+      const int h = is_k ? slot - heads : slot - heads - kv_heads;
+      dst_cache = cache + ((static_cast<size_t>(page) * 2 + (is_k ? 0 : 1)) * kv_heads + h) * page_size * D +
+                  static_cast<size_t>(off) * D + lane * EPL;
+    }
+  }
+  struct alignas(EPL * sizeof(T)) Pack { T e[EPL]; };
+  Pack in = *reinterpret_cast<const Pack*>(src);
+  if (!is_q && !is_k) {
+    if (dst_cache != nullptr) *reinterpret_cast<Pack*>(dst_cache) = in;
+    return;
+  }
+  const W* w = is_q ? q_w : k_w;
+  float v[EPL];
+  float ss = 0.0f;
+#pragma unroll
+  for (int j = 0; j < EPL; ++j) {
+    v[j] = to_float<T>(in.e[j]);
+    ss += v[j] * v[j];
+  }
+  if (w != nullptr) {
+    ss = warp_sum(ss);
+    const float scale = 1.0f / sqrtf(ss / static_cast<float>(D) + eps);
+#pragma unroll
+    for (int j = 0; j < EPL; ++j) v[j] = round_to<T>((v[j] * scale) * to_float<W>(w[lane * EPL + j]));
+  }
+  Pack outp;
+  if (rope != nullptr) {
+    int pos = positions[t];
+    if (pos < 0 || pos >= max_pos) {
+      if (lane == 0) publish_error(error, kBadPosition);
+      pos = 0;
+    }
+    const float* cs = rope + static_cast<size_t>(pos) * HALF * 2;
+    const int pair0 = (lane & 15) * EPL;            // pair index of this lane's first element
+#pragma unroll
+    for (int j = 0; j < EPL; ++j) {
+      const float other = __shfl_xor_sync(0xffffffffu, v[j], 16);
+      const float c = cs[2 * (pair0 + j)], sn = cs[2 * (pair0 + j) + 1];
+      const float r = lane < 16 ? v[j] * c - other * sn : v[j] * c + other * sn;
+      outp.e[j] = from_float<T>(r);
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < EPL; ++j) outp.e[j] = from_float<T>(v[j]);
+  }
+  *reinterpret_cast<Pack*>(src) = outp;
+  if (dst_cache != nullptr) *reinterpret_cast<Pack*>(dst_cache) = outp;
+}
+
 // ---------------------------------------------------------------------------
 // SiLU-mul: out[t,i] = round( (g / (1 + exp(-g))) * u ), g = in[t,i], u = in[t,I+i]
 // (qwen_bf16_primitives.cu:274-283)
@@ -209,9 +288,86 @@ extern "C" int pih_embedding(int dtype, const void* table, const int* ids, void*
   return 0;
 }
 
+// Vectorised variant: 16-byte loads, the row kept in registers between the two passes.
+// Needs width * sizeof(T) % 16 == 0 and width <= threads * VEC * CHUNKS.
+template <typename T, typename W, int CHUNKS>
+__global__ void rmsnorm_vec_kernel(T* __restrict__ x, const T* __restrict__ delta,
+                                   const W* __restrict__ weight, T* __restrict__ out,
+                                   const int* __restrict__ rows, int width, float eps) {
+  constexpr int VEC = 16 / sizeof(T);
+  __shared__ float scratch[33];
+  const int o = blockIdx.x;
+  const size_t r = rows != nullptr ? static_cast<size_t>(rows[o]) : static_cast<size_t>(o);
+  T* xr = x + r * width;
+  const T* dr = delta != nullptr ? delta + r * width : nullptr;
+  const bool write_back = delta != nullptr && rows == nullptr;
+  const int nvec = width / VEC;
+  float v[CHUNKS][VEC];
+  float ss = 0.0f;
+#pragma unroll
+  for (int k = 0; k < CHUNKS; ++k) {
+    const int i = threadIdx.x + k * blockDim.x;
+    if (i < nvec) {
+      uint4 raw = reinterpret_cast<const uint4*>(xr)[i];
+      const T* e = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+      for (int j = 0; j < VEC; ++j) v[k][j] = to_float<T>(e[j]);
+      if (dr != nullptr) {
+        uint4 draw = reinterpret_cast<const uint4*>(dr)[i];
+        const T* d = reinterpret_cast<const T*>(&draw);
+        uint4 packed;
+        T* pk = reinterpret_cast<T*>(&packed);
+#pragma unroll
+        for (int j = 0; j < VEC; ++j) {
+          pk[j] = from_float<T>(v[k][j] + to_float<T>(d[j]));
+          v[k][j] = to_float<T>(pk[j]);
+        }
+        if (write_back) reinterpret_cast<uint4*>(xr)[i] = packed;
+      }
+#pragma unroll
+      for (int j = 0; j < VEC; ++j) ss += v[k][j] * v[k][j];
+    }
+  }
+  ss = block_sum(ss, scratch);
+  const float scale = 1.0f / sqrtf(ss / static_cast<float>(width) + eps);
+  T* yr = out + static_cast<size_t>(o) * width;
+#pragma unroll
+  for (int k = 0; k < CHUNKS; ++k) {
+    const int i = threadIdx.x + k * blockDim.x;
+    if (i < nvec) {
+      uint4 packed;
+      T* pk = reinterpret_cast<T*>(&packed);
+#pragma unroll
+      for (int j = 0; j < VEC; ++j)
+        pk[j] = from_float<T>((v[k][j] * scale) * to_float<W>(weight[i * VEC + j]));
+      reinterpret_cast<uint4*>(yr)[i] = packed;
+    }
+  }
+}
+
 template <typename T, typename W>
 static int launch_rmsnorm(void* x, const void* delta, const void* weight, void* out, const int* rows,
                           int out_rows, int width, float eps, cudaStream_t s) {
+  constexpr int VEC = 16 / sizeof(T);
+  if ((width * sizeof(T)) % 16 == 0) {
+    const int nvec = width / VEC;
+    int threads = 32;
+    while (threads < 256 && threads * 2 <= nvec) threads *= 2;         // 32..256
+    if (nvec <= threads * 4) {
+      T* xp = static_cast<T*>(x);
+      const T* dp = static_cast<const T*>(delta);
+      const W* wp = static_cast<const W*>(weight);
+      T* op = static_cast<T*>(out);
+      if (nvec <= threads)
+        rmsnorm_vec_kernel<T, W, 1><<<out_rows, threads, 0, s>>>(xp, dp, wp, op, rows, width, eps);
+      else if (nvec <= threads * 2)
+        rmsnorm_vec_kernel<T, W, 2><<<out_rows, threads, 0, s>>>(xp, dp, wp, op, rows, width, eps);
+      else
+        rmsnorm_vec_kernel<T, W, 4><<<out_rows, threads, 0, s>>>(xp, dp, wp, op, rows, width, eps);
+      PIH_LAUNCH_CHECK();
+      return 0;
+    }
+  }
   int threads = 256;
   if (width <= 128) threads = 32;
   else if (width <= 512) threads = 128;
@@ -244,8 +400,25 @@ static int launch_qk(void* qkv, int row_stride, int rows, int heads, int kv_head
                      const void* q_w, const void* k_w, float eps, const float* rope, int rotary_dim,
                      int max_pos, const int* positions, const int* slot_mapping, void* cache,
                      int page_size, int num_pages, int write_kv, uint32_t* error, cudaStream_t s) {
-  const int warps = 4;
   const long long items = static_cast<long long>(rows) * (heads + (write_kv ? 2 * kv_heads : 0));
+  const bool whole_head = rope == nullptr || rotary_dim == head_dim;
+  if (whole_head && (head_dim == 64 || head_dim == 128 || head_dim == 256) &&
+      (row_stride * sizeof(T)) % 16 == 0) {
+    const int warps = 8;
+    const unsigned blocks = static_cast<unsigned>((items + warps - 1) / warps);
+#define PIH_QK_FAST(EPL)                                                                                   \
+  qk_norm_rope_kv_fast_kernel<T, W, EPL><<<blocks, warps * 32, 0, s>>>(                                     \
+      static_cast<T*>(qkv), row_stride, rows, heads, kv_heads, static_cast<const W*>(q_w),                 \
+      static_cast<const W*>(k_w), eps, rope, max_pos, positions, slot_mapping, static_cast<T*>(cache),     \
+      page_size, num_pages, write_kv, error)
+    if (head_dim == 64) PIH_QK_FAST(2);
+    else if (head_dim == 128) PIH_QK_FAST(4);
+    else PIH_QK_FAST(8);
+#undef PIH_QK_FAST
+    PIH_LAUNCH_CHECK();
+    return 0;
+  }
+  const int warps = 4;
   const long long blocks = (items + warps - 1) / warps;
   const size_t smem = static_cast<size_t>(warps) * head_dim * sizeof(float);
   qk_norm_rope_kv_kernel<T, W><<<static_cast<unsigned>(blocks), warps * 32, smem, s>>>(
@@ -283,24 +456,58 @@ extern "C" int pih_qk_norm_rope_kv_write(int dtype, int weight_dtype, void* qkv,
   return PIH_ERR_BAD_ARGUMENT;
 }
 
+// 16 bytes per thread; needs inter * sizeof(T) % 16 == 0
+template <typename T>
+__global__ void silu_mul_vec_kernel(const T* __restrict__ gate_up, T* __restrict__ out, long long rows,
+                                    int inter) {
+  constexpr int VEC = 16 / sizeof(T);
+  const int per_row = inter / VEC;
+  const long long total = rows * per_row;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long t = i / per_row;
+    const int c = static_cast<int>(i - t * per_row);
+    const uint4 graw = reinterpret_cast<const uint4*>(gate_up + t * 2 * inter)[c];
+    const uint4 uraw = reinterpret_cast<const uint4*>(gate_up + t * 2 * inter + inter)[c];
+    const T* g = reinterpret_cast<const T*>(&graw);
+    const T* u = reinterpret_cast<const T*>(&uraw);
+    uint4 packed;
+    T* pk = reinterpret_cast<T*>(&packed);
+#pragma unroll
+    for (int j = 0; j < VEC; ++j) {
+      const float gv = to_float<T>(g[j]);
+      pk[j] = from_float<T>((gv / (1.0f + expf(-gv))) * to_float<T>(u[j]));
+    }
+    reinterpret_cast<uint4*>(out + t * inter)[c] = packed;
+  }
+}
+
+template <typename T>
+static int launch_silu(const void* gate_up, void* out, long long rows, int inter, cudaStream_t s) {
+  const int threads = 256;
+  if ((inter * sizeof(T)) % 16 == 0) {
+    const long long total = rows * (inter / (16 / sizeof(T)));
+    const unsigned blocks = static_cast<unsigned>(min((total + threads - 1) / threads, 148LL * 32));
+    silu_mul_vec_kernel<T><<<blocks, threads, 0, s>>>(static_cast<const T*>(gate_up), static_cast<T*>(out),
+                                                      rows, inter);
+  } else {
+    const long long total = rows * inter;
+    const unsigned blocks = static_cast<unsigned>(min((total + threads - 1) / threads, 148LL * 32));
+    silu_mul_kernel<T><<<blocks, threads, 0, s>>>(static_cast<const T*>(gate_up), static_cast<T*>(out), rows,
+                                                  inter);
+  }
+  PIH_LAUNCH_CHECK();
+  return 0;
+}
+
 extern "C" int pih_silu_mul(int dtype, const void* gate_up, void* out, long long rows, int inter,
                             void* stream) {
   if (rows <= 0) return 0;
   if (inter <= 0) return PIH_ERR_BAD_ARGUMENT;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  const long long total = rows * inter;
-  const int threads = 256;
-  const unsigned blocks = static_cast<unsigned>(min((total + threads - 1) / threads, 148LL * 16));
-  if (dtype == PIH_F32)
-    silu_mul_kernel<float><<<blocks, threads, 0, s>>>(static_cast<const float*>(gate_up),
-                                                      static_cast<float*>(out), rows, inter);
-  else if (dtype == PIH_BF16)
-    silu_mul_kernel<__nv_bfloat16><<<blocks, threads, 0, s>>>(
-        static_cast<const __nv_bfloat16*>(gate_up), static_cast<__nv_bfloat16*>(out), rows, inter);
-  else
-    return PIH_ERR_BAD_ARGUMENT;
-  PIH_LAUNCH_CHECK();
-  return 0;
+  if (dtype == PIH_F32) return launch_silu<float>(gate_up, out, rows, inter, s);
+  if (dtype == PIH_BF16) return launch_silu<__nv_bfloat16>(gate_up, out, rows, inter, s);
+  return PIH_ERR_BAD_ARGUMENT;
 }
 
 extern "C" int pih_gather_rows(int dtype, const void* in, const int* rows, void* out, int out_rows,

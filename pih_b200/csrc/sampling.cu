@@ -381,15 +381,102 @@ argmax_kernel(const float* __restrict__ logits, int vocab, int* __restrict__ out
   }
 }
 
+// Two-stage argmax for long rows: stage 1 reduces a slice of the row per block to (value, id),
+// stage 2 reduces the slices.  Ties go to the lower id in both stages.
+__global__ void __launch_bounds__(256)
+argmax_slices_kernel(const float* __restrict__ logits, int vocab, int slices, float* __restrict__ part_val,
+                     int* __restrict__ part_idx, uint32_t* error) {
+  __shared__ float s_val[8];
+  __shared__ int s_idx[8];
+  const int row = blockIdx.y, slice = blockIdx.x;
+  const float* base = logits + static_cast<size_t>(row) * vocab;
+  const int per = (vocab + slices - 1) / slices;
+  const int lo = slice * per, hi = min(vocab, lo + per);
+  float best = -INFINITY;
+  int best_id = 0x7fffffff;
+  bool bad = false;
+  for (int id = lo + threadIdx.x; id < hi; id += blockDim.x) {
+    const float v = base[id];
+    if (!isfinite(v)) bad = true;
+    if (v > best || (v == best && id < best_id)) {
+      best = v;
+      best_id = id;
+    }
+  }
+  if (bad) publish_error(error, kNonFiniteLogit);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+  for (int d = 16; d > 0; d >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, best, d);
+    const int oi = __shfl_xor_sync(0xffffffffu, best_id, d);
+    if (ov > best || (ov == best && oi < best_id)) {
+      best = ov;
+      best_id = oi;
+    }
+  }
+  if (lane == 0) {
+    s_val[warp] = best;
+    s_idx[warp] = best_id;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int w = 1; w < (blockDim.x >> 5); ++w)
+      if (s_val[w] > best || (s_val[w] == best && s_idx[w] < best_id)) {
+        best = s_val[w];
+        best_id = s_idx[w];
+      }
+    part_val[row * slices + slice] = best;
+    part_idx[row * slices + slice] = best_id;
+  }
+}
+
+__global__ void argmax_final_kernel(const float* __restrict__ part_val, const int* __restrict__ part_idx,
+                                    int slices, int* __restrict__ out_tokens) {
+  const int row = blockIdx.x, lane = threadIdx.x;
+  float best = -INFINITY;
+  int best_id = 0x7fffffff;
+  for (int s = lane; s < slices; s += 32) {
+    const float v = part_val[row * slices + s];
+    const int i = part_idx[row * slices + s];
+    if (v > best || (v == best && i < best_id)) {
+      best = v;
+      best_id = i;
+    }
+  }
+#pragma unroll
+  for (int d = 16; d > 0; d >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, best, d);
+    const int oi = __shfl_xor_sync(0xffffffffu, best_id, d);
+    if (ov > best || (ov == best && oi < best_id)) {
+      best = ov;
+      best_id = oi;
+    }
+  }
+  if (lane == 0) out_tokens[row] = best_id == 0x7fffffff ? 0 : best_id;
+}
+
 }  // namespace pih
 
 using namespace pih;
 
-extern "C" int pih_argmax(const float* logits, int rows, int vocab, int* out_tokens, uint32_t* error,
-                          void* stream) {
+// scratch: rows * 64 floats followed by rows * 64 ints (used when vocab is large); may be null,
+// in which case one block reduces each row.
+extern "C" int pih_argmax(const float* logits, int rows, int vocab, int* out_tokens, void* scratch,
+                          uint32_t* error, void* stream) {
   if (rows <= 0) return 0;
   if (vocab <= 0) return PIH_ERR_BAD_ARGUMENT;
-  argmax_kernel<<<rows, kSampleThreads, 0, static_cast<cudaStream_t>(stream)>>>(logits, vocab, out_tokens, error);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (scratch != nullptr && vocab >= 8192 && rows <= 65535) {
+    const int slices = 64;
+    float* pv = static_cast<float*>(scratch);
+    int* pi = reinterpret_cast<int*>(pv + static_cast<size_t>(rows) * slices);
+    argmax_slices_kernel<<<dim3(slices, rows), 256, 0, s>>>(logits, vocab, slices, pv, pi, error);
+    PIH_LAUNCH_CHECK();
+    argmax_final_kernel<<<rows, 32, 0, s>>>(pv, pi, slices, out_tokens);
+    PIH_LAUNCH_CHECK();
+    return 0;
+  }
+  argmax_kernel<<<rows, kSampleThreads, 0, s>>>(logits, vocab, out_tokens, error);
   PIH_LAUNCH_CHECK();
   return 0;
 }

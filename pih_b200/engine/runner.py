@@ -160,7 +160,7 @@ class ModelRunner:
             for block in self.model.blocks:
                 spec = getattr(block.mixer, "spec", None)
                 if spec is not None and hasattr(spec, "heads"):
-                    ops.reserve_attention_scratch(B, 1, spec.heads, spec.head_dim, max_ctx)
+                    ops.reserve_attention_scratch(B, 1, spec.heads, spec.kv_heads, spec.head_dim, max_ctx)
         caches = [self.cache.view(i, batch.block_tables, batch.slot_mappings) for i in range(self.num_entries)]
         # once eagerly on a side stream (lazy initialisations must not happen under capture) ...
         side = torch.cuda.Stream(self.device)

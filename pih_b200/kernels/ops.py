@@ -183,16 +183,17 @@ class CudaOps:
                 tile_max_q = max(tile_max_q, n)
         return tile_max_q, dec_cap, dec_ctx
 
-    def reserve_attention_scratch(self, num_requests, dec_tok_cap, heads, head_dim, max_ctx) -> None:
+    def reserve_attention_scratch(self, num_requests, dec_tok_cap, heads, kv_heads, head_dim, max_ctx) -> None:
         """Make the split kernel's scratch large enough (before a CUDA graph that uses it is
         captured: an allocation cannot happen under capture).  A buffer that is outgrown is kept
         alive, because captured graphs hold its address."""
-        need = self.lib.pih_attention_scratch_floats(num_requests, dec_tok_cap, heads, head_dim,
+        need = self.lib.pih_attention_scratch_floats(num_requests, dec_tok_cap, heads, kv_heads, head_dim,
                                                      -(-max_ctx // self.attention_split))
         if self._attn_scratch is None or self._attn_scratch.numel() < need:
             if self._attn_scratch is not None:
                 self._retired_scratch.append(self._attn_scratch)     # captured graphs may still point at it
-            self._attn_scratch = torch.empty(int(need * 1.25) + 1024, dtype=torch.float32, device=self.device)
+            # zeroed: the leading words are the kernel's tickets, which it leaves at zero
+            self._attn_scratch = torch.zeros(int(need * 1.25) + 1024, dtype=torch.float32, device=self.device)
 
     def paged_attention_mma(self, qkv, *, heads, kv_heads, head_dim, kv_cache, block_table, step, scale,
                             window, plan=None) -> torch.Tensor:
@@ -211,12 +212,11 @@ class CudaOps:
         split = self.attention_split
         scratch = None
         if dec_cap > 0:
-            self.reserve_attention_scratch(step.num_requests, dec_cap, heads, head_dim, dec_ctx)
+            self.reserve_attention_scratch(step.num_requests, dec_cap, heads, kv_heads, head_dim, dec_ctx)
             scratch = self._attn_scratch
         rc = self.lib.pih_paged_attention_mma(
             _ptr(qkv), qkv.stride(0), _ptr(out), _ptr(kv_cache), _ptr(block_table), block_table.shape[1],
-            _ptr(step.cu_q), _ptr(step.q_start), _ptr(step.request_of_row), _ptr(step.positions), rows,
-            step.num_requests, tile_max_q, dec_cap, dec_ctx, heads, kv_heads, head_dim, page_size, num_pages,
+            _ptr(step.cu_q), _ptr(step.q_start), rows, step.num_requests, tile_max_q, dec_cap, dec_ctx, heads, kv_heads, head_dim, page_size, num_pages,
             c_float(scale), int(window), split, _ptr(scratch), self._err(), self._stream())
         self._check(rc, "paged_attention_mma")
         return out
@@ -244,7 +244,8 @@ class CudaOps:
     def argmax(self, logits: torch.Tensor) -> torch.Tensor:
         rows, vocab = logits.shape
         out = torch.empty(rows, dtype=torch.int32, device=logits.device)
-        rc = self.lib.pih_argmax(_ptr(logits), rows, vocab, _ptr(out), self._err(), self._stream())
+        scratch = torch.empty(rows * 128, dtype=torch.float32, device=logits.device) if vocab >= 8192 else None
+        rc = self.lib.pih_argmax(_ptr(logits), rows, vocab, _ptr(out), _ptr(scratch), self._err(), self._stream())
         self._check(rc, "argmax")
         return out
 
