@@ -274,6 +274,7 @@ def main() -> int:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--skip-e2e", action="store_true")
     ap.add_argument("--skip-points", action="store_true")
+    ap.add_argument("--skip-prefill", action="store_true")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm()
@@ -293,7 +294,7 @@ def main() -> int:
     if not args.skip_points:
         for b in (1, 64):
             points[f"decode_b{b}"] = round(decode_run(model, b, max(8, args.steps // 2), 3)["tok_s"], 1)
-    pre = prefill_run(model, PREFILL_TOKENS)
+    pre = {"ms": float("nan"), "tok_s": float("nan"), "flops": 0.0} if args.skip_prefill else prefill_run(model, PREFILL_TOKENS)
     e2e = None
     if not args.skip_e2e:
         from pih_b200.weights import write_random_model

@@ -1,0 +1,164 @@
+"""Times single kernels of the pack at the benchmark's sizes (Qwen3-0.6B shapes by default).
+
+    python bench_kernels.py attn_decode --batch 8 --ctx 2048
+    python bench_kernels.py attn_prefill --tokens 2048
+    python bench_kernels.py linear --m 8 --n 4096 --k 1024
+    python bench_kernels.py rmsnorm|qk|silu --rows 8
+
+Each kernel is timed with CUDA events on the launching stream after warm-up;
+between timed launches a buffer larger than the 126 MB L2 is written so that
+inputs come from HBM.  Prints one JSON line with the time, the algorithmic
+bytes or flops and the achieved rate.  It is the small case that the ncu
+summaries under profiles/ were captured on.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import sys
+from types import SimpleNamespace
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+
+def time_kernel(fn, iters, flush=True):
+    import torch
+    junk = torch.empty(160 * 1024 * 1024, dtype=torch.uint8, device="cuda") if flush else None
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    times = []
+    for _ in range(iters):
+        if junk is not None:
+            junk.fill_(1)
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        fn()
+        stop.record()
+        torch.cuda.synchronize()
+        times.append(start.elapsed_time(stop) * 1e3)
+    times.sort()
+    return times[len(times) // 2]
+
+
+def step_of(lens, new, dev):
+    import torch
+    cu = [0]
+    for n in new:
+        cu.append(cu[-1] + n)
+    starts = [l - n for l, n in zip(lens, new)]
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)
+    return SimpleNamespace(num_requests=len(lens), cu_q=i32(cu), q_start=i32(starts), host_cu_q=cu,
+                           host_q_start=starts, attention_plans={},
+                           request_of_row=i32([r for r, n in enumerate(new) for _ in range(n)]),
+                           positions=i32([starts[r] + i for r, n in enumerate(new) for i in range(n)]))
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("kernel", choices=["attn_decode", "attn_prefill", "linear", "rmsnorm", "qk", "silu", "argmax"])
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--ctx", type=int, default=2048)
+    ap.add_argument("--tokens", type=int, default=2048)
+    ap.add_argument("--heads", type=int, default=16)
+    ap.add_argument("--kv-heads", type=int, default=8)
+    ap.add_argument("--head-dim", type=int, default=128)
+    ap.add_argument("--page", type=int, default=16)
+    ap.add_argument("--m", type=int, default=8)
+    ap.add_argument("--n", type=int, default=4096)
+    ap.add_argument("--k", type=int, default=1024)
+    ap.add_argument("--rows", type=int, default=8)
+    ap.add_argument("--width", type=int, default=1024)
+    ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--no-flush", action="store_true")
+    ap.add_argument("--plain", action="store_true", help="the pack's plain (generic / FMA) kernel instead")
+    args = ap.parse_args()
+
+    import torch
+    from pih_b200.kernels import get_ops
+    dev = torch.device("cuda:0")
+    ops = get_ops(dev)
+    bf = torch.bfloat16
+    H, KV, D, P = args.heads, args.kv_heads, args.head_dim, args.page
+    out = {"kernel": args.kernel}
+
+    if args.kernel in ("attn_decode", "attn_prefill"):
+        if args.kernel == "attn_decode":
+            lens, new = [args.ctx] * args.batch, [1] * args.batch
+        else:
+            lens, new = [args.tokens], [args.tokens]
+        pages_per = [-(-n // P) for n in lens]
+        num_pages = sum(pages_per)
+        cache = torch.randn(num_pages, 2, KV, P, D, device=dev).to(bf)
+        table = torch.full((len(lens), max(pages_per)), -1, dtype=torch.int32)
+        perm = torch.randperm(num_pages).tolist()
+        for r, n in enumerate(pages_per):
+            table[r, :n] = torch.tensor([perm.pop() for _ in range(n)], dtype=torch.int32)
+        table = table.to(dev)
+        q = torch.randn(sum(new), (H + 2 * KV) * D, device=dev).to(bf)
+        step = step_of(lens, new, dev)
+        scale = 1.0 / math.sqrt(D)
+        if args.plain:
+            fn = lambda: ops.paged_attention_generic(q, heads=H, kv_heads=KV, head_dim=D, kv_cache=cache,
+                                                     block_table=table, request_of_row=step.request_of_row,
+                                                     positions=step.positions, scale=scale, window=0)
+        else:
+            fn = lambda: ops.paged_attention_mma(q, heads=H, kv_heads=KV, head_dim=D, kv_cache=cache,
+                                                 block_table=table, step=step, scale=scale, window=0)
+        us = time_kernel(fn, args.iters, not args.no_flush)
+        if args.kernel == "attn_decode":
+            nbytes = sum(lens) * 2 * KV * D * 2
+            out.update(us=round(us, 2), bytes=nbytes, gbs=round(nbytes / us / 1e3, 1), batch=args.batch, ctx=args.ctx)
+        else:
+            T = args.tokens
+            flops = 4 * H * D * T * (T + 1) // 2
+            out.update(us=round(us, 2), flops=flops, tflops=round(flops / us / 1e6, 1), tokens=T)
+    elif args.kernel == "linear":
+        x = torch.randn(args.m, args.k, device=dev).to(bf)
+        w = torch.randn(args.n, args.k, device=dev).to(bf)
+        fn = (lambda: ops.linear_plain(x, w)) if args.plain else (lambda: ops.linear(x, w))
+        us = time_kernel(fn, args.iters, not args.no_flush)
+        flops = 2 * args.m * args.n * args.k
+        nbytes = 2 * (args.m * args.k + args.n * args.k + args.m * args.n)
+        out.update(us=round(us, 2), tflops=round(flops / us / 1e6, 2), gbs=round(nbytes / us / 1e3, 1),
+                   m=args.m, n=args.n, k=args.k)
+    elif args.kernel == "rmsnorm":
+        x = torch.randn(args.rows, args.width, device=dev).to(bf)
+        d = torch.randn(args.rows, args.width, device=dev).to(bf)
+        w = torch.ones(args.width, device=dev).to(bf)
+        us = time_kernel(lambda: ops.rmsnorm(x, w, 1e-6, delta=d), args.iters, not args.no_flush)
+        nbytes = args.rows * args.width * 2 * 4
+        out.update(us=round(us, 2), gbs=round(nbytes / us / 1e3, 1), rows=args.rows, width=args.width)
+    elif args.kernel == "qk":
+        rows = args.rows
+        qkv = torch.randn(rows, (H + 2 * KV) * D, device=dev).to(bf)
+        qw = torch.ones(D, device=dev).to(bf)
+        cache = torch.zeros(-(-rows // P) + 1, 2, KV, P, D, device=dev, dtype=bf)
+        table = torch.zeros(4096, D // 2, 2, device=dev)
+        pos = torch.arange(rows, dtype=torch.int32, device=dev) % 4096
+        slots = torch.arange(rows, dtype=torch.int32, device=dev)
+        fn = lambda: ops.qk_norm_rope_kv_write(qkv, heads=H, kv_heads=KV, head_dim=D, q_norm=qw, k_norm=qw, eps=1e-6,
+                                               rope_table=table, rotary_dim=D, positions=pos, slot_mapping=slots,
+                                               kv_cache=cache, write_kv=True)
+        us = time_kernel(fn, args.iters, not args.no_flush)
+        nbytes = rows * ((H + 2 * KV) * D * 2 + (H + KV) * D * 2 + 2 * KV * D * 2)
+        out.update(us=round(us, 2), gbs=round(nbytes / us / 1e3, 1), rows=rows)
+    elif args.kernel == "silu":
+        gu = torch.randn(args.rows, 2 * 3072, device=dev).to(bf)
+        us = time_kernel(lambda: ops.silu_mul(gu), args.iters, not args.no_flush)
+        nbytes = args.rows * 3072 * 2 * 3
+        out.update(us=round(us, 2), gbs=round(nbytes / us / 1e3, 1), rows=args.rows)
+    elif args.kernel == "argmax":
+        lg = torch.randn(args.rows, 151936, device=dev)
+        us = time_kernel(lambda: ops.argmax(lg), args.iters, not args.no_flush)
+        out.update(us=round(us, 2), gbs=round(args.rows * 151936 * 4 / us / 1e3, 1), rows=args.rows)
+    ops.check_errors()
+    print(json.dumps(out))
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

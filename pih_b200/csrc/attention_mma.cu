@@ -445,20 +445,52 @@ attn_split_kernel(const AttnParams p) {
   __syncthreads();
   if (!s_last) return;
   __threadfence();
-  for (int idx = threadIdx.x; idx < packed * D; idx += THREADS) {
-    const int row = idx / D, d = idx % D;
+  // Final merge over the splits, ascending.  The weights exp2(m_s - M) of every (row, split) are
+  // formed first, with all loads of a pass in flight together; then every output element is a short
+  // sum whose loads are issued in batches.
+  const int nsp = s_hi - s_lo + 1;
+  float* Fw = reinterpret_cast<float*>(KV);          // [16][nsp] weights, then [16] sums
+  float* Lsum = Fw + 16 * nsp;
+  for (int idx = threadIdx.x; idx < packed * nsp; idx += THREADS) {
+    const int row = idx / nsp, s = s_lo + idx % nsp;
+    const size_t slot =
+        ((static_cast<size_t>(r) * p.dec_tok_cap + row / G) * p.heads + g * G + row % G) * p.max_splits + s;
+    Fw[row * nsp + (s - s_lo)] = __ldcg(p.part_ml + slot * 2);
+  }
+  __syncthreads();
+  if (threadIdx.x < packed) {
+    const int row = threadIdx.x;
     const size_t base =
         ((static_cast<size_t>(r) * p.dec_tok_cap + row / G) * p.heads + g * G + row % G) * p.max_splits;
     float mm = -INFINITY;
-    for (int s = s_lo; s <= s_hi; ++s) mm = fmaxf(mm, __ldcg(p.part_ml + (base + s) * 2));
-    float acc = 0.0f, ll = 0.0f;
-    for (int s = s_lo; s <= s_hi; ++s) {
-      const float ms = __ldcg(p.part_ml + (base + s) * 2);
-      if (ms == -INFINITY) continue;
-      const float f = exp2f(ms - mm);
-      ll += __ldcg(p.part_ml + (base + s) * 2 + 1) * f;
-      acc += __ldcg(p.part_o + (base + s) * D + d) * f;
+    for (int s = 0; s < nsp; ++s) mm = fmaxf(mm, Fw[row * nsp + s]);
+    float ll = 0.0f;
+    for (int s = 0; s < nsp; ++s) {
+      const float ms = Fw[row * nsp + s];
+      const float f = ms == -INFINITY ? 0.0f : exp2f(ms - mm);
+      Fw[row * nsp + s] = f;
+      ll += f == 0.0f ? 0.0f : __ldcg(p.part_ml + (base + s_lo + s) * 2 + 1) * f;
     }
+    Lsum[row] = ll;
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < packed * D; idx += THREADS) {
+    const int row = idx / D, d = idx % D;
+    const size_t base =
+        ((static_cast<size_t>(r) * p.dec_tok_cap + row / G) * p.heads + g * G + row % G) * p.max_splits + s_lo;
+    const float* po = p.part_o + base * D + d;
+    const float* fw = Fw + row * nsp;
+    float acc = 0.0f;
+    int s = 0;
+    for (; s + 8 <= nsp; s += 8) {
+      float v[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) v[u] = fw[s + u] == 0.0f ? 0.0f : __ldcg(po + static_cast<size_t>(s + u) * D);
+#pragma unroll
+      for (int u = 0; u < 8; ++u) acc += v[u] * fw[s + u];
+    }
+    for (; s < nsp; ++s) acc += fw[s] == 0.0f ? 0.0f : __ldcg(po + static_cast<size_t>(s) * D) * fw[s];
+    const float ll = Lsum[row];
     if (!(ll > 0.0f) || !isfinite(ll)) {
       publish_error(p.error, kAttentionDenominator);
       continue;
@@ -490,6 +522,9 @@ static int launch_both(const AttnParams& p, int R, int tile_max_q, cudaStream_t 
     int smem = (16 * LD + 2 * tiles * BN * LD) * static_cast<int>(sizeof(__nv_bfloat16));
     const int merge = 16 * LD * static_cast<int>(sizeof(__nv_bfloat16)) + (4 * 16 * D + 128) * static_cast<int>(sizeof(float));
     if (merge > smem) smem = merge;
+    const int final_merge = 16 * LD * static_cast<int>(sizeof(__nv_bfloat16)) +
+                            (16 * p.max_splits + 16) * static_cast<int>(sizeof(float));
+    if (final_merge > smem) smem = final_merge;
     if (smem > 227 * 1024) return PIH_ERR_UNSUPPORTED;
     if (split_smem_set < smem) {
       cudaError_t e = cudaFuncSetAttribute(attn_split_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);

@@ -1,0 +1,305 @@
+// C[M,N] = A[M,K] . W[N,K]^T in bf16 on the 5th-generation tensor cores:
+// tcgen05.mma with the accumulator in tensor memory, operands brought to
+// shared memory by TMA (128-byte swizzle), fp32 accumulation, bf16 or fp32
+// output rounded once.
+//
+// The reference runs every product through cuBLASLt
+// (src/backend/cuda/gemm_plan.cpp:83-199) and has no kernel of its own.
+//
+// One CTA computes one 128 x BN tile of C (BN = 128).  Warp roles:
+//   warp 0      TMA producer: one thread issues the two tile loads of a k-block
+//               (A 128 x 64, W BN x 64) into a ring of STAGES buffers;
+//   warp 1      allocates tensor memory, then one thread issues the four
+//               tcgen05.mma (K = 16 each) of a k-block and commits them to the
+//               buffer's "empty" barrier, which frees the buffer when they finish;
+//   warps 2-5   epilogue: wait for the accumulator, read it from tensor memory
+//               (tcgen05.ld, one row per thread), convert and store.
+// Both operands are K-major ("TN"): the natural layout of activations [M,K]
+// and weights [N,K].  Rows and columns beyond M, N or K are zero-filled by
+// TMA on the way in and masked on the way out, so every size is taken as long
+// as K is a multiple of 8 (a TMA row stride must be a multiple of 16 bytes).
+//
+// Every wait on an mbarrier is bounded; when a bound is hit the kernel records
+// kWaitTimedOut, stops waiting, still frees its tensor memory and returns.
+// No cluster launch and no multicast are used.
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace pih {
+
+constexpr int GM = 128;          // tile rows (UMMA M)
+constexpr int GN = 128;          // tile columns (UMMA N)
+constexpr int GK = 64;           // k-block: 64 bf16 = one 128-byte swizzle row
+constexpr int UMMA_K = 16;
+constexpr int STAGES = 5;
+constexpr long long kWaitCycles = 4000000000LL;      // about two seconds of SM clock
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(bytes));
+}
+// Bounded wait for the phase with the given parity; false when the bound was hit.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint32_t* error) {
+  const uint32_t addr = smem_u32(bar);
+  const long long t0 = clock64();
+  for (uint32_t spin = 0;; ++spin) {
+    if ((spin & 1023u) == 1023u && clock64() - t0 > kWaitCycles) break;
+    uint32_t done;
+    asm volatile(
+        "{\n.reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.b32 %0, 1, 0, p;\n}\n"
+        : "=r"(done)
+        : "r"(addr), "r"(parity)
+        : "memory");
+    if (done) return true;
+  }
+  publish_error(error, kWaitTimedOut);
+  return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n" ::
+          "r"(smem_u32(smem_dst)),
+      "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(smem_u32(bar))
+      : "memory");
+}
+
+// Shared-memory matrix descriptor of a K-major operand tile stored as rows of 128 bytes with the
+// 128-byte swizzle (what TMA writes): 8-row groups are 1024 bytes apart (stride byte offset), the
+// leading byte offset is 1 (unused for swizzled K-major), version 1, layout type 2 (SWIZZLE_128B).
+__device__ __forceinline__ uint64_t umma_smem_desc(uint32_t smem_addr) {
+  uint64_t desc = 0;
+  desc |= static_cast<uint64_t>((smem_addr & 0x3FFFF) >> 4);          // start address, bits [0,14)
+  desc |= static_cast<uint64_t>(1) << 16;                             // leading byte offset >> 4
+  desc |= static_cast<uint64_t>(1024 >> 4) << 32;                     // stride byte offset >> 4
+  desc |= static_cast<uint64_t>(1) << 46;                             // version
+  desc |= static_cast<uint64_t>(2) << 61;                             // SWIZZLE_128B
+  return desc;
+}
+
+// Instruction descriptor, kind::f16: fp32 accumulator, bf16 A and B, both K-major, N and M.
+__host__ __device__ constexpr uint32_t umma_instr_desc(int m, int n) {
+  return (1u << 4)                                  // c_format = F32
+         | (1u << 7)                                // a_format = BF16
+         | (1u << 10)                               // b_format = BF16
+         | (static_cast<uint32_t>(n >> 3) << 17)    // n_dim
+         | (static_cast<uint32_t>(m >> 4) << 24);   // m_dim
+}
+
+struct GemmSmem {
+  alignas(1024) __nv_bfloat16 a[STAGES][GM * GK];   // 16 KB per stage
+  alignas(1024) __nv_bfloat16 b[STAGES][GN * GK];   // 16 KB per stage
+  alignas(8) uint64_t full[STAGES];
+  alignas(8) uint64_t empty[STAGES];
+  alignas(8) uint64_t accum_ready;
+  uint32_t tmem_base;
+};
+
+template <typename TC>
+__global__ void __launch_bounds__(192)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
+                    TC* __restrict__ C, int M, int N, int K, long long ldc, uint32_t* error) {
+  extern __shared__ unsigned char smem_raw[];
+  GemmSmem& sm = *reinterpret_cast<GemmSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int m0 = blockIdx.y * GM, n0 = blockIdx.x * GN;
+  const int kblocks = (K + GK - 1) / GK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&sm.full[s], 1);
+      mbar_init(&sm.empty[s], 1);
+    }
+    mbar_init(&sm.accum_ready, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+  }
+  if (warp == 1) {
+    // tensor memory: GN fp32 columns for the accumulator
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(&sm.tmem_base)),
+                 "r"(GN));
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::);
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+  const uint32_t tmem_acc = sm.tmem_base;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      asm volatile("prefetch.tensormap [%0];\n" ::"l"(reinterpret_cast<uint64_t>(&map_a)) : "memory");
+      asm volatile("prefetch.tensormap [%0];\n" ::"l"(reinterpret_cast<uint64_t>(&map_w)) : "memory");
+      for (int kb = 0; kb < kblocks; ++kb) {
+        const int s = kb % STAGES;
+        const uint32_t round = kb / STAGES;
+        if (round > 0 && !mbar_wait(&sm.empty[s], (round - 1) & 1, error)) break;
+        mbar_expect_tx(&sm.full[s], (GM + GN) * GK * sizeof(__nv_bfloat16));
+        tma_load_2d(sm.a[s], &map_a, kb * GK, m0, &sm.full[s]);
+        tma_load_2d(sm.b[s], &map_w, kb * GK, n0, &sm.full[s]);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_instr_desc(GM, GN);
+      for (int kb = 0; kb < kblocks; ++kb) {
+        const int s = kb % STAGES;
+        if (!mbar_wait(&sm.full[s], (kb / STAGES) & 1, error)) break;
+        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+        const uint32_t a_addr = smem_u32(sm.a[s]), b_addr = smem_u32(sm.b[s]);
+#pragma unroll
+        for (int k = 0; k < GK / UMMA_K; ++k) {
+          const uint64_t adesc = umma_smem_desc(a_addr + k * UMMA_K * 2);
+          const uint64_t bdesc = umma_smem_desc(b_addr + k * UMMA_K * 2);
+          const uint32_t accumulate = (kb > 0 || k > 0) ? 1u : 0u;
+          asm volatile(
+              "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+              "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n" ::"r"(tmem_acc),
+              "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+              : "memory");
+        }
+        // frees the buffer when the MMAs that read it have finished
+        asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(
+                         smem_u32(&sm.empty[s]))
+                     : "memory");
+      }
+      asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(
+                       smem_u32(&sm.accum_ready))
+                   : "memory");
+    }
+  } else {
+    // epilogue: warp w may touch tensor-memory lanes 32 * (w % 4) .. + 31
+    const int quarter = warp & 3;
+    const bool ok = mbar_wait(&sm.accum_ready, 0, error);
+    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+    const int row = m0 + quarter * 32 + lane;
+    if (ok) {
+#pragma unroll 1
+      for (int c0 = 0; c0 < GN; c0 += 32) {
+        uint32_t v[32];
+        const uint32_t taddr = tmem_acc + (static_cast<uint32_t>(quarter * 32) << 16) + c0;
+        asm volatile(
+            "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+            "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+            "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
+            : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+              "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
+              "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]),
+              "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]),
+              "=r"(v[30]), "=r"(v[31])
+            : "r"(taddr));
+        asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+        if (row < M) {
+          TC* dst = C + static_cast<long long>(row) * ldc + n0 + c0;
+          const bool full = n0 + c0 + 32 <= N && (reinterpret_cast<uintptr_t>(dst) & 15) == 0;
+          if (full) {
+            if constexpr (sizeof(TC) == 2) {
+              uint32_t packed[16];
+#pragma unroll
+              for (int j = 0; j < 16; ++j) {
+                __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(v[2 * j]), __uint_as_float(v[2 * j + 1]));
+                packed[j] = *reinterpret_cast<uint32_t*>(&h);
+              }
+#pragma unroll
+              for (int j = 0; j < 4; ++j)
+                reinterpret_cast<uint4*>(dst)[j] =
+                    make_uint4(packed[4 * j], packed[4 * j + 1], packed[4 * j + 2], packed[4 * j + 3]);
+            } else {
+#pragma unroll
+              for (int j = 0; j < 8; ++j)
+                reinterpret_cast<uint4*>(dst)[j] = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+            }
+          } else {
+            for (int j = 0; j < 32; ++j)
+              if (n0 + c0 + j < N) dst[j] = from_float<TC>(__uint_as_float(v[j]));
+          }
+        }
+      }
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_acc), "r"(GN));
+  }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_tiled() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  return fn;
+}
+
+// 2-D bf16 tensor [rows, cols] with a row stride of ld elements; box = box_rows x 64 columns, 128-byte swizzle.
+static bool make_map(CUtensorMap* map, const void* base, long long rows, long long cols, long long ld, int box_rows) {
+  EncodeTiledFn fn = encode_tiled();
+  if (fn == nullptr) return false;
+  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * sizeof(__nv_bfloat16)};
+  const cuuint32_t box[2] = {static_cast<cuuint32_t>(GK), static_cast<cuuint32_t>(box_rows)};
+  const cuuint32_t elem[2] = {1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+}  // namespace pih
+
+using namespace pih;
+
+// out_dtype: PIH_BF16 or PIH_F32.  Returns PIH_ERR_UNSUPPORTED when the operands cannot be described
+// to TMA (K or a row stride not a multiple of 8 elements, a base not 16-byte aligned): the caller then
+// uses another product.
+extern "C" int pih_gemm_tcgen05(int out_dtype, const void* A, const void* W, void* C, int M, int N, int K,
+                                long long lda, long long ldw, long long ldc, uint32_t* error, void* stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if (K <= 0) return PIH_ERR_BAD_ARGUMENT;
+  if (K % 8 || lda % 8 || ldw % 8 || (reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(W) & 15))
+    return PIH_ERR_UNSUPPORTED;
+  CUtensorMap map_a, map_w;
+  if (!make_map(&map_a, A, M, K, lda, GM) || !make_map(&map_w, W, N, K, ldw, GN)) return PIH_ERR_UNSUPPORTED;
+  const int smem = static_cast<int>(sizeof(GemmSmem)) + 1024;
+  dim3 grid((N + GN - 1) / GN, (M + GM - 1) / GM);
+  if (grid.y > 65535) return PIH_ERR_UNSUPPORTED;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  static bool configured[2] = {false, false};
+  if (out_dtype == PIH_BF16) {
+    if (!configured[0]) {
+      cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<__nv_bfloat16>,
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+      if (e != cudaSuccess) return static_cast<int>(e);
+      configured[0] = true;
+    }
+    gemm_tcgen05_kernel<__nv_bfloat16><<<grid, 192, smem, s>>>(map_a, map_w, static_cast<__nv_bfloat16*>(C), M, N, K,
+                                                                ldc, error);
+  } else if (out_dtype == PIH_F32) {
+    if (!configured[1]) {
+      cudaError_t e =
+          cudaFuncSetAttribute(gemm_tcgen05_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+      if (e != cudaSuccess) return static_cast<int>(e);
+      configured[1] = true;
+    }
+    gemm_tcgen05_kernel<float><<<grid, 192, smem, s>>>(map_a, map_w, static_cast<float*>(C), M, N, K, ldc, error);
+  } else {
+    return PIH_ERR_BAD_ARGUMENT;
+  }
+  PIH_LAUNCH_CHECK();
+  return 0;
+}

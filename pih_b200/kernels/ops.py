@@ -59,6 +59,7 @@ class CudaOps:
         self._retired_scratch = []
         self.attention_split = 128         # keys per split of the decode attention kernel
         self.tensor_core_attention = True  # False: bf16 attention runs on the generic kernel too
+        self.tcgen05_min_rows = None       # bf16 products with at least this many rows use the pack's tcgen05 kernel
         self._declare()
 
     # -- plumbing ---------------------------------------------------------------
@@ -66,7 +67,7 @@ class CudaOps:
         lib = self.lib
         for name in ("pih_embedding", "pih_rmsnorm", "pih_qk_norm_rope_kv_write", "pih_silu_mul",
                      "pih_gather_rows", "pih_gemm_simt", "pih_paged_attention_generic", "pih_argmax",
-                     "pih_sample", "pih_paged_attention_mma"):
+                     "pih_sample", "pih_paged_attention_mma", "pih_gemm_tcgen05"):
             getattr(lib, name).restype = c_int
         lib.pih_attention_scratch_floats.restype = c_ll
 
@@ -126,9 +127,27 @@ class CudaOps:
                                         c_ll(w.stride(0)), c_ll(N), self._stream())
             self._check(rc, "gemm_simt")
             return out
+        if self.tcgen05_min_rows is not None and M >= self.tcgen05_min_rows:
+            out = self.linear_tcgen05(x, w, out_dtype)
+            if out is not None:
+                return out
         if out_dtype == torch.float32:
             return torch.mm(x, w.t(), out_dtype=torch.float32)
         return torch.mm(x, w.t())
+
+    def linear_tcgen05(self, x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None):
+        """The pack's tcgen05 / TMA product (bf16 in, fp32 accumulation).  Returns None when the
+        operands cannot be described to TMA (K or a row stride not a multiple of 8)."""
+        M, K = x.shape
+        N = w.shape[0]
+        out_dtype = out_dtype or x.dtype
+        out = torch.empty(M, N, dtype=out_dtype, device=x.device)
+        rc = self.lib.pih_gemm_tcgen05(_DT[out_dtype], _ptr(x), _ptr(w), _ptr(out), M, N, K, c_ll(x.stride(0)),
+                                       c_ll(w.stride(0)), c_ll(N), self._err(), self._stream())
+        if rc == -2:
+            return None
+        self._check(rc, "gemm_tcgen05")
+        return out
 
     def linear_plain(self, x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
         """The pack's FMA product for any supported dtype (plain twin of the tensor-core products)."""

@@ -100,6 +100,32 @@ def test_linear(ops, dtype, M, N, K):
         torch.testing.assert_close(out32.cpu().double(), ref, **acc)
 
 
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("M,N,K", [(128, 128, 64), (1, 8, 8), (37, 130, 96), (300, 257, 1032), (2048, 1024, 3072),
+                                   (129, 1000, 72), (64, 152, 1024)])
+def test_linear_tcgen05(ops, out_dtype, M, N, K):
+    """The tcgen05 / TMA product against a float64 reference: tiles that overhang M, N and K."""
+    x = _rand((M, K), torch.bfloat16, 3)
+    w = _rand((N, K), torch.bfloat16, 4, 0.1)
+    out = ops.linear_tcgen05(x, w, out_dtype)
+    ops.check_errors()
+    assert out is not None and out.dtype == out_dtype and out.shape == (M, N)
+    ref = x.cpu().double() @ w.cpu().double().T
+    tol = dict(rtol=1e-4, atol=1e-4) if out_dtype == torch.float32 else _tol(torch.bfloat16)
+    if out_dtype == torch.bfloat16:
+        tol = dict(rtol=8e-3, atol=1e-3 * max(1.0, float(ref.abs().max()) / 4))
+    torch.testing.assert_close(out.cpu().double(), ref, **tol)
+
+
+def test_linear_tcgen05_takes_strided_rows_and_refuses_what_tma_cannot_describe(ops):
+    x = _rand((40, 256), torch.bfloat16, 5)
+    w = _rand((512, 128), torch.bfloat16, 6, 0.1)
+    out = ops.linear_tcgen05(x[:, :128], w[:96])               # row stride 256, first 96 weight rows
+    ref = x[:, :128].cpu().double() @ w[:96].cpu().double().T
+    torch.testing.assert_close(out.cpu().double(), ref, **_tol(torch.bfloat16))
+    assert ops.linear_tcgen05(_rand((4, 20), torch.bfloat16, 7), _rand((8, 20), torch.bfloat16, 8)) is None
+
+
 def test_linear_fp32_rows_do_not_depend_on_the_batch(ops):
     """The 32-bit product gives a row the same bits alone and among others."""
     x = _rand((77, 300), torch.float32, 5)
