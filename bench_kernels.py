@@ -74,6 +74,10 @@ def main() -> int:
     ap.add_argument("--width", type=int, default=1024)
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--no-flush", action="store_true")
+    ap.add_argument("--impl", default="default", choices=["default", "tcgen05", "skinny", "library"])
+    ap.add_argument("--tile-n", type=int, default=0)
+    ap.add_argument("--split", type=int, default=0, help="keys per split of the decode attention (0: automatic)")
+    ap.add_argument("--no-tma", action="store_true", help="decode attention gathers with cp.async instead of TMA")
     ap.add_argument("--plain", action="store_true", help="the pack's plain (generic / FMA) kernel instead")
     args = ap.parse_args()
 
@@ -83,6 +87,8 @@ def main() -> int:
     ops = get_ops(dev)
     bf = torch.bfloat16
     H, KV, D, P = args.heads, args.kv_heads, args.head_dim, args.page
+    ops.attention_split = args.split
+    ops.tma_attention = not args.no_tma
     out = {"kernel": args.kernel}
 
     if args.kernel in ("attn_decode", "attn_prefill"):
@@ -119,7 +125,14 @@ def main() -> int:
     elif args.kernel == "linear":
         x = torch.randn(args.m, args.k, device=dev).to(bf)
         w = torch.randn(args.n, args.k, device=dev).to(bf)
-        fn = (lambda: ops.linear_plain(x, w)) if args.plain else (lambda: ops.linear(x, w))
+        if args.impl == "tcgen05":
+            fn = lambda: ops.linear_tcgen05(x, w, tile_n=args.tile_n)
+        elif args.impl == "skinny":
+            fn = lambda: ops.linear_skinny(x, w)
+        elif args.impl == "library":
+            fn = lambda: torch.mm(x, w.t())
+        else:
+            fn = (lambda: ops.linear_plain(x, w)) if args.plain else (lambda: ops.linear(x, w))
         us = time_kernel(fn, args.iters, not args.no_flush)
         flops = 2 * args.m * args.n * args.k
         nbytes = 2 * (args.m * args.k + args.n * args.k + args.m * args.n)

@@ -31,7 +31,9 @@
 // mma.sync.m16n8k16 is used rather than tcgen05: the M dimension of a decode
 // tile is 2..16 rows, far below the 128-row tcgen05 tile, and the kernel is
 // bound by the bandwidth of the cache reads, not by the tensor pipe.
-#include "common.cuh"
+#include <string.h>
+
+#include "ptx.cuh"
 
 namespace pih {
 
@@ -126,10 +128,25 @@ __device__ __forceinline__ void load_kv_tile(const AttnParams& p, const int* tab
   }
 }
 
-// One warp: 16 packed rows against NK keys (rows of Ks / Vs), the first of which is key j0.
-template <int D, int NK>
+// Element (row, col) of a K or V tile in shared memory, col a multiple of 8.
+//   SWZ = false: rows of D + 8 elements (what the cp.async gather writes);
+//   SWZ = true:  what TMA writes with the 128-byte swizzle: the tile is D / 64 panels of BN rows x 128
+//                bytes, and within a row the 16-byte chunk c sits at c ^ (row & 7).
+template <int D, bool SWZ>
+__device__ __forceinline__ const __nv_bfloat16* kv_at(const __nv_bfloat16* base, int row, int col) {
+  if (SWZ) {
+    const char* b = reinterpret_cast<const char*>(base) + (col >> 6) * (BN * 128) + row * 128 +
+                    ((((col & 63) >> 3) ^ (row & 7)) << 4);
+    return reinterpret_cast<const __nv_bfloat16*>(b);
+  }
+  return base + row * (D + 8) + col;
+}
+
+// One warp: 16 packed rows against the NK keys that start at row key_off of the tile Ks / Vs; j0 is
+// the position of the first of them.
+template <int D, int NK, bool SWZ>
 __device__ __forceinline__ void tile_step(const __nv_bfloat16* Qs /* this warp's 16 rows */,
-                                          const __nv_bfloat16* Ks, const __nv_bfloat16* Vs, int j0,
+                                          const __nv_bfloat16* Ks, const __nv_bfloat16* Vs, int key_off, int j0,
                                           const int (&row_pos)[2], const int (&row_first)[2], float scale_log2,
                                           float (&m)[2], float (&l)[2], float (&o)[D / 8][4]) {
   constexpr int LD = D + 8;
@@ -145,7 +162,8 @@ __device__ __forceinline__ void tile_step(const __nv_bfloat16* Qs /* this warp's
 #pragma unroll
     for (int nt = 0; nt < NK / 16; ++nt) {
       uint32_t b[4];
-      ldmatrix_x4(b, Ks + (nt * 16 + (lane & 7) + (lane >> 4) * 8) * LD + kk * 16 + ((lane >> 3) & 1) * 8);
+      ldmatrix_x4(b, kv_at<D, SWZ>(Ks, key_off + nt * 16 + (lane & 7) + (lane >> 4) * 8,
+                                   kk * 16 + ((lane >> 3) & 1) * 8));
       mma_bf16(s[2 * nt], a, b[0], b[1]);
       mma_bf16(s[2 * nt + 1], a, b[2], b[3]);
     }
@@ -205,7 +223,8 @@ __device__ __forceinline__ void tile_step(const __nv_bfloat16* Qs /* this warp's
 #pragma unroll
     for (int nt = 0; nt < D / 16; ++nt) {
       uint32_t b[4];
-      ldmatrix_x4_trans(b, Vs + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LD + nt * 16 + (lane >> 4) * 8);
+      ldmatrix_x4_trans(b, kv_at<D, SWZ>(Vs, key_off + kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8,
+                                         nt * 16 + (lane >> 4) * 8));
       mma_bf16(o[2 * nt], a, b[0], b[1]);
       mma_bf16(o[2 * nt + 1], a, b[2], b[3]);
     }
@@ -284,8 +303,8 @@ attn_tile_kernel(const AttnParams p) {
       cp_async_wait<0>();
     }
     __syncthreads();
-    tile_step<D, BN>(Qs + warp * 16 * LD, Ks0 + buf * BN * LD, Vs0 + buf * BN * LD, t * BN, row_pos, row_first,
-                     scale_log2, m, l, o);
+    tile_step<D, BN, false>(Qs + warp * 16 * LD, Ks0 + buf * BN * LD, Vs0 + buf * BN * LD, 0, t * BN, row_pos,
+                            row_first, scale_log2, m, l, o);
     __syncthreads();
   }
 #pragma unroll
@@ -312,9 +331,146 @@ attn_tile_kernel(const AttnParams p) {
   }
 }
 
-constexpr int kMaxSplitTiles = 4;      // split <= 4 * BN keys
+// The end of a split CTA: merge the four consumer warps through shared memory, write the split's
+// partial, draw a ticket, and — in the CTA that draws the last ticket of its (request, kv head) —
+// merge all splits in ascending order and write the output.  Called by every thread of the CTA
+// (threads beyond the first 128 only take part in the barriers).  `scratch` is shared memory that is
+// no longer needed, at least (4 * 16 * D + 128) and (16 * splits + 16) floats.
+template <int D>
+__device__ __forceinline__ void split_finish(const AttnParams& p, int r, int g, int sp, int s_lo, int s_hi,
+                                             int packed, int G, int row0, float (&m)[2], float (&l)[2],
+                                             float (&o)[D / 8][4], float* scratch, int* s_last) {
+  constexpr int THREADS = 128;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    l[h] += __shfl_xor_sync(0xffffffffu, l[h], 1);
+    l[h] += __shfl_xor_sync(0xffffffffu, l[h], 2);
+  }
+  // merge the four warps through shared memory (the K/V tiles are no longer needed)
+  __syncthreads();
+  float* Ow = scratch;          // [4][16][D]
+  float* Mw = Ow + 4 * 16 * D;                       // [4][16]
+  float* Lw = Mw + 4 * 16;                           // [4][16]
+#pragma unroll
+  for (int h = 0; h < 2 && warp < 4; ++h) {
+    const int row = (lane >> 2) + h * 8;
+    float* orow = Ow + (warp * 16 + row) * D;
+#pragma unroll
+    for (int n = 0; n < D / 8; ++n) {
+      const int d = n * 8 + (lane & 3) * 2;
+      *reinterpret_cast<float2*>(orow + d) = make_float2(o[n][2 * h], o[n][2 * h + 1]);
+    }
+    if ((lane & 3) == 0) {
+      Mw[warp * 16 + row] = m[h];
+      Lw[warp * 16 + row] = l[h];
+    }
+  }
+  __syncthreads();
+  const bool single = s_lo == s_hi;                    // the request fits one split: no partials, no ticket
+  for (int idx = threadIdx.x; idx < packed * D && threadIdx.x < THREADS; idx += THREADS) {
+    const int row = idx / D, d = idx % D;
+    float mm = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) mm = fmaxf(mm, Mw[w * 16 + row]);
+    float acc = 0.0f, ll = 0.0f;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      const float mw = Mw[w * 16 + row];
+      if (mw == -INFINITY) continue;
+      const float f = exp2f(mw - mm);
+      acc += Ow[(w * 16 + row) * D + d] * f;
+      ll += Lw[w * 16 + row] * f;
+    }
+    if (single) {
+      if (!(ll > 0.0f) || !isfinite(ll)) {
+        publish_error(p.error, kAttentionDenominator);
+        continue;
+      }
+      p.out[(static_cast<size_t>(row0 + row / G) * p.heads + g * G + row % G) * D + d] =
+          __float2bfloat16_rn(acc / ll);
+      continue;
+    }
+    const size_t slot =
+        ((static_cast<size_t>(r) * p.dec_tok_cap + row / G) * p.heads + g * G + row % G) * p.max_splits + sp;
+    p.part_o[slot * D + d] = acc;
+    if (d == 0) {
+      p.part_ml[slot * 2] = mm;
+      p.part_ml[slot * 2 + 1] = ll;
+    }
+  }
+  if (single) return;
+  // one ticket per CTA; the CTA that draws the last one merges the splits
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const int ticket = atomicAdd(&p.tickets[r * p.kv_heads + g], 1);
+    *s_last = ticket == (s_hi - s_lo);
+  }
+  __syncthreads();
+  if (!*s_last) return;
+  __threadfence();
+  // Final merge over the splits, ascending.  The weights exp2(m_s - M) of every (row, split) are
+  // formed first, with all loads of a pass in flight together; then every output element is a short
+  // sum whose loads are issued in batches.
+  const int nsp = s_hi - s_lo + 1;
+  float* Fw = scratch;          // [16][nsp] weights, then [16] sums
+  float* Lsum = Fw + 16 * nsp;
+  for (int idx = threadIdx.x; idx < packed * nsp && threadIdx.x < THREADS; idx += THREADS) {
+    const int row = idx / nsp, s = s_lo + idx % nsp;
+    const size_t slot =
+        ((static_cast<size_t>(r) * p.dec_tok_cap + row / G) * p.heads + g * G + row % G) * p.max_splits + s;
+    Fw[row * nsp + (s - s_lo)] = __ldcg(p.part_ml + slot * 2);
+  }
+  __syncthreads();
+  if (threadIdx.x < packed) {
+    const int row = threadIdx.x;
+    const size_t base =
+        ((static_cast<size_t>(r) * p.dec_tok_cap + row / G) * p.heads + g * G + row % G) * p.max_splits;
+    float mm = -INFINITY;
+    for (int s = 0; s < nsp; ++s) mm = fmaxf(mm, Fw[row * nsp + s]);
+    float ll = 0.0f;
+    for (int s = 0; s < nsp; ++s) {
+      const float ms = Fw[row * nsp + s];
+      const float f = ms == -INFINITY ? 0.0f : exp2f(ms - mm);
+      Fw[row * nsp + s] = f;
+      ll += f == 0.0f ? 0.0f : __ldcg(p.part_ml + (base + s_lo + s) * 2 + 1) * f;
+    }
+    Lsum[row] = ll;
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < packed * D && threadIdx.x < THREADS; idx += THREADS) {
+    const int row = idx / D, d = idx % D;
+    const size_t base =
+        ((static_cast<size_t>(r) * p.dec_tok_cap + row / G) * p.heads + g * G + row % G) * p.max_splits + s_lo;
+    const float* po = p.part_o + base * D + d;
+    const float* fw = Fw + row * nsp;
+    float acc = 0.0f;
+    int s = 0;
+    for (; s + 8 <= nsp; s += 8) {
+      float v[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) v[u] = fw[s + u] == 0.0f ? 0.0f : __ldcg(po + static_cast<size_t>(s + u) * D);
+#pragma unroll
+      for (int u = 0; u < 8; ++u) acc += v[u] * fw[s + u];
+    }
+    for (; s < nsp; ++s) acc += fw[s] == 0.0f ? 0.0f : __ldcg(po + static_cast<size_t>(s) * D) * fw[s];
+    const float ll = Lsum[row];
+    if (!(ll > 0.0f) || !isfinite(ll)) {
+      publish_error(p.error, kAttentionDenominator);
+      continue;
+    }
+    p.out[(static_cast<size_t>(row0 + row / G) * p.heads + g * G + row % G) * D + d] =
+        __float2bfloat16_rn(acc / ll);
+  }
+  if (threadIdx.x == 0) p.tickets[r * p.kv_heads + g] = 0;     // ready for the next launch
+}
+
+constexpr int kSplitStages = 3;        // ring of K/V tiles in the split kernel
 
 // Split kernel: 4 warps, at most 16 packed rows, grid (splits, kv_heads, R); decode-like requests.
+// The tiles of a split stream through a ring of kSplitStages buffers (two tiles in flight while one is
+// used), so a CTA keeps the memory system busy for the whole of its split.
 template <int D>
 __global__ void __launch_bounds__(128)
 attn_split_kernel(const AttnParams p) {
@@ -322,7 +478,7 @@ attn_split_kernel(const AttnParams p) {
   constexpr int THREADS = 128;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);
-  __nv_bfloat16* KV = Qs + 16 * LD;                  // per tile: K [BN][LD] then V [BN][LD]
+  __nv_bfloat16* KV = Qs + 16 * LD;                  // per stage: K [BN][LD] then V [BN][LD]
   __shared__ int s_last;
 
   const int r = blockIdx.z, g = blockIdx.y, sp = blockIdx.x;
@@ -350,13 +506,13 @@ attn_split_kernel(const AttnParams p) {
       src = p.q + static_cast<size_t>(row0 + row / G) * p.q_stride + static_cast<size_t>(g * G + row % G) * D + ch * 8;
     cp_async16(Qs + row * LD + ch * 8, src, valid ? 16 : 0);
   }
-  // every tile of the split is requested at once: one commit group per tile
   const int t_first = kmin / BN, t_last = kmax / BN;
-  const int ntiles = t_last - t_first + 1;           // <= split / BN <= kMaxSplitTiles
-  for (int i = 0; i < ntiles; ++i) {
-    load_kv_tile<D, THREADS>(p, table, g, (t_first + i) * BN, kmin, kmax, KV + (2 * i) * BN * LD,
-                             KV + (2 * i + 1) * BN * LD);
-    cp_async_commit();
+  const int ntiles = t_last - t_first + 1;
+  for (int i = 0; i < kSplitStages - 1; ++i) {
+    if (i < ntiles)
+      load_kv_tile<D, THREADS>(p, table, g, (t_first + i) * BN, kmin, kmax, KV + (2 * i) * BN * LD,
+                               KV + (2 * i + 1) * BN * LD);
+    cp_async_commit();                               // one group per tile slot, empty or not
   }
   int row_pos[2], row_first[2];
 #pragma unroll
@@ -377,132 +533,177 @@ attn_split_kernel(const AttnParams p) {
   const float scale_log2 = p.scale * kLog2e;
 
   for (int i = 0; i < ntiles; ++i) {
-    const int pending = ntiles - 1 - i;              // groups that may still be in flight
-    if (pending >= 3) cp_async_wait<3>();
-    else if (pending == 2) cp_async_wait<2>();
-    else if (pending == 1) cp_async_wait<1>();
-    else cp_async_wait<0>();
-    __syncthreads();
+    cp_async_wait<kSplitStages - 2>();               // tile i has landed
+    __syncthreads();                                 // ... for everyone, and tile i - 1 is no longer read
+    const int nxt = i + kSplitStages - 1;
+    if (nxt < ntiles) {
+      const int st = nxt % kSplitStages;
+      load_kv_tile<D, THREADS>(p, table, g, (t_first + nxt) * BN, kmin, kmax, KV + (2 * st) * BN * LD,
+                               KV + (2 * st + 1) * BN * LD);
+    }
+    cp_async_commit();
     // warp w takes keys 16 w .. 16 w + 15 of the tile
-    const __nv_bfloat16* Ks = KV + (2 * i) * BN * LD + warp * 16 * LD;
-    const __nv_bfloat16* Vs = KV + (2 * i + 1) * BN * LD + warp * 16 * LD;
-    tile_step<D, 16>(Qs, Ks, Vs, (t_first + i) * BN + warp * 16, row_pos, row_first, scale_log2, m, l, o);
+    const int st = i % kSplitStages;
+    tile_step<D, 16, false>(Qs, KV + (2 * st) * BN * LD, KV + (2 * st + 1) * BN * LD, warp * 16,
+                            (t_first + i) * BN + warp * 16, row_pos, row_first, scale_log2, m, l, o);
   }
-#pragma unroll
-  for (int h = 0; h < 2; ++h) {
-    l[h] += __shfl_xor_sync(0xffffffffu, l[h], 1);
-    l[h] += __shfl_xor_sync(0xffffffffu, l[h], 2);
-  }
-  // merge the four warps through shared memory (the K/V tiles are no longer needed)
-  __syncthreads();
-  float* Ow = reinterpret_cast<float*>(KV);          // [4][16][D]
-  float* Mw = Ow + 4 * 16 * D;                       // [4][16]
-  float* Lw = Mw + 4 * 16;                           // [4][16]
-#pragma unroll
-  for (int h = 0; h < 2; ++h) {
-    const int row = (lane >> 2) + h * 8;
-    float* orow = Ow + (warp * 16 + row) * D;
-#pragma unroll
-    for (int n = 0; n < D / 8; ++n) {
-      const int d = n * 8 + (lane & 3) * 2;
-      *reinterpret_cast<float2*>(orow + d) = make_float2(o[n][2 * h], o[n][2 * h + 1]);
-    }
-    if ((lane & 3) == 0) {
-      Mw[warp * 16 + row] = m[h];
-      Lw[warp * 16 + row] = l[h];
-    }
-  }
-  __syncthreads();
-  for (int idx = threadIdx.x; idx < packed * D; idx += THREADS) {
-    const int row = idx / D, d = idx % D;
-    float mm = -INFINITY;
-#pragma unroll
-    for (int w = 0; w < 4; ++w) mm = fmaxf(mm, Mw[w * 16 + row]);
-    float acc = 0.0f, ll = 0.0f;
-#pragma unroll
-    for (int w = 0; w < 4; ++w) {
-      const float mw = Mw[w * 16 + row];
-      if (mw == -INFINITY) continue;
-      const float f = exp2f(mw - mm);
-      acc += Ow[(w * 16 + row) * D + d] * f;
-      ll += Lw[w * 16 + row] * f;
-    }
-    const size_t slot =
-        ((static_cast<size_t>(r) * p.dec_tok_cap + row / G) * p.heads + g * G + row % G) * p.max_splits + sp;
-    p.part_o[slot * D + d] = acc;
-    if (d == 0) {
-      p.part_ml[slot * 2] = mm;
-      p.part_ml[slot * 2 + 1] = ll;
-    }
-  }
-  // one ticket per CTA; the CTA that draws the last one merges the splits
-  __threadfence();
-  __syncthreads();
+  cp_async_wait<0>();
+  split_finish<D>(p, r, g, sp, s_lo, s_hi, packed, G, row0, m, l, o, reinterpret_cast<float*>(KV), &s_last);
+}
+
+// Split kernel with TMA loads: the same work as attn_split_kernel, for head sizes that are multiples of 64
+// and page sizes 8, 16, 32 or 64.  A fifth warp is the producer: one thread looks up the pages of a tile
+// and issues one TMA box per (page, 64-column panel, K or V) with the 128-byte swizzle; the four consumer
+// warps never compute an address.  Pages of a tile that hold no visible key are replaced by the first
+// visible page, so that shared memory always holds finite values (they are masked by position).
+template <int D>
+__global__ void __launch_bounds__(160)
+attn_split_tma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap kv_map) {
+  constexpr int LD = D + 8;
+  constexpr int PANELS = D / 64;
+  constexpr int TILE_BYTES = BN * D * 2;               // K (or V) of one tile: PANELS panels of BN x 128 bytes
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  unsigned char* KV = base;                            // per stage: K tile then V tile
+  __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(base + kSplitStages * 2 * TILE_BYTES);
+  uint64_t* full = reinterpret_cast<uint64_t*>(Qs + 16 * LD);
+  uint64_t* empty = full + kSplitStages;
+  __shared__ int s_last;
+
+  const int r = blockIdx.z, g = blockIdx.y, sp = blockIdx.x;
+  const int G = p.heads / p.kv_heads;
+  const int row0 = p.cu_q[r];
+  const int n_tok = p.cu_q[r + 1] - row0;
+  const int packed = n_tok * G;
+  if (packed > 16) return;
+  const int start = p.q_start[r];
+  const int req_kmin = p.window > 0 ? max(0, start - p.window + 1) : 0;
+  const int req_kmax = start + n_tok - 1;
+  const int s_lo = req_kmin / p.split, s_hi = req_kmax / p.split;
+  if (sp < s_lo || sp > s_hi) return;
+  const int kmin = max(req_kmin, sp * p.split);
+  const int kmax = min(req_kmax, (sp + 1) * p.split - 1);
+  const int* table = p.block_table + static_cast<size_t>(r) * p.table_width;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t_first = kmin / BN, t_last = kmax / BN;
+  const int ntiles = t_last - t_first + 1;
+
   if (threadIdx.x == 0) {
-    const int ticket = atomicAdd(&p.tickets[r * p.kv_heads + g], 1);
-    s_last = ticket == (s_hi - s_lo);
-  }
-  __syncthreads();
-  if (!s_last) return;
-  __threadfence();
-  // Final merge over the splits, ascending.  The weights exp2(m_s - M) of every (row, split) are
-  // formed first, with all loads of a pass in flight together; then every output element is a short
-  // sum whose loads are issued in batches.
-  const int nsp = s_hi - s_lo + 1;
-  float* Fw = reinterpret_cast<float*>(KV);          // [16][nsp] weights, then [16] sums
-  float* Lsum = Fw + 16 * nsp;
-  for (int idx = threadIdx.x; idx < packed * nsp; idx += THREADS) {
-    const int row = idx / nsp, s = s_lo + idx % nsp;
-    const size_t slot =
-        ((static_cast<size_t>(r) * p.dec_tok_cap + row / G) * p.heads + g * G + row % G) * p.max_splits + s;
-    Fw[row * nsp + (s - s_lo)] = __ldcg(p.part_ml + slot * 2);
-  }
-  __syncthreads();
-  if (threadIdx.x < packed) {
-    const int row = threadIdx.x;
-    const size_t base =
-        ((static_cast<size_t>(r) * p.dec_tok_cap + row / G) * p.heads + g * G + row % G) * p.max_splits;
-    float mm = -INFINITY;
-    for (int s = 0; s < nsp; ++s) mm = fmaxf(mm, Fw[row * nsp + s]);
-    float ll = 0.0f;
-    for (int s = 0; s < nsp; ++s) {
-      const float ms = Fw[row * nsp + s];
-      const float f = ms == -INFINITY ? 0.0f : exp2f(ms - mm);
-      Fw[row * nsp + s] = f;
-      ll += f == 0.0f ? 0.0f : __ldcg(p.part_ml + (base + s_lo + s) * 2 + 1) * f;
+    for (int s = 0; s < kSplitStages; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 4);                         // one arrival per consumer warp
     }
-    Lsum[row] = ll;
+    mbar_init_fence();
   }
-  __syncthreads();
-  for (int idx = threadIdx.x; idx < packed * D; idx += THREADS) {
-    const int row = idx / D, d = idx % D;
-    const size_t base =
-        ((static_cast<size_t>(r) * p.dec_tok_cap + row / G) * p.heads + g * G + row % G) * p.max_splits + s_lo;
-    const float* po = p.part_o + base * D + d;
-    const float* fw = Fw + row * nsp;
-    float acc = 0.0f;
-    int s = 0;
-    for (; s + 8 <= nsp; s += 8) {
-      float v[8];
+  __syncthreads();                                     // barriers initialised
+
+  int row_pos[2], row_first[2];
 #pragma unroll
-      for (int u = 0; u < 8; ++u) v[u] = fw[s + u] == 0.0f ? 0.0f : __ldcg(po + static_cast<size_t>(s + u) * D);
-#pragma unroll
-      for (int u = 0; u < 8; ++u) acc += v[u] * fw[s + u];
+  for (int h = 0; h < 2; ++h) {
+    const int i = (lane >> 2) + h * 8;
+    if (i < packed) {
+      row_pos[h] = start + i / G;
+      row_first[h] = p.window > 0 ? max(0, row_pos[h] - p.window + 1) : 0;
+    } else {
+      row_pos[h] = -1;
+      row_first[h] = 0;
     }
-    for (; s < nsp; ++s) acc += fw[s] == 0.0f ? 0.0f : __ldcg(po + static_cast<size_t>(s) * D) * fw[s];
-    const float ll = Lsum[row];
-    if (!(ll > 0.0f) || !isfinite(ll)) {
-      publish_error(p.error, kAttentionDenominator);
-      continue;
-    }
-    p.out[(static_cast<size_t>(row0 + row / G) * p.heads + g * G + row % G) * D + d] =
-        __float2bfloat16_rn(acc / ll);
   }
-  if (threadIdx.x == 0) p.tickets[r * p.kv_heads + g] = 0;     // ready for the next launch
+  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.0f, 0.0f};
+  float o[D / 8][4];
+#pragma unroll
+  for (int n = 0; n < D / 8; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.0f;
+  const float scale_log2 = p.scale * kLog2e;
+
+  if (warp == 4) {
+    // producer: lane pg looks up page pg of the tile and issues its boxes; lane 0 announces the bytes
+    const int pages_per_tile = BN >> p.page_shift;
+    const int fallback = kmin >> p.page_shift;          // a page that certainly exists
+    if (lane == 0) tma_prefetch_map(&kv_map);
+    bool alive = true;
+    for (int i = 0; i < ntiles && alive; ++i) {
+      const int s = i % kSplitStages;
+      const int round = i / kSplitStages;
+      int page = 0;
+      if (lane < pages_per_tile) {                      // the look-up overlaps the wait for the buffer
+        const int j_page = (t_first + i) * BN + lane * p.page_size;
+        const bool seen = j_page <= kmax && j_page + p.page_size - 1 >= kmin;
+        page = table[seen ? (j_page >> p.page_shift) : fallback];
+        if (page < 0 || page >= p.num_pages) {
+          publish_error(p.error, kRowWithoutPage);
+          page = 0;
+        }
+      }
+      if (round > 0) alive = mbar_wait(&empty[s], (round - 1) & 1, p.error);
+      alive = __all_sync(0xffffffffu, alive);
+      if (!alive) break;
+      if (lane == 0) mbar_expect_tx(&full[s], 2 * TILE_BYTES);
+      __syncwarp();
+      if (lane < pages_per_tile) {
+        unsigned char* kdst = KV + s * 2 * TILE_BYTES + lane * p.page_size * 128;
+        unsigned char* vdst = kdst + TILE_BYTES;
+        const int zk = (page * 2) * p.kv_heads + g, zv = (page * 2 + 1) * p.kv_heads + g;
+#pragma unroll
+        for (int pn = 0; pn < PANELS; ++pn) {
+          tma_load_3d(kdst + pn * (BN * 128), &kv_map, pn * 64, 0, zk, &full[s]);
+          tma_load_3d(vdst + pn * (BN * 128), &kv_map, pn * 64, 0, zv, &full[s]);
+        }
+      }
+    }
+  } else {
+    // consumers: the query rows arrive while the first tiles are on their way
+    for (int c = threadIdx.x; c < 16 * (D / 8); c += 128) {
+      const int row = c / (D / 8), ch = c % (D / 8);
+      const bool valid = row < packed;
+      const __nv_bfloat16* src = p.q;
+      if (valid)
+        src = p.q + static_cast<size_t>(row0 + row / G) * p.q_stride + static_cast<size_t>(g * G + row % G) * D + ch * 8;
+      cp_async16(Qs + row * LD + ch * 8, src, valid ? 16 : 0);
+    }
+    cp_async_commit();
+    cp_async_wait<0>();
+    asm volatile("bar.sync 1, 128;\n" ::: "memory");   // the four consumer warps only
+    for (int i = 0; i < ntiles; ++i) {
+      const int s = i % kSplitStages;
+      mbar_wait(&full[s], (i / kSplitStages) & 1, p.error);
+      const __nv_bfloat16* Ks = reinterpret_cast<const __nv_bfloat16*>(KV + s * 2 * TILE_BYTES);
+      const __nv_bfloat16* Vs = reinterpret_cast<const __nv_bfloat16*>(KV + s * 2 * TILE_BYTES + TILE_BYTES);
+      tile_step<D, 16, true>(Qs, Ks, Vs, warp * 16, (t_first + i) * BN + warp * 16, row_pos, row_first, scale_log2,
+                             m, l, o);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&empty[s]);
+    }
+  }
+  __syncwarp();
+  split_finish<D>(p, r, g, sp, s_lo, s_hi, packed, G, row0, m, l, o, reinterpret_cast<float*>(KV), &s_last);
 }
 
 template <int D>
-static int launch_both(const AttnParams& p, int R, int tile_max_q, cudaStream_t s) {
+static int launch_split_tma(const AttnParams& p, int R, const CUtensorMap* kv_map, cudaStream_t s) {
+  if constexpr (D % 64 == 0) {
+    constexpr int LD = D + 8;
+    static int smem_set = 0;
+    int smem = 1024 + kSplitStages * 2 * BN * D * 2 + 16 * LD * 2 + 2 * kSplitStages * 8;
+    const int merge = 1024 + (4 * 16 * D + 128) * 4, final_merge = 1024 + (16 * p.max_splits + 16) * 4;
+    if (merge > smem) smem = merge;
+    if (final_merge > smem) smem = final_merge;
+    if (smem > 227 * 1024) return PIH_ERR_UNSUPPORTED;
+    if (smem_set < smem) {
+      cudaError_t e = cudaFuncSetAttribute(attn_split_tma_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+      if (e != cudaSuccess) return static_cast<int>(e);
+      smem_set = smem;
+    }
+    dim3 grid(p.max_splits, p.kv_heads, R);
+    attn_split_tma_kernel<D><<<grid, 160, smem, s>>>(p, *kv_map);
+    PIH_LAUNCH_CHECK();
+    return 0;
+  } else {
+    return PIH_ERR_UNSUPPORTED;
+  }
+}
+
+template <int D>
+static int launch_both(const AttnParams& p, int R, int tile_max_q, const CUtensorMap* kv_map, cudaStream_t s) {
   constexpr int LD = D + 8;
   const int G = p.heads / p.kv_heads;
   static int tile_smem_set = 0, split_smem_set = 0;   // per head_dim instance
@@ -517,9 +718,11 @@ static int launch_both(const AttnParams& p, int R, int tile_max_q, cudaStream_t 
     attn_tile_kernel<D><<<grid, 128, smem, s>>>(p);
     PIH_LAUNCH_CHECK();
   }
+  if (p.dec_tok_cap > 0 && kv_map != nullptr && D % 64 == 0 && p.page_shift >= 3 && p.page_size <= BN) {
+    return launch_split_tma<D>(p, R, kv_map, s);
+  }
   if (p.dec_tok_cap > 0) {
-    const int tiles = p.split / BN;
-    int smem = (16 * LD + 2 * tiles * BN * LD) * static_cast<int>(sizeof(__nv_bfloat16));
+    int smem = (16 * LD + 2 * kSplitStages * BN * LD) * static_cast<int>(sizeof(__nv_bfloat16));
     const int merge = 16 * LD * static_cast<int>(sizeof(__nv_bfloat16)) + (4 * 16 * D + 128) * static_cast<int>(sizeof(float));
     if (merge > smem) smem = merge;
     const int final_merge = 16 * LD * static_cast<int>(sizeof(__nv_bfloat16)) +
@@ -554,6 +757,31 @@ extern "C" long long pih_attention_scratch_floats(int num_requests, int dec_tok_
          static_cast<long long>(num_requests) * dec_tok_cap * heads * max_splits * (head_dim + 2);
 }
 
+// Describes one schedule entry's cache [num_pages, 2, kv_heads, page_size, head_dim] (bf16) to TMA as a
+// 3-D tensor (head_dim, page_size, num_pages * 2 * kv_heads) with boxes of 64 columns x one page and the
+// 128-byte swizzle.  `out` receives 128 bytes.  PIH_ERR_UNSUPPORTED when the shape has no such form.
+extern "C" int pih_make_kv_tensor_map(void* out, const void* cache, long long num_pages, int kv_heads,
+                                      int page_size, int head_dim) {
+  if (head_dim % 64 || page_size < 8 || page_size > 256 || (page_size & (page_size - 1)) ||
+      (reinterpret_cast<uintptr_t>(cache) & 15))
+    return PIH_ERR_UNSUPPORTED;
+  EncodeTiledFn fn = encode_tiled();
+  if (fn == nullptr) return PIH_ERR_UNSUPPORTED;
+  CUtensorMap map;
+  const cuuint64_t dims[3] = {static_cast<cuuint64_t>(head_dim), static_cast<cuuint64_t>(page_size),
+                              static_cast<cuuint64_t>(num_pages) * 2 * kv_heads};
+  const cuuint64_t strides[2] = {static_cast<cuuint64_t>(head_dim) * 2,
+                                 static_cast<cuuint64_t>(page_size) * head_dim * 2};
+  const cuuint32_t box[3] = {64, static_cast<cuuint32_t>(page_size < BN ? page_size : BN), 1};
+  const cuuint32_t elem[3] = {1, 1, 1};
+  if (fn(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(cache), dims, strides, box, elem,
+         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+    return PIH_ERR_UNSUPPORTED;
+  memcpy(out, &map, sizeof(CUtensorMap));
+  return 0;
+}
+
 // A request is "decode-like" when it brings at most 16 packed rows (rows * heads / kv_heads <= 16).
 //   tile_max_q   the most rows of a request that is NOT decode-like (0: there is none)
 //   dec_tok_cap  the most rows of a decode-like request (0: there is none)
@@ -567,10 +795,10 @@ extern "C" int pih_paged_attention_mma(const void* q, int q_stride, void* out, c
                                        const int* q_start, int rows, int num_requests, int tile_max_q,
                                        int dec_tok_cap, int dec_max_ctx, int heads, int kv_heads, int head_dim,
                                        int page_size, int num_pages, float scale, int window, int split,
-                                       float* scratch, uint32_t* error, void* stream) {
+                                       float* scratch, const void* kv_tensor_map, uint32_t* error, void* stream) {
   if (rows <= 0) return 0;
   if (heads <= 0 || kv_heads <= 0 || heads % kv_heads || page_size <= 0 || table_width <= 0 || window < 0 ||
-      split <= 0 || split % BN || split / BN > kMaxSplitTiles || num_requests <= 0 || num_requests > 65535 ||
+      split <= 0 || split % BN || num_requests <= 0 || num_requests > 65535 ||
       kv_heads > 65535 || q_stride % 8 || tile_max_q < 0 || dec_tok_cap < 0 ||
       (dec_tok_cap > 0 && (dec_max_ctx <= 0 || !scratch)))
     return PIH_ERR_BAD_ARGUMENT;
@@ -601,14 +829,20 @@ extern "C" int pih_paged_attention_mma(const void* q, int q_stride, void* out, c
   p.part_ml = p.part_o + static_cast<size_t>(num_requests) * dec_tok_cap * heads * p.max_splits * head_dim;
   p.error = error;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  CUtensorMap map_storage;
+  const CUtensorMap* kv_map = nullptr;
+  if (kv_tensor_map != nullptr) {
+    memcpy(&map_storage, kv_tensor_map, sizeof(CUtensorMap));
+    kv_map = &map_storage;
+  }
   switch (head_dim) {
-    case 16: return launch_both<16>(p, num_requests, tile_max_q, s);
-    case 32: return launch_both<32>(p, num_requests, tile_max_q, s);
-    case 64: return launch_both<64>(p, num_requests, tile_max_q, s);
-    case 80: return launch_both<80>(p, num_requests, tile_max_q, s);
-    case 96: return launch_both<96>(p, num_requests, tile_max_q, s);
-    case 128: return launch_both<128>(p, num_requests, tile_max_q, s);
-    case 256: return launch_both<256>(p, num_requests, tile_max_q, s);
+    case 16: return launch_both<16>(p, num_requests, tile_max_q, kv_map, s);
+    case 32: return launch_both<32>(p, num_requests, tile_max_q, kv_map, s);
+    case 64: return launch_both<64>(p, num_requests, tile_max_q, kv_map, s);
+    case 80: return launch_both<80>(p, num_requests, tile_max_q, kv_map, s);
+    case 96: return launch_both<96>(p, num_requests, tile_max_q, kv_map, s);
+    case 128: return launch_both<128>(p, num_requests, tile_max_q, kv_map, s);
+    case 256: return launch_both<256>(p, num_requests, tile_max_q, kv_map, s);
     default: return PIH_ERR_UNSUPPORTED;
   }
 }

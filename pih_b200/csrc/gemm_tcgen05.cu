@@ -6,7 +6,9 @@
 // The reference runs every product through cuBLASLt
 // (src/backend/cuda/gemm_plan.cpp:83-199) and has no kernel of its own.
 //
-// One CTA computes one 128 x BN tile of C (BN = 128).  Warp roles:
+// A tile of C is 128 x BN (BN = 64, 128 or 256); the kernel is persistent, one CTA per SM
+// walking over tiles, with two accumulators in tensor memory so that the epilogue of one
+// tile overlaps the products of the next.  Warp roles:
 //   warp 0      TMA producer: one thread issues the two tile loads of a k-block
 //               (A 128 x 64, W BN x 64) into a ring of STAGES buffers;
 //   warp 1      allocates tensor memory, then one thread issues the four
@@ -22,57 +24,13 @@
 // Every wait on an mbarrier is bounded; when a bound is hit the kernel records
 // kWaitTimedOut, stops waiting, still frees its tensor memory and returns.
 // No cluster launch and no multicast are used.
-#include <cuda.h>
-
-#include "common.cuh"
+#include "ptx.cuh"
 
 namespace pih {
 
 constexpr int GM = 128;          // tile rows (UMMA M)
-constexpr int GN = 128;          // tile columns (UMMA N)
 constexpr int GK = 64;           // k-block: 64 bf16 = one 128-byte swizzle row
 constexpr int UMMA_K = 16;
-constexpr int STAGES = 5;
-constexpr long long kWaitCycles = 4000000000LL;      // about two seconds of SM clock
-
-__device__ __forceinline__ uint32_t smem_u32(const void* p) {
-  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
-}
-
-__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(bytes));
-}
-// Bounded wait for the phase with the given parity; false when the bound was hit.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint32_t* error) {
-  const uint32_t addr = smem_u32(bar);
-  const long long t0 = clock64();
-  for (uint32_t spin = 0;; ++spin) {
-    if ((spin & 1023u) == 1023u && clock64() - t0 > kWaitCycles) break;
-    uint32_t done;
-    asm volatile(
-        "{\n.reg .pred p;\n"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
-        "selp.b32 %0, 1, 0, p;\n}\n"
-        : "=r"(done)
-        : "r"(addr), "r"(parity)
-        : "memory");
-    if (done) return true;
-  }
-  publish_error(error, kWaitTimedOut);
-  return false;
-}
-
-__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n" ::
-          "r"(smem_u32(smem_dst)),
-      "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(smem_u32(bar))
-      : "memory");
-}
-
 // Shared-memory matrix descriptor of a K-major operand tile stored as rows of 128 bytes with the
 // 128-byte swizzle (what TMA writes): 8-row groups are 1024 bytes apart (stride byte offset), the
 // leading byte offset is 1 (unused for swizzled K-major), version 1, layout type 2 (SWIZZLE_128B).
@@ -95,96 +53,129 @@ __host__ __device__ constexpr uint32_t umma_instr_desc(int m, int n) {
          | (static_cast<uint32_t>(m >> 4) << 24);   // m_dim
 }
 
+template <int BN, int NSTAGES>
 struct GemmSmem {
-  alignas(1024) __nv_bfloat16 a[STAGES][GM * GK];   // 16 KB per stage
-  alignas(1024) __nv_bfloat16 b[STAGES][GN * GK];   // 16 KB per stage
-  alignas(8) uint64_t full[STAGES];
-  alignas(8) uint64_t empty[STAGES];
-  alignas(8) uint64_t accum_ready;
+  alignas(1024) __nv_bfloat16 a[NSTAGES][GM * GK];   // 16 KB per stage
+  alignas(1024) __nv_bfloat16 b[NSTAGES][BN * GK];   // BN / 8 KB per stage
+  alignas(8) uint64_t full[NSTAGES];
+  alignas(8) uint64_t empty[NSTAGES];
+  alignas(8) uint64_t accum_full[2];
+  alignas(8) uint64_t accum_empty[2];
   uint32_t tmem_base;
 };
 
-template <typename TC>
+// Persistent: CTA b computes tiles b, b + gridDim.x, ... (tile t = (t % tiles_m, t / tiles_m), so that the
+// CTAs that run together share a panel of W in L2).  Two accumulators in tensor memory alternate, so the
+// epilogue of one tile overlaps the products of the next.
+template <typename TC, int BN, int NSTAGES>
 __global__ void __launch_bounds__(192)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                     TC* __restrict__ C, int M, int N, int K, long long ldc, uint32_t* error) {
+  using Smem = GemmSmem<BN, NSTAGES>;
   extern __shared__ unsigned char smem_raw[];
-  GemmSmem& sm = *reinterpret_cast<GemmSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  Smem& sm = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int m0 = blockIdx.y * GM, n0 = blockIdx.x * GN;
   const int kblocks = (K + GK - 1) / GK;
+  const int tiles_m = (M + GM - 1) / GM, tiles_n = (N + BN - 1) / BN;
+  const int tiles = tiles_m * tiles_n;
+  constexpr uint32_t TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;       // a power of two: BN is 64, 128 or 256
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < STAGES; ++s) {
+    for (int s = 0; s < NSTAGES; ++s) {
       mbar_init(&sm.full[s], 1);
       mbar_init(&sm.empty[s], 1);
     }
-    mbar_init(&sm.accum_ready, 1);
-    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&sm.accum_full[b], 1);
+      mbar_init(&sm.accum_empty[b], 4);          // one arrival per epilogue warp
+    }
+    mbar_init_fence();
   }
   if (warp == 1) {
-    // tensor memory: GN fp32 columns for the accumulator
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(&sm.tmem_base)),
-                 "r"(GN));
+                 "r"(TMEM_COLS));
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::);
   }
   asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-  const uint32_t tmem_acc = sm.tmem_base;
+  const uint32_t tmem_base = sm.tmem_base;
 
   if (warp == 0) {
     if (lane == 0) {
-      asm volatile("prefetch.tensormap [%0];\n" ::"l"(reinterpret_cast<uint64_t>(&map_a)) : "memory");
-      asm volatile("prefetch.tensormap [%0];\n" ::"l"(reinterpret_cast<uint64_t>(&map_w)) : "memory");
-      for (int kb = 0; kb < kblocks; ++kb) {
-        const int s = kb % STAGES;
-        const uint32_t round = kb / STAGES;
-        if (round > 0 && !mbar_wait(&sm.empty[s], (round - 1) & 1, error)) break;
-        mbar_expect_tx(&sm.full[s], (GM + GN) * GK * sizeof(__nv_bfloat16));
-        tma_load_2d(sm.a[s], &map_a, kb * GK, m0, &sm.full[s]);
-        tma_load_2d(sm.b[s], &map_w, kb * GK, n0, &sm.full[s]);
+      tma_prefetch_map(&map_a);
+      tma_prefetch_map(&map_w);
+      uint32_t it = 0;                           // k-blocks issued so far, over all tiles
+      bool alive = true;
+      for (int t = blockIdx.x; t < tiles && alive; t += gridDim.x) {
+        const int m0 = (t % tiles_m) * GM, n0 = (t / tiles_m) * BN;
+        for (int kb = 0; kb < kblocks; ++kb, ++it) {
+          const int s = it % NSTAGES;
+          const uint32_t round = it / NSTAGES;
+          if (round > 0 && !mbar_wait(&sm.empty[s], (round - 1) & 1, error)) {
+            alive = false;
+            break;
+          }
+          mbar_expect_tx(&sm.full[s], (GM + BN) * GK * sizeof(__nv_bfloat16));
+          tma_load_2d(sm.a[s], &map_a, kb * GK, m0, &sm.full[s]);
+          tma_load_2d(sm.b[s], &map_w, kb * GK, n0, &sm.full[s]);
+        }
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      constexpr uint32_t idesc = umma_instr_desc(GM, GN);
-      for (int kb = 0; kb < kblocks; ++kb) {
-        const int s = kb % STAGES;
-        if (!mbar_wait(&sm.full[s], (kb / STAGES) & 1, error)) break;
+      constexpr uint32_t idesc = umma_instr_desc(GM, BN);
+      uint32_t it = 0, local = 0;
+      bool alive = true;
+      for (int t = blockIdx.x; t < tiles && alive; t += gridDim.x, ++local) {
+        const uint32_t buf = local & 1, use = local >> 1;       // use-th time this accumulator is filled
+        if (use > 0 && !mbar_wait(&sm.accum_empty[buf], (use - 1) & 1, error)) break;
         asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-        const uint32_t a_addr = smem_u32(sm.a[s]), b_addr = smem_u32(sm.b[s]);
+        const uint32_t tmem_acc = tmem_base + buf * BN;
+        for (int kb = 0; kb < kblocks; ++kb, ++it) {
+          const int s = it % NSTAGES;
+          if (!mbar_wait(&sm.full[s], (it / NSTAGES) & 1, error)) {
+            alive = false;
+            break;
+          }
+          asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+          const uint32_t a_addr = smem_u32(sm.a[s]), b_addr = smem_u32(sm.b[s]);
 #pragma unroll
-        for (int k = 0; k < GK / UMMA_K; ++k) {
-          const uint64_t adesc = umma_smem_desc(a_addr + k * UMMA_K * 2);
-          const uint64_t bdesc = umma_smem_desc(b_addr + k * UMMA_K * 2);
-          const uint32_t accumulate = (kb > 0 || k > 0) ? 1u : 0u;
-          asm volatile(
-              "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
-              "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n" ::"r"(tmem_acc),
-              "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
-              : "memory");
+          for (int k = 0; k < GK / UMMA_K; ++k) {
+            const uint64_t adesc = umma_smem_desc(a_addr + k * UMMA_K * 2);
+            const uint64_t bdesc = umma_smem_desc(b_addr + k * UMMA_K * 2);
+            const uint32_t accumulate = (kb > 0 || k > 0) ? 1u : 0u;
+            asm volatile(
+                "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+                "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n" ::"r"(tmem_acc),
+                "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+                : "memory");
+          }
+          // frees the buffer when the MMAs that read it have finished
+          asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(
+                           smem_u32(&sm.empty[s]))
+                       : "memory");
         }
-        // frees the buffer when the MMAs that read it have finished
+        if (!alive) break;
         asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(
-                         smem_u32(&sm.empty[s]))
+                         smem_u32(&sm.accum_full[buf]))
                      : "memory");
       }
-      asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(
-                       smem_u32(&sm.accum_ready))
-                   : "memory");
     }
   } else {
     // epilogue: warp w may touch tensor-memory lanes 32 * (w % 4) .. + 31
     const int quarter = warp & 3;
-    const bool ok = mbar_wait(&sm.accum_ready, 0, error);
-    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-    const int row = m0 + quarter * 32 + lane;
-    if (ok) {
+    uint32_t local = 0;
+    for (int t = blockIdx.x; t < tiles; t += gridDim.x, ++local) {
+      const uint32_t buf = local & 1, use = local >> 1;
+      const int m0 = (t % tiles_m) * GM, n0 = (t / tiles_m) * BN;
+      if (!mbar_wait(&sm.accum_full[buf], use & 1, error)) break;
+      asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+      const int row = m0 + quarter * 32 + lane;
 #pragma unroll 1
-      for (int c0 = 0; c0 < GN; c0 += 32) {
+      for (int c0 = 0; c0 < BN; c0 += 32) {
         uint32_t v[32];
-        const uint32_t taddr = tmem_acc + (static_cast<uint32_t>(quarter * 32) << 16) + c0;
+        const uint32_t taddr = tmem_base + buf * BN + (static_cast<uint32_t>(quarter * 32) << 16) + c0;
         asm volatile(
             "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
             "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
@@ -196,7 +187,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
               "=r"(v[30]), "=r"(v[31])
             : "r"(taddr));
         asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
-        if (row < M) {
+        if (row < M && n0 + c0 < N) {
           TC* dst = C + static_cast<long long>(row) * ldc + n0 + c0;
           const bool full = n0 + c0 + 32 <= N && (reinterpret_cast<uintptr_t>(dst) & 15) == 0;
           if (full) {
@@ -222,29 +213,17 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
           }
         }
       }
+      // the accumulator may be overwritten once all four epilogue warps have read it
+      asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&sm.accum_empty[buf]);
     }
   }
   asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
   __syncthreads();
   if (warp == 1) {
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_acc), "r"(GN));
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(TMEM_COLS));
   }
-}
-
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn encode_tiled() {
-  static EncodeTiledFn fn = nullptr;
-  if (fn == nullptr) {
-    void* p = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
-        q == cudaDriverEntryPointSuccess)
-      fn = reinterpret_cast<EncodeTiledFn>(p);
-  }
-  return fn;
 }
 
 // 2-D bf16 tensor [rows, cols] with a row stride of ld elements; box = box_rows x 64 columns, 128-byte swizzle.
@@ -267,39 +246,68 @@ using namespace pih;
 // out_dtype: PIH_BF16 or PIH_F32.  Returns PIH_ERR_UNSUPPORTED when the operands cannot be described
 // to TMA (K or a row stride not a multiple of 8 elements, a base not 16-byte aligned): the caller then
 // uses another product.
-extern "C" int pih_gemm_tcgen05(int out_dtype, const void* A, const void* W, void* C, int M, int N, int K,
-                                long long lda, long long ldw, long long ldc, uint32_t* error, void* stream) {
-  if (M <= 0 || N <= 0) return 0;
-  if (K <= 0) return PIH_ERR_BAD_ARGUMENT;
-  if (K % 8 || lda % 8 || ldw % 8 || (reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(W) & 15))
-    return PIH_ERR_UNSUPPORTED;
-  CUtensorMap map_a, map_w;
-  if (!make_map(&map_a, A, M, K, lda, GM) || !make_map(&map_w, W, N, K, ldw, GN)) return PIH_ERR_UNSUPPORTED;
-  const int smem = static_cast<int>(sizeof(GemmSmem)) + 1024;
-  dim3 grid((N + GN - 1) / GN, (M + GM - 1) / GM);
-  if (grid.y > 65535) return PIH_ERR_UNSUPPORTED;
-  cudaStream_t s = static_cast<cudaStream_t>(stream);
-  static bool configured[2] = {false, false};
-  if (out_dtype == PIH_BF16) {
-    if (!configured[0]) {
-      cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<__nv_bfloat16>,
-                                           cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-      if (e != cudaSuccess) return static_cast<int>(e);
-      configured[0] = true;
-    }
-    gemm_tcgen05_kernel<__nv_bfloat16><<<grid, 192, smem, s>>>(map_a, map_w, static_cast<__nv_bfloat16*>(C), M, N, K,
-                                                                ldc, error);
-  } else if (out_dtype == PIH_F32) {
-    if (!configured[1]) {
-      cudaError_t e =
-          cudaFuncSetAttribute(gemm_tcgen05_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-      if (e != cudaSuccess) return static_cast<int>(e);
-      configured[1] = true;
-    }
-    gemm_tcgen05_kernel<float><<<grid, 192, smem, s>>>(map_a, map_w, static_cast<float*>(C), M, N, K, ldc, error);
-  } else {
-    return PIH_ERR_BAD_ARGUMENT;
+template <typename TC, int BN, int NSTAGES>
+static int launch_gemm(const CUtensorMap& map_a, const CUtensorMap& map_w, void* C, int M, int N, int K,
+                       long long ldc, uint32_t* error, int sms, cudaStream_t s) {
+  const int smem = static_cast<int>(sizeof(GemmSmem<BN, NSTAGES>)) + 1024;
+  static bool configured = false;                     // per instance
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<TC, BN, NSTAGES>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    configured = true;
   }
+  const long long tiles = static_cast<long long>((M + GM - 1) / GM) * ((N + BN - 1) / BN);
+  const int grid = static_cast<int>(tiles < sms ? tiles : sms);
+  gemm_tcgen05_kernel<TC, BN, NSTAGES><<<grid, 192, smem, s>>>(map_a, map_w, static_cast<TC*>(C), M, N, K, ldc, error);
   PIH_LAUNCH_CHECK();
   return 0;
+}
+
+template <typename TC>
+static int launch_gemm_bn(int bn, const CUtensorMap& map_a, const CUtensorMap& map_w, void* C, int M, int N, int K,
+                          long long ldc, uint32_t* error, int sms, cudaStream_t s) {
+  if (bn == 256) return launch_gemm<TC, 256, 4>(map_a, map_w, C, M, N, K, ldc, error, sms, s);
+  if (bn == 128) return launch_gemm<TC, 128, 6>(map_a, map_w, C, M, N, K, ldc, error, sms, s);
+  return launch_gemm<TC, 64, 8>(map_a, map_w, C, M, N, K, ldc, error, sms, s);
+}
+
+// out_dtype: PIH_BF16 or PIH_F32.  tile_n: 64, 128 or 256 columns per tile, or 0 to let the entry point
+// choose (the widest tile that still gives every SM work).  Returns PIH_ERR_UNSUPPORTED when the operands
+// cannot be described to TMA (K or a row stride not a multiple of 8 elements, a base not 16-byte aligned):
+// the caller then uses another product.
+extern "C" int pih_gemm_tcgen05(int out_dtype, const void* A, const void* W, void* C, int M, int N, int K,
+                                long long lda, long long ldw, long long ldc, int tile_n, uint32_t* error,
+                                void* stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if (K <= 0 || (tile_n != 0 && tile_n != 64 && tile_n != 128 && tile_n != 256)) return PIH_ERR_BAD_ARGUMENT;
+  if (K % 8 || lda % 8 || ldw % 8 || (reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(W) & 15))
+    return PIH_ERR_UNSUPPORTED;
+  static int sms = 0;
+  if (sms == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (sms <= 0) sms = 148;
+  }
+  int bn = tile_n;
+  if (bn == 0) {
+    // fewest "waves x (tile width + fixed cost)" wins
+    const long long tiles_m = (M + GM - 1) / GM;
+    long long best = -1;
+    for (int cand = 64; cand <= 256; cand *= 2) {
+      const long long tiles = tiles_m * ((N + cand - 1) / cand);
+      const long long cost = ((tiles + sms - 1) / sms) * (cand + 64);
+      if (best < 0 || cost <= best) {
+        best = cost;
+        bn = cand;
+      }
+    }
+  }
+  CUtensorMap map_a, map_w;
+  if (!make_map(&map_a, A, M, K, lda, GM) || !make_map(&map_w, W, N, K, ldw, bn)) return PIH_ERR_UNSUPPORTED;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (out_dtype == PIH_BF16) return launch_gemm_bn<__nv_bfloat16>(bn, map_a, map_w, C, M, N, K, ldc, error, sms, s);
+  if (out_dtype == PIH_F32) return launch_gemm_bn<float>(bn, map_a, map_w, C, M, N, K, ldc, error, sms, s);
+  return PIH_ERR_BAD_ARGUMENT;
 }

@@ -57,7 +57,9 @@ class CudaOps:
         self.launches = 0
         self._attn_scratch = None          # partials of the split-KV attention kernel, grown on demand
         self._retired_scratch = []
-        self.attention_split = 128         # keys per split of the decode attention kernel
+        self._kv_maps = {}                 # cache tensor (address, shape) -> 128-byte TMA descriptor
+        self.tma_attention = True          # False: the split kernel gathers with cp.async instead of TMA
+        self.attention_split = 0           # keys per split of the decode attention kernel; 0: chosen per call
         self.tensor_core_attention = True  # False: bf16 attention runs on the generic kernel too
         self.tcgen05_min_rows = None       # bf16 products with at least this many rows use the pack's tcgen05 kernel
         self._declare()
@@ -67,7 +69,7 @@ class CudaOps:
         lib = self.lib
         for name in ("pih_embedding", "pih_rmsnorm", "pih_qk_norm_rope_kv_write", "pih_silu_mul",
                      "pih_gather_rows", "pih_gemm_simt", "pih_paged_attention_generic", "pih_argmax",
-                     "pih_sample", "pih_paged_attention_mma", "pih_gemm_tcgen05"):
+                     "pih_sample", "pih_paged_attention_mma", "pih_gemm_tcgen05", "pih_make_kv_tensor_map"):
             getattr(lib, name).restype = c_int
         lib.pih_attention_scratch_floats.restype = c_ll
 
@@ -135,7 +137,8 @@ class CudaOps:
             return torch.mm(x, w.t(), out_dtype=torch.float32)
         return torch.mm(x, w.t())
 
-    def linear_tcgen05(self, x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None):
+    def linear_tcgen05(self, x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
+                       tile_n: int = 0):
         """The pack's tcgen05 / TMA product (bf16 in, fp32 accumulation).  Returns None when the
         operands cannot be described to TMA (K or a row stride not a multiple of 8)."""
         M, K = x.shape
@@ -143,7 +146,7 @@ class CudaOps:
         out_dtype = out_dtype or x.dtype
         out = torch.empty(M, N, dtype=out_dtype, device=x.device)
         rc = self.lib.pih_gemm_tcgen05(_DT[out_dtype], _ptr(x), _ptr(w), _ptr(out), M, N, K, c_ll(x.stride(0)),
-                                       c_ll(w.stride(0)), c_ll(N), self._err(), self._stream())
+                                       c_ll(w.stride(0)), c_ll(N), tile_n, self._err(), self._stream())
         if rc == -2:
             return None
         self._check(rc, "gemm_tcgen05")
@@ -202,17 +205,38 @@ class CudaOps:
                 tile_max_q = max(tile_max_q, n)
         return tile_max_q, dec_cap, dec_ctx
 
+    def split_for(self, num_requests: int, kv_heads: int, max_ctx: int) -> int:
+        """Keys per split: the widest of 128..4096 that still fills three quarters of the 2 x 148 CTA slots, so that
+        small batches are cut finely (enough CTAs to pull bandwidth) and large ones coarsely (less
+        merging).  A function of the step's shape only."""
+        if self.attention_split:
+            return self.attention_split
+        split = 4096
+        while split > 128 and num_requests * kv_heads * -(-max_ctx // split) < 222:
+            split //= 2
+        return split
+
     def reserve_attention_scratch(self, num_requests, dec_tok_cap, heads, kv_heads, head_dim, max_ctx) -> None:
         """Make the split kernel's scratch large enough (before a CUDA graph that uses it is
         captured: an allocation cannot happen under capture).  A buffer that is outgrown is kept
         alive, because captured graphs hold its address."""
         need = self.lib.pih_attention_scratch_floats(num_requests, dec_tok_cap, heads, kv_heads, head_dim,
-                                                     -(-max_ctx // self.attention_split))
+                                                     -(-max_ctx // 128))
         if self._attn_scratch is None or self._attn_scratch.numel() < need:
             if self._attn_scratch is not None:
                 self._retired_scratch.append(self._attn_scratch)     # captured graphs may still point at it
             # zeroed: the leading words are the kernel's tickets, which it leaves at zero
             self._attn_scratch = torch.zeros(int(need * 1.25) + 1024, dtype=torch.float32, device=self.device)
+
+    def kv_tensor_map(self, kv_cache: torch.Tensor):
+        """The TMA descriptor of one schedule entry's cache, made once; None when TMA cannot describe it."""
+        key = (kv_cache.data_ptr(), tuple(kv_cache.shape))
+        if key not in self._kv_maps:
+            buf = ctypes.create_string_buffer(128)
+            num_pages, _, kv_heads, page_size, head_dim = kv_cache.shape
+            rc = self.lib.pih_make_kv_tensor_map(buf, _ptr(kv_cache), c_ll(num_pages), kv_heads, page_size, head_dim)
+            self._kv_maps[key] = buf if rc == 0 else None
+        return self._kv_maps[key]
 
     def paged_attention_mma(self, qkv, *, heads, kv_heads, head_dim, kv_cache, block_table, step, scale,
                             window, plan=None) -> torch.Tensor:
@@ -228,7 +252,7 @@ class CudaOps:
         tile_max_q, dec_cap, dec_ctx = plan
         out = torch.empty(rows, heads * head_dim, dtype=qkv.dtype, device=qkv.device)
         num_pages, page_size = kv_cache.shape[0], kv_cache.shape[3]
-        split = self.attention_split
+        split = self.split_for(step.num_requests, kv_heads, max(dec_ctx, 1))
         scratch = None
         if dec_cap > 0:
             self.reserve_attention_scratch(step.num_requests, dec_cap, heads, kv_heads, head_dim, dec_ctx)
@@ -236,7 +260,9 @@ class CudaOps:
         rc = self.lib.pih_paged_attention_mma(
             _ptr(qkv), qkv.stride(0), _ptr(out), _ptr(kv_cache), _ptr(block_table), block_table.shape[1],
             _ptr(step.cu_q), _ptr(step.q_start), rows, step.num_requests, tile_max_q, dec_cap, dec_ctx, heads, kv_heads, head_dim, page_size, num_pages,
-            c_float(scale), int(window), split, _ptr(scratch), self._err(), self._stream())
+            c_float(scale), int(window), split, _ptr(scratch),
+            self.kv_tensor_map(kv_cache) if (self.tma_attention and dec_cap > 0) else None,
+            self._err(), self._stream())
         self._check(rc, "paged_attention_mma")
         return out
 

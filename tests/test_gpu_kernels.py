@@ -101,13 +101,15 @@ def test_linear(ops, dtype, M, N, K):
 
 
 @pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("tile_n", [0, 64, 128, 256])
 @pytest.mark.parametrize("M,N,K", [(128, 128, 64), (1, 8, 8), (37, 130, 96), (300, 257, 1032), (2048, 1024, 3072),
-                                   (129, 1000, 72), (64, 152, 1024)])
-def test_linear_tcgen05(ops, out_dtype, M, N, K):
-    """The tcgen05 / TMA product against a float64 reference: tiles that overhang M, N and K."""
+                                   (129, 1000, 72), (64, 152, 1024), (4000, 2300, 520)])
+def test_linear_tcgen05(ops, out_dtype, tile_n, M, N, K):
+    """The tcgen05 / TMA product against a float64 reference: tiles that overhang M, N and K, every tile
+    width, and enough tiles that a CTA walks over several (both accumulators, ring wrap-around)."""
     x = _rand((M, K), torch.bfloat16, 3)
     w = _rand((N, K), torch.bfloat16, 4, 0.1)
-    out = ops.linear_tcgen05(x, w, out_dtype)
+    out = ops.linear_tcgen05(x, w, out_dtype, tile_n=tile_n)
     ops.check_errors()
     assert out is not None and out.dtype == out_dtype and out.shape == (M, N)
     ref = x.cpu().double() @ w.cpu().double().T
