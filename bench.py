@@ -233,10 +233,11 @@ def e2e_run(config, model_dir_weights, batch: int, steps: int, warmup: int):
     from pih_b200.sampling import SamplingParams
 
     engine = Engine(model_dir_weights, "bfloat16", page_size=PAGE,
-                    max_cache_tokens=batch * (CONTEXT + steps + warmup + 2 * PAGE),
+                    max_cache_tokens=batch * (CONTEXT + steps + warmup + batch + 16 + 2 * PAGE),
                     maximum_batch_sequences=batch, maximum_batch_tokens=4096)
     g = torch.Generator().manual_seed(7)
-    params = SamplingParams(max_tokens=steps + warmup + 1, ignore_eos=True)
+    # long enough that no request finishes inside the timed region (prompts finish prefill on different steps)
+    params = SamplingParams(max_tokens=steps + warmup + batch + 16, ignore_eos=True)
     reqs = []
     for _ in range(batch):
         rid = engine.submit(torch.randint(0, config.vocab_size, (CONTEXT,), generator=g).tolist(), params)
@@ -246,13 +247,16 @@ def e2e_run(config, model_dir_weights, batch: int, steps: int, warmup: int):
     for _ in range(warmup - 1):
         engine.step()
     torch.cuda.synchronize()
+    before = sum(len(r.outputs) for r in reqs)
     t0 = time.perf_counter()
     for _ in range(steps):
         engine.step()
     torch.cuda.synchronize()
     dt = time.perf_counter() - t0
+    produced = sum(len(r.outputs) for r in reqs) - before
+    assert produced == batch * steps, (produced, batch, steps)
     h2d = engine.runner.builder.last_bytes
-    return {"value": batch * steps / dt, "unit": "tok/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4 * batch,
+    return {"value": produced / dt, "unit": "tok/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4 * batch,
             "ms_per_step": dt / steps * 1e3}
 
 

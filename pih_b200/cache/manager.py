@@ -33,6 +33,7 @@ from __future__ import annotations
 from dataclasses import dataclass, field
 from typing import Dict, Hashable, List, Optional, Sequence, Tuple
 
+import numpy as np
 import torch
 
 from ..parts.registry import PagedKVNeed, StateNeed
@@ -47,13 +48,69 @@ class CacheGroup:
     kv: Optional[torch.Tensor] = None  # [entries, pages, 2, kv_heads, page_size, head_dim]
 
 
+class PageList:
+    """A request's page ids of one group, by page index, in an int32 array that grows by doubling
+    (the batch builder copies slices of it straight into the step's block table).  -1 marks a page
+    that was given back."""
+
+    __slots__ = ("arr", "n")
+
+    def __init__(self):
+        self.arr = np.empty(16, dtype=np.int32)
+        self.n = 0
+
+    def __len__(self) -> int:
+        return self.n
+
+    def __getitem__(self, i):
+        if isinstance(i, slice):
+            return self.arr[:self.n][i].tolist()
+        if not -self.n <= i < self.n:
+            raise IndexError(i)
+        return int(self.arr[i if i >= 0 else self.n + i])
+
+    def __iter__(self):
+        return iter(self.arr[:self.n].tolist())
+
+    def __eq__(self, other):
+        return list(self) == list(other)
+
+    def extend(self, pages) -> None:
+        k = len(pages)
+        if self.n + k > self.arr.shape[0]:
+            grown = np.empty(max(2 * self.arr.shape[0], self.n + k), dtype=np.int32)
+            grown[:self.n] = self.arr[:self.n]
+            self.arr = grown
+        self.arr[self.n:self.n + k] = pages
+        self.n += k
+
+    def truncate(self, keep: int):
+        """Drop the entries from index ``keep`` on and return them."""
+        gone = self.arr[keep:self.n].tolist()
+        self.n = min(self.n, keep)
+        return gone
+
+    def give_back(self, lo: int, hi: int):
+        """Mark entries lo..hi-1 as given back and return the page ids they held."""
+        gone = [p for p in self.arr[lo:hi].tolist() if p >= 0]
+        self.arr[lo:hi] = -1
+        return gone
+
+    def held(self):
+        a = self.arr[:self.n]
+        return a[a >= 0].tolist()
+
+    def view(self) -> np.ndarray:
+        return self.arr[:self.n]
+
+
 @dataclass
 class RequestCache:
     rid: Hashable
     slot: int
     num_tokens: int = 0                               # committed length
     pending: int = 0                                  # tokens appended, not yet committed
-    pages: List[List[int]] = field(default_factory=list)   # per group: page id per page index, -1 = given back
+    pages: List[PageList] = field(default_factory=list)    # per group: page id per page index, -1 = given back
     first_live: List[int] = field(default_factory=list)    # per group: first page index still held
 
 
@@ -128,7 +185,7 @@ class CacheManager:
         if rid in self.requests:
             raise ValueError(f"request {rid!r} is already live")
         slot = self.slots.acquire(rid)
-        rc = RequestCache(rid, slot, pages=[[] for _ in self.groups], first_live=[0 for _ in self.groups])
+        rc = RequestCache(rid, slot, pages=[PageList() for _ in self.groups], first_live=[0 for _ in self.groups])
         self.requests[rid] = rc
         for t in self.state_tensors.values():
             t[slot].zero_()
@@ -176,9 +233,7 @@ class CacheManager:
         rc = self.requests[rid]
         keep = -(-rc.num_tokens // self.page_size)
         for g, grp in enumerate(self.groups):
-            extra = rc.pages[g][keep:]
-            del rc.pages[g][keep:]
-            grp.pool.free([p for p in extra if p >= 0], rid)
+            grp.pool.free([p for p in rc.pages[g].truncate(keep) if p >= 0], rid)
         rc.pending = 0
 
     def commit(self, rid: Hashable) -> None:
@@ -190,16 +245,13 @@ class CacheManager:
         for g, grp in enumerate(self.groups):
             first = self._first_needed_page(grp, rc.num_tokens)
             if first > rc.first_live[g]:
-                gone = rc.pages[g][rc.first_live[g]:first]
-                grp.pool.free([p for p in gone if p >= 0], rid)
-                for i in range(rc.first_live[g], first):
-                    rc.pages[g][i] = -1
+                grp.pool.free(rc.pages[g].give_back(rc.first_live[g], first), rid)
                 rc.first_live[g] = first
 
     def release(self, rid: Hashable) -> None:
         rc = self.requests.pop(rid)
         for g, grp in enumerate(self.groups):
-            grp.pool.free([p for p in rc.pages[g] if p >= 0], rid)
+            grp.pool.free(rc.pages[g].held(), rid)
         self.slots.release(rc.slot, rid)
 
     def reset(self, rid: Hashable) -> None:
@@ -207,8 +259,8 @@ class CacheManager:
         (preemption: its tokens will be computed again)."""
         rc = self.requests[rid]
         for g, grp in enumerate(self.groups):
-            grp.pool.free([p for p in rc.pages[g] if p >= 0], rid)
-            rc.pages[g] = []
+            grp.pool.free(rc.pages[g].held(), rid)
+            rc.pages[g] = PageList()
             rc.first_live[g] = 0
         rc.num_tokens = 0
         rc.pending = 0
@@ -245,9 +297,17 @@ class CacheManager:
     def block_table_rows(self, g: int, rids: Sequence[Hashable], width: int) -> List[List[int]]:
         rows = []
         for r in rids:
-            pages = self.requests[r].pages[g]
+            pages = list(self.requests[r].pages[g])
             rows.append(pages + [-1] * (width - len(pages)))
         return rows
+
+    def fill_block_table(self, g: int, rids: Sequence[Hashable], out: np.ndarray) -> None:
+        """Write the block-table rows of ``rids`` (group g) into ``out`` [len(rids), width]."""
+        for i, r in enumerate(rids):
+            pages = self.requests[r].pages[g]
+            n = pages.n
+            out[i, :n] = pages.arr[:n]
+            out[i, n:] = -1
 
     def slot_mapping(self, g: int, rid: Hashable, start: int, n: int) -> List[int]:
         pages = self.requests[rid].pages[g]

@@ -22,6 +22,7 @@ from __future__ import annotations
 from dataclasses import dataclass, field
 from typing import Hashable, List, Optional, Sequence
 
+import numpy as np
 import torch
 
 
@@ -67,6 +68,8 @@ class BatchBuilder:
         self._pinned = None
         self._capacity = 0
         self.last_bytes = 0
+        self._copy_done = None
+        self._copy_pending = False
 
     def _host(self, n: int) -> torch.Tensor:
         if n > self._capacity:
@@ -87,42 +90,65 @@ class BatchBuilder:
         """
         R = len(entries)
         rids = [e.rid for e in entries]
+        reqs = [cache.requests[r] for r in rids]
         counts = [len(e.tokens) for e in entries]
         T = sum(counts)
-        starts = [cache.requests[r].num_tokens for r in rids]
+        starts = [rc.num_tokens for rc in reqs]
         G = len(cache.groups)
+        ps = cache.page_size
         if width is None:
             width = cache.table_width(rids)
-        token_ids, positions, req_of_row, logit_rows, cu_q = [], [], [], [], [0]
+        cu_q = [0]
+        for n in counts:
+            cu_q.append(cu_q[-1] + n)
+        logit_rows = []
         for r, e in enumerate(entries):
-            token_ids.extend(e.tokens)
-            positions.extend(range(starts[r], starts[r] + counts[r]))
-            req_of_row.extend([r] * counts[r])
             for w in e.want:
                 if not 0 <= w < counts[r]:
                     raise ValueError(f"request {e.rid!r}: wanted place {w} is outside its {counts[r]} tokens")
-                logit_rows.append(cu_q[-1] + int(w))
-            cu_q.append(cu_q[-1] + counts[r])
+                logit_rows.append(cu_q[r] + int(w))
         S = len(logit_rows)
-        fields = [token_ids, positions, req_of_row, logit_rows, cu_q, starts,
-                  [starts[r] + counts[r] for r in range(R)],
-                  [cache.requests[r].slot for r in rids]]
-        for g in range(G):
-            fields.append([p for row in cache.block_table_rows(g, rids, width) for p in row])
-            sm = []
-            for r, rid in enumerate(rids):
-                sm.extend(cache.slot_mapping(g, rid, starts[r], counts[r]))
-            fields.append(sm)
+        sizes = self._sizes(T, R, S, G, width)
         offsets, total = [], 0
-        for f in fields:
+        for n in sizes:
             offsets.append(total)
-            total += _align(max(len(f), 1))
+            total += _align(max(n, 1))
         self.wait_copy()
         host = self._host(total)
-        view = host.numpy()
-        for off, f in zip(offsets, fields):
-            if f:
-                view[off:off + len(f)] = f
+        v = host.numpy()
+        o = offsets
+        if T == R:                                   # one token each: no per-request loops over rows
+            v[o[0]:o[0] + T] = [e.tokens[0] for e in entries]
+            v[o[1]:o[1] + T] = starts
+            v[o[2]:o[2] + T] = np.arange(R, dtype=np.int32)
+        else:
+            for r, e in enumerate(entries):
+                lo, hi = cu_q[r], cu_q[r + 1]
+                v[o[0] + lo:o[0] + hi] = e.tokens
+                v[o[1] + lo:o[1] + hi] = np.arange(starts[r], starts[r] + counts[r], dtype=np.int32)
+                v[o[2] + lo:o[2] + hi] = r
+        if S:
+            v[o[3]:o[3] + S] = logit_rows
+        v[o[4]:o[4] + R + 1] = cu_q
+        v[o[5]:o[5] + R] = starts
+        v[o[6]:o[6] + R] = [starts[r] + counts[r] for r in range(R)]
+        v[o[7]:o[7] + R] = [rc.slot for rc in reqs]
+        for g in range(G):
+            table = v[o[8 + 2 * g]:o[8 + 2 * g] + R * width].reshape(R, width)
+            cache.fill_block_table(g, rids, table)
+            sm = v[o[9 + 2 * g]:o[9 + 2 * g] + T]
+            for r, rc in enumerate(reqs):
+                pages = rc.pages[g].arr
+                lo, n, st = cu_q[r], counts[r], starts[r]
+                if n == 1:
+                    page = pages[st // ps]
+                    sm[lo] = page * ps + st % ps if page >= 0 else -1
+                else:
+                    pos = np.arange(st, st + n, dtype=np.int64)
+                    page = pages[pos // ps].astype(np.int64)
+                    sm[lo:lo + n] = np.where(page >= 0, page * ps + pos % ps, -1)
+            if (sm < 0).any():
+                raise AssertionError("a row of this step lies in a page that was given back")
         self.last_bytes = total * 4
         if device_buffer is None:
             dev = torch.empty(total, dtype=torch.int32, device=self.device)
@@ -133,8 +159,10 @@ class BatchBuilder:
         dev.copy_(host, non_blocking=True)
         # the pinned buffer is reused by the next build: the copy must have left it
         if self.device.type == "cuda":
-            self._copy_done = torch.cuda.Event()
+            if self._copy_done is None:
+                self._copy_done = torch.cuda.Event()
             self._copy_done.record()
+            self._copy_pending = True
 
         def part(i, n):
             return dev[offsets[i]:offsets[i] + n]
@@ -151,15 +179,18 @@ class BatchBuilder:
         return batch
 
     @staticmethod
-    def buffer_size(rows: int, requests: int, wanted: int, groups: int, width: int) -> int:
-        """int32 elements that ``build`` needs for a step of this shape."""
+    def _sizes(rows: int, requests: int, wanted: int, groups: int, width: int):
         sizes = [rows, rows, rows, wanted, requests + 1, requests, requests, requests]
         for _ in range(groups):
             sizes += [requests * width, rows]
-        return sum(_align(max(n, 1)) for n in sizes)
+        return sizes
+
+    @staticmethod
+    def buffer_size(rows: int, requests: int, wanted: int, groups: int, width: int) -> int:
+        """int32 elements that ``build`` needs for a step of this shape."""
+        return sum(_align(max(n, 1)) for n in BatchBuilder._sizes(rows, requests, wanted, groups, width))
 
     def wait_copy(self) -> None:
-        ev = getattr(self, "_copy_done", None)
-        if ev is not None:
-            ev.synchronize()
-            self._copy_done = None
+        if self._copy_pending:
+            self._copy_done.synchronize()
+            self._copy_pending = False

@@ -88,6 +88,23 @@ class SchedulerOutput:
         return sum(len(s.tokens) for s in self.scheduled)
 
 
+class _Granted:
+    """Pages granted so far in one scheduling decision, per cache group."""
+
+    def __init__(self, cache):
+        self.cache = cache
+        self.taken = [0] * len(cache.groups)
+
+    def fits(self, rid, n: int) -> bool:
+        need = self.cache.pages_needed(rid, n)
+        free = self.cache.num_free_pages()
+        return all(self.taken[g] + need[g] <= free[g] for g in range(len(need)))
+
+    def grant(self, rid, n: int) -> None:
+        for g, c in enumerate(self.cache.pages_needed(rid, n)):
+            self.taken[g] += c
+
+
 class Scheduler:
     def __init__(self, cache, max_batch_sequences: int = 32, max_batch_tokens: int = 4096,
                  max_context: Optional[int] = None):
@@ -129,19 +146,19 @@ class Scheduler:
     def schedule(self) -> SchedulerOutput:
         out = SchedulerOutput([], [], [])
         budget = self.max_batch_tokens
-        asks = []                                           # (rid, n) already granted this step
+        asks = _Granted(self.cache)                         # pages already granted this step, per group
         # running requests, oldest first
         for req in sorted(self.running, key=lambda r: r.arrival):
             if req.status != "running" or budget == 0:
                 continue
             n = min(req.num_tokens - req.num_computed, budget)
-            while not self.cache.can_append(asks + [(req.rid, n)]):
+            while not asks.fits(req.rid, n):
                 victims = [r for r in self.running if r.status == "running" and r is not req
                            and all(s.request is not r for s in out.scheduled)]
                 if not victims:
                     break
                 self._preempt(max(victims, key=lambda r: r.arrival), out)
-            if not self.cache.can_append(asks + [(req.rid, n)]):
+            if not asks.fits(req.rid, n):
                 others = [s for s in out.scheduled]
                 if others:
                     continue                                  # wait for a later step: others will finish
@@ -151,9 +168,9 @@ class Scheduler:
                 req.status, req.finish_reason = "finished", "capacity"
                 out.failed.append(req)
                 continue
-            asks.append((req.rid, n))
+            asks.grant(req.rid, n)
             start = req.num_computed
-            out.scheduled.append(Scheduled(req, req.tokens[start:start + n], start + n == req.num_tokens))
+            out.scheduled.append(Scheduled(req, self._next_tokens(req, start, n), start + n == req.num_tokens))
             budget -= n
         # admit waiting requests in order, no overtaking; not in a step that preempted
         while self.waiting and budget > 0 and len(self.running) < self.max_batch_sequences \
@@ -161,7 +178,7 @@ class Scheduler:
             req = self.waiting[0]
             n = min(req.num_tokens - req.num_computed, budget)
             self.cache.add_request(req.rid)
-            if not self.cache.can_append(asks + [(req.rid, n)]):
+            if not asks.fits(req.rid, n):
                 self.cache.release(req.rid)
                 if not self.running and not out.scheduled:
                     # nothing else holds pages: even an empty pool is too small for this portion;
@@ -178,16 +195,26 @@ class Scheduler:
             self.waiting.popleft()
             req.status = "running"
             self.running.append(req)
-            asks.append((req.rid, n))
+            asks.grant(req.rid, n)
             start = req.num_computed
-            out.scheduled.append(Scheduled(req, req.tokens[start:start + n], start + n == req.num_tokens))
+            out.scheduled.append(Scheduled(req, self._next_tokens(req, start, n), start + n == req.num_tokens))
             budget -= n
         return out
+
+    @staticmethod
+    def _next_tokens(req: Request, start: int, n: int) -> List[int]:
+        """Tokens start..start+n-1 of prompt + outputs, without building the whole list."""
+        p = len(req.prompt)
+        if start >= p:
+            return req.outputs[start - p:start - p + n]
+        if start + n <= p:
+            return req.prompt[start:start + n]
+        return req.prompt[start:] + req.outputs[:start + n - p]
 
     def _largest_fit(self, req: Request, n: int, asks) -> int:
         self.cache.add_request(req.rid)
         try:
-            while n > 0 and not self.cache.can_append(asks + [(req.rid, n)]):
+            while n > 0 and not asks.fits(req.rid, n):
                 n -= 1
             return n
         finally:
