@@ -1,0 +1,467 @@
+// Causal grouped-query attention of prompt portions on the 5th-generation tensor cores: S = Q K^T and
+// O += P V are tcgen05.mma with S and O in tensor memory; K and V pages come by TMA.
+//
+// Formula as the reference's kernel (kernels/cuda/qwen_bf16_primitives.cu:660-733): score = (q . k) * scale,
+// causal mask by position, online softmax in 32-bit, one rounding of acc / sum.  Execution:
+//
+//   tile       128 packed rows (token i / G, head g G + i % G) of one (request, kv head) x 128 keys
+//   warps 0-3  softmax: thread t owns row t = tensor-memory lane t: reads its 128 scores (tcgen05.ld), masks,
+//              exponentiates, writes P (bf16) into shared memory in the 128-byte-swizzled K-major layout, keeps the
+//              row sum; rescales O in tensor memory only when the running maximum grew by more than 2^8
+//              (otherwise the old reference maximum stays, which is exact because the final division uses the
+//              sum formed with the same reference);
+//   warp 4     producer: lane p looks up page p of the key tile and issues its TMA boxes (K ring and V ring of
+//              two stages each);
+//   warp 5     one thread issues the MMAs: S_j = Q K_j^T (8 x K=16) into one of two S buffers, then
+//              O += P_{j-1} V_{j-1}; S_j therefore overlaps the softmax of tile j-1.
+//
+// Tensor memory: S0 [0,128) S1 [128,256) O [256, 256 + D).  Every mbarrier wait is bounded.
+// No cluster, no multicast.
+#include <string.h>
+
+#include "ptx.cuh"
+
+namespace pih {
+
+constexpr int TQ = 128;                 // packed rows per tile
+constexpr int TK = 128;                 // keys per tile
+constexpr int KV_STAGES = 2;
+constexpr float kLog2e5 = 1.4426950408889634f;
+constexpr float kRescaleThreshold = 8.0f;   // log2 units
+
+struct PrefillParams {
+  const __nv_bfloat16* q;
+  int q_stride;
+  __nv_bfloat16* out;
+  const int* block_table;
+  int table_width;
+  const int* cu_q;
+  const int* q_start;
+  int heads, kv_heads, page_size, page_shift, num_pages;
+  float scale;
+  int window;
+  uint32_t* error;
+};
+
+// K-major operand tile [rows x 64 bf16] with the 128-byte swizzle: see gemm_tcgen05.cu
+__device__ __forceinline__ uint64_t desc_kmajor(uint32_t smem_addr) {
+  uint64_t desc = 0;
+  desc |= static_cast<uint64_t>((smem_addr & 0x3FFFF) >> 4);
+  desc |= static_cast<uint64_t>(1) << 16;
+  desc |= static_cast<uint64_t>(1024 >> 4) << 32;
+  desc |= static_cast<uint64_t>(1) << 46;
+  desc |= static_cast<uint64_t>(2) << 61;
+  return desc;
+}
+// MN-major operand (V as B of P V: N = head dim contiguous, K = keys along rows of 128 bytes): panels of 64
+// columns are `panel_bytes` apart (leading byte offset), groups of 8 keys 1024 bytes apart (stride byte offset).
+__device__ __forceinline__ uint64_t desc_mnmajor(uint32_t smem_addr, uint32_t panel_bytes) {
+  uint64_t desc = 0;
+  desc |= static_cast<uint64_t>((smem_addr & 0x3FFFF) >> 4);
+  desc |= static_cast<uint64_t>((panel_bytes >> 4) & 0x3FFF) << 16;
+  desc |= static_cast<uint64_t>(1024 >> 4) << 32;
+  desc |= static_cast<uint64_t>(1) << 46;
+  desc |= static_cast<uint64_t>(2) << 61;
+  return desc;
+}
+__host__ __device__ constexpr uint32_t idesc_bf16(int m, int n, bool b_mn_major) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | (b_mn_major ? (1u << 16) : 0u) |
+         (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(m >> 4) << 24);
+}
+__device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t acc) {
+  asm volatile(
+      "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n" ::"r"(tmem_d),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(acc)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void proxy_fence() { asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory"); }
+
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+        "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
+        "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
+        "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+      : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&v)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};\n" ::"r"(taddr),
+      "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]), "r"(v[9]),
+      "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]), "r"(v[16]), "r"(v[17]), "r"(v[18]),
+      "r"(v[19]), "r"(v[20]), "r"(v[21]), "r"(v[22]), "r"(v[23]), "r"(v[24]), "r"(v[25]), "r"(v[26]), "r"(v[27]),
+      "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory"); }
+__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory"); }
+
+__device__ __forceinline__ void cp16(void* smem, const void* gmem, int bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(smem_u32(smem)), "l"(gmem), "r"(bytes));
+}
+
+template <int D>
+struct PrefillSmem {
+  static constexpr int PANELS = D / 64;
+  static constexpr int PANEL_BYTES = 128 * 128;                 // 128 rows x 128 bytes
+  alignas(1024) unsigned char q[PANELS * PANEL_BYTES];
+  alignas(1024) unsigned char k[KV_STAGES][PANELS * PANEL_BYTES];
+  alignas(1024) unsigned char v[KV_STAGES][PANELS * PANEL_BYTES];
+  alignas(1024) unsigned char p[2 * PANEL_BYTES];               // two panels of 64 keys
+  alignas(8) uint64_t q_full, o_ready, p_full, p_empty;
+  alignas(8) uint64_t k_full[KV_STAGES], k_empty[KV_STAGES], v_full[KV_STAGES], v_empty[KV_STAGES];
+  alignas(8) uint64_t s_full[2], s_empty[2];
+  uint32_t tmem_base;
+};
+
+template <int D>
+__global__ void __launch_bounds__(192)
+attn_prefill_tcgen05_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap kv_map) {
+  using Smem = PrefillSmem<D>;
+  constexpr int PANELS = Smem::PANELS;
+  constexpr int PANEL_BYTES = Smem::PANEL_BYTES;
+  extern __shared__ unsigned char smem_raw[];
+  Smem& sm = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+
+  const int r = blockIdx.z, g = blockIdx.y;
+  const int G = p.heads / p.kv_heads;
+  const int row0 = p.cu_q[r];
+  const int n_tok = p.cu_q[r + 1] - row0;
+  const int packed = n_tok * G;
+  if (packed <= 16) return;                                     // decode-like: the split kernel's
+  // long tiles first: the last rows of a prompt see the most keys
+  const int tiles_q = (packed + TQ - 1) / TQ;
+  const int qt = tiles_q - 1 - static_cast<int>(blockIdx.x);
+  if (qt < 0) return;
+  const int tile_row0 = qt * TQ;
+  const int start = p.q_start[r];
+  const int tok_lo = tile_row0 / G;
+  const int tok_hi = min(packed - 1, tile_row0 + TQ - 1) / G;
+  const int kmin = p.window > 0 ? max(0, start + tok_lo - p.window + 1) : 0;
+  const int kmax = start + tok_hi;
+  const int t_first = kmin / TK, t_last = kmax / TK;
+  const int ntiles = t_last - t_first + 1;
+  const int* table = p.block_table + static_cast<size_t>(r) * p.table_width;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    mbar_init(&sm.q_full, 128);
+    mbar_init(&sm.o_ready, 1);
+    mbar_init(&sm.p_full, 128);
+    mbar_init(&sm.p_empty, 1);
+    for (int s = 0; s < KV_STAGES; ++s) {
+      mbar_init(&sm.k_full[s], 1);
+      mbar_init(&sm.k_empty[s], 1);
+      mbar_init(&sm.v_full[s], 1);
+      mbar_init(&sm.v_empty[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&sm.s_full[b], 1);
+      mbar_init(&sm.s_empty[b], 128);
+    }
+    mbar_init_fence();
+  }
+  if (warp == 5) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(&sm.tmem_base)),
+                 "r"(512));
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::);
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = sm.tmem_base;
+  const uint32_t tmem_o = tmem + 256;
+
+  if (warp == 4) {
+    // ---------------- producer ----------------
+    const int pages_per_tile = TK >> p.page_shift;
+    const int fallback = kmin >> p.page_shift;
+    if (lane == 0) tma_prefetch_map(&kv_map);
+    bool alive = true;
+    for (int j = 0; j < ntiles && alive; ++j) {
+      const int s = j % KV_STAGES;
+      const int use = j / KV_STAGES;
+      int page = 0;
+      if (lane < pages_per_tile) {
+        const int j_page = (t_first + j) * TK + lane * p.page_size;
+        const bool seen = j_page <= kmax && j_page + p.page_size - 1 >= kmin;
+        page = table[seen ? (j_page >> p.page_shift) : fallback];
+        if (page < 0 || page >= p.num_pages) {
+          publish_error(p.error, kRowWithoutPage);
+          page = 0;
+        }
+      }
+      const int off = lane * p.page_size * 128;
+      // K tile
+      if (use > 0) alive = mbar_wait(&sm.k_empty[s], (use - 1) & 1, p.error);
+      alive = __all_sync(0xffffffffu, alive);
+      if (!alive) break;
+      if (lane == 0) mbar_expect_tx(&sm.k_full[s], PANELS * PANEL_BYTES);
+      __syncwarp();
+      if (lane < pages_per_tile) {
+        const int zk = (page * 2) * p.kv_heads + g;
+#pragma unroll
+        for (int pn = 0; pn < PANELS; ++pn) tma_load_3d(sm.k[s] + pn * PANEL_BYTES + off, &kv_map, pn * 64, 0, zk, &sm.k_full[s]);
+      }
+      // V tile
+      if (use > 0) alive = mbar_wait(&sm.v_empty[s], (use - 1) & 1, p.error);
+      alive = __all_sync(0xffffffffu, alive);
+      if (!alive) break;
+      if (lane == 0) mbar_expect_tx(&sm.v_full[s], PANELS * PANEL_BYTES);
+      __syncwarp();
+      if (lane < pages_per_tile) {
+        const int zv = (page * 2 + 1) * p.kv_heads + g;
+#pragma unroll
+        for (int pn = 0; pn < PANELS; ++pn) tma_load_3d(sm.v[s] + pn * PANEL_BYTES + off, &kv_map, pn * 64, 0, zv, &sm.v_full[s]);
+      }
+    }
+  } else if (warp == 5) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      constexpr uint32_t idesc_s = idesc_bf16(TQ, TK, false);
+      constexpr uint32_t idesc_o = idesc_bf16(TQ, D, true);
+      const uint32_t q_addr = smem_u32(sm.q), p_addr = smem_u32(sm.p);
+      bool alive = mbar_wait(&sm.q_full, 0, p.error);
+      tc_fence_after();
+      for (int j = 0; j <= ntiles && alive; ++j) {
+        if (j < ntiles) {
+          // S_b = Q K_j^T
+          const int b = j & 1, use = j >> 1, s = j % KV_STAGES;
+          if (use > 0 && !mbar_wait(&sm.s_empty[b], (use - 1) & 1, p.error)) break;
+          if (!mbar_wait(&sm.k_full[s], (j / KV_STAGES) & 1, p.error)) break;
+          tc_fence_after();
+          const uint32_t k_addr = smem_u32(sm.k[s]);
+#pragma unroll
+          for (int kk = 0; kk < D / 16; ++kk) {
+            const uint32_t offs = (kk / 4) * PANEL_BYTES + (kk % 4) * 32;
+            umma(tmem + b * TK, desc_kmajor(q_addr + offs), desc_kmajor(k_addr + offs), idesc_s, kk > 0 ? 1u : 0u);
+          }
+          umma_commit(&sm.k_empty[s]);
+          umma_commit(&sm.s_full[b]);
+        }
+        if (j >= 1) {
+          // O += P_{j-1} V_{j-1}
+          const int i = j - 1, s = i % KV_STAGES;
+          if (!mbar_wait(&sm.p_full, i & 1, p.error)) break;
+          if (!mbar_wait(&sm.v_full[s], (i / KV_STAGES) & 1, p.error)) break;
+          tc_fence_after();
+          const uint32_t v_addr = smem_u32(sm.v[s]);
+#pragma unroll
+          for (int kk = 0; kk < TK / 16; ++kk) {
+            const uint64_t adesc = desc_kmajor(p_addr + (kk / 4) * PANEL_BYTES + (kk % 4) * 32);
+            const uint64_t bdesc = desc_mnmajor(v_addr + kk * 16 * 128, PANEL_BYTES);
+            umma(tmem_o, adesc, bdesc, idesc_o, (i > 0 || kk > 0) ? 1u : 0u);
+          }
+          umma_commit(&sm.v_empty[s]);
+          umma_commit(&sm.p_empty);
+          if (i == ntiles - 1) umma_commit(&sm.o_ready);
+        }
+      }
+    }
+  } else {
+    // ---------------- softmax / epilogue: thread = row ----------------
+    const int t = threadIdx.x;                           // 0..127 = tensor-memory lane
+    const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
+    // Q rows into the swizzled K-major layout
+    for (int c = t; c < TQ * (D / 8); c += 128) {
+      const int row = c / (D / 8), ch = c % (D / 8);
+      const int i = tile_row0 + row;
+      const bool valid = i < packed;
+      const __nv_bfloat16* src = p.q;
+      if (valid)
+        src = p.q + static_cast<size_t>(row0 + i / G) * p.q_stride + static_cast<size_t>(g * G + i % G) * D + ch * 8;
+      unsigned char* dst = sm.q + (ch >> 3) * PANEL_BYTES + row * 128 + (((ch & 7) ^ (row & 7)) << 4);
+      cp16(dst, src, valid ? 16 : 0);
+    }
+    asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;\n" ::: "memory");
+    proxy_fence();
+    mbar_arrive(&sm.q_full);
+
+    const int i_row = tile_row0 + t;
+    const bool row_valid = i_row < packed;
+    const int pos = row_valid ? start + i_row / G : -1;
+    const int first = (row_valid && p.window > 0) ? max(0, pos - p.window + 1) : 0;
+    const float sl = p.scale * kLog2e5;
+    float m_ref = -INFINITY, l = 0.0f;
+    unsigned char* p_row = sm.p + t * 128;
+    bool alive = true;
+
+    for (int j = 0; j < ntiles && alive; ++j) {
+      const int b = j & 1;
+      if (!mbar_wait(&sm.s_full[b], (j >> 1) & 1, p.error)) break;
+      tc_fence_after();
+      uint32_t sv[4][32];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) tmem_ld32(tmem + lane_base + b * TK + c * 32, sv[c]);
+      tmem_wait_ld();
+      tc_fence_before();
+      mbar_arrive(&sm.s_empty[b]);
+      // mask, scale, maximum
+      const int j0 = (t_first + j) * TK;
+      float m_tile = -INFINITY;
+#pragma unroll
+      for (int c = 0; c < 4; ++c)
+#pragma unroll
+        for (int e = 0; e < 32; ++e) {
+          const int key = j0 + c * 32 + e;
+          const float x = (key <= pos && key >= first) ? __uint_as_float(sv[c][e]) * sl : -INFINITY;
+          sv[c][e] = __float_as_uint(x);
+          m_tile = fmaxf(m_tile, x);
+        }
+      float alpha = 1.0f;
+      bool grow = false;
+      if (m_tile > m_ref + kRescaleThreshold || (m_ref == -INFINITY && m_tile > -INFINITY)) {
+        alpha = m_ref == -INFINITY ? 0.0f : exp2f(m_ref - m_tile);
+        m_ref = m_tile;
+        grow = true;
+      }
+      const float m_use = m_ref == -INFINITY ? 0.0f : m_ref;
+      // P and O may be touched once the previous P V product has finished
+      if (j > 0) {
+        if (!mbar_wait(&sm.p_empty, (j - 1) & 1, p.error)) break;
+        tc_fence_after();
+        if (__any_sync(0xffffffffu, grow)) {
+#pragma unroll 1
+          for (int c = 0; c < D / 32; ++c) {
+            uint32_t ov[32];
+            tmem_ld32(tmem_o + lane_base + c * 32, ov);
+            tmem_wait_ld();
+#pragma unroll
+            for (int e = 0; e < 32; ++e) ov[e] = __float_as_uint(__uint_as_float(ov[e]) * alpha);
+            tmem_st32(tmem_o + lane_base + c * 32, ov);
+          }
+          tmem_wait_st();
+        }
+      }
+      // exponentials; the P row goes out in chunks of 8 bf16: 128 keys = 2 panels x 8 chunks
+      float sum = 0.0f;
+#pragma unroll
+      for (int c = 0; c < 4; ++c)
+#pragma unroll
+        for (int q8 = 0; q8 < 4; ++q8) {
+          uint32_t pk[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float p0 = exp2f(__uint_as_float(sv[c][q8 * 8 + 2 * e]) - m_use);
+            const float p1 = exp2f(__uint_as_float(sv[c][q8 * 8 + 2 * e + 1]) - m_use);
+            sum += p0 + p1;
+            __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
+            pk[e] = *reinterpret_cast<uint32_t*>(&h);
+          }
+          const int ch = c * 4 + q8;                     // chunk 0..15 of the row
+          unsigned char* dst = p_row + (ch >> 3) * PANEL_BYTES + (((ch & 7) ^ (t & 7)) << 4);
+          *reinterpret_cast<uint4*>(dst) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+        }
+      l = l * alpha + sum;
+      proxy_fence();
+      tc_fence_before();
+      mbar_arrive(&sm.p_full);
+    }
+    // epilogue
+    if (alive && mbar_wait(&sm.o_ready, 0, p.error)) {
+      tc_fence_after();
+      const float inv = (l > 0.0f) ? 1.0f / l : 0.0f;
+      if (row_valid && (!(l > 0.0f) || !isfinite(l))) publish_error(p.error, kAttentionDenominator);
+      __nv_bfloat16* orow = nullptr;
+      if (row_valid)
+        orow = p.out + (static_cast<size_t>(row0 + i_row / G) * p.heads + g * G + i_row % G) * D;
+#pragma unroll 1
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t ov[32];
+        tmem_ld32(tmem_o + lane_base + c * 32, ov);
+        tmem_wait_ld();
+        if (row_valid) {
+          uint32_t pk[16];
+#pragma unroll
+          for (int e = 0; e < 16; ++e) {
+            __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(ov[2 * e]) * inv, __uint_as_float(ov[2 * e + 1]) * inv);
+            pk[e] = *reinterpret_cast<uint32_t*>(&h);
+          }
+#pragma unroll
+          for (int e = 0; e < 4; ++e)
+            reinterpret_cast<uint4*>(orow + c * 32)[e] = make_uint4(pk[4 * e], pk[4 * e + 1], pk[4 * e + 2], pk[4 * e + 3]);
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 5) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(512));
+  }
+}
+
+}  // namespace pih
+
+using namespace pih;
+
+// Attention of the requests that bring more than 16 packed rows (prompt portions); rows of other requests
+// are left untouched.  head_dim 64 or 128, page_size 8..64 (a power of two), kv_tensor_map from
+// pih_make_kv_tensor_map.  tile_max_q: the most rows of such a request.  PIH_ERR_UNSUPPORTED otherwise.
+extern "C" int pih_attention_prefill_tcgen05(const void* q, int q_stride, void* out, const int* block_table,
+                                             int table_width, const int* cu_q, const int* q_start, int num_requests,
+                                             int tile_max_q, int heads, int kv_heads, int head_dim, int page_size,
+                                             int num_pages, float scale, int window, const void* kv_tensor_map,
+                                             uint32_t* error, void* stream) {
+  if (tile_max_q <= 0) return 0;
+  if (heads <= 0 || kv_heads <= 0 || heads % kv_heads || num_requests <= 0 || num_requests > 65535 ||
+      kv_heads > 65535 || q_stride % 8 || window < 0 || table_width <= 0)
+    return PIH_ERR_BAD_ARGUMENT;
+  int shift = -1;
+  for (int s = 3; s <= 6; ++s)
+    if ((1 << s) == page_size) shift = s;
+  if (shift < 0 || kv_tensor_map == nullptr || (head_dim != 64 && head_dim != 128)) return PIH_ERR_UNSUPPORTED;
+  PrefillParams p;
+  p.q = static_cast<const __nv_bfloat16*>(q);
+  p.q_stride = q_stride;
+  p.out = static_cast<__nv_bfloat16*>(out);
+  p.block_table = block_table;
+  p.table_width = table_width;
+  p.cu_q = cu_q;
+  p.q_start = q_start;
+  p.heads = heads;
+  p.kv_heads = kv_heads;
+  p.page_size = page_size;
+  p.page_shift = shift;
+  p.num_pages = num_pages;
+  p.scale = scale;
+  p.window = window;
+  p.error = error;
+  CUtensorMap map;
+  memcpy(&map, kv_tensor_map, sizeof(CUtensorMap));
+  const int G = heads / kv_heads;
+  dim3 grid((tile_max_q * G + TQ - 1) / TQ, kv_heads, num_requests);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  static bool configured[2] = {false, false};
+  if (head_dim == 128) {
+    const int smem = static_cast<int>(sizeof(PrefillSmem<128>)) + 1024;
+    if (!configured[0]) {
+      cudaError_t e = cudaFuncSetAttribute(attn_prefill_tcgen05_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+      if (e != cudaSuccess) return static_cast<int>(e);
+      configured[0] = true;
+    }
+    attn_prefill_tcgen05_kernel<128><<<grid, 192, smem, s>>>(p, map);
+  } else {
+    const int smem = static_cast<int>(sizeof(PrefillSmem<64>)) + 1024;
+    if (!configured[1]) {
+      cudaError_t e = cudaFuncSetAttribute(attn_prefill_tcgen05_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+      if (e != cudaSuccess) return static_cast<int>(e);
+      configured[1] = true;
+    }
+    attn_prefill_tcgen05_kernel<64><<<grid, 192, smem, s>>>(p, map);
+  }
+  PIH_LAUNCH_CHECK();
+  return 0;
+}

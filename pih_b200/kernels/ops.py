@@ -59,6 +59,7 @@ class CudaOps:
         self._retired_scratch = []
         self._kv_maps = {}                 # cache tensor (address, shape) -> 128-byte TMA descriptor
         self.tma_attention = True          # False: the split kernel gathers with cp.async instead of TMA
+        self.tcgen05_attention = True      # False: prompt portions use the mma.sync tile kernel
         self.attention_split = 0           # keys per split of the decode attention kernel; 0: chosen per call
         self.tensor_core_attention = True  # False: bf16 attention runs on the generic kernel too
         self.tcgen05_min_rows = None       # bf16 products with at least this many rows use the pack's tcgen05 kernel
@@ -69,7 +70,8 @@ class CudaOps:
         lib = self.lib
         for name in ("pih_embedding", "pih_rmsnorm", "pih_qk_norm_rope_kv_write", "pih_silu_mul",
                      "pih_gather_rows", "pih_gemm_simt", "pih_paged_attention_generic", "pih_argmax",
-                     "pih_sample", "pih_paged_attention_mma", "pih_gemm_tcgen05", "pih_make_kv_tensor_map"):
+                     "pih_sample", "pih_paged_attention_mma", "pih_gemm_tcgen05", "pih_make_kv_tensor_map",
+                     "pih_attention_prefill_tcgen05"):
             getattr(lib, name).restype = c_int
         lib.pih_attention_scratch_floats.restype = c_ll
 
@@ -257,11 +259,22 @@ class CudaOps:
         if dec_cap > 0:
             self.reserve_attention_scratch(step.num_requests, dec_cap, heads, kv_heads, head_dim, dec_ctx)
             scratch = self._attn_scratch
+        kv_map = self.kv_tensor_map(kv_cache) if (self.tma_attention or self.tcgen05_attention) else None
+        if tile_max_q > 0 and self.tcgen05_attention and kv_map is not None and head_dim in (64, 128) \
+                and page_size in (8, 16, 32, 64):
+            rc = self.lib.pih_attention_prefill_tcgen05(
+                _ptr(qkv), qkv.stride(0), _ptr(out), _ptr(block_table), block_table.shape[1], _ptr(step.cu_q),
+                _ptr(step.q_start), step.num_requests, tile_max_q, heads, kv_heads, head_dim, page_size, num_pages,
+                c_float(scale), int(window), kv_map, self._err(), self._stream())
+            self._check(rc, "attention_prefill_tcgen05")
+            tile_max_q = 0                                  # done; what is left is decode-like
+            if dec_cap == 0:
+                return out
         rc = self.lib.pih_paged_attention_mma(
             _ptr(qkv), qkv.stride(0), _ptr(out), _ptr(kv_cache), _ptr(block_table), block_table.shape[1],
             _ptr(step.cu_q), _ptr(step.q_start), rows, step.num_requests, tile_max_q, dec_cap, dec_ctx, heads, kv_heads, head_dim, page_size, num_pages,
             c_float(scale), int(window), split, _ptr(scratch),
-            self.kv_tensor_map(kv_cache) if (self.tma_attention and dec_cap > 0) else None,
+            kv_map if (self.tma_attention and dec_cap > 0) else None,
             self._err(), self._stream())
         self._check(rc, "paged_attention_mma")
         return out

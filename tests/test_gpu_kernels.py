@@ -295,8 +295,26 @@ MMA_CASES = [c for c in ATTN_CASES if c[2] != 48] + [
 ]
 
 
+@pytest.fixture(params=["tcgen05+tma", "mma.sync+cp.async"])
+def attention_variant(request, ops):
+    """Both families of tensor-core attention kernels: tcgen05 tiles with TMA-fed splits, and the
+    mma.sync tile kernel with cp.async splits (which also serve the sizes the first does not take)."""
+    modern = request.param == "tcgen05+tma"
+    ops.tcgen05_attention, ops.tma_attention = modern, modern
+    yield request.param
+    ops.tcgen05_attention, ops.tma_attention = True, True
+
+
+MMA_CASES += [
+    (16, 8, 128, 16, [2048], [2048], None),                      # a whole 2048-token prompt: 32 row tiles x 16 key tiles
+    (16, 8, 128, 16, [1500, 900], [300, 900], 257),              # portions that start deep in the context, window
+    (8, 1, 64, 32, [333], [333], None),                          # G = 8, head_dim 64, pages of 32
+    (4, 4, 128, 64, [200, 50], [200, 50], None),                 # G = 1, pages of 64
+]
+
+
 @pytest.mark.parametrize("case", MMA_CASES, ids=[f"h{c[0]}kv{c[1]}d{c[2]}p{c[3]}w{c[6]}n{max(c[5])}r{len(c[4])}" for c in MMA_CASES])
-def test_paged_attention_tensor_core(ops, case):
+def test_paged_attention_tensor_core(ops, attention_variant, case):
     heads, kv_heads, D, page, lens, new, window = case
     s = _paged_setup(torch.bfloat16, lens, new, heads, kv_heads, D, page, seed=13)
     scale = 1.0 / math.sqrt(D)
