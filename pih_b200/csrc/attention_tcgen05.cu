@@ -5,15 +5,17 @@
 // causal mask by position, online softmax in 32-bit, one rounding of acc / sum.  Execution:
 //
 //   tile       128 packed rows (token i / G, head g G + i % G) of one (request, kv head) x 128 keys
-//   warps 0-3  softmax: thread t owns row t = tensor-memory lane t: reads its 128 scores (tcgen05.ld), masks,
-//              exponentiates, writes P (bf16) into shared memory in the 128-byte-swizzled K-major layout, keeps the
-//              row sum; rescales O in tensor memory only when the running maximum grew by more than 2^8
-//              (otherwise the old reference maximum stays, which is exact because the final division uses the
-//              sum formed with the same reference);
-//   warp 4     producer: lane p looks up page p of the key tile and issues its TMA boxes (K ring and V ring of
+//   warps 0-7  softmax: a row (= tensor-memory lane) is shared by two threads, one per half of the 128 key
+//              columns: each reads its 64 scores twice (tcgen05.ld; once for the maximum, once for the
+//              exponentials), masks, writes P (bf16) into shared memory in the 128-byte-swizzled K-major layout and
+//              keeps its part of the row sum; O in tensor memory is rescaled only when the running maximum grew by
+//              more than 2^8 (otherwise the old reference maximum stays, which is exact because the final division
+//              uses the sum formed with the same reference);
+//   warp 8     producer: lane p looks up page p of the key tile and issues its TMA boxes (K ring and V ring of
 //              two stages each);
-//   warp 5     one thread issues the MMAs: S_j = Q K_j^T (8 x K=16) into one of two S buffers, then
+//   warp 9     one thread issues the MMAs: S_j = Q K_j^T (8 x K=16) into one of two S buffers, then
 //              O += P_{j-1} V_{j-1}; S_j therefore overlaps the softmax of tile j-1.
+//   A CTA takes a late row tile (many keys) and then its early mirror image (few keys), so CTAs are balanced.
 //
 // Tensor memory: S0 [0,128) S1 [128,256) O [256, 256 + D).  Every mbarrier wait is bounded.
 // No cluster, no multicast.
@@ -94,6 +96,23 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
         "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
       : "r"(taddr));
 }
+__device__ __forceinline__ void tmem_ld64(uint32_t taddr, uint32_t (&v)[64]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x64.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, "
+      "%32, %33, %34, %35, %36, %37, %38, %39, %40, %41, %42, %43, %44, %45, %46, %47, "
+      "%48, %49, %50, %51, %52, %53, %54, %55, %56, %57, %58, %59, %60, %61, %62, %63}, [%64];\n"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+        "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
+        "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
+        "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31]), "=r"(v[32]),
+        "=r"(v[33]), "=r"(v[34]), "=r"(v[35]), "=r"(v[36]), "=r"(v[37]), "=r"(v[38]), "=r"(v[39]), "=r"(v[40]),
+        "=r"(v[41]), "=r"(v[42]), "=r"(v[43]), "=r"(v[44]), "=r"(v[45]), "=r"(v[46]), "=r"(v[47]), "=r"(v[48]),
+        "=r"(v[49]), "=r"(v[50]), "=r"(v[51]), "=r"(v[52]), "=r"(v[53]), "=r"(v[54]), "=r"(v[55]), "=r"(v[56]),
+        "=r"(v[57]), "=r"(v[58]), "=r"(v[59]), "=r"(v[60]), "=r"(v[61]), "=r"(v[62]), "=r"(v[63])
+      : "r"(taddr));
+}
 __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&v)[32]) {
   asm volatile(
       "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
@@ -107,6 +126,13 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&v)[32
 }
 __device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory"); }
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory"); }
+
+// 2^x by the special-function unit (ex2.approx: 2 ulp; -inf gives 0)
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 
 __device__ __forceinline__ void cp16(void* smem, const void* gmem, int bytes) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(smem_u32(smem)), "l"(gmem), "r"(bytes));
@@ -123,11 +149,24 @@ struct PrefillSmem {
   alignas(8) uint64_t q_full, o_ready, p_full, p_empty;
   alignas(8) uint64_t k_full[KV_STAGES], k_empty[KV_STAGES], v_full[KV_STAGES], v_empty[KV_STAGES];
   alignas(8) uint64_t s_full[2], s_empty[2];
+  float xmax[2][2][128];                                        // [tile parity][column half][row] maxima
+  float xsum[2][128];                                           // row sums of the two column halves
   uint32_t tmem_base;
 };
 
+constexpr int kSoftmaxThreads = 256;     // warps 0-7: two threads per row, one per half of the key columns
+constexpr int kProducerWarp = 8, kMmaWarp = 9;
+
+__device__ __forceinline__ void softmax_sync() { asm volatile("bar.sync 1, 256;\n" ::: "memory"); }
+// the two softmax warps (w and w + 4) that share tensor-memory lanes 32 quarter .. 32 quarter + 31
+__device__ __forceinline__ void pair_sync(int quarter) {
+  asm volatile("bar.sync %0, 64;\n" ::"r"(2 + quarter) : "memory");
+}
+
+// One CTA works through up to two row tiles of its (request, kv head): a long one (late rows, many keys)
+// and its short mirror image, so that every CTA has about the same number of key tiles.
 template <int D>
-__global__ void __launch_bounds__(192)
+__global__ void __launch_bounds__(320)
 attn_prefill_tcgen05_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap kv_map) {
   using Smem = PrefillSmem<D>;
   constexpr int PANELS = Smem::PANELS;
@@ -141,265 +180,285 @@ attn_prefill_tcgen05_kernel(const PrefillParams p, const __grid_constant__ CUten
   const int n_tok = p.cu_q[r + 1] - row0;
   const int packed = n_tok * G;
   if (packed <= 16) return;                                     // decode-like: the split kernel's
-  // long tiles first: the last rows of a prompt see the most keys
   const int tiles_q = (packed + TQ - 1) / TQ;
-  const int qt = tiles_q - 1 - static_cast<int>(blockIdx.x);
-  if (qt < 0) return;
-  const int tile_row0 = qt * TQ;
+  const int bx = static_cast<int>(blockIdx.x);
+  if (2 * bx > tiles_q - 1) return;
+  const int items = (2 * bx < tiles_q - 1) ? 2 : 1;              // the middle tile of an odd count stands alone
   const int start = p.q_start[r];
-  const int tok_lo = tile_row0 / G;
-  const int tok_hi = min(packed - 1, tile_row0 + TQ - 1) / G;
-  const int kmin = p.window > 0 ? max(0, start + tok_lo - p.window + 1) : 0;
-  const int kmax = start + tok_hi;
-  const int t_first = kmin / TK, t_last = kmax / TK;
-  const int ntiles = t_last - t_first + 1;
   const int* table = p.block_table + static_cast<size_t>(r) * p.table_width;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
-  if (threadIdx.x == 0) {
-    mbar_init(&sm.q_full, 128);
-    mbar_init(&sm.o_ready, 1);
-    mbar_init(&sm.p_full, 128);
-    mbar_init(&sm.p_empty, 1);
-    for (int s = 0; s < KV_STAGES; ++s) {
-      mbar_init(&sm.k_full[s], 1);
-      mbar_init(&sm.k_empty[s], 1);
-      mbar_init(&sm.v_full[s], 1);
-      mbar_init(&sm.v_empty[s], 1);
-    }
-    for (int b = 0; b < 2; ++b) {
-      mbar_init(&sm.s_full[b], 1);
-      mbar_init(&sm.s_empty[b], 128);
-    }
-    mbar_init_fence();
-  }
-  if (warp == 5) {
+  if (warp == kMmaWarp) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(&sm.tmem_base)),
                  "r"(512));
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::);
   }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem = sm.tmem_base;
-  const uint32_t tmem_o = tmem + 256;
 
-  if (warp == 4) {
-    // ---------------- producer ----------------
-    const int pages_per_tile = TK >> p.page_shift;
-    const int fallback = kmin >> p.page_shift;
-    if (lane == 0) tma_prefetch_map(&kv_map);
-    bool alive = true;
-    for (int j = 0; j < ntiles && alive; ++j) {
-      const int s = j % KV_STAGES;
-      const int use = j / KV_STAGES;
-      int page = 0;
-      if (lane < pages_per_tile) {
-        const int j_page = (t_first + j) * TK + lane * p.page_size;
-        const bool seen = j_page <= kmax && j_page + p.page_size - 1 >= kmin;
-        page = table[seen ? (j_page >> p.page_shift) : fallback];
-        if (page < 0 || page >= p.num_pages) {
-          publish_error(p.error, kRowWithoutPage);
-          page = 0;
-        }
+  for (int item = 0; item < items; ++item) {
+    const int qt = item == 0 ? tiles_q - 1 - bx : bx;
+    const int tile_row0 = qt * TQ;
+    const int tok_lo = tile_row0 / G;
+    const int tok_hi = min(packed - 1, tile_row0 + TQ - 1) / G;
+    const int kmin = p.window > 0 ? max(0, start + tok_lo - p.window + 1) : 0;
+    const int kmax = start + tok_hi;
+    const int t_first = kmin / TK, t_last = kmax / TK;
+    const int ntiles = t_last - t_first + 1;
+
+    // (re)initialise the barriers: everything of the previous item has completed (its epilogue waited for the
+    // last MMA, and every load had been consumed by an MMA)
+    if (threadIdx.x == 0) {
+      if (item > 0) {
+        uint64_t* all[] = {&sm.q_full, &sm.o_ready, &sm.p_full, &sm.p_empty, &sm.k_full[0], &sm.k_full[1],
+                           &sm.k_empty[0], &sm.k_empty[1], &sm.v_full[0], &sm.v_full[1], &sm.v_empty[0],
+                           &sm.v_empty[1], &sm.s_full[0], &sm.s_full[1], &sm.s_empty[0], &sm.s_empty[1]};
+        for (uint64_t* bar : all) asm volatile("mbarrier.inval.shared::cta.b64 [%0];\n" ::"r"(smem_u32(bar)) : "memory");
       }
-      const int off = lane * p.page_size * 128;
-      // K tile
-      if (use > 0) alive = mbar_wait(&sm.k_empty[s], (use - 1) & 1, p.error);
-      alive = __all_sync(0xffffffffu, alive);
-      if (!alive) break;
-      if (lane == 0) mbar_expect_tx(&sm.k_full[s], PANELS * PANEL_BYTES);
-      __syncwarp();
-      if (lane < pages_per_tile) {
-        const int zk = (page * 2) * p.kv_heads + g;
-#pragma unroll
-        for (int pn = 0; pn < PANELS; ++pn) tma_load_3d(sm.k[s] + pn * PANEL_BYTES + off, &kv_map, pn * 64, 0, zk, &sm.k_full[s]);
+      mbar_init(&sm.q_full, kSoftmaxThreads);
+      mbar_init(&sm.o_ready, 1);
+      mbar_init(&sm.p_full, kSoftmaxThreads);
+      mbar_init(&sm.p_empty, 1);
+      for (int s = 0; s < KV_STAGES; ++s) {
+        mbar_init(&sm.k_full[s], 1);
+        mbar_init(&sm.k_empty[s], 1);
+        mbar_init(&sm.v_full[s], 1);
+        mbar_init(&sm.v_empty[s], 1);
       }
-      // V tile
-      if (use > 0) alive = mbar_wait(&sm.v_empty[s], (use - 1) & 1, p.error);
-      alive = __all_sync(0xffffffffu, alive);
-      if (!alive) break;
-      if (lane == 0) mbar_expect_tx(&sm.v_full[s], PANELS * PANEL_BYTES);
-      __syncwarp();
-      if (lane < pages_per_tile) {
-        const int zv = (page * 2 + 1) * p.kv_heads + g;
-#pragma unroll
-        for (int pn = 0; pn < PANELS; ++pn) tma_load_3d(sm.v[s] + pn * PANEL_BYTES + off, &kv_map, pn * 64, 0, zv, &sm.v_full[s]);
+      for (int b = 0; b < 2; ++b) {
+        mbar_init(&sm.s_full[b], 1);
+        mbar_init(&sm.s_empty[b], kSoftmaxThreads);
       }
+      mbar_init_fence();
     }
-  } else if (warp == 5) {
-    // ---------------- MMA issuer ----------------
-    if (lane == 0) {
-      constexpr uint32_t idesc_s = idesc_bf16(TQ, TK, false);
-      constexpr uint32_t idesc_o = idesc_bf16(TQ, D, true);
-      const uint32_t q_addr = smem_u32(sm.q), p_addr = smem_u32(sm.p);
-      bool alive = mbar_wait(&sm.q_full, 0, p.error);
-      tc_fence_after();
-      for (int j = 0; j <= ntiles && alive; ++j) {
-        if (j < ntiles) {
-          // S_b = Q K_j^T
-          const int b = j & 1, use = j >> 1, s = j % KV_STAGES;
-          if (use > 0 && !mbar_wait(&sm.s_empty[b], (use - 1) & 1, p.error)) break;
-          if (!mbar_wait(&sm.k_full[s], (j / KV_STAGES) & 1, p.error)) break;
-          tc_fence_after();
-          const uint32_t k_addr = smem_u32(sm.k[s]);
-#pragma unroll
-          for (int kk = 0; kk < D / 16; ++kk) {
-            const uint32_t offs = (kk / 4) * PANEL_BYTES + (kk % 4) * 32;
-            umma(tmem + b * TK, desc_kmajor(q_addr + offs), desc_kmajor(k_addr + offs), idesc_s, kk > 0 ? 1u : 0u);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = sm.tmem_base;
+    const uint32_t tmem_o = tmem + 256;
+
+    if (warp == kProducerWarp) {
+      // ---------------- producer ----------------
+      const int pages_per_tile = TK >> p.page_shift;
+      const int fallback = kmin >> p.page_shift;
+      if (lane == 0 && item == 0) tma_prefetch_map(&kv_map);
+      bool alive = true;
+      for (int j = 0; j < ntiles && alive; ++j) {
+        const int s = j % KV_STAGES;
+        const int use = j / KV_STAGES;
+        int page = 0;
+        if (lane < pages_per_tile) {
+          const int j_page = (t_first + j) * TK + lane * p.page_size;
+          const bool seen = j_page <= kmax && j_page + p.page_size - 1 >= kmin;
+          page = table[seen ? (j_page >> p.page_shift) : fallback];
+          if (page < 0 || page >= p.num_pages) {
+            publish_error(p.error, kRowWithoutPage);
+            page = 0;
           }
-          umma_commit(&sm.k_empty[s]);
-          umma_commit(&sm.s_full[b]);
         }
-        if (j >= 1) {
-          // O += P_{j-1} V_{j-1}
-          const int i = j - 1, s = i % KV_STAGES;
-          if (!mbar_wait(&sm.p_full, i & 1, p.error)) break;
-          if (!mbar_wait(&sm.v_full[s], (i / KV_STAGES) & 1, p.error)) break;
-          tc_fence_after();
-          const uint32_t v_addr = smem_u32(sm.v[s]);
+        const int off = lane * p.page_size * 128;
+        if (use > 0) alive = mbar_wait(&sm.k_empty[s], (use - 1) & 1, p.error);
+        alive = __all_sync(0xffffffffu, alive);
+        if (!alive) break;
+        if (lane == 0) mbar_expect_tx(&sm.k_full[s], PANELS * PANEL_BYTES);
+        __syncwarp();
+        if (lane < pages_per_tile) {
+          const int zk = (page * 2) * p.kv_heads + g;
 #pragma unroll
-          for (int kk = 0; kk < TK / 16; ++kk) {
-            const uint64_t adesc = desc_kmajor(p_addr + (kk / 4) * PANEL_BYTES + (kk % 4) * 32);
-            const uint64_t bdesc = desc_mnmajor(v_addr + kk * 16 * 128, PANEL_BYTES);
-            umma(tmem_o, adesc, bdesc, idesc_o, (i > 0 || kk > 0) ? 1u : 0u);
-          }
-          umma_commit(&sm.v_empty[s]);
-          umma_commit(&sm.p_empty);
-          if (i == ntiles - 1) umma_commit(&sm.o_ready);
+          for (int pn = 0; pn < PANELS; ++pn)
+            tma_load_3d(sm.k[s] + pn * PANEL_BYTES + off, &kv_map, pn * 64, 0, zk, &sm.k_full[s]);
+        }
+        if (use > 0) alive = mbar_wait(&sm.v_empty[s], (use - 1) & 1, p.error);
+        alive = __all_sync(0xffffffffu, alive);
+        if (!alive) break;
+        if (lane == 0) mbar_expect_tx(&sm.v_full[s], PANELS * PANEL_BYTES);
+        __syncwarp();
+        if (lane < pages_per_tile) {
+          const int zv = (page * 2 + 1) * p.kv_heads + g;
+#pragma unroll
+          for (int pn = 0; pn < PANELS; ++pn)
+            tma_load_3d(sm.v[s] + pn * PANEL_BYTES + off, &kv_map, pn * 64, 0, zv, &sm.v_full[s]);
         }
       }
-    }
-  } else {
-    // ---------------- softmax / epilogue: thread = row ----------------
-    const int t = threadIdx.x;                           // 0..127 = tensor-memory lane
-    const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
-    // Q rows into the swizzled K-major layout
-    for (int c = t; c < TQ * (D / 8); c += 128) {
-      const int row = c / (D / 8), ch = c % (D / 8);
-      const int i = tile_row0 + row;
-      const bool valid = i < packed;
-      const __nv_bfloat16* src = p.q;
-      if (valid)
-        src = p.q + static_cast<size_t>(row0 + i / G) * p.q_stride + static_cast<size_t>(g * G + i % G) * D + ch * 8;
-      unsigned char* dst = sm.q + (ch >> 3) * PANEL_BYTES + row * 128 + (((ch & 7) ^ (row & 7)) << 4);
-      cp16(dst, src, valid ? 16 : 0);
-    }
-    asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;\n" ::: "memory");
-    proxy_fence();
-    mbar_arrive(&sm.q_full);
-
-    const int i_row = tile_row0 + t;
-    const bool row_valid = i_row < packed;
-    const int pos = row_valid ? start + i_row / G : -1;
-    const int first = (row_valid && p.window > 0) ? max(0, pos - p.window + 1) : 0;
-    const float sl = p.scale * kLog2e5;
-    float m_ref = -INFINITY, l = 0.0f;
-    unsigned char* p_row = sm.p + t * 128;
-    bool alive = true;
-
-    for (int j = 0; j < ntiles && alive; ++j) {
-      const int b = j & 1;
-      if (!mbar_wait(&sm.s_full[b], (j >> 1) & 1, p.error)) break;
-      tc_fence_after();
-      uint32_t sv[4][32];
-#pragma unroll
-      for (int c = 0; c < 4; ++c) tmem_ld32(tmem + lane_base + b * TK + c * 32, sv[c]);
-      tmem_wait_ld();
-      tc_fence_before();
-      mbar_arrive(&sm.s_empty[b]);
-      // mask, scale, maximum
-      const int j0 = (t_first + j) * TK;
-      float m_tile = -INFINITY;
-#pragma unroll
-      for (int c = 0; c < 4; ++c)
-#pragma unroll
-        for (int e = 0; e < 32; ++e) {
-          const int key = j0 + c * 32 + e;
-          const float x = (key <= pos && key >= first) ? __uint_as_float(sv[c][e]) * sl : -INFINITY;
-          sv[c][e] = __float_as_uint(x);
-          m_tile = fmaxf(m_tile, x);
-        }
-      float alpha = 1.0f;
-      bool grow = false;
-      if (m_tile > m_ref + kRescaleThreshold || (m_ref == -INFINITY && m_tile > -INFINITY)) {
-        alpha = m_ref == -INFINITY ? 0.0f : exp2f(m_ref - m_tile);
-        m_ref = m_tile;
-        grow = true;
-      }
-      const float m_use = m_ref == -INFINITY ? 0.0f : m_ref;
-      // P and O may be touched once the previous P V product has finished
-      if (j > 0) {
-        if (!mbar_wait(&sm.p_empty, (j - 1) & 1, p.error)) break;
+    } else if (warp == kMmaWarp) {
+      // ---------------- MMA issuer ----------------
+      if (lane == 0) {
+        constexpr uint32_t idesc_s = idesc_bf16(TQ, TK, false);
+        constexpr uint32_t idesc_o = idesc_bf16(TQ, D, true);
+        const uint32_t q_addr = smem_u32(sm.q), p_addr = smem_u32(sm.p);
+        bool alive = mbar_wait(&sm.q_full, 0, p.error);
         tc_fence_after();
-        if (__any_sync(0xffffffffu, grow)) {
-#pragma unroll 1
-          for (int c = 0; c < D / 32; ++c) {
-            uint32_t ov[32];
-            tmem_ld32(tmem_o + lane_base + c * 32, ov);
-            tmem_wait_ld();
+        for (int j = 0; j <= ntiles && alive; ++j) {
+          if (j < ntiles) {
+            const int b = j & 1, use = j >> 1, s = j % KV_STAGES;
+            if (use > 0 && !mbar_wait(&sm.s_empty[b], (use - 1) & 1, p.error)) break;
+            if (!mbar_wait(&sm.k_full[s], (j / KV_STAGES) & 1, p.error)) break;
+            tc_fence_after();
+            const uint32_t k_addr = smem_u32(sm.k[s]);
 #pragma unroll
-            for (int e = 0; e < 32; ++e) ov[e] = __float_as_uint(__uint_as_float(ov[e]) * alpha);
-            tmem_st32(tmem_o + lane_base + c * 32, ov);
+            for (int kk = 0; kk < D / 16; ++kk) {
+              const uint32_t offs = (kk / 4) * PANEL_BYTES + (kk % 4) * 32;
+              umma(tmem + b * TK, desc_kmajor(q_addr + offs), desc_kmajor(k_addr + offs), idesc_s, kk > 0 ? 1u : 0u);
+            }
+            umma_commit(&sm.k_empty[s]);
+            umma_commit(&sm.s_full[b]);
           }
-          tmem_wait_st();
+          if (j >= 1) {
+            const int i = j - 1, s = i % KV_STAGES;
+            if (!mbar_wait(&sm.p_full, i & 1, p.error)) break;
+            if (!mbar_wait(&sm.v_full[s], (i / KV_STAGES) & 1, p.error)) break;
+            tc_fence_after();
+            const uint32_t v_addr = smem_u32(sm.v[s]);
+#pragma unroll
+            for (int kk = 0; kk < TK / 16; ++kk) {
+              const uint64_t adesc = desc_kmajor(p_addr + (kk / 4) * PANEL_BYTES + (kk % 4) * 32);
+              const uint64_t bdesc = desc_mnmajor(v_addr + kk * 16 * 128, PANEL_BYTES);
+              umma(tmem_o, adesc, bdesc, idesc_o, (i > 0 || kk > 0) ? 1u : 0u);
+            }
+            umma_commit(&sm.v_empty[s]);
+            umma_commit(&sm.p_empty);
+            if (i == ntiles - 1) umma_commit(&sm.o_ready);
+          }
         }
       }
-      // exponentials; the P row goes out in chunks of 8 bf16: 128 keys = 2 panels x 8 chunks
-      float sum = 0.0f;
+    } else {
+      // ---------------- softmax / epilogue: two threads per row ----------------
+      const int t = threadIdx.x;                                 // 0..255
+      const int half = warp >> 2;                                // which 64 of the 128 key columns (and of D)
+      const int row = (warp & 3) * 32 + lane;                    // tensor-memory lane
+      const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
+      for (int c = t; c < TQ * (D / 8); c += kSoftmaxThreads) {
+        const int qrow = c / (D / 8), ch = c % (D / 8);
+        const int i = tile_row0 + qrow;
+        const bool valid = i < packed;
+        const __nv_bfloat16* src = p.q;
+        if (valid)
+          src = p.q + static_cast<size_t>(row0 + i / G) * p.q_stride + static_cast<size_t>(g * G + i % G) * D + ch * 8;
+        unsigned char* dst = sm.q + (ch >> 3) * PANEL_BYTES + qrow * 128 + (((ch & 7) ^ (qrow & 7)) << 4);
+        cp16(dst, src, valid ? 16 : 0);
+      }
+      asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;\n" ::: "memory");
+      proxy_fence();
+      mbar_arrive(&sm.q_full);
+
+      const int i_row = tile_row0 + row;
+      const bool row_valid = i_row < packed;
+      const int pos = row_valid ? start + i_row / G : -1;
+      const int first = (row_valid && p.window > 0) ? max(0, pos - p.window + 1) : 0;
+      const float sl = p.scale * kLog2e5;
+      float m_ref = -INFINITY, l = 0.0f;
+      unsigned char* p_row = sm.p + half * PANEL_BYTES + row * 128;   // this thread's 64 keys are one panel
+      bool ok = true;
+
+      for (int j = 0; j < ntiles; ++j) {
+        const int b = j & 1;
+        if (!mbar_wait(&sm.s_full[b], (j >> 1) & 1, p.error)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t s_addr = tmem + lane_base + b * TK + half * 64;
+        const int j0 = (t_first + j) * TK + half * 64;
+        // a tile that lies wholly inside every row's visible range needs no mask (the usual case)
+        const bool unmasked = __all_sync(0xffffffffu, j0 + 63 <= pos && j0 >= first);
+        // this thread's 64 scores, read once
+        uint32_t sv[64];
+        tmem_ld64(s_addr, sv);
+        tmem_wait_ld();
+        tc_fence_before();
+        mbar_arrive(&sm.s_empty[b]);                             // S_b is in registers: the next-but-one S may land
+        float m_half = -INFINITY;
+        if (unmasked) {
 #pragma unroll
-      for (int c = 0; c < 4; ++c)
+          for (int e = 0; e < 64; ++e) m_half = fmaxf(m_half, __uint_as_float(sv[e]));
+        } else {
 #pragma unroll
-        for (int q8 = 0; q8 < 4; ++q8) {
+          for (int e = 0; e < 64; ++e) {
+            const int key = j0 + e;
+            if (key <= pos && key >= first) m_half = fmaxf(m_half, __uint_as_float(sv[e]));
+            else sv[e] = 0xff800000u;                            // -inf: masked for good
+          }
+        }
+        m_half *= sl;                                            // scale > 0
+        sm.xmax[b][half][row] = m_half;
+        pair_sync(warp & 3);                                     // the two warps that share these 32 rows
+        const float m_tile = fmaxf(m_half, sm.xmax[b][half ^ 1][row]);
+        float alpha = 1.0f;
+        bool grow = false;
+        if (m_tile > m_ref + kRescaleThreshold || (m_ref == -INFINITY && m_tile > -INFINITY)) {
+          alpha = m_ref == -INFINITY ? 0.0f : exp2f(m_ref - m_tile);
+          m_ref = m_tile;
+          grow = true;
+        }
+        const float m_use = m_ref == -INFINITY ? 0.0f : m_ref;
+        // P and O may be touched once the previous P V product has finished
+        if (j > 0) {
+          if (!mbar_wait(&sm.p_empty, (j - 1) & 1, p.error)) { ok = false; break; }
+          tc_fence_after();
+          if (__any_sync(0xffffffffu, grow)) {
+#pragma unroll 1
+            for (int c = 0; c < D / 64; ++c) {                   // this thread's half of the O columns
+              uint32_t ov[32];
+              const uint32_t o_addr = tmem_o + lane_base + half * (D / 2) + c * 32;
+              tmem_ld32(o_addr, ov);
+              tmem_wait_ld();
+#pragma unroll
+              for (int e = 0; e < 32; ++e) ov[e] = __float_as_uint(__uint_as_float(ov[e]) * alpha);
+              tmem_st32(o_addr, ov);
+            }
+            tmem_wait_st();
+          }
+        }
+        // exponentials; the P row goes out in chunks of 8 bf16 (a masked score is -inf and gives 0)
+        float sum = 0.0f;
+#pragma unroll
+        for (int ch = 0; ch < 8; ++ch) {
           uint32_t pk[4];
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
-            const float p0 = exp2f(__uint_as_float(sv[c][q8 * 8 + 2 * e]) - m_use);
-            const float p1 = exp2f(__uint_as_float(sv[c][q8 * 8 + 2 * e + 1]) - m_use);
+            const float p0 = fast_exp2(fmaf(__uint_as_float(sv[ch * 8 + 2 * e]), sl, -m_use));
+            const float p1 = fast_exp2(fmaf(__uint_as_float(sv[ch * 8 + 2 * e + 1]), sl, -m_use));
             sum += p0 + p1;
             __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
             pk[e] = *reinterpret_cast<uint32_t*>(&h);
           }
-          const int ch = c * 4 + q8;                     // chunk 0..15 of the row
-          unsigned char* dst = p_row + (ch >> 3) * PANEL_BYTES + (((ch & 7) ^ (t & 7)) << 4);
-          *reinterpret_cast<uint4*>(dst) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+          *reinterpret_cast<uint4*>(p_row + ((ch ^ (row & 7)) << 4)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
         }
-      l = l * alpha + sum;
-      proxy_fence();
-      tc_fence_before();
-      mbar_arrive(&sm.p_full);
-    }
-    // epilogue
-    if (alive && mbar_wait(&sm.o_ready, 0, p.error)) {
-      tc_fence_after();
-      const float inv = (l > 0.0f) ? 1.0f / l : 0.0f;
-      if (row_valid && (!(l > 0.0f) || !isfinite(l))) publish_error(p.error, kAttentionDenominator);
-      __nv_bfloat16* orow = nullptr;
-      if (row_valid)
-        orow = p.out + (static_cast<size_t>(row0 + i_row / G) * p.heads + g * G + i_row % G) * D;
+        l = l * alpha + sum;
+        proxy_fence();
+        tc_fence_before();
+        mbar_arrive(&sm.p_full);
+      }
+      // epilogue: the two halves of a row share the row sum
+      sm.xsum[half][row] = l;
+      softmax_sync();
+      const float l_row = l + sm.xsum[half ^ 1][row];
+      if (ok && mbar_wait(&sm.o_ready, 0, p.error)) {
+        tc_fence_after();
+        const float inv = (l_row > 0.0f) ? 1.0f / l_row : 0.0f;
+        if (row_valid && half == 0 && (!(l_row > 0.0f) || !isfinite(l_row))) publish_error(p.error, kAttentionDenominator);
+        __nv_bfloat16* orow = nullptr;
+        if (row_valid)
+          orow = p.out + (static_cast<size_t>(row0 + i_row / G) * p.heads + g * G + i_row % G) * D + half * (D / 2);
 #pragma unroll 1
-      for (int c = 0; c < D / 32; ++c) {
-        uint32_t ov[32];
-        tmem_ld32(tmem_o + lane_base + c * 32, ov);
-        tmem_wait_ld();
-        if (row_valid) {
-          uint32_t pk[16];
+        for (int c = 0; c < D / 64; ++c) {
+          uint32_t ov[32];
+          tmem_ld32(tmem_o + lane_base + half * (D / 2) + c * 32, ov);
+          tmem_wait_ld();
+          if (row_valid) {
+            uint32_t pk[16];
 #pragma unroll
-          for (int e = 0; e < 16; ++e) {
-            __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(ov[2 * e]) * inv, __uint_as_float(ov[2 * e + 1]) * inv);
-            pk[e] = *reinterpret_cast<uint32_t*>(&h);
+            for (int e = 0; e < 16; ++e) {
+              __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(ov[2 * e]) * inv, __uint_as_float(ov[2 * e + 1]) * inv);
+              pk[e] = *reinterpret_cast<uint32_t*>(&h);
+            }
+#pragma unroll
+            for (int e = 0; e < 4; ++e)
+              reinterpret_cast<uint4*>(orow + c * 32)[e] = make_uint4(pk[4 * e], pk[4 * e + 1], pk[4 * e + 2], pk[4 * e + 3]);
           }
-#pragma unroll
-          for (int e = 0; e < 4; ++e)
-            reinterpret_cast<uint4*>(orow + c * 32)[e] = make_uint4(pk[4 * e], pk[4 * e + 1], pk[4 * e + 2], pk[4 * e + 3]);
         }
       }
     }
+    tc_fence_before();
+    __syncthreads();                                             // the item is finished everywhere
   }
-  tc_fence_before();
-  __syncthreads();
-  if (warp == 5) {
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(512));
+  if (warp == kMmaWarp) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(sm.tmem_base), "r"(512));
   }
 }
 
@@ -442,7 +501,8 @@ extern "C" int pih_attention_prefill_tcgen05(const void* q, int q_stride, void* 
   CUtensorMap map;
   memcpy(&map, kv_tensor_map, sizeof(CUtensorMap));
   const int G = heads / kv_heads;
-  dim3 grid((tile_max_q * G + TQ - 1) / TQ, kv_heads, num_requests);
+  const int tiles_q = (tile_max_q * G + TQ - 1) / TQ;
+  dim3 grid((tiles_q + 1) / 2, kv_heads, num_requests);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   static bool configured[2] = {false, false};
   if (head_dim == 128) {
@@ -452,7 +512,7 @@ extern "C" int pih_attention_prefill_tcgen05(const void* q, int q_stride, void* 
       if (e != cudaSuccess) return static_cast<int>(e);
       configured[0] = true;
     }
-    attn_prefill_tcgen05_kernel<128><<<grid, 192, smem, s>>>(p, map);
+    attn_prefill_tcgen05_kernel<128><<<grid, 320, smem, s>>>(p, map);
   } else {
     const int smem = static_cast<int>(sizeof(PrefillSmem<64>)) + 1024;
     if (!configured[1]) {
@@ -460,7 +520,7 @@ extern "C" int pih_attention_prefill_tcgen05(const void* q, int q_stride, void* 
       if (e != cudaSuccess) return static_cast<int>(e);
       configured[1] = true;
     }
-    attn_prefill_tcgen05_kernel<64><<<grid, 192, smem, s>>>(p, map);
+    attn_prefill_tcgen05_kernel<64><<<grid, 320, smem, s>>>(p, map);
   }
   PIH_LAUNCH_CHECK();
   return 0;
