@@ -76,6 +76,7 @@ def main() -> int:
     ap.add_argument("--no-flush", action="store_true")
     ap.add_argument("--impl", default="default", choices=["default", "tcgen05", "skinny", "library"])
     ap.add_argument("--tile-n", type=int, default=0)
+    ap.add_argument("--chain", action="store_true", help="linear: many products back to back in a CUDA graph")
     ap.add_argument("--split", type=int, default=0, help="keys per split of the decode attention (0: automatic)")
     ap.add_argument("--no-tma", action="store_true", help="decode attention gathers with cp.async instead of TMA")
     ap.add_argument("--plain", action="store_true", help="the pack's plain (generic / FMA) kernel instead")
@@ -122,6 +123,32 @@ def main() -> int:
             T = args.tokens
             flops = 4 * H * D * T * (T + 1) // 2
             out.update(us=round(us, 2), flops=flops, tflops=round(flops / us / 1e6, 1), tokens=T)
+    elif args.kernel == "linear" and args.chain:
+        # many products with different weights back to back (together larger than L2) in one timed region:
+        # per-launch time as a decode step sees it, launch gaps included, measured inside a CUDA graph
+        x = torch.randn(args.m, args.k, device=dev).to(bf)
+        reps = max(4, int(200e6 / (args.n * args.k * 2)) + 1)
+        ws = [torch.randn(args.n, args.k, device=dev).to(bf) for _ in range(reps)]
+        call = {"skinny": lambda w: ops.linear_skinny(x, w), "library": lambda w: torch.mm(x, w.t()),
+                "tcgen05": lambda w: ops.linear_tcgen05(x, w, tile_n=args.tile_n)}.get(args.impl, lambda w: ops.linear(x, w))
+        for w in ws[:2]:
+            call(w)
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for w in ws:
+                call(w)
+        g.replay()
+        torch.cuda.synchronize()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for _ in range(5):
+            g.replay()
+        stop.record()
+        torch.cuda.synchronize()
+        us = start.elapsed_time(stop) * 1e3 / (5 * reps)
+        nbytes = 2 * (args.m * args.k + args.n * args.k + args.m * args.n)
+        out.update(us=round(us, 2), gbs=round(nbytes / us / 1e3, 1), m=args.m, n=args.n, k=args.k, chained=reps)
     elif args.kernel == "linear":
         x = torch.randn(args.m, args.k, device=dev).to(bf)
         w = torch.randn(args.n, args.k, device=dev).to(bf)

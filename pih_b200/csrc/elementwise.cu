@@ -242,16 +242,19 @@ __global__ void qk_norm_rope_kv_fast_kernel(T* __restrict__ qkv, int row_stride,
 // SiLU-mul: out[t,i] = round( (g / (1 + exp(-g))) * u ), g = in[t,i], u = in[t,I+i]
 // (qwen_bf16_primitives.cu:274-283)
 // ---------------------------------------------------------------------------
+// Columns of gate_up come in blocks of 2 * il: il gate columns, then their il up columns (il = inter:
+// all gates, then all ups).
 template <typename T>
 __global__ void silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ out, long long rows,
-                                int inter) {
+                                int inter, int il) {
   const long long total = rows * inter;
   for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
        i += static_cast<long long>(gridDim.x) * blockDim.x) {
     const long long t = i / inter;
     const int c = static_cast<int>(i - t * inter);
-    const float g = to_float<T>(gate_up[t * 2 * inter + c]);
-    const float u = to_float<T>(gate_up[t * 2 * inter + inter + c]);
+    const int gc = (c / il) * 2 * il + c % il;
+    const float g = to_float<T>(gate_up[t * 2 * inter + gc]);
+    const float u = to_float<T>(gate_up[t * 2 * inter + gc + il]);
     out[i] = from_float<T>((g / (1.0f + expf(-g))) * u);
   }
 }
@@ -456,10 +459,10 @@ extern "C" int pih_qk_norm_rope_kv_write(int dtype, int weight_dtype, void* qkv,
   return PIH_ERR_BAD_ARGUMENT;
 }
 
-// 16 bytes per thread; needs inter * sizeof(T) % 16 == 0
+// 16 bytes per thread; needs inter * sizeof(T) % 16 == 0 and il a multiple of the vector length
 template <typename T>
 __global__ void silu_mul_vec_kernel(const T* __restrict__ gate_up, T* __restrict__ out, long long rows,
-                                    int inter) {
+                                    int inter, int il) {
   constexpr int VEC = 16 / sizeof(T);
   const int per_row = inter / VEC;
   const long long total = rows * per_row;
@@ -467,8 +470,10 @@ __global__ void silu_mul_vec_kernel(const T* __restrict__ gate_up, T* __restrict
        i += static_cast<long long>(gridDim.x) * blockDim.x) {
     const long long t = i / per_row;
     const int c = static_cast<int>(i - t * per_row);
-    const uint4 graw = reinterpret_cast<const uint4*>(gate_up + t * 2 * inter)[c];
-    const uint4 uraw = reinterpret_cast<const uint4*>(gate_up + t * 2 * inter + inter)[c];
+    const int col = c * VEC;
+    const int gc = (col / il) * 2 * il + col % il;
+    const uint4 graw = *reinterpret_cast<const uint4*>(gate_up + t * 2 * inter + gc);
+    const uint4 uraw = *reinterpret_cast<const uint4*>(gate_up + t * 2 * inter + gc + il);
     const T* g = reinterpret_cast<const T*>(&graw);
     const T* u = reinterpret_cast<const T*>(&uraw);
     uint4 packed;
@@ -483,30 +488,32 @@ __global__ void silu_mul_vec_kernel(const T* __restrict__ gate_up, T* __restrict
 }
 
 template <typename T>
-static int launch_silu(const void* gate_up, void* out, long long rows, int inter, cudaStream_t s) {
+static int launch_silu(const void* gate_up, void* out, long long rows, int inter, int il, cudaStream_t s) {
   const int threads = 256;
-  if ((inter * sizeof(T)) % 16 == 0) {
+  if ((inter * sizeof(T)) % 16 == 0 && il % (16 / sizeof(T)) == 0) {
     const long long total = rows * (inter / (16 / sizeof(T)));
     const unsigned blocks = static_cast<unsigned>(min((total + threads - 1) / threads, 148LL * 32));
     silu_mul_vec_kernel<T><<<blocks, threads, 0, s>>>(static_cast<const T*>(gate_up), static_cast<T*>(out),
-                                                      rows, inter);
+                                                      rows, inter, il);
   } else {
     const long long total = rows * inter;
     const unsigned blocks = static_cast<unsigned>(min((total + threads - 1) / threads, 148LL * 32));
     silu_mul_kernel<T><<<blocks, threads, 0, s>>>(static_cast<const T*>(gate_up), static_cast<T*>(out), rows,
-                                                  inter);
+                                                  inter, il);
   }
   PIH_LAUNCH_CHECK();
   return 0;
 }
 
+// interleave: gate_up columns come in blocks of `interleave` gate columns followed by their up columns
+// (interleave == inter: all gates, then all ups); it must divide inter.
 extern "C" int pih_silu_mul(int dtype, const void* gate_up, void* out, long long rows, int inter,
-                            void* stream) {
+                            int interleave, void* stream) {
   if (rows <= 0) return 0;
-  if (inter <= 0) return PIH_ERR_BAD_ARGUMENT;
+  if (inter <= 0 || interleave <= 0 || inter % interleave) return PIH_ERR_BAD_ARGUMENT;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (dtype == PIH_F32) return launch_silu<float>(gate_up, out, rows, inter, s);
-  if (dtype == PIH_BF16) return launch_silu<__nv_bfloat16>(gate_up, out, rows, inter, s);
+  if (dtype == PIH_F32) return launch_silu<float>(gate_up, out, rows, inter, interleave, s);
+  if (dtype == PIH_BF16) return launch_silu<__nv_bfloat16>(gate_up, out, rows, inter, interleave, s);
   return PIH_ERR_BAD_ARGUMENT;
 }
 

@@ -1,0 +1,264 @@
+// Products with few rows (decode: 1..16 tokens): out[M,N] = act[M,K] . W[N,K]^T, bound by reading W once.
+//
+// The reference pads every decode step to 4096 rows and calls cuBLASLt for each of q, k, v, o, gate, up and
+// down (plugins/model-qwen3/nvidia_qwen3_bf16_engine.cpp:391-392; src/backend/cuda/gemm_plan.cpp:192-197),
+// with RMSNorm, residual add and SiLU-mul as kernels of their own between them
+// (kernels/cuda/qwen_bf16_primitives.cu:264-324).  Here one kernel streams the weight rows once and does
+// the small work around the product itself:
+//
+//   prologue   optional residual add (h <- round(h + delta), written back once) and RMSNorm of the M rows,
+//              recomputed by every CTA from the 2 KB rows (cheaper than a kernel of its own and a round trip);
+//   product    mma.sync m16n8k16 with the TOKENS as the 16-row operand and 8 weight rows as the 8-column
+//              operand, so a warp needs only 8 weight rows; each thread reads 16 contiguous bytes of a weight
+//              row per 32-wide k block (the k order inside a block is permuted the same way for both operands,
+//              which a dot product does not notice); the eight warps of a CTA take every eighth k block and
+//              their partial sums are added in a fixed order; the kernel is persistent (two CTAs per SM walk
+//              over the weight tiles) so the prologue runs once per CTA and weight loads stay in flight;
+//   epilogue   store, or SwiGLU when the CTA's 16 weight rows are 8 gate rows followed by their 8 up rows:
+//              out = round(silu(round(g)) * round(u))  (rounding places of the separate kernels).
+//
+// A row's result does not depend on the other rows of the batch.
+#include "common.cuh"
+
+namespace pih {
+
+__device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                         uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint4 ldg_nc16(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p));
+  return v;
+}
+
+constexpr int SK_WARPS = 8;
+constexpr int SK_THREADS = SK_WARPS * 32;
+constexpr int SK_UN = 4;                 // k blocks (of 32) whose weight loads a warp keeps in flight
+
+// MR: rows of the token operand kept in shared memory (8 or 16).  TILES: 8-row weight tiles per warp (1 or 2).
+// Persistent: a CTA prepares the token rows once and then walks over weight tiles blockIdx.x, + gridDim.x, ...
+template <int MR, int TILES, bool NORM, bool SWIGLU, typename NW>
+__global__ void __launch_bounds__(SK_THREADS)
+skinny_gemm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ delta,
+                   __nv_bfloat16* __restrict__ x_out, const NW* __restrict__ norm_w, float eps,
+                   const __nv_bfloat16* __restrict__ W, __nv_bfloat16* __restrict__ out, int M, int N, int K,
+                   long long ldx, long long ldw, long long ldo) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  const int LDS = K + 8;                                   // padded row: 16-byte loads of 8 rows hit 8 bank groups
+  __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(smem_raw);         // [MR][LDS]
+  float* red = reinterpret_cast<float*>(xs + MR * LDS);                   // [SK_WARPS][TILES][16 * 8]
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int gid = lane >> 2, q = lane & 3;
+  const int kblocks = K / 32;
+  const int ntiles = (N + 8 * TILES - 1) / (8 * TILES);
+
+  uint4 wv[SK_UN][TILES];
+  auto issue = [&](int tile, int first_block) {            // weight loads of k blocks first_block, + WARPS, ...
+#pragma unroll
+    for (int t = 0; t < TILES; ++t) {
+      const int row = min(tile * 8 * TILES + t * 8 + gid, N - 1);
+      const __nv_bfloat16* wrow = W + static_cast<long long>(row) * ldw + 8 * q;
+#pragma unroll
+      for (int u = 0; u < SK_UN; ++u) {
+        const int b = first_block + SK_WARPS * u;
+        wv[u][t] = (b < kblocks) ? ldg_nc16(wrow + b * 32) : make_uint4(0, 0, 0, 0);
+      }
+    }
+  };
+  int tile = blockIdx.x;
+  // the weight stream does not wait for the prologue: the first loads are in flight now
+  issue(tile, warp);
+
+  // prologue, once per CTA: token rows into shared memory, residual add, norm
+  const int chunks = K / 8;
+  for (int c = threadIdx.x; c < MR * chunks; c += SK_THREADS) {
+    const int row = c / chunks, ch = c % chunks;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (row < M) {
+      v = *reinterpret_cast<const uint4*>(x + row * ldx + ch * 8);
+      if (delta != nullptr) {
+        const uint4 d = *reinterpret_cast<const uint4*>(delta + row * ldx + ch * 8);
+        __nv_bfloat16* ve = reinterpret_cast<__nv_bfloat16*>(&v);
+        const __nv_bfloat16* de = reinterpret_cast<const __nv_bfloat16*>(&d);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) ve[j] = __float2bfloat16_rn(__bfloat162float(ve[j]) + __bfloat162float(de[j]));
+        // the sum goes to a buffer of its own: other CTAs are still reading x
+        if (blockIdx.x == 0) *reinterpret_cast<uint4*>(x_out + row * ldx + ch * 8) = v;
+      }
+    }
+    *reinterpret_cast<uint4*>(xs + row * LDS + ch * 8) = v;
+  }
+  __syncthreads();
+  if (NORM) {
+    for (int row = warp; row < M; row += SK_WARPS) {
+      float ss = 0.0f;
+      for (int c = lane; c < chunks; c += 32) {
+        const uint4 v = *reinterpret_cast<const uint4*>(xs + row * LDS + c * 8);
+        const __nv_bfloat16* ve = reinterpret_cast<const __nv_bfloat16*>(&v);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const float f = __bfloat162float(ve[j]);
+          ss += f * f;
+        }
+      }
+      ss = warp_sum(ss);
+      const float scale = 1.0f / sqrtf(ss / static_cast<float>(K) + eps);
+      for (int c = lane; c < chunks; c += 32) {
+        uint4 v = *reinterpret_cast<const uint4*>(xs + row * LDS + c * 8);
+        __nv_bfloat16* ve = reinterpret_cast<__nv_bfloat16*>(&v);
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          ve[j] = __float2bfloat16_rn((__bfloat162float(ve[j]) * scale) * to_float<NW>(norm_w[c * 8 + j]));
+        *reinterpret_cast<uint4*>(xs + row * LDS + c * 8) = v;
+      }
+    }
+    __syncthreads();
+  }
+
+  const __nv_bfloat16* xa = xs + gid * LDS + 8 * q;                       // tokens gid (and gid + 8 when MR = 16)
+  for (; tile < ntiles; tile += gridDim.x) {
+    const int n0 = tile * 8 * TILES;
+    float acc[TILES][4];
+#pragma unroll
+    for (int t = 0; t < TILES; ++t) acc[t][0] = acc[t][1] = acc[t][2] = acc[t][3] = 0.0f;
+    for (int kb = warp; kb < kblocks; kb += SK_WARPS * SK_UN) {
+      uint4 cur[SK_UN][TILES];
+#pragma unroll
+      for (int u = 0; u < SK_UN; ++u)
+#pragma unroll
+        for (int t = 0; t < TILES; ++t) cur[u][t] = wv[u][t];
+      // the next batch of weight loads — of this tile, or the first of the CTA's next tile — before this one is used
+      const int nb = kb + SK_WARPS * SK_UN;
+      if (nb < kblocks) issue(tile, nb);
+      else if (tile + gridDim.x < ntiles) issue(tile + gridDim.x, warp);
+#pragma unroll
+      for (int u = 0; u < SK_UN; ++u) {
+        const int b = kb + SK_WARPS * u;
+        if (b >= kblocks) break;
+        const uint4 xlo = *reinterpret_cast<const uint4*>(xa + b * 32);
+        uint4 xhi = make_uint4(0, 0, 0, 0);
+        if (MR == 16) xhi = *reinterpret_cast<const uint4*>(xa + 8 * LDS + b * 32);
+#pragma unroll
+        for (int t = 0; t < TILES; ++t) {
+          mma16816(acc[t], xlo.x, xhi.x, xlo.y, xhi.y, cur[u][t].x, cur[u][t].y);
+          mma16816(acc[t], xlo.z, xhi.z, xlo.w, xhi.w, cur[u][t].z, cur[u][t].w);
+        }
+      }
+    }
+    // the warps' partial sums, added in warp order
+#pragma unroll
+    for (int t = 0; t < TILES; ++t) {
+      float* r = red + (warp * TILES + t) * 128;
+      r[gid * 8 + q * 2] = acc[t][0];
+      r[gid * 8 + q * 2 + 1] = acc[t][1];
+      r[(gid + 8) * 8 + q * 2] = acc[t][2];
+      r[(gid + 8) * 8 + q * 2 + 1] = acc[t][3];
+    }
+    __syncthreads();
+    if (SWIGLU) {
+      // tile 0: 8 gate rows, tile 1: their 8 up rows -> 8 output columns
+      const int tok = threadIdx.x >> 3, col = threadIdx.x & 7;
+      if (threadIdx.x < 128 && tok < M && n0 / 2 + col < N / 2) {
+        float g = 0.0f, u = 0.0f;
+#pragma unroll
+        for (int w = 0; w < SK_WARPS; ++w) {
+          g += red[(w * TILES + 0) * 128 + tok * 8 + col];
+          u += red[(w * TILES + (TILES - 1)) * 128 + tok * 8 + col];
+        }
+        g = __bfloat162float(__float2bfloat16_rn(g));
+        u = __bfloat162float(__float2bfloat16_rn(u));
+        out[tok * ldo + n0 / 2 + col] = __float2bfloat16_rn((g / (1.0f + expf(-g))) * u);
+      }
+    } else {
+      for (int e = threadIdx.x; e < TILES * 128; e += SK_THREADS) {
+        const int t = e >> 7, tok = (e & 127) >> 3, col = e & 7;
+        if (tok < M && n0 + t * 8 + col < N) {
+          float s = 0.0f;
+#pragma unroll
+          for (int w = 0; w < SK_WARPS; ++w) s += red[(w * TILES + t) * 128 + tok * 8 + col];
+          out[tok * ldo + n0 + t * 8 + col] = __float2bfloat16_rn(s);
+        }
+      }
+    }
+    __syncthreads();                                       // red is reused by the next tile
+  }
+}
+
+template <int MR, int TILES, bool NORM, bool SWIGLU, typename NW>
+static int launch_skinny(const void* x, const void* delta, void* x_out, const void* norm_w, float eps, const void* W,
+                         void* out, int M, int N, int K, long long ldx, long long ldw, long long ldo,
+                         cudaStream_t s) {
+  const int smem = MR * (K + 8) * 2 + SK_WARPS * TILES * 128 * 4;
+  static int smem_set = 0;                                 // per instance
+  if (smem > 227 * 1024) return PIH_ERR_UNSUPPORTED;
+  if (smem > 48 * 1024 && smem_set < smem) {
+    cudaError_t e = cudaFuncSetAttribute(skinny_gemm_kernel<MR, TILES, NORM, SWIGLU, NW>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    smem_set = smem;
+  }
+  static int sms = 0;
+  if (sms == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (sms <= 0) sms = 148;
+  }
+  const int ntiles = (N + 8 * TILES - 1) / (8 * TILES);
+  const int grid = ntiles < 2 * sms ? ntiles : 2 * sms;
+  skinny_gemm_kernel<MR, TILES, NORM, SWIGLU, NW><<<grid, SK_THREADS, smem, s>>>(
+      static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(delta),
+      static_cast<__nv_bfloat16*>(x_out), static_cast<const NW*>(norm_w), eps,
+      static_cast<const __nv_bfloat16*>(W), static_cast<__nv_bfloat16*>(out), M, N, K, ldx, ldw, ldo);
+  PIH_LAUNCH_CHECK();
+  return 0;
+}
+
+template <int MR, bool NORM, typename NW>
+static int dispatch_skinny(int tiles, bool swiglu, const void* x, const void* delta, void* x_out, const void* norm_w,
+                           float eps, const void* W, void* out, int M, int N, int K, long long ldx, long long ldw,
+                           long long ldo, cudaStream_t s) {
+  if (swiglu)
+    return launch_skinny<MR, 2, NORM, true, NW>(x, delta, x_out, norm_w, eps, W, out, M, N, K, ldx, ldw, ldo, s);
+  if (tiles == 2)
+    return launch_skinny<MR, 2, NORM, false, NW>(x, delta, x_out, norm_w, eps, W, out, M, N, K, ldx, ldw, ldo, s);
+  return launch_skinny<MR, 1, NORM, false, NW>(x, delta, x_out, norm_w, eps, W, out, M, N, K, ldx, ldw, ldo, s);
+}
+
+}  // namespace pih
+
+using namespace pih;
+
+// bf16 only.  M <= 16 rows; K a multiple of 32; x rows, W rows and out rows 16-byte aligned.
+//   delta      nullable: the rows are round(x + delta), as the fused add of a pre-norm block; the sums are also
+//              written to x_out (a buffer other than x: CTAs read x while one of them writes)
+//   norm_w     nullable: RMSNorm (weight dtype norm_dtype, eps) of the rows before the product
+//   swiglu     W rows come in blocks of 16 = 8 gate rows + their 8 up rows; out is [M, N / 2]
+// Returns PIH_ERR_UNSUPPORTED for shapes it does not take (the caller uses the separate kernels).
+extern "C" int pih_gemm_skinny(const void* x, const void* delta, void* x_out, int norm_dtype, const void* norm_w,
+                               float eps, const void* W, void* out, int M, int N, int K, long long ldx,
+                               long long ldw, long long ldo, int swiglu, void* stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if (M > 16 || K <= 0 || K % 32 || ldx % 8 || ldw % 8 || (swiglu && N % 16) ||
+      (reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(W) & 15) ||
+      (delta != nullptr && ((reinterpret_cast<uintptr_t>(delta) & 15) || x_out == nullptr || x_out == x)))
+    return PIH_ERR_UNSUPPORTED;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  // 16 weight rows per tile when that still gives every SM a tile, else 8
+  const int tiles = (swiglu || N >= 148 * 16) ? 2 : 1;
+  const bool sw = swiglu != 0;
+#define PIH_SKINNY(MR, NORM, NW) \
+  dispatch_skinny<MR, NORM, NW>(tiles, sw, x, delta, x_out, norm_w, eps, W, out, M, N, K, ldx, ldw, ldo, s)
+  if (norm_w == nullptr) return M <= 8 ? PIH_SKINNY(8, false, float) : PIH_SKINNY(16, false, float);
+  if (norm_dtype == PIH_F32) return M <= 8 ? PIH_SKINNY(8, true, float) : PIH_SKINNY(16, true, float);
+  if (norm_dtype == PIH_BF16) return M <= 8 ? PIH_SKINNY(8, true, __nv_bfloat16) : PIH_SKINNY(16, true, __nv_bfloat16);
+#undef PIH_SKINNY
+  return PIH_ERR_BAD_ARGUMENT;
+}

@@ -63,6 +63,7 @@ class CudaOps:
         self.attention_split = 0           # keys per split of the decode attention kernel; 0: chosen per call
         self.tensor_core_attention = True  # False: bf16 attention runs on the generic kernel too
         self.tcgen05_min_rows = None       # bf16 products with at least this many rows use the pack's tcgen05 kernel
+        self.skinny_max_rows = 16          # bf16 products with at most this many rows use the fused few-rows kernel
         self._declare()
 
     # -- plumbing ---------------------------------------------------------------
@@ -71,7 +72,7 @@ class CudaOps:
         for name in ("pih_embedding", "pih_rmsnorm", "pih_qk_norm_rope_kv_write", "pih_silu_mul",
                      "pih_gather_rows", "pih_gemm_simt", "pih_paged_attention_generic", "pih_argmax",
                      "pih_sample", "pih_paged_attention_mma", "pih_gemm_tcgen05", "pih_make_kv_tensor_map",
-                     "pih_attention_prefill_tcgen05"):
+                     "pih_attention_prefill_tcgen05", "pih_gemm_skinny"):
             getattr(lib, name).restype = c_int
         lib.pih_attention_scratch_floats.restype = c_ll
 
@@ -131,6 +132,10 @@ class CudaOps:
                                         c_ll(w.stride(0)), c_ll(N), self._stream())
             self._check(rc, "gemm_simt")
             return out
+        if out_dtype == torch.bfloat16 and M <= self.skinny_max_rows:
+            out = self.linear_skinny(x, w)
+            if out is not None:
+                return out
         if self.tcgen05_min_rows is not None and M >= self.tcgen05_min_rows:
             out = self.linear_tcgen05(x, w, out_dtype)
             if out is not None:
@@ -138,6 +143,48 @@ class CudaOps:
         if out_dtype == torch.float32:
             return torch.mm(x, w.t(), out_dtype=torch.float32)
         return torch.mm(x, w.t())
+
+    def linear_skinny(self, x: torch.Tensor, w: torch.Tensor, *, delta=None, norm_weight=None, eps: float = 0.0,
+                      swiglu: bool = False):
+        """The few-rows product (bf16, at most 16 rows) with its optional fused residual add, RMSNorm and
+        SwiGLU.  Returns ``out`` — or ``(x + delta, out)`` when ``delta`` is given — or None when the kernel
+        does not take the shape."""
+        M, K = x.shape
+        N = w.shape[0]
+        if (x.dtype != torch.bfloat16 or M > 16 or K % 32 or K > 16384 or x.stride(1) != 1 or w.stride(1) != 1
+                or (swiglu and N % 16)):
+            return None
+        out = torch.empty(M, N // 2 if swiglu else N, dtype=torch.bfloat16, device=x.device)
+        x_out = torch.empty_like(x) if delta is not None else None
+        nd = _DT[norm_weight.dtype] if norm_weight is not None else 0
+        rc = self.lib.pih_gemm_skinny(_ptr(x), _ptr(delta), _ptr(x_out), nd, _ptr(norm_weight), c_float(eps), _ptr(w),
+                                      _ptr(out), M, N, K, c_ll(x.stride(0)), c_ll(w.stride(0)), c_ll(out.stride(0)),
+                                      1 if swiglu else 0, self._stream())
+        if rc == -2:
+            return None
+        self._check(rc, "gemm_skinny")
+        return out if delta is None else (x_out, out)
+
+    def norm_linear(self, h: torch.Tensor, delta: Optional[torch.Tensor], norm_weight: torch.Tensor, eps: float,
+                    w: torch.Tensor, swiglu_interleave: int = 0):
+        """``h' = h + delta`` (when delta is given), ``out = rmsnorm(h') . w^T`` and, with
+        ``swiglu_interleave``, SiLU-mul over gate/up column blocks of that size.  Returns ``(h', out)``;
+        ``h'`` may be ``h`` updated in place or a new tensor.  One kernel for few rows, else the separate ones."""
+        if h.dtype == torch.bfloat16 and h.shape[0] <= self.skinny_max_rows and swiglu_interleave in (0, 8):
+            if delta is not None:
+                res = self.linear_skinny(h, w, delta=delta, norm_weight=norm_weight, eps=eps,
+                                         swiglu=swiglu_interleave == 8)
+                if res is not None:
+                    return res
+            else:
+                out = self.linear_skinny(h, w, norm_weight=norm_weight, eps=eps, swiglu=swiglu_interleave == 8)
+                if out is not None:
+                    return h, out
+        xn = self.rmsnorm(h, norm_weight, eps, delta=delta)
+        out = self.linear(xn, w)
+        if swiglu_interleave:
+            out = self.silu_mul(out, swiglu_interleave)
+        return h, out
 
     def linear_tcgen05(self, x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
                        tile_n: int = 0):
@@ -291,11 +338,14 @@ class CudaOps:
         self._check(rc, "paged_attention_generic")
         return out
 
-    def silu_mul(self, gate_up: torch.Tensor) -> torch.Tensor:
+    def silu_mul(self, gate_up: torch.Tensor, interleave: Optional[int] = None) -> torch.Tensor:
+        """``silu(g) * u``; the columns of ``gate_up`` come in blocks of ``interleave`` gate columns
+        followed by their up columns (default: all gates, then all ups)."""
         rows, two_i = gate_up.shape
         inter = two_i // 2
         out = torch.empty(rows, inter, dtype=gate_up.dtype, device=gate_up.device)
-        rc = self.lib.pih_silu_mul(_DT[gate_up.dtype], _ptr(gate_up), _ptr(out), c_ll(rows), inter, self._stream())
+        rc = self.lib.pih_silu_mul(_DT[gate_up.dtype], _ptr(gate_up), _ptr(out), c_ll(rows), inter,
+                                   interleave or inter, self._stream())
         self._check(rc, "silu_mul")
         return out
 

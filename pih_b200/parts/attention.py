@@ -65,6 +65,18 @@ class PagedAttention:
             qkv = ops.linear(x, self.w_qkv)                 # [T, q_size + 2 kv_size]
         else:
             qkv = ops.linear(x, self.w_qkv[:s.q_size])      # another entry's cache: only q is needed
+        return self._attend(qkv, step, cache)
+
+    def forward_prenorm(self, h, delta, norm, step, cache):
+        """``h' = h + delta; y = mixer(norm(h'))`` with the add and the norm fused into the q/k/v product
+        where the kernels can; returns ``(h', y)``."""
+        s, ops = self.spec, self.rt.ops
+        w = self.w_qkv if cache.writable else self.w_qkv[:s.q_size]
+        h, qkv = ops.norm_linear(h, delta, norm.weight, norm.spec.eps, w)
+        return h, self._attend(qkv, step, cache)
+
+    def _attend(self, qkv, step, cache):
+        s, ops = self.spec, self.rt.ops
         table = self.position.rotation_table() if self.position is not None else None
         rotary = self.position.rotary_dim if self.position is not None else 0
         ops.qk_norm_rope_kv_write(

@@ -45,7 +45,12 @@ class PreNormBlock:
         self.ffn = ffn_cls(spec.ffn, _sub(weights, ffn_cls.expected_tensors(spec.ffn)), rt)
 
     def forward(self, h, delta, step, cache):
-        xn = self.norm_in.add_forward(h, delta)
-        a = self.mixer.forward(xn, step, cache)
-        xn = self.norm_post.add_forward(h, a)
-        return h, self.ffn.forward(xn)
+        # a part that can take "add, norm, then me" as one call gets it (fewer kernels for few rows);
+        # any other part gets the normed rows
+        if getattr(self.norm_in, "fusable", False) and hasattr(self.mixer, "forward_prenorm"):
+            h, a = self.mixer.forward_prenorm(h, delta, self.norm_in, step, cache)
+        else:
+            a = self.mixer.forward(self.norm_in.add_forward(h, delta), step, cache)
+        if getattr(self.norm_post, "fusable", False) and hasattr(self.ffn, "forward_prenorm"):
+            return self.ffn.forward_prenorm(h, a, self.norm_post)
+        return h, self.ffn.forward(self.norm_post.add_forward(h, a))

@@ -17,6 +17,8 @@ from ._bind import bind_vector
 
 @register_norm("rmsnorm")
 class RMSNorm:
+    fusable = True        # (weight, spec.eps) may be handed to an op that fuses this norm into a product
+
     @classmethod
     def expected_tensors(cls, spec):
         return {"weight": TensorInfo((spec.width,), "one_plus_normal")}

@@ -4,8 +4,9 @@ Reference order and rounding (plugins/model-qwen3/qwen3_bf16_execution_schedule.
 kernels/cuda/qwen_bf16_primitives.cu:274-283): gate and up products are
 rounded to the stream's dtype, ``(g / (1 + exp(-g))) * u`` is computed in
 32-bit and rounded once, then the down product.  The reference runs gate and
-up as two library products; here their weights are stacked ``[gate; up]`` so
-that one product reads the activations once.
+up as two library products; here their weights are stacked (in blocks of 8
+gate rows and their 8 up rows) so that one product reads the activations
+once and can apply SiLU-mul in its epilogue.
 """
 from __future__ import annotations
 
@@ -30,11 +31,25 @@ class SwiGLU:
         self.spec = spec
         self.rt = rt
         n = spec.names
-        self.w_gate_up = bind_matrix(torch.cat([weights[n["gate"]], weights[n["up"]]], dim=0), rt)
+        gate, up = weights[n["gate"]], weights[n["up"]]
+        # rows in blocks of 8 gate rows followed by their 8 up rows, so that a 16-row tile of the product
+        # holds both halves of 8 outputs (the fused few-rows kernel applies SiLU-mul in its epilogue)
+        self.interleave = 8 if spec.intermediate % 8 == 0 else spec.intermediate
+        il = self.interleave
+        stacked = torch.stack([gate.reshape(-1, il, spec.hidden), up.reshape(-1, il, spec.hidden)], dim=1)
+        self.w_gate_up = bind_matrix(stacked.reshape(2 * spec.intermediate, spec.hidden), rt)
         self.w_down = bind_matrix(weights[n["down"]], rt)
 
     def forward(self, x):
         ops = self.rt.ops
         gate_up = ops.linear(x, self.w_gate_up)
-        act = ops.silu_mul(gate_up)
+        act = ops.silu_mul(gate_up, self.interleave)
         return ops.linear(act, self.w_down)
+
+    def forward_prenorm(self, h, delta, norm):
+        """``h' = h + delta; y = ffn(norm(h'))`` with the add, the norm and SiLU-mul fused into the
+        gate-up product where the kernels can; returns ``(h', y)``."""
+        ops = self.rt.ops
+        h, act = ops.norm_linear(h, delta, norm.weight, norm.spec.eps, self.w_gate_up,
+                                 swiglu_interleave=self.interleave)
+        return h, ops.linear(act, self.w_down)

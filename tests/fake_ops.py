@@ -87,10 +87,19 @@ class FakeOps:
                 out[t, h] = torch.softmax(s, dim=0) @ V[:, h // group, :]
         return out.reshape(T, heads * D).to(qkv.dtype)
 
-    def silu_mul(self, gate_up):
+    def silu_mul(self, gate_up, interleave=None):
         inter = gate_up.shape[1] // 2
-        g, u = gate_up[:, :inter].float(), gate_up[:, inter:].float()
+        il = interleave or inter
+        blocks = gate_up.reshape(gate_up.shape[0], inter // il, 2, il).float()
+        g, u = blocks[:, :, 0, :].reshape(-1, inter), blocks[:, :, 1, :].reshape(-1, inter)
         return ((g / (1.0 + torch.exp(-g))) * u).to(gate_up.dtype)
+
+    def norm_linear(self, h, delta, norm_weight, eps, w, swiglu_interleave=0):
+        xn = self.rmsnorm(h, norm_weight, eps, delta=delta)
+        out = self.linear(xn, w)
+        if swiglu_interleave:
+            out = self.silu_mul(out, swiglu_interleave)
+        return h, out
 
     def argmax(self, logits):
         return torch.argmax(logits, dim=-1).to(torch.int32)

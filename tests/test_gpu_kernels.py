@@ -128,6 +128,66 @@ def test_linear_tcgen05_takes_strided_rows_and_refuses_what_tma_cannot_describe(
     assert ops.linear_tcgen05(_rand((4, 20), torch.bfloat16, 7), _rand((8, 20), torch.bfloat16, 8)) is None
 
 
+@pytest.mark.parametrize("M", [1, 3, 8, 9, 16])
+@pytest.mark.parametrize("N,K", [(8, 32), (24, 64), (4096, 1024), (1024, 3072), (1000, 96), (6144, 1024)])
+def test_linear_skinny(ops, M, N, K):
+    """The few-rows product alone: every row count up to 16, widths that are no multiple of the tile."""
+    x = _rand((M, K), torch.bfloat16, 3)
+    w = _rand((N, K), torch.bfloat16, 4, 0.1)
+    out = ops.linear_skinny(x, w)
+    assert out is not None and out.shape == (M, N)
+    ref = x.cpu().double() @ w.cpu().double().T
+    torch.testing.assert_close(out.cpu().double(), ref, rtol=8e-3, atol=1e-3 * max(1.0, float(ref.abs().max()) / 4))
+    # a row alone gives the same bits as among others
+    assert torch.equal(ops.linear_skinny(x[M - 1:].contiguous(), w)[0], out[M - 1])
+
+
+@pytest.mark.parametrize("M", [1, 8, 13])
+@pytest.mark.parametrize("norm_dtype", [torch.bfloat16, torch.float32])
+def test_linear_skinny_fused_add_norm_and_swiglu(ops, M, norm_dtype):
+    """h' = h + delta, norm, product, SiLU-mul in one kernel, against the separate roundings of the plain parts."""
+    K, inter = 1024, 3072
+    h = _rand((M, K), torch.bfloat16, 5, 2.0)
+    d = _rand((M, K), torch.bfloat16, 6)
+    nw = (1 + 0.1 * torch.randn(K)).to(norm_dtype).to(DEV)
+    gate = _rand((inter, K), torch.bfloat16, 7, 0.05)
+    up = _rand((inter, K), torch.bfloat16, 8, 0.05)
+    w = torch.stack([gate.reshape(-1, 8, K), up.reshape(-1, 8, K)], dim=1).reshape(2 * inter, K).contiguous()
+    eps = 1e-6
+    # plain: every op rounds once
+    hs = plain_impl.residual_add(h.cpu(), d.cpu(), "bf16")
+    xn = plain_impl.rms_norm(hs, nw.cpu().double(), eps, "bf16")
+    g_ref, u_ref = plain_impl.linear(xn, gate.cpu(), "bf16"), plain_impl.linear(xn, up.cpu(), "bf16")
+    act_ref = plain_impl.silu_mul(g_ref, u_ref, "bf16")
+    # fused add + norm + product
+    h2, qkv = ops.linear_skinny(h, w, delta=d, norm_weight=nw, eps=eps)
+    assert torch.equal(h2.cpu().double(), hs) and torch.equal(h, _rand((M, K), torch.bfloat16, 5, 2.0))   # h untouched
+    gu_ref = torch.stack([g_ref.reshape(M, -1, 8), u_ref.reshape(M, -1, 8)], dim=2).reshape(M, 2 * inter)
+    tol = dict(rtol=1.6e-2, atol=4e-3)          # two roundings upstream of the product may flip
+    torch.testing.assert_close(qkv.cpu().double(), gu_ref, **tol)
+    # ... and with SiLU-mul in the epilogue
+    h3, act = ops.linear_skinny(h, w, delta=d, norm_weight=nw, eps=eps, swiglu=True)
+    assert torch.equal(h3, h2) and act.shape == (M, inter)
+    torch.testing.assert_close(act.cpu().double(), act_ref, **tol)
+    # the unfused path of the same op agrees
+    ops.skinny_max_rows = 0
+    try:
+        h4 = h.clone()
+        h4b, act2 = ops.norm_linear(h4, d, nw, eps, w, swiglu_interleave=8)
+    finally:
+        ops.skinny_max_rows = 16
+    assert torch.equal(h4b, h2)
+    torch.testing.assert_close(act2.float(), act.float(), **tol)
+
+
+def test_silu_mul_interleaved(ops):
+    for dtype in DTYPES:
+        gu = _rand((5, 2 * 48), dtype, 9, 2.0)
+        blocks = gu.reshape(5, 6, 2, 8)
+        ref = plain_impl.silu_mul(blocks[:, :, 0, :].reshape(5, 48).cpu(), blocks[:, :, 1, :].reshape(5, 48).cpu())
+        torch.testing.assert_close(ops.silu_mul(gu, 8).cpu().double(), ref, **_tol(dtype))
+
+
 def test_linear_fp32_rows_do_not_depend_on_the_batch(ops):
     """The 32-bit product gives a row the same bits alone and among others."""
     x = _rand((77, 300), torch.float32, 5)
