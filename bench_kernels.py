@@ -52,7 +52,7 @@ def step_of(lens, new, dev):
     starts = [l - n for l, n in zip(lens, new)]
     i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)
     return SimpleNamespace(num_requests=len(lens), cu_q=i32(cu), q_start=i32(starts), host_cu_q=cu,
-                           host_q_start=starts, attention_plans={},
+                           host_q_start=starts, attention_plans={}, meta=i32([max(lens), sum(new), len(lens), 0]),
                            request_of_row=i32([r for r, n in enumerate(new) for _ in range(n)]),
                            positions=i32([starts[r] + i for r, n in enumerate(new) for i in range(n)]))
 

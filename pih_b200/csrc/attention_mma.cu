@@ -52,8 +52,9 @@ struct AttnParams {
   int heads, kv_heads, page_size, num_pages;
   float scale;
   int window;                          // 0: none
-  int split;                           // keys per split (split kernel)
-  int max_splits;
+  int split;                           // keys per split (split kernel); 0: derived on the device, see split_of
+  const int* max_ctx_ptr;              // device word: the longest context of this step (used when split == 0)
+  int max_splits;                      // grid.x of the split kernel = splits per request at most
   int dec_tok_cap;                     // most rows of one decode-like request
   float* part_o;                       // [R, dec_tok_cap, heads, max_splits, D]
   float* part_ml;                      // [R, dec_tok_cap, heads, max_splits, 2]
@@ -93,6 +94,16 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], 
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// Keys per split.  Either fixed by the host, or the context of the step cut into max_splits equal parts
+// (rounded up to whole tiles): then the grid depends on the batch size alone and the cut follows the
+// context as it grows, which a captured CUDA graph needs.
+__device__ __forceinline__ int split_of(const AttnParams& p) {
+  if (p.split > 0) return p.split;
+  const int ctx = max(*p.max_ctx_ptr, 1);
+  const int per = (ctx + p.max_splits - 1) / p.max_splits;
+  return max(BN, (per + BN - 1) / BN * BN);
 }
 
 // Gather one tile of BN keys (K and V of kv head g) starting at key j0 into shared memory.
@@ -491,10 +502,11 @@ attn_split_kernel(const AttnParams p) {
   // keys that any row of the request sees, and the splits that hold them
   const int req_kmin = p.window > 0 ? max(0, start - p.window + 1) : 0;
   const int req_kmax = start + n_tok - 1;
-  const int s_lo = req_kmin / p.split, s_hi = req_kmax / p.split;
+  const int split = split_of(p);
+  const int s_lo = req_kmin / split, s_hi = req_kmax / split;
   if (sp < s_lo || sp > s_hi) return;
-  const int kmin = max(req_kmin, sp * p.split);
-  const int kmax = min(req_kmax, (sp + 1) * p.split - 1);
+  const int kmin = max(req_kmin, sp * split);
+  const int kmax = min(req_kmax, (sp + 1) * split - 1);
   const int* table = p.block_table + static_cast<size_t>(r) * p.table_width;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
@@ -579,10 +591,11 @@ attn_split_tma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap kv
   const int start = p.q_start[r];
   const int req_kmin = p.window > 0 ? max(0, start - p.window + 1) : 0;
   const int req_kmax = start + n_tok - 1;
-  const int s_lo = req_kmin / p.split, s_hi = req_kmax / p.split;
+  const int split = split_of(p);
+  const int s_lo = req_kmin / split, s_hi = req_kmax / split;
   if (sp < s_lo || sp > s_hi) return;
-  const int kmin = max(req_kmin, sp * p.split);
-  const int kmax = min(req_kmax, (sp + 1) * p.split - 1);
+  const int kmin = max(req_kmin, sp * split);
+  const int kmax = min(req_kmax, (sp + 1) * split - 1);
   const int* table = p.block_table + static_cast<size_t>(r) * p.table_width;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int t_first = kmin / BN, t_last = kmax / BN;
@@ -786,6 +799,8 @@ extern "C" int pih_make_kv_tensor_map(void* out, const void* cache, long long nu
 //   tile_max_q   the most rows of a request that is NOT decode-like (0: there is none)
 //   dec_tok_cap  the most rows of a decode-like request (0: there is none)
 //   dec_max_ctx  the longest context (after the step) of a decode-like request
+//   split        keys per split; or 0 with max_splits > 0 and max_ctx_ptr a device word holding the step's longest
+//                context: each request is then cut into max_splits parts of that context
 // scratch holds pih_attention_scratch_floats(num_requests, dec_tok_cap, heads, kv_heads, head_dim,
 // ceil(dec_max_ctx / split)) words, the leading ticket words zero.  Launches that share the scratch
 // must not overlap on the device.  Returns PIH_ERR_UNSUPPORTED for a head_dim that has no
@@ -795,10 +810,12 @@ extern "C" int pih_paged_attention_mma(const void* q, int q_stride, void* out, c
                                        const int* q_start, int rows, int num_requests, int tile_max_q,
                                        int dec_tok_cap, int dec_max_ctx, int heads, int kv_heads, int head_dim,
                                        int page_size, int num_pages, float scale, int window, int split,
-                                       float* scratch, const void* kv_tensor_map, uint32_t* error, void* stream) {
+                                       int max_splits, const int* max_ctx_ptr, float* scratch,
+                                       const void* kv_tensor_map, uint32_t* error, void* stream) {
   if (rows <= 0) return 0;
   if (heads <= 0 || kv_heads <= 0 || heads % kv_heads || page_size <= 0 || table_width <= 0 || window < 0 ||
-      split <= 0 || split % BN || num_requests <= 0 || num_requests > 65535 ||
+      split < 0 || split % BN || (split == 0 && dec_tok_cap > 0 && (max_splits <= 0 || max_ctx_ptr == nullptr)) ||
+      num_requests <= 0 || num_requests > 65535 ||
       kv_heads > 65535 || q_stride % 8 || tile_max_q < 0 || dec_tok_cap < 0 ||
       (dec_tok_cap > 0 && (dec_max_ctx <= 0 || !scratch)))
     return PIH_ERR_BAD_ARGUMENT;
@@ -818,7 +835,8 @@ extern "C" int pih_paged_attention_mma(const void* q, int q_stride, void* out, c
   p.scale = scale;
   p.window = window;
   p.split = split;
-  p.max_splits = dec_tok_cap > 0 ? (dec_max_ctx + split - 1) / split : 0;
+  p.max_ctx_ptr = max_ctx_ptr;
+  p.max_splits = dec_tok_cap == 0 ? 0 : (split > 0 ? (dec_max_ctx + split - 1) / split : max_splits);
   p.dec_tok_cap = dec_tok_cap;
   p.page_shift = -1;
   for (int sft = 0; sft < 20; ++sft)

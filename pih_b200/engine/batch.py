@@ -48,6 +48,7 @@ class StepBatch:
     q_start: torch.Tensor
     ctx_len: torch.Tensor
     state_slots: torch.Tensor
+    meta: torch.Tensor = None              # int32 [4] on the device: (longest context after the step, rows, requests, wanted)
     block_tables: List[torch.Tensor] = field(default_factory=list)
     slot_mappings: List[torch.Tensor] = field(default_factory=list)
     # host copies for planning kernel launches
@@ -133,10 +134,11 @@ class BatchBuilder:
         v[o[5]:o[5] + R] = starts
         v[o[6]:o[6] + R] = [starts[r] + counts[r] for r in range(R)]
         v[o[7]:o[7] + R] = [rc.slot for rc in reqs]
+        v[o[8]:o[8] + 4] = [max(starts[r] + counts[r] for r in range(R)), T, R, S]
         for g in range(G):
-            table = v[o[8 + 2 * g]:o[8 + 2 * g] + R * width].reshape(R, width)
+            table = v[o[9 + 2 * g]:o[9 + 2 * g] + R * width].reshape(R, width)
             cache.fill_block_table(g, rids, table)
-            sm = v[o[9 + 2 * g]:o[9 + 2 * g] + T]
+            sm = v[o[10 + 2 * g]:o[10 + 2 * g] + T]
             for r, rc in enumerate(reqs):
                 pages = rc.pages[g].arr
                 lo, n, st = cu_q[r], counts[r], starts[r]
@@ -172,15 +174,15 @@ class BatchBuilder:
             max_ctx=max(starts[r] + counts[r] for r in range(R)),
             token_ids=part(0, T), positions=part(1, T), request_of_row=part(2, T),
             logit_rows=part(3, S), cu_q=part(4, R + 1), q_start=part(5, R), ctx_len=part(6, R),
-            state_slots=part(7, R), host_cu_q=cu_q, host_q_start=starts)
+            state_slots=part(7, R), meta=part(8, 4), host_cu_q=cu_q, host_q_start=starts)
         for g in range(G):
-            batch.block_tables.append(part(8 + 2 * g, R * width).view(R, width))
-            batch.slot_mappings.append(part(9 + 2 * g, T))
+            batch.block_tables.append(part(9 + 2 * g, R * width).view(R, width))
+            batch.slot_mappings.append(part(10 + 2 * g, T))
         return batch
 
     @staticmethod
     def _sizes(rows: int, requests: int, wanted: int, groups: int, width: int):
-        sizes = [rows, rows, rows, wanted, requests + 1, requests, requests, requests]
+        sizes = [rows, rows, rows, wanted, requests + 1, requests, requests, requests, 4]
         for _ in range(groups):
             sizes += [requests * width, rows]
         return sizes

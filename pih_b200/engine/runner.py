@@ -45,6 +45,7 @@ class ModelRunner:
         self.num_entries = len(model.spec.schedule)
         self.steps_run = 0
         self._graphs = {}
+        self._sightings = {}
         self._graph_pool = None
 
     def prepare(self, entries: Sequence[StepEntry]) -> StepBatch:
@@ -96,43 +97,65 @@ class ModelRunner:
         self.steps_run += 1
         return logits
 
-    # -- decode steps replayed from CUDA graphs ------------------------------------------
-    # A decode step of B requests is ~10 launches per layer; at small B the launches, not the
-    # kernels, bound the step.  Steps in which every request brings one token and wants its logits
-    # are captured once per (B, block-table width bucket) and replayed: the batch arrays live in
-    # a static device buffer whose layout depends on that key alone.
+    # -- steps replayed from CUDA graphs --------------------------------------------------
+    # A step is ~7-10 launches per layer; for few rows the launches, not the kernels, bound it.  The
+    # launch geometry of every kernel depends only on (rows, requests, wanted rows, block-table width,
+    # the attention plan); which request owns which row is data in the step's device buffer.  So a step
+    # can be captured once per such key and replayed with fresh data written into the same buffer:
+    #   * decode steps (every request one token that wants its logits): captured at first sight;
+    #   * a prompt portion of one request with at least GRAPH_MIN_PORTION rows (chunked prefill repeats
+    #     its chunk size): captured when its key is seen the second time.
     GRAPH_WIDTH_STEP = 64           # block-table widths are rounded up to a multiple of this many pages
+    GRAPH_MIN_PORTION = 128
 
     def _graphable(self, entries) -> bool:
-        return (self.cuda_graphs and self.device.type == "cuda" and not self.cache.state_tensors
-                and all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries))
+        return self._graph_key(entries) is not None
 
-    def _graph_step(self, entries) -> torch.Tensor:
+    def _graph_key(self, entries):
+        if not (self.cuda_graphs and self.device.type == "cuda") or self.cache.state_tensors:
+            return None
+        if all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries):
+            return ("decode", len(entries))
+        if len(entries) == 1 and len(entries[0].tokens) >= self.GRAPH_MIN_PORTION:
+            e = entries[0]
+            want = list(e.want)
+            if want in ([], [len(e.tokens) - 1]):
+                return ("portion", len(e.tokens), len(want))
+        return None
+
+    def _graph_step(self, entries) -> Optional[torch.Tensor]:
+        kind = self._graph_key(entries)
         for e in entries:
             if not self.cache.has_request(e.rid):
                 self.cache.add_request(e.rid)
         done = []
         try:
             for e in entries:
-                self.cache.append(e.rid, 1)
+                self.cache.append(e.rid, len(e.tokens))
                 done.append(e.rid)
         except OutOfPages:
             for rid in done:
                 self.cache.rollback(rid)
             raise
-        B = len(entries)
         rids = [e.rid for e in entries]
         step_w = self.GRAPH_WIDTH_STEP
         width = -(-self.cache.table_width(rids) // step_w) * step_w
-        key = (B, width)
+        key = kind + (width,)
         state = self._graphs.get(key)
         try:
-            if state is None:
-                state = self._capture(entries, key)
+            if state is None and kind[0] == "portion" and self._sightings.get(key, 0) == 0:
+                # first sight of this portion shape: run it as it is; capture if it comes again
+                self._sightings[key] = 1
+                batch = self.builder.build(entries, self.cache)
+                logits = self.run(batch)
+            elif state is None:
+                state = self._capture(entries, key, width)
+                logits = state["logits"]
             else:
                 self.builder.build(entries, self.cache, width=width, device_buffer=state["buffer"])
                 state["graph"].replay()
                 self._count_launches(state["launches"])
+                logits = state["logits"]
         except Exception:
             for rid in rids:
                 self.cache.rollback(rid)
@@ -140,23 +163,26 @@ class ModelRunner:
         for rid in rids:
             self.cache.commit(rid)
         self.steps_run += 1
-        return state["logits"]
+        return logits
 
     def _count_launches(self, n: int) -> None:
         ops = self.model.rt.ops
         if hasattr(ops, "launches"):
             ops.launches += n
 
-    def _capture(self, entries, key):
-        B, width = key
+    def _capture(self, entries, key, width):
         G = len(self.cache.groups)
-        buffer = torch.empty(self.builder.buffer_size(B, B, B, G, width), dtype=torch.int32, device=self.device)
+        T = sum(len(e.tokens) for e in entries)
+        B = len(entries)
+        S = sum(len(e.want) for e in entries)
+        buffer = torch.empty(self.builder.buffer_size(T, B, S, G, width), dtype=torch.int32, device=self.device)
         batch = self.builder.build(entries, self.cache, width=width, device_buffer=buffer)
-        # the attention plan of the graph covers every context that fits the table width
         max_ctx = width * self.cache.page_size
-        batch.attention_plans = _FixedPlans((0, 1, max_ctx))
         ops = self.model.rt.ops
-        if hasattr(ops, "reserve_attention_scratch"):
+        if key[0] == "decode":
+            # the attention plan of the graph covers every context that fits the table width
+            batch.attention_plans = _FixedPlans((0, 1, max_ctx))
+        if key[0] == "decode" and hasattr(ops, "reserve_attention_scratch"):
             for block in self.model.blocks:
                 spec = getattr(block.mixer, "spec", None)
                 if spec is not None and hasattr(spec, "heads"):

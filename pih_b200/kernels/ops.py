@@ -60,7 +60,7 @@ class CudaOps:
         self._kv_maps = {}                 # cache tensor (address, shape) -> 128-byte TMA descriptor
         self.tma_attention = True          # False: the split kernel gathers with cp.async instead of TMA
         self.tcgen05_attention = True      # False: prompt portions use the mma.sync tile kernel
-        self.attention_split = 0           # keys per split of the decode attention kernel; 0: chosen per call
+        self.attention_split = 0           # keys per split of the decode attention kernel; 0: from the context, on the device
         self.tensor_core_attention = True  # False: bf16 attention runs on the generic kernel too
         self.tcgen05_min_rows = None       # bf16 products with at least this many rows use the pack's tcgen05 kernel
         self.skinny_max_rows = 16          # bf16 products with at most this many rows use the fused few-rows kernel
@@ -254,23 +254,19 @@ class CudaOps:
                 tile_max_q = max(tile_max_q, n)
         return tile_max_q, dec_cap, dec_ctx
 
-    def split_for(self, num_requests: int, kv_heads: int, max_ctx: int) -> int:
-        """Keys per split: the widest of 128..4096 that still fills three quarters of the 2 x 148 CTA slots, so that
-        small batches are cut finely (enough CTAs to pull bandwidth) and large ones coarsely (less
-        merging).  A function of the step's shape only."""
-        if self.attention_split:
-            return self.attention_split
-        split = 4096
-        while split > 128 and num_requests * kv_heads * -(-max_ctx // split) < 222:
-            split //= 2
-        return split
+    def splits_for(self, num_requests: int, kv_heads: int) -> int:
+        """Splits per request of the decode attention: as many as fill the 2 x 148 CTA slots of the GPU in
+        one wave (small batches are cut finely so that enough CTAs pull bandwidth, large ones not at all).
+        A function of the batch size only; the keys per split follow the context on the device."""
+        return max(1, min(64, (2 * 148) // max(1, num_requests * kv_heads)))
 
     def reserve_attention_scratch(self, num_requests, dec_tok_cap, heads, kv_heads, head_dim, max_ctx) -> None:
         """Make the split kernel's scratch large enough (before a CUDA graph that uses it is
         captured: an allocation cannot happen under capture).  A buffer that is outgrown is kept
         alive, because captured graphs hold its address."""
-        need = self.lib.pih_attention_scratch_floats(num_requests, dec_tok_cap, heads, kv_heads, head_dim,
-                                                     -(-max_ctx // 128))
+        splits = (-(-max_ctx // self.attention_split) if self.attention_split
+                  else self.splits_for(num_requests, kv_heads))
+        need = self.lib.pih_attention_scratch_floats(num_requests, dec_tok_cap, heads, kv_heads, head_dim, splits)
         if self._attn_scratch is None or self._attn_scratch.numel() < need:
             if self._attn_scratch is not None:
                 self._retired_scratch.append(self._attn_scratch)     # captured graphs may still point at it
@@ -301,7 +297,11 @@ class CudaOps:
         tile_max_q, dec_cap, dec_ctx = plan
         out = torch.empty(rows, heads * head_dim, dtype=qkv.dtype, device=qkv.device)
         num_pages, page_size = kv_cache.shape[0], kv_cache.shape[3]
-        split = self.split_for(step.num_requests, kv_heads, max(dec_ctx, 1))
+        split = self.attention_split                       # 0: cut on the device into `nsplits` parts
+        nsplits = self.splits_for(step.num_requests, kv_heads)
+        max_ctx_ptr = getattr(step, "meta", None)
+        if split == 0 and max_ctx_ptr is None:              # a caller without a packed batch: fix the cut here
+            split = max(64, -(-(-(-max(dec_ctx, 1) // nsplits)) // 64) * 64)
         scratch = None
         if dec_cap > 0:
             self.reserve_attention_scratch(step.num_requests, dec_cap, heads, kv_heads, head_dim, dec_ctx)
@@ -320,7 +320,7 @@ class CudaOps:
         rc = self.lib.pih_paged_attention_mma(
             _ptr(qkv), qkv.stride(0), _ptr(out), _ptr(kv_cache), _ptr(block_table), block_table.shape[1],
             _ptr(step.cu_q), _ptr(step.q_start), rows, step.num_requests, tile_max_q, dec_cap, dec_ctx, heads, kv_heads, head_dim, page_size, num_pages,
-            c_float(scale), int(window), split, _ptr(scratch),
+            c_float(scale), int(window), split, nsplits, _ptr(max_ctx_ptr), _ptr(scratch),
             kv_map if (self.tma_attention and dec_cap > 0) else None,
             self._err(), self._stream())
         self._check(rc, "paged_attention_mma")

@@ -340,7 +340,7 @@ def _step_of(lens, new):
     i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
     return SimpleNamespace(num_requests=len(lens), cu_q=i32(cu), q_start=i32(starts), host_cu_q=cu,
                            host_q_start=starts, request_of_row=i32(req_of_row), positions=i32(positions),
-                           attention_plans={})
+                           attention_plans={}, meta=i32([max(lens), sum(new), len(lens), 0]))
 
 
 # the tensor-core kernels round the probabilities to bf16 before the PV product (one more 2^-9
@@ -388,6 +388,21 @@ def test_paged_attention_tensor_core(ops, attention_variant, case):
                                         block_table=s["table"], request_of_row=step.request_of_row,
                                         positions=step.positions, scale=scale, window=window or 0)
     torch.testing.assert_close(out.float(), plain.float(), **MMA_TOL)
+
+
+@pytest.mark.parametrize("split", [64, 128, 512])
+def test_split_attention_with_a_fixed_cut(ops, split):
+    """The keys per split may also be fixed by the host; every cut gives the same attention."""
+    heads, kv_heads, D, page, lens, new = 16, 8, 128, 16, [1000, 77, 2048], [1, 1, 1]
+    s = _paged_setup(torch.bfloat16, lens, new, heads, kv_heads, D, page, seed=15)
+    ops.attention_split = split
+    try:
+        out = ops.paged_attention_mma(s["q"], heads=heads, kv_heads=kv_heads, head_dim=D, kv_cache=s["cache"],
+                                      block_table=s["table"], step=_step_of(lens, new), scale=0.09, window=0)
+    finally:
+        ops.attention_split = 0
+    ops.check_errors()
+    torch.testing.assert_close(out.cpu().double(), _attention_reference(s, lens, new, 0.09, None), **MMA_TOL)
 
 
 def test_tensor_core_attention_reads_q_from_the_fused_projection_buffer(ops):

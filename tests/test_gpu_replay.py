@@ -116,6 +116,38 @@ def test_32bit_and_bf16_cuttings_agree_with_each_other(model_dirs, requests_of, 
             assert diff <= bound, (family, rid, diff)
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_steps_replayed_from_cuda_graphs_match(model_dirs, tiny_configs, dtype):
+    """Prompt portions of a repeated size and decode steps are captured into CUDA graphs and replayed with
+    other requests' data: first sight (as it is), second (capture) and third (replay) all match the plain
+    implementation, also when the replayed request starts deep in its context."""
+    from pih_b200.engine import StepEntry
+    from pih_b200.engine.factory import create_runner
+    name = "A"
+    reqs = traces.make_requests(tiny_configs[name]["vocab_size"], [300, 300, 300, 428], seed=31)
+    _, model, cache, runner = create_runner(model_dirs[name], dtype, page_size=16, max_cache_tokens=1024,
+                                            max_requests=4, cuda_graphs=True)
+    got = {}
+    for rid, toks in reqs.items():
+        lead = len(toks) - 300                     # r3 first brings 128 rows (another shape), then 300 like the others
+        rows = []
+        if lead:
+            rows.append(runner.step([StepEntry(rid, toks[:lead], [lead - 1])]).float().cpu())
+        rows.append(runner.step([StepEntry(rid, toks[lead:lead + 172], [171])]).float().cpu())   # 172 rows, last wanted
+        rows.append(runner.step([StepEntry(rid, toks[lead + 172:], [127])]).float().cpu())       # 128 rows, last wanted
+        got[rid] = torch.cat(rows)
+        runner.finish(rid)
+    model.rt.ops.check_errors()
+    assert any(k[0] == "portion" for k in runner._graphs), "no prompt portion was replayed from a graph"
+    cfg, w = load_plain_weights(model_dirs[name])
+    for rid, toks in reqs.items():
+        lead = len(toks) - 300
+        places = ([lead - 1] if lead else []) + [lead + 171, len(toks) - 1]
+        truth = plain_impl.forward(cfg, w, toks)[places]
+        plain = plain_impl.forward(cfg, w, toks, "bf16")[places] if dtype == "bfloat16" else None
+        compare({rid: got[rid]}, {rid: truth}, dtype, f"graph {rid}", {rid: plain} if plain is not None else None)
+
+
 def _run_trace_run(model_dir, dtype, steps, out_dir, max_tokens, env=None):
     cmd = [sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", model_dir, "--dtype", dtype,
            "--out", out_dir, "--max-tokens", str(max_tokens)]
