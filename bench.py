@@ -279,6 +279,8 @@ def main() -> int:
     ap.add_argument("--skip-e2e", action="store_true")
     ap.add_argument("--skip-points", action="store_true")
     ap.add_argument("--skip-prefill", action="store_true")
+    ap.add_argument("--plain-launches", action="store_true",
+                    help="launch kernels fully serialised instead of with programmatic dependent launch")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm()
@@ -291,6 +293,8 @@ def main() -> int:
     import torch
     hbm_gbs, bf16_tflops, peak_src = peaks()
     config, model = build_model(args.layers)
+    if args.plain_launches:
+        model.rt.ops.set_dependent_launch(False)
     with ClockSampler() as clocks:
         main_run = decode_run(model, args.batch, args.steps, args.warmup)
         clock_summary = clocks.summary()

@@ -77,6 +77,8 @@ def main() -> int:
     ap.add_argument("--impl", default="default", choices=["default", "tcgen05", "skinny", "library"])
     ap.add_argument("--tile-n", type=int, default=0)
     ap.add_argument("--chain", action="store_true", help="linear: many products back to back in a CUDA graph")
+    ap.add_argument("--chain-mb", type=float, default=200.0,
+                    help="linear --chain: total size of the distinct weights (below the L2 size they stay resident)")
     ap.add_argument("--split", type=int, default=0, help="keys per split of the decode attention (0: automatic)")
     ap.add_argument("--no-tma", action="store_true", help="decode attention gathers with cp.async instead of TMA")
     ap.add_argument("--plain", action="store_true", help="the pack's plain (generic / FMA) kernel instead")
@@ -127,7 +129,7 @@ def main() -> int:
         # many products with different weights back to back (together larger than L2) in one timed region:
         # per-launch time as a decode step sees it, launch gaps included, measured inside a CUDA graph
         x = torch.randn(args.m, args.k, device=dev).to(bf)
-        reps = max(4, int(200e6 / (args.n * args.k * 2)) + 1)
+        reps = max(4, int(args.chain_mb * 1e6 / (args.n * args.k * 2)) + 1)
         ws = [torch.randn(args.n, args.k, device=dev).to(bf) for _ in range(reps)]
         call = {"skinny": lambda w: ops.linear_skinny(x, w), "library": lambda w: torch.mm(x, w.t()),
                 "tcgen05": lambda w: ops.linear_tcgen05(x, w, tile_n=args.tile_n)}.get(args.impl, lambda w: ops.linear(x, w))

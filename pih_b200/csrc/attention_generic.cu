@@ -27,6 +27,7 @@ __global__ void paged_attention_generic_kernel(
     const int* __restrict__ block_table, int table_width, const int* __restrict__ request_of_row,
     const int* __restrict__ positions, int rows, int heads, int kv_heads, int head_dim, int page_size,
     int num_pages, float scale, int window, uint32_t* error) {
+  wait_for_prior_kernels();
   extern __shared__ float smem[];
   const int warps_per_block = blockDim.x >> 5;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -124,12 +125,12 @@ extern "C" int pih_paged_attention_generic(int dtype, const void* q, int q_strid
   const unsigned blocks = static_cast<unsigned>((items + warps - 1) / warps);
   const size_t smem = static_cast<size_t>(warps) * head_dim * sizeof(float);
   if (dtype == PIH_F32)
-    paged_attention_generic_kernel<float><<<blocks, warps * 32, smem, s>>>(
+    launch_kernel(paged_attention_generic_kernel<float>, dim3(blocks), dim3(warps * 32), smem, s, 
         static_cast<const float*>(q), q_stride, static_cast<float*>(out),
         static_cast<const float*>(cache), block_table, table_width, request_of_row, positions, rows,
         heads, kv_heads, head_dim, page_size, num_pages, scale, window, error);
   else if (dtype == PIH_BF16)
-    paged_attention_generic_kernel<__nv_bfloat16><<<blocks, warps * 32, smem, s>>>(
+    launch_kernel(paged_attention_generic_kernel<__nv_bfloat16>, dim3(blocks), dim3(warps * 32), smem, s, 
         static_cast<const __nv_bfloat16*>(q), q_stride, static_cast<__nv_bfloat16*>(out),
         static_cast<const __nv_bfloat16*>(cache), block_table, table_width, request_of_row, positions,
         rows, heads, kv_heads, head_dim, page_size, num_pages, scale, window, error);

@@ -246,6 +246,7 @@ __device__ __forceinline__ void tile_step(const __nv_bfloat16* Qs /* this warp's
 template <int D>
 __global__ void __launch_bounds__(128)
 attn_tile_kernel(const AttnParams p) {
+  wait_for_prior_kernels();
   constexpr int LD = D + 8;
   constexpr int BM = 64;
   constexpr int THREADS = 128;
@@ -485,6 +486,7 @@ constexpr int kSplitStages = 3;        // ring of K/V tiles in the split kernel
 template <int D>
 __global__ void __launch_bounds__(128)
 attn_split_kernel(const AttnParams p) {
+  wait_for_prior_kernels();
   constexpr int LD = D + 8;
   constexpr int THREADS = 128;
   extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -571,6 +573,7 @@ attn_split_kernel(const AttnParams p) {
 template <int D>
 __global__ void __launch_bounds__(160)
 attn_split_tma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap kv_map) {
+  wait_for_prior_kernels();
   constexpr int LD = D + 8;
   constexpr int PANELS = D / 64;
   constexpr int TILE_BYTES = BN * D * 2;               // K (or V) of one tile: PANELS panels of BN x 128 bytes
@@ -707,7 +710,7 @@ static int launch_split_tma(const AttnParams& p, int R, const CUtensorMap* kv_ma
       smem_set = smem;
     }
     dim3 grid(p.max_splits, p.kv_heads, R);
-    attn_split_tma_kernel<D><<<grid, 160, smem, s>>>(p, *kv_map);
+    launch_kernel(attn_split_tma_kernel<D>, dim3(grid), dim3(160), smem, s, p, *kv_map);
     PIH_LAUNCH_CHECK();
     return 0;
   } else {
@@ -728,7 +731,7 @@ static int launch_both(const AttnParams& p, int R, int tile_max_q, const CUtenso
       tile_smem_set = smem;
     }
     dim3 grid((tile_max_q * G + 63) / 64, p.kv_heads, R);
-    attn_tile_kernel<D><<<grid, 128, smem, s>>>(p);
+    launch_kernel(attn_tile_kernel<D>, dim3(grid), dim3(128), smem, s, p);
     PIH_LAUNCH_CHECK();
   }
   if (p.dec_tok_cap > 0 && kv_map != nullptr && D % 64 == 0 && p.page_shift >= 3 && p.page_size <= BN) {
@@ -748,7 +751,7 @@ static int launch_both(const AttnParams& p, int R, int tile_max_q, const CUtenso
       split_smem_set = smem;
     }
     dim3 grid(p.max_splits, p.kv_heads, R);
-    attn_split_kernel<D><<<grid, 128, smem, s>>>(p);
+    launch_kernel(attn_split_kernel<D>, dim3(grid), dim3(128), smem, s, p);
     PIH_LAUNCH_CHECK();
   }
   return 0;

@@ -168,6 +168,7 @@ __device__ __forceinline__ void pair_sync(int quarter) {
 template <int D>
 __global__ void __launch_bounds__(320)
 attn_prefill_tcgen05_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap kv_map) {
+  wait_for_prior_kernels();
   using Smem = PrefillSmem<D>;
   constexpr int PANELS = Smem::PANELS;
   constexpr int PANEL_BYTES = Smem::PANEL_BYTES;
@@ -512,7 +513,7 @@ extern "C" int pih_attention_prefill_tcgen05(const void* q, int q_stride, void* 
       if (e != cudaSuccess) return static_cast<int>(e);
       configured[0] = true;
     }
-    attn_prefill_tcgen05_kernel<128><<<grid, 320, smem, s>>>(p, map);
+    launch_kernel(attn_prefill_tcgen05_kernel<128>, dim3(grid), dim3(320), smem, s, p, map);
   } else {
     const int smem = static_cast<int>(sizeof(PrefillSmem<64>)) + 1024;
     if (!configured[1]) {
@@ -520,7 +521,7 @@ extern "C" int pih_attention_prefill_tcgen05(const void* q, int q_stride, void* 
       if (e != cudaSuccess) return static_cast<int>(e);
       configured[1] = true;
     }
-    attn_prefill_tcgen05_kernel<64><<<grid, 320, smem, s>>>(p, map);
+    launch_kernel(attn_prefill_tcgen05_kernel<64>, dim3(grid), dim3(320), smem, s, p, map);
   }
   PIH_LAUNCH_CHECK();
   return 0;

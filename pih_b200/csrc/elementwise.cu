@@ -14,6 +14,7 @@ template <typename T>
 __global__ void embedding_kernel(const T* __restrict__ table, const int* __restrict__ ids,
                                  T* __restrict__ out, int rows, int hidden, int vocab,
                                  uint32_t* error) {
+  wait_for_prior_kernels();
   const int t = blockIdx.x;
   if (t >= rows) return;
   int id = ids[t];
@@ -46,6 +47,7 @@ template <typename T, typename W>
 __global__ void rmsnorm_kernel(T* __restrict__ x, const T* __restrict__ delta,
                                const W* __restrict__ weight, T* __restrict__ out,
                                const int* __restrict__ rows, int width, float eps) {
+  wait_for_prior_kernels();
   __shared__ float scratch[33];
   const int o = blockIdx.x;
   const size_t r = rows != nullptr ? static_cast<size_t>(rows[o]) : static_cast<size_t>(o);
@@ -89,6 +91,7 @@ __global__ void qk_norm_rope_kv_kernel(T* __restrict__ qkv, int row_stride, int 
                                        const int* __restrict__ positions,
                                        const int* __restrict__ slot_mapping, T* __restrict__ cache,
                                        int page_size, int num_pages, int write_kv, uint32_t* error) {
+  wait_for_prior_kernels();
   extern __shared__ float smem[];
   const int warps_per_block = blockDim.x >> 5;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -170,6 +173,7 @@ __global__ void qk_norm_rope_kv_fast_kernel(T* __restrict__ qkv, int row_stride,
                                             const int* __restrict__ positions,
                                             const int* __restrict__ slot_mapping, T* __restrict__ cache,
                                             int page_size, int num_pages, int write_kv, uint32_t* error) {
+  wait_for_prior_kernels();
   constexpr int D = 32 * EPL;
   constexpr int HALF = D / 2;
   const int warps_per_block = blockDim.x >> 5;
@@ -247,6 +251,7 @@ __global__ void qk_norm_rope_kv_fast_kernel(T* __restrict__ qkv, int row_stride,
 template <typename T>
 __global__ void silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ out, long long rows,
                                 int inter, int il) {
+  wait_for_prior_kernels();
   const long long total = rows * inter;
   for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
        i += static_cast<long long>(gridDim.x) * blockDim.x) {
@@ -263,6 +268,7 @@ __global__ void silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ o
 template <typename T>
 __global__ void gather_rows_kernel(const T* __restrict__ in, const int* __restrict__ rows,
                                    T* __restrict__ out, int width) {
+  wait_for_prior_kernels();
   const T* s = in + static_cast<size_t>(rows[blockIdx.x]) * width;
   T* d = out + static_cast<size_t>(blockIdx.x) * width;
   for (int c = threadIdx.x; c < width; c += blockDim.x) d[c] = s[c];
@@ -272,6 +278,16 @@ __global__ void gather_rows_kernel(const T* __restrict__ in, const int* __restri
 
 using namespace pih;
 
+int pih::g_dependent_launch = 1;
+
+// 1 (the default): kernels of the pack are launched so that each may begin while the one before it drains
+// (see common.cuh); 0: plain launches.  Returns the previous setting.
+extern "C" int pih_set_dependent_launch(int on) {
+  const int before = pih::g_dependent_launch;
+  pih::g_dependent_launch = on ? 1 : 0;
+  return before;
+}
+
 extern "C" int pih_embedding(int dtype, const void* table, const int* ids, void* out, int rows,
                              int hidden, int vocab, uint32_t* error, void* stream) {
   if (rows <= 0) return 0;
@@ -279,10 +295,10 @@ extern "C" int pih_embedding(int dtype, const void* table, const int* ids, void*
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const int threads = 128;
   if (dtype == PIH_F32)
-    embedding_kernel<float><<<rows, threads, 0, s>>>(static_cast<const float*>(table), ids,
+    launch_kernel(embedding_kernel<float>, dim3(rows), dim3(threads), 0, s, static_cast<const float*>(table), ids,
                                                      static_cast<float*>(out), rows, hidden, vocab, error);
   else if (dtype == PIH_BF16)
-    embedding_kernel<__nv_bfloat16><<<rows, threads, 0, s>>>(
+    launch_kernel(embedding_kernel<__nv_bfloat16>, dim3(rows), dim3(threads), 0, s, 
         static_cast<const __nv_bfloat16*>(table), ids, static_cast<__nv_bfloat16*>(out), rows, hidden,
         vocab, error);
   else
@@ -297,6 +313,7 @@ template <typename T, typename W, int CHUNKS>
 __global__ void rmsnorm_vec_kernel(T* __restrict__ x, const T* __restrict__ delta,
                                    const W* __restrict__ weight, T* __restrict__ out,
                                    const int* __restrict__ rows, int width, float eps) {
+  wait_for_prior_kernels();
   constexpr int VEC = 16 / sizeof(T);
   __shared__ float scratch[33];
   const int o = blockIdx.x;
@@ -362,11 +379,11 @@ static int launch_rmsnorm(void* x, const void* delta, const void* weight, void* 
       const W* wp = static_cast<const W*>(weight);
       T* op = static_cast<T*>(out);
       if (nvec <= threads)
-        rmsnorm_vec_kernel<T, W, 1><<<out_rows, threads, 0, s>>>(xp, dp, wp, op, rows, width, eps);
+        launch_kernel(rmsnorm_vec_kernel<T, W, 1>, dim3(out_rows), dim3(threads), 0, s, xp, dp, wp, op, rows, width, eps);
       else if (nvec <= threads * 2)
-        rmsnorm_vec_kernel<T, W, 2><<<out_rows, threads, 0, s>>>(xp, dp, wp, op, rows, width, eps);
+        launch_kernel(rmsnorm_vec_kernel<T, W, 2>, dim3(out_rows), dim3(threads), 0, s, xp, dp, wp, op, rows, width, eps);
       else
-        rmsnorm_vec_kernel<T, W, 4><<<out_rows, threads, 0, s>>>(xp, dp, wp, op, rows, width, eps);
+        launch_kernel(rmsnorm_vec_kernel<T, W, 4>, dim3(out_rows), dim3(threads), 0, s, xp, dp, wp, op, rows, width, eps);
       PIH_LAUNCH_CHECK();
       return 0;
     }
@@ -375,7 +392,7 @@ static int launch_rmsnorm(void* x, const void* delta, const void* weight, void* 
   if (width <= 128) threads = 32;
   else if (width <= 512) threads = 128;
   else if (width >= 4096) threads = 512;
-  rmsnorm_kernel<T, W><<<out_rows, threads, 0, s>>>(static_cast<T*>(x), static_cast<const T*>(delta),
+  launch_kernel(rmsnorm_kernel<T, W>, dim3(out_rows), dim3(threads), 0, s, static_cast<T*>(x), static_cast<const T*>(delta),
                                                     static_cast<const W*>(weight), static_cast<T*>(out),
                                                     rows, width, eps);
   PIH_LAUNCH_CHECK();
@@ -410,7 +427,7 @@ static int launch_qk(void* qkv, int row_stride, int rows, int heads, int kv_head
     const int warps = 8;
     const unsigned blocks = static_cast<unsigned>((items + warps - 1) / warps);
 #define PIH_QK_FAST(EPL)                                                                                   \
-  qk_norm_rope_kv_fast_kernel<T, W, EPL><<<blocks, warps * 32, 0, s>>>(                                     \
+  launch_kernel(qk_norm_rope_kv_fast_kernel<T, W, EPL>, dim3(blocks), dim3(warps * 32), 0, s,                                      \
       static_cast<T*>(qkv), row_stride, rows, heads, kv_heads, static_cast<const W*>(q_w),                 \
       static_cast<const W*>(k_w), eps, rope, max_pos, positions, slot_mapping, static_cast<T*>(cache),     \
       page_size, num_pages, write_kv, error)
@@ -424,7 +441,7 @@ static int launch_qk(void* qkv, int row_stride, int rows, int heads, int kv_head
   const int warps = 4;
   const long long blocks = (items + warps - 1) / warps;
   const size_t smem = static_cast<size_t>(warps) * head_dim * sizeof(float);
-  qk_norm_rope_kv_kernel<T, W><<<static_cast<unsigned>(blocks), warps * 32, smem, s>>>(
+  launch_kernel(qk_norm_rope_kv_kernel<T, W>, dim3(static_cast<unsigned>(blocks)), dim3(warps * 32), smem, s, 
       static_cast<T*>(qkv), row_stride, rows, heads, kv_heads, head_dim, static_cast<const W*>(q_w),
       static_cast<const W*>(k_w), eps, rope, rotary_dim, max_pos, positions, slot_mapping,
       static_cast<T*>(cache), page_size, num_pages, write_kv, error);
@@ -463,6 +480,7 @@ extern "C" int pih_qk_norm_rope_kv_write(int dtype, int weight_dtype, void* qkv,
 template <typename T>
 __global__ void silu_mul_vec_kernel(const T* __restrict__ gate_up, T* __restrict__ out, long long rows,
                                     int inter, int il) {
+  wait_for_prior_kernels();
   constexpr int VEC = 16 / sizeof(T);
   const int per_row = inter / VEC;
   const long long total = rows * per_row;
@@ -493,12 +511,12 @@ static int launch_silu(const void* gate_up, void* out, long long rows, int inter
   if ((inter * sizeof(T)) % 16 == 0 && il % (16 / sizeof(T)) == 0) {
     const long long total = rows * (inter / (16 / sizeof(T)));
     const unsigned blocks = static_cast<unsigned>(min((total + threads - 1) / threads, 148LL * 32));
-    silu_mul_vec_kernel<T><<<blocks, threads, 0, s>>>(static_cast<const T*>(gate_up), static_cast<T*>(out),
+    launch_kernel(silu_mul_vec_kernel<T>, dim3(blocks), dim3(threads), 0, s, static_cast<const T*>(gate_up), static_cast<T*>(out),
                                                       rows, inter, il);
   } else {
     const long long total = rows * inter;
     const unsigned blocks = static_cast<unsigned>(min((total + threads - 1) / threads, 148LL * 32));
-    silu_mul_kernel<T><<<blocks, threads, 0, s>>>(static_cast<const T*>(gate_up), static_cast<T*>(out), rows,
+    launch_kernel(silu_mul_kernel<T>, dim3(blocks), dim3(threads), 0, s, static_cast<const T*>(gate_up), static_cast<T*>(out), rows,
                                                   inter, il);
   }
   PIH_LAUNCH_CHECK();
@@ -522,10 +540,10 @@ extern "C" int pih_gather_rows(int dtype, const void* in, const int* rows, void*
   if (out_rows <= 0) return 0;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (dtype == PIH_F32)
-    gather_rows_kernel<float><<<out_rows, 128, 0, s>>>(static_cast<const float*>(in), rows,
+    launch_kernel(gather_rows_kernel<float>, dim3(out_rows), dim3(128), 0, s, static_cast<const float*>(in), rows,
                                                        static_cast<float*>(out), width);
   else if (dtype == PIH_BF16)
-    gather_rows_kernel<__nv_bfloat16><<<out_rows, 128, 0, s>>>(
+    launch_kernel(gather_rows_kernel<__nv_bfloat16>, dim3(out_rows), dim3(128), 0, s, 
         static_cast<const __nv_bfloat16*>(in), rows, static_cast<__nv_bfloat16*>(out), width);
   else
     return PIH_ERR_BAD_ARGUMENT;

@@ -20,6 +20,7 @@ template <typename TA, typename TC>
 __global__ void __launch_bounds__(256)
 gemm_simt_kernel(const TA* __restrict__ A, const TA* __restrict__ W, TC* __restrict__ C, int M, int N,
                  int K, long long lda, long long ldw, long long ldc) {
+  wait_for_prior_kernels();
   __shared__ float As[BK][BM + 4];
   __shared__ float Ws[BK][BN + 4];
   const int tid = threadIdx.x;
@@ -81,15 +82,15 @@ extern "C" int pih_gemm_simt(int in_dtype, int out_dtype, const void* A, const v
   dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
   if (grid.y > 65535) return PIH_ERR_UNSUPPORTED;
   if (in_dtype == PIH_F32 && out_dtype == PIH_F32)
-    gemm_simt_kernel<float, float><<<grid, 256, 0, s>>>(static_cast<const float*>(A),
+    launch_kernel(gemm_simt_kernel<float, float>, dim3(grid), dim3(256), 0, s, static_cast<const float*>(A),
                                                         static_cast<const float*>(W),
                                                         static_cast<float*>(C), M, N, K, lda, ldw, ldc);
   else if (in_dtype == PIH_BF16 && out_dtype == PIH_BF16)
-    gemm_simt_kernel<__nv_bfloat16, __nv_bfloat16><<<grid, 256, 0, s>>>(
+    launch_kernel(gemm_simt_kernel<__nv_bfloat16, __nv_bfloat16>, dim3(grid), dim3(256), 0, s, 
         static_cast<const __nv_bfloat16*>(A), static_cast<const __nv_bfloat16*>(W),
         static_cast<__nv_bfloat16*>(C), M, N, K, lda, ldw, ldc);
   else if (in_dtype == PIH_BF16 && out_dtype == PIH_F32)
-    gemm_simt_kernel<__nv_bfloat16, float><<<grid, 256, 0, s>>>(
+    launch_kernel(gemm_simt_kernel<__nv_bfloat16, float>, dim3(grid), dim3(256), 0, s, 
         static_cast<const __nv_bfloat16*>(A), static_cast<const __nv_bfloat16*>(W),
         static_cast<float*>(C), M, N, K, lda, ldw, ldc);
   else

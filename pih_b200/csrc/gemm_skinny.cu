@@ -73,8 +73,10 @@ skinny_gemm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
     }
   };
   int tile = blockIdx.x;
-  // the weight stream does not wait for the prologue: the first loads are in flight now
+  // the weight stream waits neither for the prologue nor for the kernel before this one (weights are never
+  // written): the first loads are in flight while that kernel's last blocks finish
   issue(tile, warp);
+  wait_for_prior_kernels();
 
   // prologue, once per CTA: token rows into shared memory, residual add, norm
   const int chunks = K / 8;
@@ -213,7 +215,7 @@ static int launch_skinny(const void* x, const void* delta, void* x_out, const vo
   }
   const int ntiles = (N + 8 * TILES - 1) / (8 * TILES);
   const int grid = ntiles < 2 * sms ? ntiles : 2 * sms;
-  skinny_gemm_kernel<MR, TILES, NORM, SWIGLU, NW><<<grid, SK_THREADS, smem, s>>>(
+  launch_kernel(skinny_gemm_kernel<MR, TILES, NORM, SWIGLU, NW>, dim3(grid), dim3(SK_THREADS), smem, s, 
       static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(delta),
       static_cast<__nv_bfloat16*>(x_out), static_cast<const NW*>(norm_w), eps,
       static_cast<const __nv_bfloat16*>(W), static_cast<__nv_bfloat16*>(out), M, N, K, ldx, ldw, ldo);

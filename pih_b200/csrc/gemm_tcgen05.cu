@@ -71,6 +71,7 @@ template <typename TC, int BN, int NSTAGES>
 __global__ void __launch_bounds__(192)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                     TC* __restrict__ C, int M, int N, int K, long long ldc, uint32_t* error) {
+  wait_for_prior_kernels();
   using Smem = GemmSmem<BN, NSTAGES>;
   extern __shared__ unsigned char smem_raw[];
   Smem& sm = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -259,7 +260,7 @@ static int launch_gemm(const CUtensorMap& map_a, const CUtensorMap& map_w, void*
   }
   const long long tiles = static_cast<long long>((M + GM - 1) / GM) * ((N + BN - 1) / BN);
   const int grid = static_cast<int>(tiles < sms ? tiles : sms);
-  gemm_tcgen05_kernel<TC, BN, NSTAGES><<<grid, 192, smem, s>>>(map_a, map_w, static_cast<TC*>(C), M, N, K, ldc, error);
+  launch_kernel(gemm_tcgen05_kernel<TC, BN, NSTAGES>, dim3(grid), dim3(192), smem, s, map_a, map_w, static_cast<TC*>(C), M, N, K, ldc, error);
   PIH_LAUNCH_CHECK();
   return 0;
 }

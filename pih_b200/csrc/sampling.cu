@@ -230,6 +230,7 @@ __device__ Prefix find_crossing(const RowView& rv, const Prefix& p, bool use_mas
 __global__ void __launch_bounds__(kSampleThreads)
 sample_kernel(const float* __restrict__ logits, int vocab, const float* __restrict__ fparams,
               const int* __restrict__ iparams, int* __restrict__ out_tokens, uint32_t* error) {
+  wait_for_prior_kernels();
   __shared__ int s_sup[kMaxSuppressed];
   __shared__ unsigned long long s_hist[256];
   __shared__ unsigned long long s_scratch[40];
@@ -335,6 +336,7 @@ sample_kernel(const float* __restrict__ logits, int vocab, const float* __restri
 // argmax per row, ties to the lower id (qwen_bf16_primitives.cu:761-807)
 __global__ void __launch_bounds__(kSampleThreads)
 argmax_kernel(const float* __restrict__ logits, int vocab, int* __restrict__ out_tokens, uint32_t* error) {
+  wait_for_prior_kernels();
   __shared__ float s_val[32];
   __shared__ int s_idx[32];
   const float* row = logits + static_cast<size_t>(blockIdx.x) * vocab;
@@ -386,6 +388,7 @@ argmax_kernel(const float* __restrict__ logits, int vocab, int* __restrict__ out
 __global__ void __launch_bounds__(256)
 argmax_slices_kernel(const float* __restrict__ logits, int vocab, int slices, float* __restrict__ part_val,
                      int* __restrict__ part_idx, uint32_t* error) {
+  wait_for_prior_kernels();
   __shared__ float s_val[8];
   __shared__ int s_idx[8];
   const int row = blockIdx.y, slice = blockIdx.x;
@@ -432,6 +435,7 @@ argmax_slices_kernel(const float* __restrict__ logits, int vocab, int slices, fl
 
 __global__ void argmax_final_kernel(const float* __restrict__ part_val, const int* __restrict__ part_idx,
                                     int slices, int* __restrict__ out_tokens) {
+  wait_for_prior_kernels();
   const int row = blockIdx.x, lane = threadIdx.x;
   float best = -INFINITY;
   int best_id = 0x7fffffff;
@@ -470,13 +474,13 @@ extern "C" int pih_argmax(const float* logits, int rows, int vocab, int* out_tok
     const int slices = 64;
     float* pv = static_cast<float*>(scratch);
     int* pi = reinterpret_cast<int*>(pv + static_cast<size_t>(rows) * slices);
-    argmax_slices_kernel<<<dim3(slices, rows), 256, 0, s>>>(logits, vocab, slices, pv, pi, error);
+    launch_kernel(argmax_slices_kernel, dim3(dim3(slices, rows)), dim3(256), 0, s, logits, vocab, slices, pv, pi, error);
     PIH_LAUNCH_CHECK();
-    argmax_final_kernel<<<rows, 32, 0, s>>>(pv, pi, slices, out_tokens);
+    launch_kernel(argmax_final_kernel, dim3(rows), dim3(32), 0, s, pv, pi, slices, out_tokens);
     PIH_LAUNCH_CHECK();
     return 0;
   }
-  argmax_kernel<<<rows, kSampleThreads, 0, s>>>(logits, vocab, out_tokens, error);
+  launch_kernel(argmax_kernel, dim3(rows), dim3(kSampleThreads), 0, s, logits, vocab, out_tokens, error);
   PIH_LAUNCH_CHECK();
   return 0;
 }
@@ -487,7 +491,7 @@ extern "C" int pih_sample(const float* logits, int rows, int vocab, const float*
                           const int* iparams, int* out_tokens, uint32_t* error, void* stream) {
   if (rows <= 0) return 0;
   if (vocab <= 0) return PIH_ERR_BAD_ARGUMENT;
-  sample_kernel<<<rows, kSampleThreads, 0, static_cast<cudaStream_t>(stream)>>>(logits, vocab, fparams,
+  launch_kernel(sample_kernel, dim3(rows), dim3(kSampleThreads), 0, static_cast<cudaStream_t>(stream), logits, vocab, fparams,
                                                                                   iparams, out_tokens, error);
   PIH_LAUNCH_CHECK();
   return 0;

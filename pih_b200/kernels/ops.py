@@ -72,9 +72,15 @@ class CudaOps:
         for name in ("pih_embedding", "pih_rmsnorm", "pih_qk_norm_rope_kv_write", "pih_silu_mul",
                      "pih_gather_rows", "pih_gemm_simt", "pih_paged_attention_generic", "pih_argmax",
                      "pih_sample", "pih_paged_attention_mma", "pih_gemm_tcgen05", "pih_make_kv_tensor_map",
-                     "pih_attention_prefill_tcgen05", "pih_gemm_skinny"):
+                     "pih_attention_prefill_tcgen05", "pih_gemm_skinny", "pih_set_dependent_launch"):
             getattr(lib, name).restype = c_int
         lib.pih_attention_scratch_floats.restype = c_ll
+
+    def set_dependent_launch(self, on: bool) -> bool:
+        """Whether the pack's kernels are launched so that each may begin while the one before it drains
+        (programmatic dependent launch; the default).  Returns the previous setting.  The setting is the
+        library's, not this object's; CUDA graphs keep the setting they were captured under."""
+        return bool(self.lib.pih_set_dependent_launch(1 if on else 0))
 
     def _stream(self):
         return c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
