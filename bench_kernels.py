@@ -9,7 +9,10 @@ Each kernel is timed with CUDA events on the launching stream after warm-up;
 between timed launches a buffer larger than the 126 MB L2 is written so that
 inputs come from HBM.  Prints one JSON line with the time, the algorithmic
 bytes or flops and the achieved rate.  It is the small case that the ncu
-summaries under profiles/ were captured on.
+summaries under profiles/ were captured on.  Event times of one launch come in
+steps of a few microseconds on this hardware; for kernels of that size use
+``--chain``: many calls on different inputs (together larger than L2) back to back in
+one CUDA graph, which gives the time of one call as a step sees it.
 """
 from __future__ import annotations
 
@@ -76,11 +79,13 @@ def main() -> int:
     ap.add_argument("--no-flush", action="store_true")
     ap.add_argument("--impl", default="default", choices=["default", "tcgen05", "skinny", "library"])
     ap.add_argument("--tile-n", type=int, default=0)
-    ap.add_argument("--chain", action="store_true", help="linear: many products back to back in a CUDA graph")
+    ap.add_argument("--chain", action="store_true", help="many calls on different inputs back to back in a CUDA graph: the time of one call inside a step")
     ap.add_argument("--chain-mb", type=float, default=200.0,
-                    help="linear --chain: total size of the distinct weights (below the L2 size they stay resident)")
+                    help="--chain: total size of the distinct weights (below the L2 size they stay resident)")
     ap.add_argument("--split", type=int, default=0, help="keys per split of the decode attention (0: automatic)")
     ap.add_argument("--no-tma", action="store_true", help="decode attention gathers with cp.async instead of TMA")
+    ap.add_argument("--tickets", action="store_true",
+                    help="decode attention merges its splits through scratch memory and tickets, not as a cluster")
     ap.add_argument("--plain", action="store_true", help="the pack's plain (generic / FMA) kernel instead")
     args = ap.parse_args()
 
@@ -92,54 +97,97 @@ def main() -> int:
     H, KV, D, P = args.heads, args.kv_heads, args.head_dim, args.page
     ops.attention_split = args.split
     ops.tma_attention = not args.no_tma
+    if args.tickets:
+        ops.set_attention_cluster_merge(False)
     out = {"kernel": args.kernel}
 
-    if args.kernel in ("attn_decode", "attn_prefill"):
-        if args.kernel == "attn_decode":
-            lens, new = [args.ctx] * args.batch, [1] * args.batch
-        else:
-            lens, new = [args.tokens], [args.tokens]
-        pages_per = [-(-n // P) for n in lens]
-        num_pages = sum(pages_per)
-        cache = torch.randn(num_pages, 2, KV, P, D, device=dev).to(bf)
-        table = torch.full((len(lens), max(pages_per)), -1, dtype=torch.int32)
-        perm = torch.randperm(num_pages).tolist()
-        for r, n in enumerate(pages_per):
-            table[r, :n] = torch.tensor([perm.pop() for _ in range(n)], dtype=torch.int32)
-        table = table.to(dev)
-        q = torch.randn(sum(new), (H + 2 * KV) * D, device=dev).to(bf)
-        step = step_of(lens, new, dev)
-        scale = 1.0 / math.sqrt(D)
-        if args.plain:
-            fn = lambda: ops.paged_attention_generic(q, heads=H, kv_heads=KV, head_dim=D, kv_cache=cache,
-                                                     block_table=table, request_of_row=step.request_of_row,
-                                                     positions=step.positions, scale=scale, window=0)
-        else:
-            fn = lambda: ops.paged_attention_mma(q, heads=H, kv_heads=KV, head_dim=D, kv_cache=cache,
-                                                 block_table=table, step=step, scale=scale, window=0)
-        us = time_kernel(fn, args.iters, not args.no_flush)
-        if args.kernel == "attn_decode":
-            nbytes = sum(lens) * 2 * KV * D * 2
-            out.update(us=round(us, 2), bytes=nbytes, gbs=round(nbytes / us / 1e3, 1), batch=args.batch, ctx=args.ctx)
-        else:
-            T = args.tokens
-            flops = 4 * H * D * T * (T + 1) // 2
-            out.update(us=round(us, 2), flops=flops, tflops=round(flops / us / 1e6, 1), tokens=T)
-    elif args.kernel == "linear" and args.chain:
-        # many products with different weights back to back (together larger than L2) in one timed region:
-        # per-launch time as a decode step sees it, launch gaps included, measured inside a CUDA graph
-        x = torch.randn(args.m, args.k, device=dev).to(bf)
-        reps = max(4, int(args.chain_mb * 1e6 / (args.n * args.k * 2)) + 1)
-        ws = [torch.randn(args.n, args.k, device=dev).to(bf) for _ in range(reps)]
-        call = {"skinny": lambda w: ops.linear_skinny(x, w), "library": lambda w: torch.mm(x, w.t()),
-                "tcgen05": lambda w: ops.linear_tcgen05(x, w, tile_n=args.tile_n)}.get(args.impl, lambda w: ops.linear(x, w))
-        for w in ws[:2]:
-            call(w)
+    scale = 1.0 / math.sqrt(D)
+    rates = {}                                        # filled by make(): algorithmic bytes / flops of one call
+
+    def make():
+        """One call of the chosen kernel on inputs of its own; returns (closure, bytes the inputs occupy)."""
+        k = args.kernel
+        if k in ("attn_decode", "attn_prefill"):
+            if k == "attn_decode":
+                lens, new = [args.ctx] * args.batch, [1] * args.batch
+            else:
+                lens, new = [args.tokens], [args.tokens]
+            pages_per = [-(-n // P) for n in lens]
+            num_pages = sum(pages_per)
+            cache = torch.randn(num_pages, 2, KV, P, D, device=dev).to(bf)
+            table = torch.full((len(lens), max(pages_per)), -1, dtype=torch.int32)
+            perm = torch.randperm(num_pages).tolist()
+            for r, n in enumerate(pages_per):
+                table[r, :n] = torch.tensor([perm.pop() for _ in range(n)], dtype=torch.int32)
+            table = table.to(dev)
+            q = torch.randn(sum(new), (H + 2 * KV) * D, device=dev).to(bf)
+            step = step_of(lens, new, dev)
+            if k == "attn_decode":
+                rates.update(bytes=sum(lens) * 2 * KV * D * 2, batch=args.batch, ctx=args.ctx)
+            else:
+                rates.update(flops=4 * H * D * args.tokens * (args.tokens + 1) // 2, tokens=args.tokens)
+            if args.plain:
+                fn = lambda: ops.paged_attention_generic(q, heads=H, kv_heads=KV, head_dim=D, kv_cache=cache,
+                                                         block_table=table, request_of_row=step.request_of_row,
+                                                         positions=step.positions, scale=scale, window=0)
+            else:
+                fn = lambda: ops.paged_attention_mma(q, heads=H, kv_heads=KV, head_dim=D, kv_cache=cache,
+                                                     block_table=table, step=step, scale=scale, window=0)
+            return fn, cache.numel() * 2
+        if k == "linear":
+            x = torch.randn(args.m, args.k, device=dev).to(bf)
+            w = torch.randn(args.n, args.k, device=dev).to(bf)
+            rates.update(flops=2 * args.m * args.n * args.k, m=args.m, n=args.n, k=args.k,
+                         bytes=2 * (args.m * args.k + args.n * args.k + args.m * args.n))
+            if args.impl == "tcgen05":
+                fn = lambda: ops.linear_tcgen05(x, w, tile_n=args.tile_n)
+            elif args.impl == "skinny":
+                fn = lambda: ops.linear_skinny(x, w)
+            elif args.impl == "library":
+                fn = lambda: torch.mm(x, w.t())
+            else:
+                fn = (lambda: ops.linear_plain(x, w)) if args.plain else (lambda: ops.linear(x, w))
+            return fn, (x.numel() + w.numel()) * 2
+        if k == "rmsnorm":
+            x = torch.randn(args.rows, args.width, device=dev).to(bf)
+            d = torch.randn(args.rows, args.width, device=dev).to(bf)
+            w = torch.ones(args.width, device=dev).to(bf)
+            rates.update(bytes=args.rows * args.width * 2 * 4, rows=args.rows, width=args.width)
+            return (lambda: ops.rmsnorm(x, w, 1e-6, delta=d)), x.numel() * 4
+        if k == "qk":
+            rows = args.rows
+            qkv = torch.randn(rows, (H + 2 * KV) * D, device=dev).to(bf)
+            qw = torch.ones(D, device=dev).to(bf)
+            cache = torch.zeros(-(-rows // P) + 1, 2, KV, P, D, device=dev, dtype=bf)
+            table = torch.zeros(4096, D // 2, 2, device=dev)
+            pos = torch.arange(rows, dtype=torch.int32, device=dev) % 4096
+            slots = torch.arange(rows, dtype=torch.int32, device=dev)
+            rates.update(bytes=rows * ((H + 2 * KV) * D * 2 + (H + KV) * D * 2 + 2 * KV * D * 2), rows=rows)
+            fn = lambda: ops.qk_norm_rope_kv_write(qkv, heads=H, kv_heads=KV, head_dim=D, q_norm=qw, k_norm=qw,
+                                                   eps=1e-6, rope_table=table, rotary_dim=D, positions=pos,
+                                                   slot_mapping=slots, kv_cache=cache, write_kv=True)
+            return fn, (qkv.numel() + cache.numel()) * 2
+        if k == "silu":
+            gu = torch.randn(args.rows, 2 * 3072, device=dev).to(bf)
+            rates.update(bytes=args.rows * 3072 * 2 * 3, rows=args.rows)
+            return (lambda: ops.silu_mul(gu)), gu.numel() * 3
+        lg = torch.randn(args.rows, 151936, device=dev)
+        rates.update(bytes=args.rows * 151936 * 4, rows=args.rows)
+        return (lambda: ops.argmax(lg)), lg.numel() * 4
+
+    if args.chain:
+        # many calls on different inputs (together larger than L2 unless --chain-mb says otherwise) back to back
+        # in one CUDA graph: the time of one call as a step sees it, boundaries between kernels included
+        fn, size = make()
+        reps = max(4, min(256, int(args.chain_mb * 1e6 / max(size, 1)) + 1))
+        fns = [fn] + [make()[0] for _ in range(reps - 1)]
+        for f in fns[:2]:
+            f()
         torch.cuda.synchronize()
         g = torch.cuda.CUDAGraph()
         with torch.cuda.graph(g):
-            for w in ws:
-                call(w)
+            for f in fns:
+                f()
         g.replay()
         torch.cuda.synchronize()
         start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -149,54 +197,15 @@ def main() -> int:
         stop.record()
         torch.cuda.synchronize()
         us = start.elapsed_time(stop) * 1e3 / (5 * reps)
-        nbytes = 2 * (args.m * args.k + args.n * args.k + args.m * args.n)
-        out.update(us=round(us, 2), gbs=round(nbytes / us / 1e3, 1), m=args.m, n=args.n, k=args.k, chained=reps)
-    elif args.kernel == "linear":
-        x = torch.randn(args.m, args.k, device=dev).to(bf)
-        w = torch.randn(args.n, args.k, device=dev).to(bf)
-        if args.impl == "tcgen05":
-            fn = lambda: ops.linear_tcgen05(x, w, tile_n=args.tile_n)
-        elif args.impl == "skinny":
-            fn = lambda: ops.linear_skinny(x, w)
-        elif args.impl == "library":
-            fn = lambda: torch.mm(x, w.t())
-        else:
-            fn = (lambda: ops.linear_plain(x, w)) if args.plain else (lambda: ops.linear(x, w))
-        us = time_kernel(fn, args.iters, not args.no_flush)
-        flops = 2 * args.m * args.n * args.k
-        nbytes = 2 * (args.m * args.k + args.n * args.k + args.m * args.n)
-        out.update(us=round(us, 2), tflops=round(flops / us / 1e6, 2), gbs=round(nbytes / us / 1e3, 1),
-                   m=args.m, n=args.n, k=args.k)
-    elif args.kernel == "rmsnorm":
-        x = torch.randn(args.rows, args.width, device=dev).to(bf)
-        d = torch.randn(args.rows, args.width, device=dev).to(bf)
-        w = torch.ones(args.width, device=dev).to(bf)
-        us = time_kernel(lambda: ops.rmsnorm(x, w, 1e-6, delta=d), args.iters, not args.no_flush)
-        nbytes = args.rows * args.width * 2 * 4
-        out.update(us=round(us, 2), gbs=round(nbytes / us / 1e3, 1), rows=args.rows, width=args.width)
-    elif args.kernel == "qk":
-        rows = args.rows
-        qkv = torch.randn(rows, (H + 2 * KV) * D, device=dev).to(bf)
-        qw = torch.ones(D, device=dev).to(bf)
-        cache = torch.zeros(-(-rows // P) + 1, 2, KV, P, D, device=dev, dtype=bf)
-        table = torch.zeros(4096, D // 2, 2, device=dev)
-        pos = torch.arange(rows, dtype=torch.int32, device=dev) % 4096
-        slots = torch.arange(rows, dtype=torch.int32, device=dev)
-        fn = lambda: ops.qk_norm_rope_kv_write(qkv, heads=H, kv_heads=KV, head_dim=D, q_norm=qw, k_norm=qw, eps=1e-6,
-                                               rope_table=table, rotary_dim=D, positions=pos, slot_mapping=slots,
-                                               kv_cache=cache, write_kv=True)
-        us = time_kernel(fn, args.iters, not args.no_flush)
-        nbytes = rows * ((H + 2 * KV) * D * 2 + (H + KV) * D * 2 + 2 * KV * D * 2)
-        out.update(us=round(us, 2), gbs=round(nbytes / us / 1e3, 1), rows=rows)
-    elif args.kernel == "silu":
-        gu = torch.randn(args.rows, 2 * 3072, device=dev).to(bf)
-        us = time_kernel(lambda: ops.silu_mul(gu), args.iters, not args.no_flush)
-        nbytes = args.rows * 3072 * 2 * 3
-        out.update(us=round(us, 2), gbs=round(nbytes / us / 1e3, 1), rows=args.rows)
-    elif args.kernel == "argmax":
-        lg = torch.randn(args.rows, 151936, device=dev)
-        us = time_kernel(lambda: ops.argmax(lg), args.iters, not args.no_flush)
-        out.update(us=round(us, 2), gbs=round(args.rows * 151936 * 4 / us / 1e3, 1), rows=args.rows)
+        out["chained"] = reps
+    else:
+        us = time_kernel(make()[0], args.iters, not args.no_flush)
+    out["us"] = round(us, 2)
+    if "flops" in rates:
+        out["tflops"] = round(rates.pop("flops") / us / 1e6, 2)
+    if "bytes" in rates:
+        out["gbs"] = round(rates.pop("bytes") / us / 1e3, 1)
+    out.update(rates)
     ops.check_errors()
     print(json.dumps(out))
     return 0

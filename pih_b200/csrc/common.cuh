@@ -98,19 +98,37 @@ __device__ __forceinline__ void wait_for_prior_kernels() { asm volatile("griddep
 // 1: kernels are launched with programmatic stream serialisation; 0: plain launches.  Set by pih_set_dependent_launch.
 extern int g_dependent_launch;
 
+// cluster_x > 1: thread-block clusters of that many blocks along x (grid.x must be a multiple of it)
 template <typename... P, typename... A>
-inline void launch_kernel(void (*kernel)(P...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, A&&... args) {
+inline void launch_kernel_clustered(void (*kernel)(P...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                    unsigned cluster_x, A&&... args) {
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid;
   cfg.blockDim = block;
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
-  cudaLaunchAttribute attr = {};
-  attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr.val.programmaticStreamSerializationAllowed = 1;
-  cfg.attrs = &attr;
-  cfg.numAttrs = g_dependent_launch ? 1 : 0;
+  cudaLaunchAttribute attrs[2] = {};
+  unsigned n = 0;
+  if (g_dependent_launch) {
+    attrs[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attrs[n].val.programmaticStreamSerializationAllowed = 1;
+    ++n;
+  }
+  if (cluster_x > 1) {
+    attrs[n].id = cudaLaunchAttributeClusterDimension;
+    attrs[n].val.clusterDim.x = cluster_x;
+    attrs[n].val.clusterDim.y = 1;
+    attrs[n].val.clusterDim.z = 1;
+    ++n;
+  }
+  cfg.attrs = attrs;
+  cfg.numAttrs = n;
   cudaLaunchKernelEx(&cfg, kernel, static_cast<P>(args)...);   // the caller reads cudaGetLastError()
+}
+
+template <typename... P, typename... A>
+inline void launch_kernel(void (*kernel)(P...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, A&&... args) {
+  launch_kernel_clustered(kernel, grid, block, smem, stream, 1u, static_cast<A&&>(args)...);
 }
 
 }  // namespace pih

@@ -40,11 +40,12 @@ __device__ __forceinline__ uint4 ldg_nc16(const void* p) {
 
 constexpr int SK_WARPS = 8;
 constexpr int SK_THREADS = SK_WARPS * 32;
-constexpr int SK_UN = 4;                 // k blocks (of 32) whose weight loads a warp keeps in flight
+constexpr int SK_UN = 4;                 // k blocks in flight per warp unless the product has a long k
 
 // MR: rows of the token operand kept in shared memory (8 or 16).  TILES: 8-row weight tiles per warp (1 or 2).
+// UN: k blocks (of 32) whose weight loads a warp keeps in flight.
 // Persistent: a CTA prepares the token rows once and then walks over weight tiles blockIdx.x, + gridDim.x, ...
-template <int MR, int TILES, bool NORM, bool SWIGLU, typename NW>
+template <int MR, int TILES, int UN, bool NORM, bool SWIGLU, typename NW>
 __global__ void __launch_bounds__(SK_THREADS)
 skinny_gemm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ delta,
                    __nv_bfloat16* __restrict__ x_out, const NW* __restrict__ norm_w, float eps,
@@ -59,14 +60,14 @@ skinny_gemm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
   const int kblocks = K / 32;
   const int ntiles = (N + 8 * TILES - 1) / (8 * TILES);
 
-  uint4 wv[SK_UN][TILES];
+  uint4 wv[UN][TILES];
   auto issue = [&](int tile, int first_block) {            // weight loads of k blocks first_block, + WARPS, ...
 #pragma unroll
     for (int t = 0; t < TILES; ++t) {
       const int row = min(tile * 8 * TILES + t * 8 + gid, N - 1);
       const __nv_bfloat16* wrow = W + static_cast<long long>(row) * ldw + 8 * q;
 #pragma unroll
-      for (int u = 0; u < SK_UN; ++u) {
+      for (int u = 0; u < UN; ++u) {
         const int b = first_block + SK_WARPS * u;
         wv[u][t] = (b < kblocks) ? ldg_nc16(wrow + b * 32) : make_uint4(0, 0, 0, 0);
       }
@@ -130,18 +131,18 @@ skinny_gemm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
     float acc[TILES][4];
 #pragma unroll
     for (int t = 0; t < TILES; ++t) acc[t][0] = acc[t][1] = acc[t][2] = acc[t][3] = 0.0f;
-    for (int kb = warp; kb < kblocks; kb += SK_WARPS * SK_UN) {
-      uint4 cur[SK_UN][TILES];
+    for (int kb = warp; kb < kblocks; kb += SK_WARPS * UN) {
+      uint4 cur[UN][TILES];
 #pragma unroll
-      for (int u = 0; u < SK_UN; ++u)
+      for (int u = 0; u < UN; ++u)
 #pragma unroll
         for (int t = 0; t < TILES; ++t) cur[u][t] = wv[u][t];
       // the next batch of weight loads — of this tile, or the first of the CTA's next tile — before this one is used
-      const int nb = kb + SK_WARPS * SK_UN;
+      const int nb = kb + SK_WARPS * UN;
       if (nb < kblocks) issue(tile, nb);
       else if (tile + gridDim.x < ntiles) issue(tile + gridDim.x, warp);
 #pragma unroll
-      for (int u = 0; u < SK_UN; ++u) {
+      for (int u = 0; u < UN; ++u) {
         const int b = kb + SK_WARPS * u;
         if (b >= kblocks) break;
         const uint4 xlo = *reinterpret_cast<const uint4*>(xa + b * 32);
@@ -193,7 +194,7 @@ skinny_gemm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
   }
 }
 
-template <int MR, int TILES, bool NORM, bool SWIGLU, typename NW>
+template <int MR, int TILES, int UN, bool NORM, bool SWIGLU, typename NW>
 static int launch_skinny(const void* x, const void* delta, void* x_out, const void* norm_w, float eps, const void* W,
                          void* out, int M, int N, int K, long long ldx, long long ldw, long long ldo,
                          cudaStream_t s) {
@@ -201,7 +202,7 @@ static int launch_skinny(const void* x, const void* delta, void* x_out, const vo
   static int smem_set = 0;                                 // per instance
   if (smem > 227 * 1024) return PIH_ERR_UNSUPPORTED;
   if (smem > 48 * 1024 && smem_set < smem) {
-    cudaError_t e = cudaFuncSetAttribute(skinny_gemm_kernel<MR, TILES, NORM, SWIGLU, NW>,
+    cudaError_t e = cudaFuncSetAttribute(skinny_gemm_kernel<MR, TILES, UN, NORM, SWIGLU, NW>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return static_cast<int>(e);
     smem_set = smem;
@@ -215,7 +216,7 @@ static int launch_skinny(const void* x, const void* delta, void* x_out, const vo
   }
   const int ntiles = (N + 8 * TILES - 1) / (8 * TILES);
   const int grid = ntiles < 2 * sms ? ntiles : 2 * sms;
-  launch_kernel(skinny_gemm_kernel<MR, TILES, NORM, SWIGLU, NW>, dim3(grid), dim3(SK_THREADS), smem, s, 
+  launch_kernel(skinny_gemm_kernel<MR, TILES, UN, NORM, SWIGLU, NW>, dim3(grid), dim3(SK_THREADS), smem, s, 
       static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(delta),
       static_cast<__nv_bfloat16*>(x_out), static_cast<const NW*>(norm_w), eps,
       static_cast<const __nv_bfloat16*>(W), static_cast<__nv_bfloat16*>(out), M, N, K, ldx, ldw, ldo);
@@ -228,10 +229,16 @@ static int dispatch_skinny(int tiles, bool swiglu, const void* x, const void* de
                            float eps, const void* W, void* out, int M, int N, int K, long long ldx, long long ldw,
                            long long ldo, cudaStream_t s) {
   if (swiglu)
-    return launch_skinny<MR, 2, NORM, true, NW>(x, delta, x_out, norm_w, eps, W, out, M, N, K, ldx, ldw, ldo, s);
+    return launch_skinny<MR, 2, SK_UN, NORM, true, NW>(x, delta, x_out, norm_w, eps, W, out, M, N, K, ldx, ldw, ldo, s);
   if (tiles == 2)
-    return launch_skinny<MR, 2, NORM, false, NW>(x, delta, x_out, norm_w, eps, W, out, M, N, K, ldx, ldw, ldo, s);
-  return launch_skinny<MR, 1, NORM, false, NW>(x, delta, x_out, norm_w, eps, W, out, M, N, K, ldx, ldw, ldo, s);
+    return launch_skinny<MR, 2, SK_UN, NORM, false, NW>(x, delta, x_out, norm_w, eps, W, out, M, N, K, ldx, ldw, ldo, s);
+  // a long k with 8-row tiles: twice the loads in flight per warp, so that a block's life is one or two round
+  // trips to memory instead of three (1024 x 3072: 5.6 -> 4.7 us; 1024 x 2048: 3.7 -> 3.4 us inside a step).
+  // Pairs of blocks in a cluster that split k and add through distributed shared memory were measured too:
+  // no faster than one block per tile (5.5 and 4.1 us).
+  if (K > 32 * SK_WARPS * SK_UN)
+    return launch_skinny<MR, 1, 2 * SK_UN, NORM, false, NW>(x, delta, x_out, norm_w, eps, W, out, M, N, K, ldx, ldw, ldo, s);
+  return launch_skinny<MR, 1, SK_UN, NORM, false, NW>(x, delta, x_out, norm_w, eps, W, out, M, N, K, ldx, ldw, ldo, s);
 }
 
 }  // namespace pih

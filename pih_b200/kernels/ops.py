@@ -60,6 +60,7 @@ class CudaOps:
         self._kv_maps = {}                 # cache tensor (address, shape) -> 128-byte TMA descriptor
         self.tma_attention = True          # False: the split kernel gathers with cp.async instead of TMA
         self.tcgen05_attention = True      # False: prompt portions use the mma.sync tile kernel
+        self.cluster_attention = True      # False: splits always merge through scratch memory and tickets
         self.attention_split = 0           # keys per split of the decode attention kernel; 0: from the context, on the device
         self.tensor_core_attention = True  # False: bf16 attention runs on the generic kernel too
         self.tcgen05_min_rows = None       # bf16 products with at least this many rows use the pack's tcgen05 kernel
@@ -72,7 +73,7 @@ class CudaOps:
         for name in ("pih_embedding", "pih_rmsnorm", "pih_qk_norm_rope_kv_write", "pih_silu_mul",
                      "pih_gather_rows", "pih_gemm_simt", "pih_paged_attention_generic", "pih_argmax",
                      "pih_sample", "pih_paged_attention_mma", "pih_gemm_tcgen05", "pih_make_kv_tensor_map",
-                     "pih_attention_prefill_tcgen05", "pih_gemm_skinny", "pih_set_dependent_launch"):
+                     "pih_attention_prefill_tcgen05", "pih_gemm_skinny", "pih_set_dependent_launch", "pih_set_attention_cluster_merge"):
             getattr(lib, name).restype = c_int
         lib.pih_attention_scratch_floats.restype = c_ll
 
@@ -81,6 +82,13 @@ class CudaOps:
         (programmatic dependent launch; the default).  Returns the previous setting.  The setting is the
         library's, not this object's; CUDA graphs keep the setting they were captured under."""
         return bool(self.lib.pih_set_dependent_launch(1 if on else 0))
+
+    def set_attention_cluster_merge(self, on: bool) -> bool:
+        """Whether 2 to 8 splits of one (request, kv head) of the decode attention run as a thread-block
+        cluster that merges through distributed shared memory (the default) or through scratch memory and
+        tickets.  Returns the previous setting; the setting is the library's."""
+        self.cluster_attention = bool(on)
+        return bool(self.lib.pih_set_attention_cluster_merge(1 if on else 0))
 
     def _stream(self):
         return c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
@@ -264,7 +272,10 @@ class CudaOps:
         """Splits per request of the decode attention: as many as fill the 2 x 148 CTA slots of the GPU in
         one wave (small batches are cut finely so that enough CTAs pull bandwidth, large ones not at all).
         A function of the batch size only; the keys per split follow the context on the device."""
-        return max(1, min(64, (2 * 148) // max(1, num_requests * kv_heads)))
+        slots = (2 * 148) // max(1, num_requests * kv_heads)
+        if self.cluster_attention and self.tma_attention and slots > 8:
+            return 8                                   # one portable cluster per (request, kv head)
+        return max(1, min(64, slots))
 
     def reserve_attention_scratch(self, num_requests, dec_tok_cap, heads, kv_heads, head_dim, max_ctx) -> None:
         """Make the split kernel's scratch large enough (before a CUDA graph that uses it is

@@ -129,9 +129,11 @@ def test_linear_tcgen05_takes_strided_rows_and_refuses_what_tma_cannot_describe(
 
 
 @pytest.mark.parametrize("M", [1, 3, 8, 9, 16])
-@pytest.mark.parametrize("N,K", [(8, 32), (24, 64), (4096, 1024), (1024, 3072), (1000, 96), (6144, 1024)])
+@pytest.mark.parametrize("N,K", [(8, 32), (24, 64), (4096, 1024), (1024, 3072), (1000, 96), (6144, 1024),
+                                 (1000, 2080), (40, 2048), (1184, 4096)])
 def test_linear_skinny(ops, M, N, K):
-    """The few-rows product alone: every row count up to 16, widths that are no multiple of the tile."""
+    """The few-rows product alone: every row count up to 16, widths that are no multiple of the tile; few
+    columns with a long k go to pairs of blocks that split k (an odd number of k blocks among them)."""
     x = _rand((M, K), torch.bfloat16, 3)
     w = _rand((N, K), torch.bfloat16, 4, 0.1)
     out = ops.linear_skinny(x, w)
@@ -355,14 +357,18 @@ MMA_CASES = [c for c in ATTN_CASES if c[2] != 48] + [
 ]
 
 
-@pytest.fixture(params=["tcgen05+tma", "mma.sync+cp.async"])
+@pytest.fixture(params=["tcgen05+tma", "tcgen05+tma+tickets", "mma.sync+cp.async"])
 def attention_variant(request, ops):
-    """Both families of tensor-core attention kernels: tcgen05 tiles with TMA-fed splits, and the
-    mma.sync tile kernel with cp.async splits (which also serve the sizes the first does not take)."""
-    modern = request.param == "tcgen05+tma"
+    """The families of tensor-core attention kernels: tcgen05 tiles with TMA-fed splits that merge as a
+    thread-block cluster; the same with the splits merged through scratch memory and tickets (what more than
+    eight splits use); and the mma.sync tile kernel with cp.async splits (which also serve the sizes the
+    first does not take)."""
+    modern = request.param != "mma.sync+cp.async"
     ops.tcgen05_attention, ops.tma_attention = modern, modern
+    ops.set_attention_cluster_merge(request.param != "tcgen05+tma+tickets")
     yield request.param
     ops.tcgen05_attention, ops.tma_attention = True, True
+    ops.set_attention_cluster_merge(True)
 
 
 MMA_CASES += [
