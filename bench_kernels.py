@@ -78,6 +78,8 @@ def main() -> int:
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--no-flush", action="store_true")
     ap.add_argument("--impl", default="default", choices=["default", "tcgen05", "skinny", "library"])
+    ap.add_argument("--fused", default="none", choices=["none", "norm", "swiglu"],
+                    help="linear --impl skinny: with the fused residual add + RMSNorm prologue (and SwiGLU epilogue)")
     ap.add_argument("--tile-n", type=int, default=0)
     ap.add_argument("--chain", action="store_true", help="many calls on different inputs back to back in a CUDA graph: the time of one call inside a step")
     ap.add_argument("--chain-mb", type=float, default=200.0,
@@ -141,6 +143,10 @@ def main() -> int:
                          bytes=2 * (args.m * args.k + args.n * args.k + args.m * args.n))
             if args.impl == "tcgen05":
                 fn = lambda: ops.linear_tcgen05(x, w, tile_n=args.tile_n)
+            elif args.impl == "skinny" and args.fused != "none":
+                d = torch.randn(args.m, args.k, device=dev).to(bf)
+                nw = torch.ones(args.k, device=dev).to(bf)
+                fn = lambda: ops.linear_skinny(x, w, delta=d, norm_weight=nw, eps=1e-6, swiglu=args.fused == "swiglu")
             elif args.impl == "skinny":
                 fn = lambda: ops.linear_skinny(x, w)
             elif args.impl == "library":

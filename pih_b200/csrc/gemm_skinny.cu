@@ -7,7 +7,10 @@
 // the small work around the product itself:
 //
 //   prologue   optional residual add (h <- round(h + delta), written back once) and RMSNorm of the M rows,
-//              recomputed by every CTA from the 2 KB rows (cheaper than a kernel of its own and a round trip);
+//              recomputed by every CTA from the 2 KB rows (cheaper than a kernel of its own and a round trip):
+//              a warp per row, all of a lane's loads issued together, the squares summed in registers — one
+//              trip to memory, one warp reduction, one barrier (a loop that loaded, added and stored chunk by
+//              chunk cost 3 us per product, more than the separate norm kernel it replaced);
 //   product    mma.sync m16n8k16 with the TOKENS as the 16-row operand and 8 weight rows as the 8-column
 //              operand, so a warp needs only 8 weight rows; each thread reads 16 contiguous bytes of a weight
 //              row per 32-wide k block (the k order inside a block is permuted the same way for both operands,
@@ -74,56 +77,90 @@ skinny_gemm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
     }
   };
   int tile = blockIdx.x;
-  // the weight stream waits neither for the prologue nor for the kernel before this one (weights are never
-  // written): the first loads are in flight while that kernel's last blocks finish
+  // neither the weight stream nor the norm weights wait for the prologue or for the kernel before this one
+  // (no kernel writes weights): the first loads are in flight while that kernel's last blocks finish
   issue(tile, warp);
+  const int chunks = K / 8;                                // 16-byte chunks of a token row
+  constexpr int NWV = 8 * sizeof(NW) / 16;                 // 16-byte loads per 8 norm weights
+  uint4 wpre[4][NWV];                                      // norm weights of the lane's first four chunks
+  if (NORM) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int c = lane + 32 * j;
+#pragma unroll
+      for (int v = 0; v < NWV; ++v)
+        wpre[j][v] = c < chunks ? ldg_nc16(reinterpret_cast<const uint4*>(norm_w + c * 8) + v) : make_uint4(0, 0, 0, 0);
+    }
+  }
   wait_for_prior_kernels();
 
-  // prologue, once per CTA: token rows into shared memory, residual add, norm
-  const int chunks = K / 8;
-  for (int c = threadIdx.x; c < MR * chunks; c += SK_THREADS) {
-    const int row = c / chunks, ch = c % chunks;
-    uint4 v = make_uint4(0, 0, 0, 0);
-    if (row < M) {
-      v = *reinterpret_cast<const uint4*>(x + row * ldx + ch * 8);
-      if (delta != nullptr) {
-        const uint4 d = *reinterpret_cast<const uint4*>(delta + row * ldx + ch * 8);
-        __nv_bfloat16* ve = reinterpret_cast<__nv_bfloat16*>(&v);
-        const __nv_bfloat16* de = reinterpret_cast<const __nv_bfloat16*>(&d);
-#pragma unroll
-        for (int j = 0; j < 8; ++j) ve[j] = __float2bfloat16_rn(__bfloat162float(ve[j]) + __bfloat162float(de[j]));
-        // the sum goes to a buffer of its own: other CTAs are still reading x
-        if (blockIdx.x == 0) *reinterpret_cast<uint4*>(x_out + row * ldx + ch * 8) = v;
-      }
+  // prologue, once per block: warp w prepares token rows w, w + 8.  A lane takes chunks lane, lane + 32, ...,
+  // four at a time with their loads issued together; the residual sum is rounded and kept (one block writes
+  // it out), its squares are summed on the way, and the normed row replaces it in shared memory.
+  for (int row = warp; row < MR; row += SK_WARPS) {
+    __nv_bfloat16* xrow = xs + row * LDS;
+    if (row >= M) {
+      for (int c = lane; c < chunks; c += 32) *reinterpret_cast<uint4*>(xrow + c * 8) = make_uint4(0, 0, 0, 0);
+      continue;
     }
-    *reinterpret_cast<uint4*>(xs + row * LDS + ch * 8) = v;
-  }
-  __syncthreads();
-  if (NORM) {
-    for (int row = warp; row < M; row += SK_WARPS) {
-      float ss = 0.0f;
-      for (int c = lane; c < chunks; c += 32) {
-        const uint4 v = *reinterpret_cast<const uint4*>(xs + row * LDS + c * 8);
-        const __nv_bfloat16* ve = reinterpret_cast<const __nv_bfloat16*>(&v);
+    float ss = 0.0f;
+    for (int c0 = 0; c0 < chunks; c0 += 128) {
+      uint4 v[4], d[4];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const float f = __bfloat162float(ve[j]);
-          ss += f * f;
+      for (int j = 0; j < 4; ++j) {
+        const int c = c0 + lane + 32 * j;
+        v[j] = d[j] = make_uint4(0, 0, 0, 0);
+        if (c < chunks) {
+          v[j] = *reinterpret_cast<const uint4*>(x + row * ldx + c * 8);
+          if (delta != nullptr) d[j] = *reinterpret_cast<const uint4*>(delta + row * ldx + c * 8);
         }
       }
-      ss = warp_sum(ss);
-      const float scale = 1.0f / sqrtf(ss / static_cast<float>(K) + eps);
-      for (int c = lane; c < chunks; c += 32) {
-        uint4 v = *reinterpret_cast<const uint4*>(xs + row * LDS + c * 8);
-        __nv_bfloat16* ve = reinterpret_cast<__nv_bfloat16*>(&v);
 #pragma unroll
-        for (int j = 0; j < 8; ++j)
-          ve[j] = __float2bfloat16_rn((__bfloat162float(ve[j]) * scale) * to_float<NW>(norm_w[c * 8 + j]));
-        *reinterpret_cast<uint4*>(xs + row * LDS + c * 8) = v;
+      for (int j = 0; j < 4; ++j) {
+        const int c = c0 + lane + 32 * j;
+        if (c >= chunks) continue;
+        __nv_bfloat16* ve = reinterpret_cast<__nv_bfloat16*>(&v[j]);
+        if (delta != nullptr) {
+          const __nv_bfloat16* de = reinterpret_cast<const __nv_bfloat16*>(&d[j]);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) ve[e] = __float2bfloat16_rn(__bfloat162float(ve[e]) + __bfloat162float(de[e]));
+          // the sum goes to a buffer of its own: other blocks are still reading x
+          if (blockIdx.x == 0) *reinterpret_cast<uint4*>(x_out + row * ldx + c * 8) = v[j];
+        }
+        if (NORM) {
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            const float f = __bfloat162float(ve[e]);
+            ss += f * f;
+          }
+        }
+        *reinterpret_cast<uint4*>(xrow + c * 8) = v[j];
       }
     }
-    __syncthreads();
+    if (NORM) {
+      ss = warp_sum(ss);
+      const float scale = 1.0f / sqrtf(ss / static_cast<float>(K) + eps);
+      for (int c0 = 0; c0 < chunks; c0 += 128) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int c = c0 + lane + 32 * j;
+          if (c >= chunks) continue;
+          uint4 wq[NWV];
+#pragma unroll
+          for (int u = 0; u < NWV; ++u)
+            wq[u] = c0 == 0 ? wpre[j][u] : ldg_nc16(reinterpret_cast<const uint4*>(norm_w + c * 8) + u);
+          const NW* we = reinterpret_cast<const NW*>(wq);
+          uint4 v = *reinterpret_cast<const uint4*>(xrow + c * 8);    // the lane's own store
+          __nv_bfloat16* ve = reinterpret_cast<__nv_bfloat16*>(&v);
+#pragma unroll
+          for (int e = 0; e < 8; ++e)
+            ve[e] = __float2bfloat16_rn((__bfloat162float(ve[e]) * scale) * to_float<NW>(we[e]));
+          *reinterpret_cast<uint4*>(xrow + c * 8) = v;
+        }
+      }
+    }
   }
+  __syncthreads();
 
   const __nv_bfloat16* xa = xs + gid * LDS + 8 * q;                       // tokens gid (and gid + 8 when MR = 16)
   for (; tile < ntiles; tile += gridDim.x) {
@@ -257,6 +294,7 @@ extern "C" int pih_gemm_skinny(const void* x, const void* delta, void* x_out, in
   if (M <= 0 || N <= 0) return 0;
   if (M > 16 || K <= 0 || K % 32 || ldx % 8 || ldw % 8 || (swiglu && N % 16) ||
       (reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(W) & 15) ||
+      (reinterpret_cast<uintptr_t>(norm_w) & 15) ||
       (delta != nullptr && ((reinterpret_cast<uintptr_t>(delta) & 15) || x_out == nullptr || x_out == x)))
     return PIH_ERR_UNSUPPORTED;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
