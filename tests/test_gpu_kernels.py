@@ -151,7 +151,7 @@ def test_linear_skinny_fused_add_norm_and_swiglu(ops, M, norm_dtype):
     K, inter = 1024, 3072
     h = _rand((M, K), torch.bfloat16, 5, 2.0)
     d = _rand((M, K), torch.bfloat16, 6)
-    nw = (1 + 0.1 * torch.randn(K)).to(norm_dtype).to(DEV)
+    nw = (1 + 0.1 * torch.randn(K, generator=torch.Generator().manual_seed(9))).to(norm_dtype).to(DEV)
     gate = _rand((inter, K), torch.bfloat16, 7, 0.05)
     up = _rand((inter, K), torch.bfloat16, 8, 0.05)
     w = torch.stack([gate.reshape(-1, 8, K), up.reshape(-1, 8, K)], dim=1).reshape(2 * inter, K).contiguous()
@@ -170,7 +170,16 @@ def test_linear_skinny_fused_add_norm_and_swiglu(ops, M, norm_dtype):
     # ... and with SiLU-mul in the epilogue
     h3, act = ops.linear_skinny(h, w, delta=d, norm_weight=nw, eps=eps, swiglu=True)
     assert torch.equal(h3, h2) and act.shape == (M, inter)
-    torch.testing.assert_close(act.cpu().double(), act_ref, **tol)
+    # Kernel and reference add the same products in another order, so g and u may each land on the other
+    # side of a bf16 rounding boundary (one ulp = 2^-7 of the value's power of two), and so may the result.
+    # What one such flip does to silu(g) * u is bounded element by element: near g = -5 the slope of silu is
+    # four times silu / g, which a flat relative tolerance does not cover.
+    ulp = lambda t: torch.exp2(torch.floor(torch.log2(t.abs().clamp_min(1e-30))) - 7)
+    sig = torch.sigmoid(g_ref)
+    silu, dsilu = g_ref * sig, sig * (1 + g_ref * (1 - sig))
+    bound = ulp(g_ref) * (dsilu * u_ref).abs() + ulp(u_ref) * silu.abs() + ulp(act_ref) + 1e-6
+    err = (act.cpu().double() - act_ref).abs()
+    assert bool((err <= 1.05 * bound).all()), float((err / bound).max())
     # the unfused path of the same op agrees
     ops.skinny_max_rows = 0
     try:
@@ -179,7 +188,8 @@ def test_linear_skinny_fused_add_norm_and_swiglu(ops, M, norm_dtype):
     finally:
         ops.skinny_max_rows = 16
     assert torch.equal(h4b, h2)
-    torch.testing.assert_close(act2.float(), act.float(), **tol)
+    err2 = (act2.cpu().double() - act.cpu().double()).abs()
+    assert bool((err2 <= 2.1 * bound).all()), float((err2 / bound).max())
 
 
 def test_silu_mul_interleaved(ops):
