@@ -33,12 +33,34 @@ from .scheduler import Request, Scheduler
 RESULT_SCHEMA = "pih.token-generation-result.v1"
 
 
+class _InFlight:
+    """A step that has been queued on the device: its plan and the ids it samples, on the device and — by a
+    copy queued right behind the sampler, before any later step — in pinned host memory."""
+
+    def __init__(self, out, tokens):
+        self.out = out
+        self.tokens = tokens
+        self.host = self.copied = None
+        if tokens is not None and tokens.device.type == "cuda":
+            self.host = torch.empty(tokens.shape, dtype=tokens.dtype, pin_memory=True)
+            self.host.copy_(tokens, non_blocking=True)
+            self.copied = torch.cuda.Event()
+            self.copied.record()
+
+    def token_list(self) -> List[int]:
+        """The sampled ids; waits for this step only, not for steps queued after it."""
+        if self.host is None:
+            return self.tokens.tolist()
+        self.copied.synchronize()
+        return self.host.tolist()
+
+
 class Engine:
     def __init__(self, model_dir: str, dtype: str = "bfloat16", *, device: str = "cuda:0",
                  page_size: int = 16, max_cache_tokens: Optional[int] = None,
                  maximum_batch_sequences: int = 32, maximum_batch_tokens: int = 4096,
                  maximum_context_tokens: Optional[int] = None, cuda_graphs: bool = True,
-                 ops: Optional[object] = None):
+                 run_ahead: bool = True, ops: Optional[object] = None):
         from ..config.registry import load_config
         self.model_dir = model_dir
         self.device = torch.device(device)
@@ -56,6 +78,9 @@ class Engine:
         self.sampler = Sampler(self.rt.ops, spec.vocab, self.device)
         self._ids = itertools.count()
         self._live: Dict[Hashable, Request] = {}
+        self.run_ahead = run_ahead       # plan and queue the next decode step before this one's ids are read
+        self._inflight: Optional[_InFlight] = None
+        self.steps_planned_ahead = 0
 
     # -- the reference client's small calls ---------------------------------------
     def ready(self) -> bool:
@@ -87,35 +112,63 @@ class Engine:
             self._live.pop(rid, None)
 
     def has_work(self) -> bool:
-        return self.scheduler.has_work()
+        return self._inflight is not None or self.scheduler.has_work()
 
-    def step(self) -> List[Request]:
-        """One scheduler turn and one model step; returns the requests that
-        produced a token in it (finished ones have ``status == 'finished'``)."""
-        out = self.scheduler.schedule()
-        for req in out.failed:
-            self._live.pop(req.rid, None)
-        if not out.scheduled:
-            return list(out.failed)
+    # -- one step ---------------------------------------------------------------------
+    # A step's sampled ids are needed on the host only to book them and to see who stops.  So while
+    # step N runs, step N + 1 is planned (Scheduler.plan_ahead: every request decodes one more token),
+    # its batch is built and it is queued behind N with its input ids fed on the device from N's
+    # samples; only then does the host wait for N's ids.  The device never waits for the scheduler, the
+    # batch builder or the copy of the ids.  A request that N's token stops has one token too many
+    # computed in N + 1; it is dropped.  Whenever the plain path has a decision to make (admission, a
+    # request at its length limit, pages that run out) nothing is planned ahead.
+    def _launch(self, out, feed=None) -> "_InFlight":
+        pending = 1 if feed is not None else 0
         entries = [StepEntry(s.request.rid, s.tokens, [len(s.tokens) - 1] if s.samples else [])
                    for s in out.scheduled]
-        logits = self.runner.step(entries)
+        logits = self.runner.step(entries, token_feed=feed)
         sampling = [s.request for s in out.scheduled if s.samples]
-        sampled: List[Optional[int]] = [None] * len(out.scheduled)
+        tokens = None
         if sampling:
-            tokens = self.sampler.sample(
-                logits, [r.params for r in sampling], [len(r.outputs) for r in sampling],
-                [self.scheduler.suppressed_ids(r) for r in sampling])
-            it = iter(tokens)
+            tokens = self.sampler.sample_on_device(
+                logits, [r.params for r in sampling], [len(r.outputs) + pending for r in sampling],
+                [self.scheduler.suppressed_ids(r, pending) for r in sampling])
+        return _InFlight(out, tokens)
+
+    def _collect(self, flight: "_InFlight") -> List[Request]:
+        out = flight.out
+        sampled: List[Optional[int]] = [None] * len(out.scheduled)
+        if flight.tokens is not None:
+            it = iter(flight.token_list())             # waits for this step
             for i, s in enumerate(out.scheduled):
                 if s.samples:
                     sampled[i] = next(it)
+        live = [s.request for s in out.scheduled if s.samples and s.request.status != "finished"]
         self.scheduler.update(out, sampled)
-        progressed = [s.request for s in out.scheduled if s.samples] + list(out.failed)
+        progressed = live + list(out.failed)
         for req in progressed:
             if req.status == "finished":
                 self._live.pop(req.rid, None)
         return progressed
+
+    def step(self) -> List[Request]:
+        """One scheduler turn and one model step; returns the requests that
+        produced a token in it (finished ones have ``status == 'finished'``)."""
+        flight = self._inflight
+        self._inflight = None
+        if flight is None:
+            out = self.scheduler.schedule()
+            for req in out.failed:
+                self._live.pop(req.rid, None)
+            if not out.scheduled:
+                return list(out.failed)
+            flight = self._launch(out)
+        if self.run_ahead and flight.tokens is not None:
+            plan = self.scheduler.plan_ahead(flight.out)
+            if plan is not None:
+                self._inflight = self._launch(plan, feed=flight.tokens)
+                self.steps_planned_ahead += 1
+        return self._collect(flight)
 
     # -- whole generations ------------------------------------------------------------
     @staticmethod

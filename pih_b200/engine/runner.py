@@ -77,16 +77,21 @@ class ModelRunner:
                   for i in range(self.num_entries)]
         return self.model.forward(batch, caches)
 
-    def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+    def step(self, entries: Sequence[StepEntry], token_feed: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
         """Run ``entries`` as one batch; returns fp32 logits ``[wanted, vocab]``
         in the order of the entries and of their ``want`` lists, or None.
 
-        The returned tensor may be reused by the next step: read it before
+        ``token_feed``: an int32 tensor on the device with one id per row of the step, which replaces the
+        entries' token ids on the device — the ids that an earlier step sampled and that the host has not
+        read yet.
+
+        The returned tensor may be reused by the next step: use it (or queue the kernel that does) before
         calling ``step`` again."""
         if self._graphable(entries):
-            return self._graph_step(entries)
+            return self._graph_step(entries, token_feed)
         batch = self.prepare(entries)
         try:
+            self._feed(batch, token_feed)
             logits = self.run(batch)
         except Exception:
             for e in entries:
@@ -123,7 +128,14 @@ class ModelRunner:
                 return ("portion", len(e.tokens), len(want))
         return None
 
-    def _graph_step(self, entries) -> Optional[torch.Tensor]:
+    @staticmethod
+    def _feed(batch: StepBatch, token_feed: Optional[torch.Tensor]) -> None:
+        if token_feed is not None:
+            if token_feed.shape != batch.token_ids.shape or token_feed.dtype != batch.token_ids.dtype:
+                raise ValueError("token_feed needs one int32 id per row of the step")
+            batch.token_ids.copy_(token_feed)          # queued behind the batch's own copy to the device
+
+    def _graph_step(self, entries, token_feed=None) -> Optional[torch.Tensor]:
         kind = self._graph_key(entries)
         for e in entries:
             if not self.cache.has_request(e.rid):
@@ -147,12 +159,14 @@ class ModelRunner:
                 # first sight of this portion shape: run it as it is; capture if it comes again
                 self._sightings[key] = 1
                 batch = self.builder.build(entries, self.cache)
+                self._feed(batch, token_feed)
                 logits = self.run(batch)
             elif state is None:
-                state = self._capture(entries, key, width)
+                state = self._capture(entries, key, width, token_feed)
                 logits = state["logits"]
             else:
-                self.builder.build(entries, self.cache, width=width, device_buffer=state["buffer"])
+                batch = self.builder.build(entries, self.cache, width=width, device_buffer=state["buffer"])
+                self._feed(batch, token_feed)
                 state["graph"].replay()
                 self._count_launches(state["launches"])
                 logits = state["logits"]
@@ -170,13 +184,14 @@ class ModelRunner:
         if hasattr(ops, "launches"):
             ops.launches += n
 
-    def _capture(self, entries, key, width):
+    def _capture(self, entries, key, width, token_feed=None):
         G = len(self.cache.groups)
         T = sum(len(e.tokens) for e in entries)
         B = len(entries)
         S = sum(len(e.want) for e in entries)
         buffer = torch.empty(self.builder.buffer_size(T, B, S, G, width), dtype=torch.int32, device=self.device)
         batch = self.builder.build(entries, self.cache, width=width, device_buffer=buffer)
+        self._feed(batch, token_feed)
         max_ctx = width * self.cache.page_size
         ops = self.model.rt.ops
         if key[0] == "decode":

@@ -201,6 +201,33 @@ class Scheduler:
             budget -= n
         return out
 
+    def plan_ahead(self, prev: SchedulerOutput) -> Optional[SchedulerOutput]:
+        """The step after ``prev``, planned while ``prev`` is still running on the device and its sampled
+        tokens are not known yet: every request of ``prev`` decodes one more token, which the device feeds
+        from ``prev``'s samples (the entries carry a placeholder id, in ``prev``'s order).  Returns None
+        whenever the plain path has a decision to make, and then nothing has changed: a request waits, a
+        request of ``prev`` did not sample or ends with ``prev``'s token by length, a running request was
+        left out of ``prev``, or the pool cannot hold one more token of each.  A request that ``prev``'s
+        token turns out to stop is only found out afterwards: the token this step computes for it is then
+        dropped by ``update``, and its pages are back in the pool before any later step can use them."""
+        if self.waiting or prev.preempted or prev.failed or not prev.scheduled:
+            return None
+        if len(prev.scheduled) != len(self.running) or len(prev.scheduled) > self.max_batch_tokens:
+            return None
+        asks = _Granted(self.cache)
+        scheduled = []
+        for s in prev.scheduled:
+            req = s.request
+            if not s.samples or req.status != "running":
+                return None
+            if len(req.outputs) + 1 >= req.params.max_tokens:     # prev's token is its last
+                return None
+            if not asks.fits(req.rid, 1):
+                return None
+            asks.grant(req.rid, 1)
+            scheduled.append(Scheduled(req, [0], True))
+        return SchedulerOutput(scheduled, [], [])
+
     @staticmethod
     def _next_tokens(req: Request, start: int, n: int) -> List[int]:
         """Tokens start..start+n-1 of prompt + outputs, without building the whole list."""
@@ -227,6 +254,8 @@ class Scheduler:
         finished = []
         for s, tok in zip(out.scheduled, sampled):
             req = s.request
+            if req.status == "finished":
+                continue                   # it ended while this step was in flight (planned ahead): dropped
             req.num_computed += len(s.tokens)
             if not s.samples:
                 continue
@@ -263,10 +292,11 @@ class Scheduler:
                 return req
         return None
 
-    def suppressed_ids(self, req: Request) -> List[int]:
+    def suppressed_ids(self, req: Request, pending: int = 0) -> List[int]:
         """Stop ids may not be sampled before ``minimum_new_tokens`` tokens exist
-        (plugins/model-qwen3/controller_packed_driver.cpp:114-143)."""
-        if len(req.outputs) >= req.params.minimum_new_tokens:
+        (plugins/model-qwen3/controller_packed_driver.cpp:114-143).  ``pending``: tokens sampled on the
+        device that are not in ``outputs`` yet."""
+        if len(req.outputs) + pending >= req.params.minimum_new_tokens:
             return []
         ids = set(req.params.stop_token_ids)
         if not req.params.ignore_eos:

@@ -35,11 +35,16 @@ class Sampler:
 
     def sample(self, logits: torch.Tensor, params: Sequence[SamplingParams], ordinals: Sequence[int],
                suppressed: Sequence[Sequence[int]]) -> List[int]:
+        return self.sample_on_device(logits, params, ordinals, suppressed).tolist()
+
+    def sample_on_device(self, logits: torch.Tensor, params: Sequence[SamplingParams], ordinals: Sequence[int],
+                         suppressed: Sequence[Sequence[int]]) -> torch.Tensor:
+        """The sampled ids as an int32 tensor on the device, without waiting for them."""
         S = logits.shape[0]
         if not (len(params) == len(ordinals) == len(suppressed) == S):
             raise ValueError("one set of sampling parameters per row of logits is needed")
         if all(p.greedy for p in params) and not any(suppressed):
-            return self.ops.argmax(logits).tolist()
+            return self.ops.argmax(logits)
         fl = torch.empty(S, 2, dtype=torch.float32)
         it = torch.empty(S, 6 + MAX_SUPPRESSED, dtype=torch.int32)
         for i, (p, o, sup) in enumerate(zip(params, ordinals, suppressed)):
@@ -51,5 +56,4 @@ class Sampler:
             row = [k, p.seed & 0xFFFFFFFF, (p.seed >> 32) & 0xFFFFFFFF, o & 0xFFFFFFFF, (o >> 32) & 0xFFFFFFFF,
                    len(sup)] + list(sup) + [-1] * (MAX_SUPPRESSED - len(sup))
             it[i] = torch.tensor([v - (1 << 32) if v >= (1 << 31) else v for v in row], dtype=torch.int32)
-        tokens = self.ops.sample(logits, fl.to(self.device), it.to(self.device))
-        return tokens.tolist()
+        return self.ops.sample(logits, fl.to(self.device), it.to(self.device))

@@ -1,0 +1,82 @@
+"""Planning the next decode step while the current one runs must not change a single token.
+
+Runs the engine on the CPU with the torch stand-in for the kernels: the same requests with and without
+run-ahead — different lengths, a stop token in the middle of a generation, temperature sampling, a request
+that arrives late, one that is cancelled, and a pool so small that requests are preempted."""
+import pytest
+
+from fake_ops import FakeOps
+from pih_b200.engine import Engine
+from pih_b200.sampling import SamplingParams
+import traces
+
+
+def _engine(model_dir, run_ahead, **kw):
+    args = dict(device="cpu", ops=FakeOps(), page_size=8, max_cache_tokens=1024, maximum_batch_sequences=4,
+                maximum_batch_tokens=16, run_ahead=run_ahead)
+    args.update(kw)
+    return Engine(model_dir, "float32", **args)
+
+
+def _prompts(vocab, lengths, seed):
+    return list(traces.make_requests(vocab, lengths, seed=seed).values())
+
+
+@pytest.mark.parametrize("temperature", [0.0, 0.8])
+def test_run_ahead_gives_the_same_tokens(model_dirs, tiny_configs, temperature):
+    prompts = _prompts(tiny_configs["B"]["vocab_size"], [3, 20, 9, 33], seed=5)
+    per_prompt = [dict(max_tokens=m) for m in (14, 5, 9, 1)]
+    kw = dict(temperature=temperature, seed=3, ignore_eos=True, parameters_per_prompt=per_prompt)
+    plain = _engine(model_dirs["B"], False)
+    ahead = _engine(model_dirs["B"], True)
+    want = plain.complete_batch(prompts, **kw)
+    got = ahead.complete_batch(prompts, **kw)
+    assert got == want
+    assert plain.steps_planned_ahead == 0 and ahead.steps_planned_ahead >= 5
+    for e in (plain, ahead):
+        e.cache.check()
+        assert all(f == e.cache.num_pages for f in e.cache.num_free_pages())
+        assert not e.has_work()
+
+
+def test_a_stop_token_found_late_drops_the_token_computed_ahead(model_dirs, tiny_configs):
+    prompts = _prompts(tiny_configs["A"]["vocab_size"], [12, 7], seed=8)
+    free = _engine(model_dirs["A"], False, page_size=16).complete_batch(prompts, max_tokens=12, ignore_eos=True)
+    stop = free[0]["token_ids"][5]                     # the first request produces this id as its sixth token at the latest
+    kw = dict(max_tokens=12, ignore_eos=True, stop_token_ids=[stop])
+    want = _engine(model_dirs["A"], False, page_size=16).complete_batch(prompts, **kw)
+    ahead = _engine(model_dirs["A"], True, page_size=16)
+    got = ahead.complete_batch(prompts, **kw)
+    assert got == want and want[0]["finish_reason"] == "stop" and len(want[0]["token_ids"]) <= 6
+    assert ahead.steps_planned_ahead > 0
+    ahead.cache.check()
+    assert all(f == ahead.cache.num_pages for f in ahead.cache.num_free_pages())
+
+
+def test_run_ahead_with_late_arrival_cancel_and_preemption(model_dirs, tiny_configs):
+    vocab = tiny_configs["B"]["vocab_size"]
+    prompts = _prompts(vocab, [30, 25, 28, 6], seed=13)
+
+    def run(run_ahead):
+        # 16 pages of 8: the three long requests (8 + 7 + 8 pages at their ends) do not fit together
+        e = _engine(model_dirs["B"], run_ahead, max_cache_tokens=128, maximum_batch_tokens=32)
+        reqs = [e._live[e.submit(p, SamplingParams(max_tokens=30, ignore_eos=True))] for p in prompts[:3]]
+        steps = 0
+        late = victim = None
+        while e.has_work():
+            e.step()
+            steps += 1
+            if steps == 4:
+                late = e._live[e.submit(prompts[3], SamplingParams(max_tokens=6, ignore_eos=True))]
+            if steps == 16:
+                victim = reqs[1]
+                e.cancel(victim.rid)
+        e.cache.check()
+        assert all(f == e.cache.num_pages for f in e.cache.num_free_pages())
+        outs = [(r.outputs if r is not victim else None, r.finish_reason) for r in reqs + [late]]
+        return outs, sum(r.preemptions for r in reqs + [late]), e.steps_planned_ahead
+
+    want, preempted, _ = run(False)
+    got, preempted_ahead, planned = run(True)
+    assert preempted > 0 and planned > 0
+    assert got == want
