@@ -48,11 +48,11 @@ constexpr int SK_UN = 4;                 // k blocks in flight per warp unless t
 // MR: rows of the token operand kept in shared memory (8 or 16).  TILES: 8-row weight tiles per warp (1 or 2).
 // UN: k blocks (of 32) whose weight loads a warp keeps in flight.
 // Persistent: a CTA prepares the token rows once and then walks over weight tiles blockIdx.x, + gridDim.x, ...
-template <int MR, int TILES, int UN, bool NORM, bool SWIGLU, typename NW>
+template <int MR, int TILES, int UN, bool NORM, bool SWIGLU, typename NW, typename OT>
 __global__ void __launch_bounds__(SK_THREADS)
 skinny_gemm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ delta,
                    __nv_bfloat16* __restrict__ x_out, const NW* __restrict__ norm_w, float eps,
-                   const __nv_bfloat16* __restrict__ W, __nv_bfloat16* __restrict__ out, int M, int N, int K,
+                   const __nv_bfloat16* __restrict__ W, OT* __restrict__ out, int M, int N, int K,
                    long long ldx, long long ldw, long long ldo) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int LDS = K + 8;                                   // padded row: 16-byte loads of 8 rows hit 8 bank groups
@@ -214,7 +214,7 @@ skinny_gemm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
         }
         g = __bfloat162float(__float2bfloat16_rn(g));
         u = __bfloat162float(__float2bfloat16_rn(u));
-        out[tok * ldo + n0 / 2 + col] = __float2bfloat16_rn((g / (1.0f + expf(-g))) * u);
+        out[tok * ldo + n0 / 2 + col] = from_float<OT>((g / (1.0f + expf(-g))) * u);
       }
     } else {
       for (int e = threadIdx.x; e < TILES * 128; e += SK_THREADS) {
@@ -223,7 +223,7 @@ skinny_gemm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
           float s = 0.0f;
 #pragma unroll
           for (int w = 0; w < SK_WARPS; ++w) s += red[(w * TILES + t) * 128 + tok * 8 + col];
-          out[tok * ldo + n0 + t * 8 + col] = __float2bfloat16_rn(s);
+          out[tok * ldo + n0 + t * 8 + col] = from_float<OT>(s);
         }
       }
     }
@@ -231,7 +231,7 @@ skinny_gemm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
   }
 }
 
-template <int MR, int TILES, int UN, bool NORM, bool SWIGLU, typename NW>
+template <int MR, int TILES, int UN, bool NORM, bool SWIGLU, typename NW, typename OT = __nv_bfloat16>
 static int launch_skinny(const void* x, const void* delta, void* x_out, const void* norm_w, float eps, const void* W,
                          void* out, int M, int N, int K, long long ldx, long long ldw, long long ldo,
                          cudaStream_t s) {
@@ -239,7 +239,7 @@ static int launch_skinny(const void* x, const void* delta, void* x_out, const vo
   static int smem_set = 0;                                 // per instance
   if (smem > 227 * 1024) return PIH_ERR_UNSUPPORTED;
   if (smem > 48 * 1024 && smem_set < smem) {
-    cudaError_t e = cudaFuncSetAttribute(skinny_gemm_kernel<MR, TILES, UN, NORM, SWIGLU, NW>,
+    cudaError_t e = cudaFuncSetAttribute(skinny_gemm_kernel<MR, TILES, UN, NORM, SWIGLU, NW, OT>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return static_cast<int>(e);
     smem_set = smem;
@@ -253,10 +253,10 @@ static int launch_skinny(const void* x, const void* delta, void* x_out, const vo
   }
   const int ntiles = (N + 8 * TILES - 1) / (8 * TILES);
   const int grid = ntiles < 2 * sms ? ntiles : 2 * sms;
-  launch_kernel(skinny_gemm_kernel<MR, TILES, UN, NORM, SWIGLU, NW>, dim3(grid), dim3(SK_THREADS), smem, s, 
+  launch_kernel(skinny_gemm_kernel<MR, TILES, UN, NORM, SWIGLU, NW, OT>, dim3(grid), dim3(SK_THREADS), smem, s, 
       static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(delta),
       static_cast<__nv_bfloat16*>(x_out), static_cast<const NW*>(norm_w), eps,
-      static_cast<const __nv_bfloat16*>(W), static_cast<__nv_bfloat16*>(out), M, N, K, ldx, ldw, ldo);
+      static_cast<const __nv_bfloat16*>(W), static_cast<OT*>(out), M, N, K, ldx, ldw, ldo);
   PIH_LAUNCH_CHECK();
   return 0;
 }
@@ -308,4 +308,22 @@ extern "C" int pih_gemm_skinny(const void* x, const void* delta, void* x_out, in
   if (norm_dtype == PIH_BF16) return M <= 8 ? PIH_SKINNY(8, true, __nv_bfloat16) : PIH_SKINNY(16, true, __nv_bfloat16);
 #undef PIH_SKINNY
   return PIH_ERR_BAD_ARGUMENT;
+}
+
+// The same product with 32-bit output and nothing fused: out[M, N] (float) = x[M, K] . W[N, K]^T, for the LM
+// head of a decode step (the reference gives the head an fp32 output, src/backend/cuda/gemm_plan.cpp:111-113).
+extern "C" int pih_gemm_skinny_f32out(const void* x, const void* W, void* out, int M, int N, int K, long long ldx,
+                                      long long ldw, long long ldo, void* stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if (M > 16 || K <= 0 || K % 32 || ldx % 8 || ldw % 8 || (reinterpret_cast<uintptr_t>(x) & 15) ||
+      (reinterpret_cast<uintptr_t>(W) & 15))
+    return PIH_ERR_UNSUPPORTED;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const bool wide = N >= 148 * 16;
+#define PIH_SKINNY_F32(MR, TILES, UN) \
+  launch_skinny<MR, TILES, UN, false, false, float, float>(x, nullptr, nullptr, nullptr, 0.0f, W, out, M, N, K, ldx, ldw, ldo, s)
+  if (wide) return M <= 8 ? PIH_SKINNY_F32(8, 2, SK_UN) : PIH_SKINNY_F32(16, 2, SK_UN);
+  if (K > 32 * SK_WARPS * SK_UN) return M <= 8 ? PIH_SKINNY_F32(8, 1, 2 * SK_UN) : PIH_SKINNY_F32(16, 1, 2 * SK_UN);
+  return M <= 8 ? PIH_SKINNY_F32(8, 1, SK_UN) : PIH_SKINNY_F32(16, 1, SK_UN);
+#undef PIH_SKINNY_F32
 }

@@ -73,7 +73,8 @@ class CudaOps:
         for name in ("pih_embedding", "pih_rmsnorm", "pih_qk_norm_rope_kv_write", "pih_silu_mul",
                      "pih_gather_rows", "pih_gemm_simt", "pih_paged_attention_generic", "pih_argmax",
                      "pih_sample", "pih_paged_attention_mma", "pih_gemm_tcgen05", "pih_make_kv_tensor_map",
-                     "pih_attention_prefill_tcgen05", "pih_gemm_skinny", "pih_set_dependent_launch", "pih_set_attention_cluster_merge"):
+                     "pih_attention_prefill_tcgen05", "pih_gemm_skinny", "pih_set_dependent_launch", "pih_set_attention_cluster_merge",
+                     "pih_gemm_skinny_f32out"):
             getattr(lib, name).restype = c_int
         lib.pih_attention_scratch_floats.restype = c_ll
 
@@ -149,6 +150,13 @@ class CudaOps:
         if out_dtype == torch.bfloat16 and M <= self.skinny_max_rows:
             out = self.linear_skinny(x, w)
             if out is not None:
+                return out
+        if out_dtype == torch.float32 and M <= self.skinny_max_rows and K % 32 == 0:
+            out = torch.empty(M, N, dtype=torch.float32, device=x.device)
+            rc = self.lib.pih_gemm_skinny_f32out(_ptr(x), _ptr(w), _ptr(out), M, N, K, c_ll(x.stride(0)),
+                                                 c_ll(w.stride(0)), c_ll(N), self._stream())
+            if rc != -2:
+                self._check(rc, "gemm_skinny_f32out")
                 return out
         if self.tcgen05_min_rows is not None and M >= self.tcgen05_min_rows:
             out = self.linear_tcgen05(x, w, out_dtype)

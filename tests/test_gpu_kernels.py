@@ -84,7 +84,8 @@ def test_rmsnorm_keeps_a_32bit_weight_with_a_bf16_stream(ops):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("M,N,K", [(1, 7, 5), (37, 130, 96), (64, 64, 64), (130, 257, 1027), (3, 1000, 33)])
+@pytest.mark.parametrize("M,N,K", [(1, 7, 5), (37, 130, 96), (64, 64, 64), (130, 257, 1027), (3, 1000, 33),
+                                   (5, 3001, 96), (16, 151, 1024), (9, 2500, 2080)])   # few rows: the fused kernel, fp32 out too
 def test_linear(ops, dtype, M, N, K):
     x = _rand((M, K), dtype, 3)
     w = _rand((N, K), dtype, 4, 0.1)
