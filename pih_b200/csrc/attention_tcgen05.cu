@@ -27,7 +27,8 @@ namespace pih {
 
 constexpr int TQ = 128;                 // packed rows per tile
 constexpr int TK = 128;                 // keys per tile
-constexpr int KV_STAGES = 2;
+constexpr int KV_STAGES = TK == 64 ? 4 : 2;
+constexpr int P_BUFS = TK == 64 ? 2 : 1;  // P tiles in shared memory (what fits beside Q and the K/V rings)
 constexpr float kLog2e5 = 1.4426950408889634f;
 constexpr float kRescaleThreshold = 8.0f;   // log2 units
 
@@ -138,40 +139,50 @@ __device__ __forceinline__ void cp16(void* smem, const void* gmem, int bytes) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(smem_u32(smem)), "l"(gmem), "r"(bytes));
 }
 
-template <int D>
+template <int D, int SPLIT>
 struct PrefillSmem {
   static constexpr int PANELS = D / 64;
-  static constexpr int PANEL_BYTES = 128 * 128;                 // 128 rows x 128 bytes
+  static constexpr int PANEL_BYTES = TQ * 128;                  // a panel of Q or P: 128 rows x 128 bytes
+  static constexpr int KV_PANEL_BYTES = TK * 128;               // a panel of K or V: TK keys x 128 bytes
   alignas(1024) unsigned char q[PANELS * PANEL_BYTES];
-  alignas(1024) unsigned char k[KV_STAGES][PANELS * PANEL_BYTES];
-  alignas(1024) unsigned char v[KV_STAGES][PANELS * PANEL_BYTES];
-  alignas(1024) unsigned char p[2 * PANEL_BYTES];               // two panels of 64 keys
-  alignas(8) uint64_t q_full, o_ready, p_full, p_empty;
+  alignas(1024) unsigned char k[KV_STAGES][PANELS * KV_PANEL_BYTES];
+  alignas(1024) unsigned char v[KV_STAGES][PANELS * KV_PANEL_BYTES];
+  alignas(1024) unsigned char p[P_BUFS][(TK / 64) * PANEL_BYTES];   // TK / 64 panels of 64 keys each
+  alignas(8) uint64_t q_full, o_ready, p_full[P_BUFS], p_empty[P_BUFS];
   alignas(8) uint64_t k_full[KV_STAGES], k_empty[KV_STAGES], v_full[KV_STAGES], v_empty[KV_STAGES];
   alignas(8) uint64_t s_full[2], s_empty[2];
-  float xmax[2][2][128];                                        // [tile parity][column half][row] maxima
-  float xsum[2][128];                                           // row sums of the two column halves
+  float xmax[2][SPLIT][128];                                    // [tile parity][column part][row] maxima
+  float xsum[SPLIT][128];                                       // row sums of the column parts
   uint32_t tmem_base;
 };
 
-constexpr int kSoftmaxThreads = 256;     // warps 0-7: two threads per row, one per half of the key columns
-constexpr int kProducerWarp = 8, kMmaWarp = 9;
-
-__device__ __forceinline__ void softmax_sync() { asm volatile("bar.sync 1, 256;\n" ::: "memory"); }
-// the two softmax warps (w and w + 4) that share tensor-memory lanes 32 quarter .. 32 quarter + 31
-__device__ __forceinline__ void pair_sync(int quarter) {
-  asm volatile("bar.sync %0, 64;\n" ::"r"(2 + quarter) : "memory");
+// SPLIT threads share a row (= tensor-memory lane), each with 128 / SPLIT of the key columns and D / SPLIT of
+// the output columns: warps 0 .. 4 SPLIT - 1 are softmax warps, then the producer warp, then the MMA warp.
+template <int THREADS> __device__ __forceinline__ void softmax_sync() {
+  asm volatile("bar.sync 1, %0;\n" ::"n"(THREADS) : "memory");
+}
+// the SPLIT softmax warps (w, w + 4, ...) that share tensor-memory lanes 32 quarter .. 32 quarter + 31
+template <int THREADS> __device__ __forceinline__ void row_group_sync(int quarter) {
+  asm volatile("bar.sync %0, %1;\n" ::"r"(2 + quarter), "n"(THREADS) : "memory");
 }
 
 // One CTA works through up to two row tiles of its (request, kv head): a long one (late rows, many keys)
 // and its short mirror image, so that every CTA has about the same number of key tiles.
-template <int D>
-__global__ void __launch_bounds__(320)
+template <int D, int SPLIT>
+__global__ void __launch_bounds__(128 * SPLIT + 64)
 attn_prefill_tcgen05_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap kv_map) {
   wait_for_prior_kernels();
-  using Smem = PrefillSmem<D>;
+  using Smem = PrefillSmem<D, SPLIT>;
+  constexpr int kSoftmaxThreads = 128 * SPLIT;
+  constexpr int kSoftmaxWarps = 4 * SPLIT;
+  constexpr int kProducerWarp = 4 * SPLIT, kMmaWarp = 4 * SPLIT + 1;
+  constexpr int CW = TK / SPLIT;                                  // key columns of a softmax thread
+  constexpr int OW = D / SPLIT;                                   // output columns of a softmax thread
+  static_assert(CW == 64 || CW == 32, "a thread reads its scores with one tcgen05.ld of 32 or 64 columns");
+  static_assert(OW % 32 == 0, "a thread rescales and stores its output columns 32 at a time");
   constexpr int PANELS = Smem::PANELS;
   constexpr int PANEL_BYTES = Smem::PANEL_BYTES;
+  constexpr int KV_PANEL_BYTES = Smem::KV_PANEL_BYTES;
   extern __shared__ unsigned char smem_raw[];
   Smem& sm = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
 
@@ -209,15 +220,34 @@ attn_prefill_tcgen05_kernel(const PrefillParams p, const __grid_constant__ CUten
     // last MMA, and every load had been consumed by an MMA)
     if (threadIdx.x == 0) {
       if (item > 0) {
-        uint64_t* all[] = {&sm.q_full, &sm.o_ready, &sm.p_full, &sm.p_empty, &sm.k_full[0], &sm.k_full[1],
-                           &sm.k_empty[0], &sm.k_empty[1], &sm.v_full[0], &sm.v_full[1], &sm.v_empty[0],
-                           &sm.v_empty[1], &sm.s_full[0], &sm.s_full[1], &sm.s_empty[0], &sm.s_empty[1]};
-        for (uint64_t* bar : all) asm volatile("mbarrier.inval.shared::cta.b64 [%0];\n" ::"r"(smem_u32(bar)) : "memory");
+        auto inval = [](uint64_t* bar) {
+          asm volatile("mbarrier.inval.shared::cta.b64 [%0];\n" ::"r"(smem_u32(bar)) : "memory");
+        };
+        inval(&sm.q_full);
+        inval(&sm.o_ready);
+        for (int s = 0; s < KV_STAGES; ++s) {
+          inval(&sm.k_full[s]);
+          inval(&sm.k_empty[s]);
+          inval(&sm.v_full[s]);
+          inval(&sm.v_empty[s]);
+        }
+        for (int b = 0; b < 2; ++b) {
+          inval(&sm.s_full[b]);
+          inval(&sm.s_empty[b]);
+        }
+        for (int b = 0; b < P_BUFS; ++b) {
+          inval(&sm.p_full[b]);
+          inval(&sm.p_empty[b]);
+        }
       }
-      mbar_init(&sm.q_full, kSoftmaxThreads);
+      // the softmax warps arrive once per warp (lane 0, after the warp has synchronised): 256 arrivals of
+      // single threads on one barrier word cost more than the tile's arithmetic
+      mbar_init(&sm.q_full, kSoftmaxWarps);
       mbar_init(&sm.o_ready, 1);
-      mbar_init(&sm.p_full, kSoftmaxThreads);
-      mbar_init(&sm.p_empty, 1);
+      for (int b = 0; b < P_BUFS; ++b) {
+        mbar_init(&sm.p_full[b], kSoftmaxWarps);
+        mbar_init(&sm.p_empty[b], 1);
+      }
       for (int s = 0; s < KV_STAGES; ++s) {
         mbar_init(&sm.k_full[s], 1);
         mbar_init(&sm.k_empty[s], 1);
@@ -226,7 +256,7 @@ attn_prefill_tcgen05_kernel(const PrefillParams p, const __grid_constant__ CUten
       }
       for (int b = 0; b < 2; ++b) {
         mbar_init(&sm.s_full[b], 1);
-        mbar_init(&sm.s_empty[b], kSoftmaxThreads);
+        mbar_init(&sm.s_empty[b], kSoftmaxWarps);
       }
       mbar_init_fence();
     }
@@ -259,24 +289,24 @@ attn_prefill_tcgen05_kernel(const PrefillParams p, const __grid_constant__ CUten
         if (use > 0) alive = mbar_wait(&sm.k_empty[s], (use - 1) & 1, p.error);
         alive = __all_sync(0xffffffffu, alive);
         if (!alive) break;
-        if (lane == 0) mbar_expect_tx(&sm.k_full[s], PANELS * PANEL_BYTES);
+        if (lane == 0) mbar_expect_tx(&sm.k_full[s], PANELS * KV_PANEL_BYTES);
         __syncwarp();
         if (lane < pages_per_tile) {
           const int zk = (page * 2) * p.kv_heads + g;
 #pragma unroll
           for (int pn = 0; pn < PANELS; ++pn)
-            tma_load_3d(sm.k[s] + pn * PANEL_BYTES + off, &kv_map, pn * 64, 0, zk, &sm.k_full[s]);
+            tma_load_3d(sm.k[s] + pn * KV_PANEL_BYTES + off, &kv_map, pn * 64, 0, zk, &sm.k_full[s]);
         }
         if (use > 0) alive = mbar_wait(&sm.v_empty[s], (use - 1) & 1, p.error);
         alive = __all_sync(0xffffffffu, alive);
         if (!alive) break;
-        if (lane == 0) mbar_expect_tx(&sm.v_full[s], PANELS * PANEL_BYTES);
+        if (lane == 0) mbar_expect_tx(&sm.v_full[s], PANELS * KV_PANEL_BYTES);
         __syncwarp();
         if (lane < pages_per_tile) {
           const int zv = (page * 2 + 1) * p.kv_heads + g;
 #pragma unroll
           for (int pn = 0; pn < PANELS; ++pn)
-            tma_load_3d(sm.v[s] + pn * PANEL_BYTES + off, &kv_map, pn * 64, 0, zv, &sm.v_full[s]);
+            tma_load_3d(sm.v[s] + pn * KV_PANEL_BYTES + off, &kv_map, pn * 64, 0, zv, &sm.v_full[s]);
         }
       }
     } else if (warp == kMmaWarp) {
@@ -284,7 +314,7 @@ attn_prefill_tcgen05_kernel(const PrefillParams p, const __grid_constant__ CUten
       if (lane == 0) {
         constexpr uint32_t idesc_s = idesc_bf16(TQ, TK, false);
         constexpr uint32_t idesc_o = idesc_bf16(TQ, D, true);
-        const uint32_t q_addr = smem_u32(sm.q), p_addr = smem_u32(sm.p);
+        const uint32_t q_addr = smem_u32(sm.q);
         bool alive = mbar_wait(&sm.q_full, 0, p.error);
         tc_fence_after();
         for (int j = 0; j <= ntiles && alive; ++j) {
@@ -295,35 +325,34 @@ attn_prefill_tcgen05_kernel(const PrefillParams p, const __grid_constant__ CUten
             tc_fence_after();
             const uint32_t k_addr = smem_u32(sm.k[s]);
 #pragma unroll
-            for (int kk = 0; kk < D / 16; ++kk) {
-              const uint32_t offs = (kk / 4) * PANEL_BYTES + (kk % 4) * 32;
-              umma(tmem + b * TK, desc_kmajor(q_addr + offs), desc_kmajor(k_addr + offs), idesc_s, kk > 0 ? 1u : 0u);
-            }
+            for (int kk = 0; kk < D / 16; ++kk)
+              umma(tmem + b * TK, desc_kmajor(q_addr + (kk / 4) * PANEL_BYTES + (kk % 4) * 32),
+                   desc_kmajor(k_addr + (kk / 4) * KV_PANEL_BYTES + (kk % 4) * 32), idesc_s, kk > 0 ? 1u : 0u);
             umma_commit(&sm.k_empty[s]);
             umma_commit(&sm.s_full[b]);
           }
           if (j >= 1) {
             const int i = j - 1, s = i % KV_STAGES;
-            if (!mbar_wait(&sm.p_full, i & 1, p.error)) break;
+            if (!mbar_wait(&sm.p_full[i % P_BUFS], (i / P_BUFS) & 1, p.error)) break;
             if (!mbar_wait(&sm.v_full[s], (i / KV_STAGES) & 1, p.error)) break;
             tc_fence_after();
-            const uint32_t v_addr = smem_u32(sm.v[s]);
+            const uint32_t v_addr = smem_u32(sm.v[s]), p_addr = smem_u32(sm.p[i % P_BUFS]);
 #pragma unroll
             for (int kk = 0; kk < TK / 16; ++kk) {
               const uint64_t adesc = desc_kmajor(p_addr + (kk / 4) * PANEL_BYTES + (kk % 4) * 32);
-              const uint64_t bdesc = desc_mnmajor(v_addr + kk * 16 * 128, PANEL_BYTES);
+              const uint64_t bdesc = desc_mnmajor(v_addr + kk * 16 * 128, KV_PANEL_BYTES);
               umma(tmem_o, adesc, bdesc, idesc_o, (i > 0 || kk > 0) ? 1u : 0u);
             }
             umma_commit(&sm.v_empty[s]);
-            umma_commit(&sm.p_empty);
+            umma_commit(&sm.p_empty[i % P_BUFS]);
             if (i == ntiles - 1) umma_commit(&sm.o_ready);
           }
         }
       }
     } else {
-      // ---------------- softmax / epilogue: two threads per row ----------------
-      const int t = threadIdx.x;                                 // 0..255
-      const int half = warp >> 2;                                // which 64 of the 128 key columns (and of D)
+      // ---------------- softmax / epilogue: SPLIT threads per row ----------------
+      const int t = threadIdx.x;                                 // 0 .. kSoftmaxThreads - 1
+      const int part = warp >> 2;                                // which CW of the 128 key columns (and OW of D)
       const int row = (warp & 3) * 32 + lane;                    // tensor-memory lane
       const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
       for (int c = t; c < TQ * (D / 8); c += kSoftmaxThreads) {
@@ -338,7 +367,8 @@ attn_prefill_tcgen05_kernel(const PrefillParams p, const __grid_constant__ CUten
       }
       asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;\n" ::: "memory");
       proxy_fence();
-      mbar_arrive(&sm.q_full);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&sm.q_full);
 
       const int i_row = tile_row0 + row;
       const bool row_valid = i_row < packed;
@@ -346,39 +376,48 @@ attn_prefill_tcgen05_kernel(const PrefillParams p, const __grid_constant__ CUten
       const int first = (row_valid && p.window > 0) ? max(0, pos - p.window + 1) : 0;
       const float sl = p.scale * kLog2e5;
       float m_ref = -INFINITY, l = 0.0f;
-      unsigned char* p_row = sm.p + half * PANEL_BYTES + row * 128;   // this thread's 64 keys are one panel
+      // this thread's CW keys lie in one panel of 64 keys, from 16-byte chunk c_base on
+      const int p_off = (part * CW / 64) * PANEL_BYTES + row * 128;
+      constexpr int CHUNKS = CW / 8;
+      const int c_base = (part * CW % 64) / 8;
       bool ok = true;
 
       for (int j = 0; j < ntiles; ++j) {
         const int b = j & 1;
         if (!mbar_wait(&sm.s_full[b], (j >> 1) & 1, p.error)) { ok = false; break; }
         tc_fence_after();
-        const uint32_t s_addr = tmem + lane_base + b * TK + half * 64;
-        const int j0 = (t_first + j) * TK + half * 64;
+        const uint32_t s_addr = tmem + lane_base + b * TK + part * CW;
+        const int j0 = (t_first + j) * TK + part * CW;
         // a tile that lies wholly inside every row's visible range needs no mask (the usual case)
-        const bool unmasked = __all_sync(0xffffffffu, j0 + 63 <= pos && j0 >= first);
-        // this thread's 64 scores, read once
-        uint32_t sv[64];
-        tmem_ld64(s_addr, sv);
+        const bool unmasked = __all_sync(0xffffffffu, j0 + CW - 1 <= pos && j0 >= first);
+        // this thread's scores, read once
+        uint32_t sv[CW];
+        if constexpr (CW == 64) tmem_ld64(s_addr, sv);
+        else tmem_ld32(s_addr, sv);
         tmem_wait_ld();
         tc_fence_before();
-        mbar_arrive(&sm.s_empty[b]);                             // S_b is in registers: the next-but-one S may land
-        float m_half = -INFINITY;
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&sm.s_empty[b]);              // S_b is in registers: the next-but-one S may land
+        float m_part = -INFINITY;
         if (unmasked) {
+          float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};   // four chains instead of one
 #pragma unroll
-          for (int e = 0; e < 64; ++e) m_half = fmaxf(m_half, __uint_as_float(sv[e]));
+          for (int e = 0; e < CW; ++e) m4[e & 3] = fmaxf(m4[e & 3], __uint_as_float(sv[e]));
+          m_part = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
         } else {
 #pragma unroll
-          for (int e = 0; e < 64; ++e) {
+          for (int e = 0; e < CW; ++e) {
             const int key = j0 + e;
-            if (key <= pos && key >= first) m_half = fmaxf(m_half, __uint_as_float(sv[e]));
+            if (key <= pos && key >= first) m_part = fmaxf(m_part, __uint_as_float(sv[e]));
             else sv[e] = 0xff800000u;                            // -inf: masked for good
           }
         }
-        m_half *= sl;                                            // scale > 0
-        sm.xmax[b][half][row] = m_half;
-        pair_sync(warp & 3);                                     // the two warps that share these 32 rows
-        const float m_tile = fmaxf(m_half, sm.xmax[b][half ^ 1][row]);
+        m_part *= sl;                                            // scale > 0
+        sm.xmax[b][part][row] = m_part;
+        row_group_sync<32 * SPLIT>(warp & 3);                    // the warps that share these 32 rows
+        float m_tile = m_part;
+#pragma unroll
+        for (int o = 0; o < SPLIT; ++o) m_tile = fmaxf(m_tile, sm.xmax[b][o][row]);
         float alpha = 1.0f;
         bool grow = false;
         if (m_tile > m_ref + kRescaleThreshold || (m_ref == -INFINITY && m_tile > -INFINITY)) {
@@ -387,15 +426,20 @@ attn_prefill_tcgen05_kernel(const PrefillParams p, const __grid_constant__ CUten
           grow = true;
         }
         const float m_use = m_ref == -INFINITY ? 0.0f : m_ref;
-        // P and O may be touched once the previous P V product has finished
+        // this tile's P buffer is free once the P V product that read it last has finished; O may only be
+        // rescaled while no P V product is running, so a (rare) rescale waits for the latest one
+        const int pb = j % P_BUFS;
+        if (j >= P_BUFS) {
+          if (!mbar_wait(&sm.p_empty[pb], (j / P_BUFS - 1) & 1, p.error)) { ok = false; break; }
+        }
         if (j > 0) {
-          if (!mbar_wait(&sm.p_empty, (j - 1) & 1, p.error)) { ok = false; break; }
-          tc_fence_after();
           if (__any_sync(0xffffffffu, grow)) {
+            if (!mbar_wait(&sm.p_empty[(j - 1) % P_BUFS], ((j - 1) / P_BUFS) & 1, p.error)) { ok = false; break; }
+            tc_fence_after();
 #pragma unroll 1
-            for (int c = 0; c < D / 64; ++c) {                   // this thread's half of the O columns
+            for (int c = 0; c < OW / 32; ++c) {                  // this thread's part of the O columns
               uint32_t ov[32];
-              const uint32_t o_addr = tmem_o + lane_base + half * (D / 2) + c * 32;
+              const uint32_t o_addr = tmem_o + lane_base + part * OW + c * 32;
               tmem_ld32(o_addr, ov);
               tmem_wait_ld();
 #pragma unroll
@@ -408,7 +452,7 @@ attn_prefill_tcgen05_kernel(const PrefillParams p, const __grid_constant__ CUten
         // exponentials; the P row goes out in chunks of 8 bf16 (a masked score is -inf and gives 0)
         float sum = 0.0f;
 #pragma unroll
-        for (int ch = 0; ch < 8; ++ch) {
+        for (int ch = 0; ch < CHUNKS; ++ch) {
           uint32_t pk[4];
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
@@ -418,28 +462,32 @@ attn_prefill_tcgen05_kernel(const PrefillParams p, const __grid_constant__ CUten
             __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
             pk[e] = *reinterpret_cast<uint32_t*>(&h);
           }
-          *reinterpret_cast<uint4*>(p_row + ((ch ^ (row & 7)) << 4)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+          *reinterpret_cast<uint4*>(sm.p[pb] + p_off + (((c_base + ch) ^ (row & 7)) << 4)) =
+              make_uint4(pk[0], pk[1], pk[2], pk[3]);
         }
         l = l * alpha + sum;
         proxy_fence();
         tc_fence_before();
-        mbar_arrive(&sm.p_full);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&sm.p_full[pb]);
       }
-      // epilogue: the two halves of a row share the row sum
-      sm.xsum[half][row] = l;
-      softmax_sync();
-      const float l_row = l + sm.xsum[half ^ 1][row];
+      // epilogue: the parts of a row share the row sum
+      sm.xsum[part][row] = l;
+      softmax_sync<kSoftmaxThreads>();
+      float l_row = 0.0f;
+#pragma unroll
+      for (int o = 0; o < SPLIT; ++o) l_row += sm.xsum[o][row];
       if (ok && mbar_wait(&sm.o_ready, 0, p.error)) {
         tc_fence_after();
         const float inv = (l_row > 0.0f) ? 1.0f / l_row : 0.0f;
-        if (row_valid && half == 0 && (!(l_row > 0.0f) || !isfinite(l_row))) publish_error(p.error, kAttentionDenominator);
+        if (row_valid && part == 0 && (!(l_row > 0.0f) || !isfinite(l_row))) publish_error(p.error, kAttentionDenominator);
         __nv_bfloat16* orow = nullptr;
         if (row_valid)
-          orow = p.out + (static_cast<size_t>(row0 + i_row / G) * p.heads + g * G + i_row % G) * D + half * (D / 2);
+          orow = p.out + (static_cast<size_t>(row0 + i_row / G) * p.heads + g * G + i_row % G) * D + part * OW;
 #pragma unroll 1
-        for (int c = 0; c < D / 64; ++c) {
+        for (int c = 0; c < OW / 32; ++c) {
           uint32_t ov[32];
-          tmem_ld32(tmem_o + lane_base + half * (D / 2) + c * 32, ov);
+          tmem_ld32(tmem_o + lane_base + part * OW + c * 32, ov);
           tmem_wait_ld();
           if (row_valid) {
             uint32_t pk[16];
@@ -507,21 +555,22 @@ extern "C" int pih_attention_prefill_tcgen05(const void* q, int q_stride, void* 
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   static bool configured[2] = {false, false};
   if (head_dim == 128) {
-    const int smem = static_cast<int>(sizeof(PrefillSmem<128>)) + 1024;
+    constexpr int SPLIT = 2;
+    const int smem = static_cast<int>(sizeof(PrefillSmem<128, SPLIT>)) + 1024;
     if (!configured[0]) {
-      cudaError_t e = cudaFuncSetAttribute(attn_prefill_tcgen05_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+      cudaError_t e = cudaFuncSetAttribute(attn_prefill_tcgen05_kernel<128, SPLIT>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
       if (e != cudaSuccess) return static_cast<int>(e);
       configured[0] = true;
     }
-    launch_kernel(attn_prefill_tcgen05_kernel<128>, dim3(grid), dim3(320), smem, s, p, map);
+    launch_kernel(attn_prefill_tcgen05_kernel<128, SPLIT>, dim3(grid), dim3(128 * SPLIT + 64), smem, s, p, map);
   } else {
-    const int smem = static_cast<int>(sizeof(PrefillSmem<64>)) + 1024;
+    const int smem = static_cast<int>(sizeof(PrefillSmem<64, 2>)) + 1024;
     if (!configured[1]) {
-      cudaError_t e = cudaFuncSetAttribute(attn_prefill_tcgen05_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+      cudaError_t e = cudaFuncSetAttribute(attn_prefill_tcgen05_kernel<64, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
       if (e != cudaSuccess) return static_cast<int>(e);
       configured[1] = true;
     }
-    launch_kernel(attn_prefill_tcgen05_kernel<64>, dim3(grid), dim3(320), smem, s, p, map);
+    launch_kernel(attn_prefill_tcgen05_kernel<64, 2>, dim3(grid), dim3(320), smem, s, p, map);
   }
   PIH_LAUNCH_CHECK();
   return 0;
