@@ -6,18 +6,21 @@
 //
 //   tile       128 packed rows (token i / G, head g G + i % G) of one (request, kv head) x 128 keys
 //   warps 0-7  softmax: a row (= tensor-memory lane) is shared by two threads, one per half of the 128 key
-//              columns: each reads its 64 scores twice (tcgen05.ld; once for the maximum, once for the
-//              exponentials), masks, writes P (bf16) into shared memory in the 128-byte-swizzled K-major layout and
-//              keeps its part of the row sum; O in tensor memory is rescaled only when the running maximum grew by
-//              more than 2^8 (otherwise the old reference maximum stays, which is exact because the final division
-//              uses the sum formed with the same reference);
-//   warp 8     producer: lane p looks up page p of the key tile and issues its TMA boxes (K ring and V ring of
-//              two stages each);
+//              columns: each reads its 64 scores once (tcgen05.ld), masks, takes the maximum, and writes P (bf16,
+//              packed in pairs) back into tensor memory (tcgen05.st), where the P V product reads it as its A
+//              operand: P never passes through shared memory, whose bandwidth the S product alone fills
+//              (Q and K tiles: 64 KB per 128 x 128 x 128 product at 128 bytes a cycle).  It keeps its part of the
+//              row sum; O in tensor memory is rescaled only when the running maximum grew by more than 2^8
+//              (otherwise the old reference maximum stays, which is exact because the final division uses the
+//              sum formed with the same reference);
+//   warps 8, 10  producers: lane p looks up page p of the key tile and issues its TMA boxes; warp 8 feeds the
+//              K ring (three stages), warp 10 the V ring (two);
 //   warp 9     one thread issues the MMAs: S_j = Q K_j^T (8 x K=16) into one of two S buffers, then
-//              O += P_{j-1} V_{j-1}; S_j therefore overlaps the softmax of tile j-1.
+//              O += P_{j-1} V_{j-1} from one of two P buffers; S_j therefore overlaps the softmax of tile j-1,
+//              and the softmax of tile j never waits for the P V product of tile j-1.
 //   A CTA takes a late row tile (many keys) and then its early mirror image (few keys), so CTAs are balanced.
 //
-// Tensor memory: S0 [0,128) S1 [128,256) O [256, 256 + D).  Every mbarrier wait is bounded.
+// Tensor memory: S0 [0,128) S1 [128,256) O [256, 256 + D) P0 [384,448) P1 [448,512).  Every mbarrier wait is bounded.
 // No cluster, no multicast.
 #include <string.h>
 
@@ -27,8 +30,9 @@ namespace pih {
 
 constexpr int TQ = 128;                 // packed rows per tile
 constexpr int TK = 128;                 // keys per tile
-constexpr int KV_STAGES = TK == 64 ? 4 : 2;
-constexpr int P_BUFS = TK == 64 ? 2 : 1;  // P tiles in shared memory (what fits beside Q and the K/V rings)
+constexpr int K_STAGES = 3;             // K tiles run ahead of the S products,
+constexpr int V_STAGES = 2;             // V tiles follow the P V products, each ring fed by a warp of its own
+constexpr int P_BUFS = 2;               // P tiles (bf16) in tensor memory
 constexpr float kLog2e5 = 1.4426950408889634f;
 constexpr float kRescaleThreshold = 8.0f;   // log2 units
 
@@ -76,6 +80,15 @@ __device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t adesc, uint64_t b
       "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
       "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n" ::"r"(tmem_d),
       "l"(adesc), "l"(bdesc), "r"(idesc), "r"(acc)
+      : "memory");
+}
+// the same with the A operand (M x 16, 16-bit elements packed in pairs: lane = row, 8 columns) in tensor memory
+__device__ __forceinline__ void umma_a_tmem(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc,
+                                            uint32_t acc) {
+  asm volatile(
+      "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}\n" ::"r"(tmem_d),
+      "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(acc)
       : "memory");
 }
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
@@ -145,11 +158,10 @@ struct PrefillSmem {
   static constexpr int PANEL_BYTES = TQ * 128;                  // a panel of Q or P: 128 rows x 128 bytes
   static constexpr int KV_PANEL_BYTES = TK * 128;               // a panel of K or V: TK keys x 128 bytes
   alignas(1024) unsigned char q[PANELS * PANEL_BYTES];
-  alignas(1024) unsigned char k[KV_STAGES][PANELS * KV_PANEL_BYTES];
-  alignas(1024) unsigned char v[KV_STAGES][PANELS * KV_PANEL_BYTES];
-  alignas(1024) unsigned char p[P_BUFS][(TK / 64) * PANEL_BYTES];   // TK / 64 panels of 64 keys each
+  alignas(1024) unsigned char k[K_STAGES][PANELS * KV_PANEL_BYTES];
+  alignas(1024) unsigned char v[V_STAGES][PANELS * KV_PANEL_BYTES];
   alignas(8) uint64_t q_full, o_ready, p_full[P_BUFS], p_empty[P_BUFS];
-  alignas(8) uint64_t k_full[KV_STAGES], k_empty[KV_STAGES], v_full[KV_STAGES], v_empty[KV_STAGES];
+  alignas(8) uint64_t k_full[K_STAGES], k_empty[K_STAGES], v_full[V_STAGES], v_empty[V_STAGES];
   alignas(8) uint64_t s_full[2], s_empty[2];
   float xmax[2][SPLIT][128];                                    // [tile parity][column part][row] maxima
   float xsum[SPLIT][128];                                       // row sums of the column parts
@@ -169,13 +181,13 @@ template <int THREADS> __device__ __forceinline__ void row_group_sync(int quarte
 // One CTA works through up to two row tiles of its (request, kv head): a long one (late rows, many keys)
 // and its short mirror image, so that every CTA has about the same number of key tiles.
 template <int D, int SPLIT>
-__global__ void __launch_bounds__(128 * SPLIT + 64)
+__global__ void __launch_bounds__(128 * SPLIT + 96)
 attn_prefill_tcgen05_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap kv_map) {
   wait_for_prior_kernels();
   using Smem = PrefillSmem<D, SPLIT>;
   constexpr int kSoftmaxThreads = 128 * SPLIT;
   constexpr int kSoftmaxWarps = 4 * SPLIT;
-  constexpr int kProducerWarp = 4 * SPLIT, kMmaWarp = 4 * SPLIT + 1;
+  constexpr int kProducerWarp = 4 * SPLIT, kMmaWarp = 4 * SPLIT + 1, kProducerWarpV = 4 * SPLIT + 2;
   constexpr int CW = TK / SPLIT;                                  // key columns of a softmax thread
   constexpr int OW = D / SPLIT;                                   // output columns of a softmax thread
   static_assert(CW == 64 || CW == 32, "a thread reads its scores with one tcgen05.ld of 32 or 64 columns");
@@ -225,9 +237,11 @@ attn_prefill_tcgen05_kernel(const PrefillParams p, const __grid_constant__ CUten
         };
         inval(&sm.q_full);
         inval(&sm.o_ready);
-        for (int s = 0; s < KV_STAGES; ++s) {
+        for (int s = 0; s < K_STAGES; ++s) {
           inval(&sm.k_full[s]);
           inval(&sm.k_empty[s]);
+        }
+        for (int s = 0; s < V_STAGES; ++s) {
           inval(&sm.v_full[s]);
           inval(&sm.v_empty[s]);
         }
@@ -248,9 +262,11 @@ attn_prefill_tcgen05_kernel(const PrefillParams p, const __grid_constant__ CUten
         mbar_init(&sm.p_full[b], kSoftmaxWarps);
         mbar_init(&sm.p_empty[b], 1);
       }
-      for (int s = 0; s < KV_STAGES; ++s) {
+      for (int s = 0; s < K_STAGES; ++s) {
         mbar_init(&sm.k_full[s], 1);
         mbar_init(&sm.k_empty[s], 1);
+      }
+      for (int s = 0; s < V_STAGES; ++s) {
         mbar_init(&sm.v_full[s], 1);
         mbar_init(&sm.v_empty[s], 1);
       }
@@ -266,15 +282,23 @@ attn_prefill_tcgen05_kernel(const PrefillParams p, const __grid_constant__ CUten
     const uint32_t tmem = sm.tmem_base;
     const uint32_t tmem_o = tmem + 256;
 
-    if (warp == kProducerWarp) {
-      // ---------------- producer ----------------
+    if (warp == kProducerWarp || warp == kProducerWarpV) {
+      // ---------------- producers: one warp feeds the K ring, one the V ring ----------------
+      // lane p looks up page p of the key tile and issues its TMA boxes; the rings are independent, so a K
+      // tile never waits for the P V product that frees a V buffer (with one warp for both, the S product
+      // waited 600 cycles a tile for its K)
+      const bool is_v = warp == kProducerWarpV;
+      const int stages = is_v ? V_STAGES : K_STAGES;
+      uint64_t* full = is_v ? sm.v_full : sm.k_full;
+      uint64_t* empty = is_v ? sm.v_empty : sm.k_empty;
+      unsigned char* ring = is_v ? sm.v[0] : sm.k[0];
       const int pages_per_tile = TK >> p.page_shift;
       const int fallback = kmin >> p.page_shift;
       if (lane == 0 && item == 0) tma_prefetch_map(&kv_map);
       bool alive = true;
       for (int j = 0; j < ntiles && alive; ++j) {
-        const int s = j % KV_STAGES;
-        const int use = j / KV_STAGES;
+        const int s = j % stages;
+        const int use = j / stages;
         int page = 0;
         if (lane < pages_per_tile) {
           const int j_page = (t_first + j) * TK + lane * p.page_size;
@@ -285,28 +309,17 @@ attn_prefill_tcgen05_kernel(const PrefillParams p, const __grid_constant__ CUten
             page = 0;
           }
         }
-        const int off = lane * p.page_size * 128;
-        if (use > 0) alive = mbar_wait(&sm.k_empty[s], (use - 1) & 1, p.error);
+        if (use > 0) alive = mbar_wait(&empty[s], (use - 1) & 1, p.error);
         alive = __all_sync(0xffffffffu, alive);
         if (!alive) break;
-        if (lane == 0) mbar_expect_tx(&sm.k_full[s], PANELS * KV_PANEL_BYTES);
+        if (lane == 0) mbar_expect_tx(&full[s], PANELS * KV_PANEL_BYTES);
         __syncwarp();
         if (lane < pages_per_tile) {
-          const int zk = (page * 2) * p.kv_heads + g;
+          const int z = (page * 2 + (is_v ? 1 : 0)) * p.kv_heads + g;
+          unsigned char* dst = ring + s * (PANELS * KV_PANEL_BYTES) + lane * p.page_size * 128;
 #pragma unroll
           for (int pn = 0; pn < PANELS; ++pn)
-            tma_load_3d(sm.k[s] + pn * KV_PANEL_BYTES + off, &kv_map, pn * 64, 0, zk, &sm.k_full[s]);
-        }
-        if (use > 0) alive = mbar_wait(&sm.v_empty[s], (use - 1) & 1, p.error);
-        alive = __all_sync(0xffffffffu, alive);
-        if (!alive) break;
-        if (lane == 0) mbar_expect_tx(&sm.v_full[s], PANELS * KV_PANEL_BYTES);
-        __syncwarp();
-        if (lane < pages_per_tile) {
-          const int zv = (page * 2 + 1) * p.kv_heads + g;
-#pragma unroll
-          for (int pn = 0; pn < PANELS; ++pn)
-            tma_load_3d(sm.v[s] + pn * KV_PANEL_BYTES + off, &kv_map, pn * 64, 0, zv, &sm.v_full[s]);
+            tma_load_3d(dst + pn * KV_PANEL_BYTES, &kv_map, pn * 64, 0, z, &full[s]);
         }
       }
     } else if (warp == kMmaWarp) {
@@ -319,9 +332,9 @@ attn_prefill_tcgen05_kernel(const PrefillParams p, const __grid_constant__ CUten
         tc_fence_after();
         for (int j = 0; j <= ntiles && alive; ++j) {
           if (j < ntiles) {
-            const int b = j & 1, use = j >> 1, s = j % KV_STAGES;
+            const int b = j & 1, use = j >> 1, s = j % K_STAGES;
             if (use > 0 && !mbar_wait(&sm.s_empty[b], (use - 1) & 1, p.error)) break;
-            if (!mbar_wait(&sm.k_full[s], (j / KV_STAGES) & 1, p.error)) break;
+            if (!mbar_wait(&sm.k_full[s], (j / K_STAGES) & 1, p.error)) break;
             tc_fence_after();
             const uint32_t k_addr = smem_u32(sm.k[s]);
 #pragma unroll
@@ -332,16 +345,16 @@ attn_prefill_tcgen05_kernel(const PrefillParams p, const __grid_constant__ CUten
             umma_commit(&sm.s_full[b]);
           }
           if (j >= 1) {
-            const int i = j - 1, s = i % KV_STAGES;
+            const int i = j - 1, s = i % V_STAGES;
             if (!mbar_wait(&sm.p_full[i % P_BUFS], (i / P_BUFS) & 1, p.error)) break;
-            if (!mbar_wait(&sm.v_full[s], (i / KV_STAGES) & 1, p.error)) break;
+            if (!mbar_wait(&sm.v_full[s], (i / V_STAGES) & 1, p.error)) break;
             tc_fence_after();
-            const uint32_t v_addr = smem_u32(sm.v[s]), p_addr = smem_u32(sm.p[i % P_BUFS]);
+            const uint32_t v_addr = smem_u32(sm.v[s]);
+            const uint32_t tmem_p = tmem + 384 + (i % P_BUFS) * (TK / 2);
 #pragma unroll
             for (int kk = 0; kk < TK / 16; ++kk) {
-              const uint64_t adesc = desc_kmajor(p_addr + (kk / 4) * PANEL_BYTES + (kk % 4) * 32);
               const uint64_t bdesc = desc_mnmajor(v_addr + kk * 16 * 128, KV_PANEL_BYTES);
-              umma(tmem_o, adesc, bdesc, idesc_o, (i > 0 || kk > 0) ? 1u : 0u);
+              umma_a_tmem(tmem_o, tmem_p + kk * 8, bdesc, idesc_o, (i > 0 || kk > 0) ? 1u : 0u);
             }
             umma_commit(&sm.v_empty[s]);
             umma_commit(&sm.p_empty[i % P_BUFS]);
@@ -376,10 +389,7 @@ attn_prefill_tcgen05_kernel(const PrefillParams p, const __grid_constant__ CUten
       const int first = (row_valid && p.window > 0) ? max(0, pos - p.window + 1) : 0;
       const float sl = p.scale * kLog2e5;
       float m_ref = -INFINITY, l = 0.0f;
-      // this thread's CW keys lie in one panel of 64 keys, from 16-byte chunk c_base on
-      const int p_off = (part * CW / 64) * PANEL_BYTES + row * 128;
-      constexpr int CHUNKS = CW / 8;
-      const int c_base = (part * CW % 64) / 8;
+      static_assert(CW == 64, "a thread stores its 32 packed pairs of P with one tcgen05.st");
       bool ok = true;
 
       for (int j = 0; j < ntiles; ++j) {
@@ -449,24 +459,21 @@ attn_prefill_tcgen05_kernel(const PrefillParams p, const __grid_constant__ CUten
             tmem_wait_st();
           }
         }
-        // exponentials; the P row goes out in chunks of 8 bf16 (a masked score is -inf and gives 0)
+        // exponentials; the thread's 64 probabilities go to tensor memory as 32 packed pairs, where the P V
+        // product reads them as its A operand (a masked score is -inf and gives 0)
         float sum = 0.0f;
+        uint32_t pk[CW / 2];
 #pragma unroll
-        for (int ch = 0; ch < CHUNKS; ++ch) {
-          uint32_t pk[4];
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const float p0 = fast_exp2(fmaf(__uint_as_float(sv[ch * 8 + 2 * e]), sl, -m_use));
-            const float p1 = fast_exp2(fmaf(__uint_as_float(sv[ch * 8 + 2 * e + 1]), sl, -m_use));
-            sum += p0 + p1;
-            __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
-            pk[e] = *reinterpret_cast<uint32_t*>(&h);
-          }
-          *reinterpret_cast<uint4*>(sm.p[pb] + p_off + (((c_base + ch) ^ (row & 7)) << 4)) =
-              make_uint4(pk[0], pk[1], pk[2], pk[3]);
+        for (int e = 0; e < CW / 2; ++e) {
+          const float p0 = fast_exp2(fmaf(__uint_as_float(sv[2 * e]), sl, -m_use));
+          const float p1 = fast_exp2(fmaf(__uint_as_float(sv[2 * e + 1]), sl, -m_use));
+          sum += p0 + p1;
+          __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
+          pk[e] = *reinterpret_cast<uint32_t*>(&h);
         }
+        tmem_st32(tmem + 384 + pb * (TK / 2) + lane_base + part * (CW / 2), pk);
+        tmem_wait_st();
         l = l * alpha + sum;
-        proxy_fence();
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&sm.p_full[pb]);
@@ -562,7 +569,7 @@ extern "C" int pih_attention_prefill_tcgen05(const void* q, int q_stride, void* 
       if (e != cudaSuccess) return static_cast<int>(e);
       configured[0] = true;
     }
-    launch_kernel(attn_prefill_tcgen05_kernel<128, SPLIT>, dim3(grid), dim3(128 * SPLIT + 64), smem, s, p, map);
+    launch_kernel(attn_prefill_tcgen05_kernel<128, SPLIT>, dim3(grid), dim3(128 * SPLIT + 96), smem, s, p, map);
   } else {
     const int smem = static_cast<int>(sizeof(PrefillSmem<64, 2>)) + 1024;
     if (!configured[1]) {
@@ -570,7 +577,7 @@ extern "C" int pih_attention_prefill_tcgen05(const void* q, int q_stride, void* 
       if (e != cudaSuccess) return static_cast<int>(e);
       configured[1] = true;
     }
-    launch_kernel(attn_prefill_tcgen05_kernel<64, 2>, dim3(grid), dim3(320), smem, s, p, map);
+    launch_kernel(attn_prefill_tcgen05_kernel<64, 2>, dim3(grid), dim3(352), smem, s, p, map);
   }
   PIH_LAUNCH_CHECK();
   return 0;
