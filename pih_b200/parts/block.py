@@ -32,6 +32,7 @@ class PreNormBlock:
 
     def __init__(self, spec, weights, rt: Runtime):
         self.spec = spec
+        self.rt = rt
         n = spec.names
         norm_in_cls = part_class("norm", spec.norm_in.kind)
         norm_post_cls = part_class("norm", spec.norm_post.kind)
@@ -47,10 +48,21 @@ class PreNormBlock:
     def forward(self, h, delta, step, cache):
         # a part that can take "add, norm, then me" as one call gets it (fewer kernels for few rows);
         # any other part gets the normed rows
-        if getattr(self.norm_in, "fusable", False) and hasattr(self.mixer, "forward_prenorm"):
+        fused_in = getattr(self.norm_in, "fusable", False)
+        fused_post = getattr(self.norm_post, "fusable", False)
+        if (fused_in and fused_post and hasattr(self.mixer, "forward_prenorm_unprojected")
+                and hasattr(self.ffn, "forward_prenorm_projected")):
+            # the mixer leaves its output projection to the feed-forward, which may run it, the add, the norm
+            # and itself as one kernel
+            h, a, w = self.mixer.forward_prenorm_unprojected(h, delta, self.norm_in, step, cache)
+            done = self.ffn.forward_prenorm_projected(h, a, w, self.norm_post)
+            if done is not None:
+                return done
+            return self.ffn.forward_prenorm(h, self.rt.ops.linear(a, w), self.norm_post)
+        if fused_in and hasattr(self.mixer, "forward_prenorm"):
             h, a = self.mixer.forward_prenorm(h, delta, self.norm_in, step, cache)
         else:
             a = self.mixer.forward(self.norm_in.add_forward(h, delta), step, cache)
-        if getattr(self.norm_post, "fusable", False) and hasattr(self.ffn, "forward_prenorm"):
+        if fused_post and hasattr(self.ffn, "forward_prenorm"):
             return self.ffn.forward_prenorm(h, a, self.norm_post)
         return h, self.ffn.forward(self.norm_post.add_forward(h, a))
