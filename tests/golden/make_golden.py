@@ -5,12 +5,12 @@ The reference (GuiminChen/pih) has no whole-model forward on the CPU and no Pyth
 oracles compile here with g++ (no CUDA needed): plugins/model-qwen3/qwen3_cpu_oracle.cpp,
 qwen3_gqa_oracle.cpp, qwen3_sampler.cpp and src/core/status.cpp.  ``oracle_driver.cpp`` (ours) strings them
 together in the order of the reference's execution schedule and supplies the matrix products, which the
-reference leaves to cuBLASLt.  This script compiles the driver against the reference's tree (default
-/root/reference; the tree is only read), feeds it a seeded random model, and stores inputs' seed and the
-outputs as JSON.  ``tests/test_golden.py`` compares the plain implementation with these numbers; it needs
+reference leaves to cuBLASLt.  This script compiles the driver against a checkout of the reference (given
+with --reference or in PIH_REFERENCE; the tree is only read), feeds it a seeded random model, and stores the
+inputs' seed and the outputs as JSON.  ``tests/test_golden.py`` compares the plain implementation with these numbers; it needs
 neither the reference nor a compiler.
 
-    python tests/golden/make_golden.py [--reference /path/to/pih]
+    python tests/golden/make_golden.py --reference /path/to/pih
 """
 import argparse
 import json
@@ -28,7 +28,8 @@ from golden_model import CONFIG, TOKENS, make_weights, tensor_order  # noqa: E40
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", default=os.environ.get("PIH_REFERENCE"), required="PIH_REFERENCE" not in os.environ,
+                    help="a checkout of GuiminChen/pih")
     args = ap.parse_args()
     ref = args.reference
     sources = [os.path.join(ref, p) for p in ("plugins/model-qwen3/qwen3_cpu_oracle.cpp",
