@@ -199,13 +199,18 @@ __global__ void qk_norm_rope_kv_fast_kernel(T* __restrict__ qkv, int row_stride,
   // what the row's slots share
   const bool any_kv = slot0 + SPW > heads;
   int m = -1;
+  size_t cache_k = 0;                                      // offset of kv head 0's K row of this token in its page
   if (any_kv) {
     m = slot_mapping[t];
     if (m < 0 || m >= num_pages * page_size) {
       if (lane == 0) publish_error(error, kRowWithoutPage);
       m = -1;
+    } else {
+      const int page = m / page_size, off = m % page_size;
+      cache_k = static_cast<size_t>(page) * 2 * kv_heads * page_size * D + static_cast<size_t>(off) * D + lane * EPL;
     }
   }
+  const size_t head_stride = static_cast<size_t>(page_size) * D;
   CsPack cs;
   if (rope != nullptr && slot0 < heads + kv_heads) {
     int pos = positions[t];
@@ -226,12 +231,7 @@ __global__ void qk_norm_rope_kv_fast_kernel(T* __restrict__ qkv, int row_stride,
     const bool is_q = slot < heads;
     const bool is_k = !is_q && slot < heads + kv_heads;
     T* dst_cache = nullptr;
-    if (!is_q && m >= 0) {
-      const int page = m / page_size, off = m % page_size;
-      const int h = is_k ? slot - heads : slot - heads - kv_heads;
-      dst_cache = cache + ((static_cast<size_t>(page) * 2 + (is_k ? 0 : 1)) * kv_heads + h) * page_size * D +
-                  static_cast<size_t>(off) * D + lane * EPL;
-    }
+    if (!is_q && m >= 0) dst_cache = cache + cache_k + static_cast<size_t>(slot - heads) * head_stride;   // K heads, then V heads
     if (!is_q && !is_k) {
       if (dst_cache != nullptr) *reinterpret_cast<Pack*>(dst_cache) = in[i];
       continue;
@@ -516,32 +516,48 @@ extern "C" int pih_qk_norm_rope_kv_write(int dtype, int weight_dtype, void* qkv,
   return PIH_ERR_BAD_ARGUMENT;
 }
 
-// 16 bytes per thread; needs inter * sizeof(T) % 16 == 0 and il a multiple of the vector length
+// silu(g) * u in 32-bit.  The 32-bit stream uses expf and a true division, as the reference's kernel does
+// (qwen_bf16_primitives.cu:274-283); the bf16 stream uses the special-function unit's exp2 and reciprocal, whose
+// two-ulp error in 32-bit is a five-hundredth of a bf16 rounding step (the exact forms made the kernel
+// instruction-bound: 11 us for 2048 x 3072 outputs).
+template <typename T> __device__ __forceinline__ float silu_times(float g, float u);
+template <> __device__ __forceinline__ float silu_times<float>(float g, float u) { return (g / (1.0f + expf(-g))) * u; }
+template <> __device__ __forceinline__ float silu_times<__nv_bfloat16>(float g, float u) {
+  return __fdividef(g, 1.0f + __expf(-g)) * u;
+}
+
+// 16 bytes per thread and row, two rows per thread with their loads issued together; needs
+// inter * sizeof(T) % 16 == 0 and il a multiple of the vector length.  grid (column vectors / 256, row pairs)
 template <typename T>
 __global__ void silu_mul_vec_kernel(const T* __restrict__ gate_up, T* __restrict__ out, long long rows,
                                     int inter, int il) {
   wait_for_prior_kernels();
   constexpr int VEC = 16 / sizeof(T);
   const int per_row = inter / VEC;
-  const long long total = rows * per_row;
-  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
-       i += static_cast<long long>(gridDim.x) * blockDim.x) {
-    const long long t = i / per_row;
-    const int c = static_cast<int>(i - t * per_row);
-    const int col = c * VEC;
-    const int gc = (col / il) * 2 * il + col % il;
-    const uint4 graw = *reinterpret_cast<const uint4*>(gate_up + t * 2 * inter + gc);
-    const uint4 uraw = *reinterpret_cast<const uint4*>(gate_up + t * 2 * inter + gc + il);
-    const T* g = reinterpret_cast<const T*>(&graw);
-    const T* u = reinterpret_cast<const T*>(&uraw);
-    uint4 packed;
-    T* pk = reinterpret_cast<T*>(&packed);
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= per_row) return;
+  const int col = c * VEC;
+  const int gc = il == VEC ? 2 * col : (col / il) * 2 * il + col % il;
+  for (long long t0 = 2LL * blockIdx.y; t0 < rows; t0 += 2LL * gridDim.y) {
+    uint4 graw[2], uraw[2];
 #pragma unroll
-    for (int j = 0; j < VEC; ++j) {
-      const float gv = to_float<T>(g[j]);
-      pk[j] = from_float<T>((gv / (1.0f + expf(-gv))) * to_float<T>(u[j]));
+    for (int r = 0; r < 2; ++r) {
+      if (t0 + r < rows) {
+        graw[r] = *reinterpret_cast<const uint4*>(gate_up + (t0 + r) * 2 * inter + gc);
+        uraw[r] = *reinterpret_cast<const uint4*>(gate_up + (t0 + r) * 2 * inter + gc + il);
+      }
     }
-    reinterpret_cast<uint4*>(out + t * inter)[c] = packed;
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      if (t0 + r >= rows) break;
+      const T* g = reinterpret_cast<const T*>(&graw[r]);
+      const T* u = reinterpret_cast<const T*>(&uraw[r]);
+      uint4 packed;
+      T* pk = reinterpret_cast<T*>(&packed);
+#pragma unroll
+      for (int j = 0; j < VEC; ++j) pk[j] = from_float<T>(silu_times<T>(to_float<T>(g[j]), to_float<T>(u[j])));
+      reinterpret_cast<uint4*>(out + (t0 + r) * inter)[c] = packed;
+    }
   }
 }
 
@@ -549,10 +565,11 @@ template <typename T>
 static int launch_silu(const void* gate_up, void* out, long long rows, int inter, int il, cudaStream_t s) {
   const int threads = 256;
   if ((inter * sizeof(T)) % 16 == 0 && il % (16 / sizeof(T)) == 0) {
-    const long long total = rows * (inter / (16 / sizeof(T)));
-    const unsigned blocks = static_cast<unsigned>(min((total + threads - 1) / threads, 148LL * 32));
-    launch_kernel(silu_mul_vec_kernel<T>, dim3(blocks), dim3(threads), 0, s, static_cast<const T*>(gate_up), static_cast<T*>(out),
-                                                      rows, inter, il);
+    const int per_row = inter / (16 / static_cast<int>(sizeof(T)));
+    const long long pairs = (rows + 1) / 2;
+    const dim3 grid((per_row + threads - 1) / threads, static_cast<unsigned>(pairs < 65535 ? pairs : 65535));
+    launch_kernel(silu_mul_vec_kernel<T>, grid, dim3(threads), 0, s, static_cast<const T*>(gate_up), static_cast<T*>(out),
+                  rows, inter, il);
   } else {
     const long long total = rows * inter;
     const unsigned blocks = static_cast<unsigned>(min((total + threads - 1) / threads, 148LL * 32));
