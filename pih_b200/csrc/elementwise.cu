@@ -269,6 +269,113 @@ __global__ void qk_norm_rope_kv_fast_kernel(T* __restrict__ qkv, int row_stride,
   }
 }
 
+// The same for many rows, with a head on 16 lanes (head_dim = 16 * EPL, EPL in {4, 8, 16}): a warp works on two
+// head slots at a time, SPW times, so the per-slot work — the reduction, the reciprocal square root, the
+// address arithmetic — is spread over twice the elements, and a lane's loads are 16 bytes for bf16 heads of 128.
+// Rotation partner: lane ^ 8.  Every lane runs every shuffle; what a lane keeps depends on its slot's kind.
+template <typename T, typename W, int EPL, int SPW>
+__global__ void qk_norm_rope_kv_wide_kernel(T* __restrict__ qkv, int row_stride, int rows, int heads,
+                                            int kv_heads, const W* __restrict__ q_w,
+                                            const W* __restrict__ k_w, float eps,
+                                            const float* __restrict__ rope, int max_pos,
+                                            const int* __restrict__ positions,
+                                            const int* __restrict__ slot_mapping, T* __restrict__ cache,
+                                            int page_size, int num_pages, int write_kv, uint32_t* error) {
+  wait_for_prior_kernels();
+  constexpr int D = 16 * EPL;
+  constexpr int HALF = D / 2;
+  const int warps_per_block = blockDim.x >> 5;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int sub = lane >> 4, l16 = lane & 15;
+  const int slots = heads + (write_kv ? 2 * kv_heads : 0);
+  const int groups = (slots + 2 * SPW - 1) / (2 * SPW);
+  const long long item = static_cast<long long>(blockIdx.x) * warps_per_block + warp;
+  if (item >= static_cast<long long>(rows) * groups) return;
+  const int t = static_cast<int>(item / groups);
+  const int slot0 = static_cast<int>(item % groups) * 2 * SPW;
+  struct alignas(EPL * sizeof(T) > 16 ? 16 : EPL * sizeof(T)) Pack { T e[EPL]; };
+  struct alignas(EPL * sizeof(W) > 16 ? 16 : EPL * sizeof(W)) WPack { W e[EPL]; };
+  struct alignas(16) CsPack { float2 e[EPL]; };
+  T* row = qkv + static_cast<size_t>(t) * row_stride + l16 * EPL;
+  Pack in[SPW];
+#pragma unroll
+  for (int i = 0; i < SPW; ++i) {
+    const int slot = min(slot0 + 2 * i + sub, slots - 1);
+    in[i] = *reinterpret_cast<const Pack*>(row + static_cast<size_t>(slot) * D);
+  }
+  int m = -1;
+  size_t cache_k = 0;
+  if (slot0 + 2 * SPW > heads) {
+    m = slot_mapping[t];
+    if (m < 0 || m >= num_pages * page_size) {
+      if (lane == 0) publish_error(error, kRowWithoutPage);
+      m = -1;
+    } else {
+      const int page = m / page_size, off = m % page_size;
+      cache_k = static_cast<size_t>(page) * 2 * kv_heads * page_size * D + static_cast<size_t>(off) * D + l16 * EPL;
+    }
+  }
+  const size_t head_stride = static_cast<size_t>(page_size) * D;
+  CsPack cs;
+#pragma unroll
+  for (int j = 0; j < EPL; ++j) cs.e[j] = make_float2(1.0f, 0.0f);
+  if (rope != nullptr && slot0 < heads + kv_heads) {
+    int pos = positions[t];
+    if (pos < 0 || pos >= max_pos) {
+      if (lane == 0) publish_error(error, kBadPosition);
+      pos = 0;
+    }
+    cs = *reinterpret_cast<const CsPack*>(rope + (static_cast<size_t>(pos) * HALF + (l16 & 7) * EPL) * 2);
+  }
+  WPack wq, wk;
+#pragma unroll
+  for (int j = 0; j < EPL; ++j) wq.e[j] = wk.e[j] = from_float<W>(1.0f);
+  if (q_w != nullptr) wq = *reinterpret_cast<const WPack*>(q_w + l16 * EPL);
+  if (k_w != nullptr) wk = *reinterpret_cast<const WPack*>(k_w + l16 * EPL);
+#pragma unroll
+  for (int i = 0; i < SPW; ++i) {
+    const int slot = slot0 + 2 * i + sub;
+    const bool live = slot < slots;
+    const bool is_q = slot < heads;
+    const bool is_k = !is_q && slot < heads + kv_heads;
+    const bool normed = is_q ? q_w != nullptr : (is_k && k_w != nullptr);
+    float v[EPL];
+    float ss = 0.0f;
+#pragma unroll
+    for (int j = 0; j < EPL; ++j) {
+      v[j] = to_float<T>(in[i].e[j]);
+      ss += v[j] * v[j];
+    }
+#pragma unroll
+    for (int d = 8; d > 0; d >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, d);      // over the head's 16 lanes
+    const float scale = 1.0f / sqrtf(ss / static_cast<float>(D) + eps);
+    if (normed) {
+#pragma unroll
+      for (int j = 0; j < EPL; ++j)
+        v[j] = round_to<T>((v[j] * scale) * to_float<W>(is_q ? wq.e[j] : wk.e[j]));
+    }
+    Pack outp;
+#pragma unroll
+    for (int j = 0; j < EPL; ++j) {
+      const float other = __shfl_xor_sync(0xffffffffu, v[j], 8);
+      float r = v[j];
+      if (rope != nullptr) {
+        const float c = cs.e[j].x, sn = cs.e[j].y;
+        r = l16 < 8 ? v[j] * c - other * sn : v[j] * c + other * sn;
+      }
+      outp.e[j] = from_float<T>(r);
+    }
+    if (!live) continue;
+    T* dst_cache = (!is_q && m >= 0) ? cache + cache_k + static_cast<size_t>(slot - heads) * head_stride : nullptr;
+    if (!is_q && !is_k) {                                  // a V head: copied as it is
+      if (dst_cache != nullptr) *reinterpret_cast<Pack*>(dst_cache) = in[i];
+      continue;
+    }
+    *reinterpret_cast<Pack*>(row + static_cast<size_t>(slot) * D) = outp;
+    if (dst_cache != nullptr) *reinterpret_cast<Pack*>(dst_cache) = outp;
+  }
+}
+
 // ---------------------------------------------------------------------------
 // SiLU-mul: out[t,i] = round( (g / (1 + exp(-g))) * u ), g = in[t,i], u = in[t,I+i]
 // (qwen_bf16_primitives.cu:274-283)
@@ -455,9 +562,25 @@ static int launch_qk(void* qkv, int row_stride, int rows, int heads, int kv_head
       aligned64(cache)) {
     const int warps = 8;
     const int slots = heads + (write_kv ? 2 * kv_heads : 0);
-    // four slots per warp save instructions when there are warps enough to fill the machine; with few rows
-    // (a decode step) one slot per warp is the shorter chain
-    const int spw = rows >= 64 ? 4 : 1;
+    // with few rows (a decode step) one slot per warp is the shortest chain
+    if (rows >= 64) {
+      // many rows: a head on 16 lanes, eight head slots per warp
+      constexpr int SPW = 4;
+      const long long work = static_cast<long long>(rows) * ((slots + 2 * SPW - 1) / (2 * SPW));
+      const unsigned blocks = static_cast<unsigned>((work + warps - 1) / warps);
+#define PIH_QK_WIDE(EPL)                                                                                   \
+  launch_kernel(qk_norm_rope_kv_wide_kernel<T, W, EPL, SPW>, dim3(blocks), dim3(warps * 32), 0, s,         \
+      static_cast<T*>(qkv), row_stride, rows, heads, kv_heads, static_cast<const W*>(q_w),                 \
+      static_cast<const W*>(k_w), eps, rope, max_pos, positions, slot_mapping, static_cast<T*>(cache),     \
+      page_size, num_pages, write_kv, error)
+      if (head_dim == 64) PIH_QK_WIDE(4);
+      else if (head_dim == 128) PIH_QK_WIDE(8);
+      else PIH_QK_WIDE(16);
+#undef PIH_QK_WIDE
+      PIH_LAUNCH_CHECK();
+      return 0;
+    }
+    const int spw = 1;
     const long long work = static_cast<long long>(rows) * ((slots + spw - 1) / spw);
     const unsigned blocks = static_cast<unsigned>((work + warps - 1) / warps);
 #define PIH_QK_FAST_SPW(EPL, SPW)                                                                          \
@@ -465,11 +588,7 @@ static int launch_qk(void* qkv, int row_stride, int rows, int heads, int kv_head
       static_cast<T*>(qkv), row_stride, rows, heads, kv_heads, static_cast<const W*>(q_w),                 \
       static_cast<const W*>(k_w), eps, rope, max_pos, positions, slot_mapping, static_cast<T*>(cache),     \
       page_size, num_pages, write_kv, error)
-#define PIH_QK_FAST(EPL)             \
-  do {                               \
-    if (spw == 4) PIH_QK_FAST_SPW(EPL, 4); \
-    else PIH_QK_FAST_SPW(EPL, 1);    \
-  } while (0)
+#define PIH_QK_FAST(EPL) PIH_QK_FAST_SPW(EPL, 1)
     if (head_dim == 64) PIH_QK_FAST(2);
     else if (head_dim == 128) PIH_QK_FAST(4);
     else PIH_QK_FAST(8);
