@@ -34,6 +34,7 @@
 #include <string.h>
 
 #include "ptx.cuh"
+#include "qk_math.cuh"
 
 namespace pih {
 
@@ -61,6 +62,17 @@ struct AttnParams {
   int* tickets;                        // [R, kv_heads], zero between launches
   int page_shift;                      // log2(page_size) or -1
   uint32_t* error;
+  // when the split kernel does the q/k norm, the rotation and the cache append itself (FUSE): q points at the raw
+  // rows [q | k | v] of the q/k/v product
+  const void* q_norm_w;                // [D] or nullptr
+  const void* k_norm_w;
+  int norm_w_f32;                      // the norm weights are float (else bf16)
+  float norm_eps;
+  const float* rope;                   // [max_pos, D / 2, 2] (cos, sin) or nullptr
+  int max_pos;
+  int write_kv;                        // append the new tokens' k and v to the cache (and use them)
+  __nv_bfloat16* cache_w;              // the cache, writable
+  int fused;                           // host: launch the FUSE variant
 };
 
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem, int src_bytes) {
@@ -699,7 +711,12 @@ attn_split_kernel(const AttnParams p) {
 // visible page, so that shared memory always holds finite values (they are masked by position).
 // CLUSTER: the blocks of one (request, kv head) are one thread-block cluster (grid.x = cluster size = splits)
 // and merge through distributed shared memory (cluster_finish) instead of scratch memory and tickets.
-template <int D, bool CLUSTER>
+// FUSE: q arrives raw from the q/k/v product, with the new tokens' k and v beside it.  The consumer warps apply the
+// per-head RMSNorm and the rotation to q on its way into shared memory; the block whose key range holds a new
+// token's position does the same for that k, appends k and v to the cache and — because its TMA boxes may have
+// read the cache before — puts them into the landed tile before it is used.  The q/k kernel between the q/k/v
+// product and the attention is then not launched (2 us a layer at batch 8).
+template <int D, bool CLUSTER, bool FUSE>
 __global__ void __launch_bounds__(160)
 attn_split_tma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap kv_map) {
   wait_for_prior_kernels();
@@ -712,6 +729,8 @@ attn_split_tma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap kv
   __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(base + kSplitStages * 2 * TILE_BYTES);
   uint64_t* full = reinterpret_cast<uint64_t*>(Qs + 16 * LD);
   uint64_t* empty = full + kSplitStages;
+  __nv_bfloat16* NewK = reinterpret_cast<__nv_bfloat16*>(empty + kSplitStages);   // FUSE: [16][D], then NewV [16][D]
+  __nv_bfloat16* NewV = NewK + 16 * D;
   __shared__ int s_last;
 
   const int r = blockIdx.z, g = blockIdx.y, sp = blockIdx.x;
@@ -798,22 +817,116 @@ attn_split_tma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap kv
     }
   } else {
     // consumers: the query rows arrive while the first tiles are on their way
-    for (int c = threadIdx.x; c < 16 * (D / 8); c += 128) {
-      const int row = c / (D / 8), ch = c % (D / 8);
-      const bool valid = row < packed;
-      const __nv_bfloat16* src = p.q;
-      if (valid)
-        src = p.q + static_cast<size_t>(row0 + row / G) * p.q_stride + static_cast<size_t>(g * G + row % G) * D + ch * 8;
-      cp_async16(Qs + row * LD + ch * 8, src, valid ? 16 : 0);
+    if (FUSE) {
+      constexpr int EPL = D / 32;
+      constexpr int HALF = D / 2;
+      struct alignas(EPL * 2) Pack { __nv_bfloat16 e[EPL]; };
+      auto weights = [&](const void* w, float (&out)[EPL]) {
+#pragma unroll
+        for (int j = 0; j < EPL; ++j)
+          out[j] = p.norm_w_f32 ? static_cast<const float*>(w)[lane * EPL + j]
+                                : __bfloat162float(static_cast<const __nv_bfloat16*>(w)[lane * EPL + j]);
+      };
+      auto angles = [&](int pos, float2 (&cs)[EPL]) {
+        if (pos < 0 || pos >= p.max_pos) {
+          if (lane == 0) publish_error(p.error, kBadPosition);
+          pos = 0;
+        }
+        const float2* src = reinterpret_cast<const float2*>(p.rope) + static_cast<size_t>(pos) * HALF + (lane & 15) * EPL;
+#pragma unroll
+        for (int j = 0; j < EPL; ++j) cs[j] = src[j];
+      };
+      float wq[EPL], wk[EPL];
+      if (p.q_norm_w != nullptr) weights(p.q_norm_w, wq);
+      if (p.k_norm_w != nullptr) weights(p.k_norm_w, wk);
+      for (int row = warp; row < 16; row += 4) {           // a row per warp at a time
+        Pack outp;
+        if (row < packed) {
+          const Pack in = *reinterpret_cast<const Pack*>(
+              p.q + static_cast<size_t>(row0 + row / G) * p.q_stride + static_cast<size_t>(g * G + row % G) * D + lane * EPL);
+          float v[EPL];
+          float2 cs[EPL];
+#pragma unroll
+          for (int j = 0; j < EPL; ++j) v[j] = __bfloat162float(in.e[j]);
+          if (p.rope != nullptr) angles(start + row / G, cs);
+          head_norm_rotate<__nv_bfloat16, float, EPL>(v, p.q_norm_w != nullptr ? wq : nullptr, p.norm_eps,
+                                                      p.rope != nullptr ? cs : nullptr, lane);
+#pragma unroll
+          for (int j = 0; j < EPL; ++j) outp.e[j] = __float2bfloat16_rn(v[j]);
+        } else {
+#pragma unroll
+          for (int j = 0; j < EPL; ++j) outp.e[j] = __float2bfloat16_rn(0.0f);
+        }
+        *reinterpret_cast<Pack*>(Qs + row * LD + lane * EPL) = outp;
+      }
+      // the new tokens whose positions lie in this block's key range: k normed and rotated, v as it is; both go
+      // to the cache and are kept for the tile that the TMA boxes may have filled from the cache's old contents
+      if (p.write_kv && has_keys) {
+        for (int tt = warp; tt < n_tok; tt += 4) {
+          const int j = start + tt;
+          if (j < kmin || j > kmax) continue;
+          const __nv_bfloat16* krow = p.q + static_cast<size_t>(row0 + tt) * p.q_stride +
+                                      static_cast<size_t>(p.heads + g) * D + lane * EPL;
+          const Pack kin = *reinterpret_cast<const Pack*>(krow);
+          const Pack vin = *reinterpret_cast<const Pack*>(krow + static_cast<size_t>(p.kv_heads) * D);
+          float v[EPL];
+          float2 cs[EPL];
+#pragma unroll
+          for (int e = 0; e < EPL; ++e) v[e] = __bfloat162float(kin.e[e]);
+          if (p.rope != nullptr) angles(j, cs);
+          head_norm_rotate<__nv_bfloat16, float, EPL>(v, p.k_norm_w != nullptr ? wk : nullptr, p.norm_eps,
+                                                      p.rope != nullptr ? cs : nullptr, lane);
+          Pack kout;
+#pragma unroll
+          for (int e = 0; e < EPL; ++e) kout.e[e] = __float2bfloat16_rn(v[e]);
+          int page = table[j >> p.page_shift];
+          if (page < 0 || page >= p.num_pages) {
+            if (lane == 0) publish_error(p.error, kRowWithoutPage);
+          } else {
+            __nv_bfloat16* dst = p.cache_w + (static_cast<size_t>(page) * 2 * p.kv_heads + g) * p.page_size * D +
+                                 static_cast<size_t>(j & (p.page_size - 1)) * D + lane * EPL;
+            *reinterpret_cast<Pack*>(dst) = kout;
+            *reinterpret_cast<Pack*>(dst + static_cast<size_t>(p.kv_heads) * p.page_size * D) = vin;
+          }
+          *reinterpret_cast<Pack*>(NewK + tt * D + lane * EPL) = kout;
+          *reinterpret_cast<Pack*>(NewV + tt * D + lane * EPL) = vin;
+        }
+      }
+    } else {
+      for (int c = threadIdx.x; c < 16 * (D / 8); c += 128) {
+        const int row = c / (D / 8), ch = c % (D / 8);
+        const bool valid = row < packed;
+        const __nv_bfloat16* src = p.q;
+        if (valid)
+          src = p.q + static_cast<size_t>(row0 + row / G) * p.q_stride + static_cast<size_t>(g * G + row % G) * D + ch * 8;
+        cp_async16(Qs + row * LD + ch * 8, src, valid ? 16 : 0);
+      }
+      cp_async_commit();
+      cp_async_wait<0>();
     }
-    cp_async_commit();
-    cp_async_wait<0>();
     asm volatile("bar.sync 1, 128;\n" ::: "memory");   // the four consumer warps only
     for (int i = 0; i < ntiles; ++i) {
       const int s = i % kSplitStages;
       mbar_wait(&full[s], (i / kSplitStages) & 1, p.error);
       const __nv_bfloat16* Ks = reinterpret_cast<const __nv_bfloat16*>(KV + s * 2 * TILE_BYTES);
       const __nv_bfloat16* Vs = reinterpret_cast<const __nv_bfloat16*>(KV + s * 2 * TILE_BYTES + TILE_BYTES);
+      if (FUSE && p.write_kv) {
+        // new tokens among this warp's 16 keys of the tile: their k and v replace what the boxes brought
+        constexpr int EPL = D / 32;
+        struct alignas(EPL * 2) Pack { __nv_bfloat16 e[EPL]; };
+        const int tile_j0 = (t_first + i) * BN;
+        const int lo = max(tile_j0 + warp * 16, max(start, kmin));
+        const int hi = min(tile_j0 + warp * 16 + 15, min(start + n_tok - 1, kmax));
+        for (int j = lo; j <= hi; ++j) {
+          const int tt = j - start, rr = j - tile_j0;
+          const int col = lane * EPL;                      // kv_at gives the 16-byte chunk; the lane's place inside it
+          *reinterpret_cast<Pack*>(const_cast<__nv_bfloat16*>(kv_at<D, true>(Ks, rr, col & ~7)) + (col & 7)) =
+              *reinterpret_cast<const Pack*>(NewK + tt * D + col);
+          *reinterpret_cast<Pack*>(const_cast<__nv_bfloat16*>(kv_at<D, true>(Vs, rr, col & ~7)) + (col & 7)) =
+              *reinterpret_cast<const Pack*>(NewV + tt * D + col);
+        }
+        __syncwarp();
+      }
       tile_step<D, 16, true>(Qs, Ks, Vs, warp * 16, (t_first + i) * BN + warp * 16, row_pos, row_first, scale_log2,
                              m, l, o);
       __syncwarp();
@@ -834,29 +947,29 @@ template <int D>
 static int launch_split_tma(const AttnParams& p, int R, const CUtensorMap* kv_map, cudaStream_t s) {
   if constexpr (D % 64 == 0) {
     constexpr int LD = D + 8;
-    static int smem_set = 0, smem_set_cluster = 0;
     const bool cluster = g_cluster_merge && p.max_splits >= 2 && p.max_splits <= kMaxCluster;
-    int smem = 1024 + kSplitStages * 2 * BN * D * 2 + 16 * LD * 2 + 2 * kSplitStages * 8;
+    int smem = 1024 + kSplitStages * 2 * BN * D * 2 + 16 * LD * 2 + 2 * kSplitStages * 8 + 2 * 16 * D * 2;
     const int merge = 1024 + (4 * 16 * D + 128 + 16 * D + 32 + 32 * p.max_splits + 16) * 4;
     if (merge > smem) smem = merge;
     if (smem > 227 * 1024) return PIH_ERR_UNSUPPORTED;
     dim3 grid(p.max_splits, p.kv_heads, R);
-    if (cluster) {
-      if (smem_set_cluster < smem) {
-        cudaError_t e = cudaFuncSetAttribute(attn_split_tma_kernel<D, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-        if (e != cudaSuccess) return static_cast<int>(e);
-        smem_set_cluster = smem;
-      }
-      launch_kernel_clustered(attn_split_tma_kernel<D, true>, grid, dim3(160), smem, s,
-                              static_cast<unsigned>(p.max_splits), p, *kv_map);
-    } else {
-      if (smem_set < smem) {
-        cudaError_t e = cudaFuncSetAttribute(attn_split_tma_kernel<D, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-        if (e != cudaSuccess) return static_cast<int>(e);
-        smem_set = smem;
-      }
-      launch_kernel(attn_split_tma_kernel<D, false>, grid, dim3(160), smem, s, p, *kv_map);
-    }
+#define PIH_SPLIT_TMA(CLUSTER, FUSE)                                                                              \
+  do {                                                                                                            \
+    static int smem_done = 0;                                                                                     \
+    if (smem_done < smem) {                                                                                       \
+      cudaError_t e = cudaFuncSetAttribute(attn_split_tma_kernel<D, CLUSTER, FUSE>,                               \
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize, smem);                    \
+      if (e != cudaSuccess) return static_cast<int>(e);                                                           \
+      smem_done = smem;                                                                                           \
+    }                                                                                                             \
+    launch_kernel_clustered(attn_split_tma_kernel<D, CLUSTER, FUSE>, grid, dim3(160), smem, s,                    \
+                            CLUSTER ? static_cast<unsigned>(p.max_splits) : 1u, p, *kv_map);                      \
+  } while (0)
+    if (cluster && p.fused) PIH_SPLIT_TMA(true, true);
+    else if (cluster) PIH_SPLIT_TMA(true, false);
+    else if (p.fused) PIH_SPLIT_TMA(false, true);
+    else PIH_SPLIT_TMA(false, false);
+#undef PIH_SPLIT_TMA
     PIH_LAUNCH_CHECK();
     return 0;
   } else {
@@ -963,13 +1076,25 @@ extern "C" int pih_make_kv_tensor_map(void* out, const void* cache, long long nu
 // ceil(dec_max_ctx / split)) words, the leading ticket words zero.  Launches that share the scratch
 // must not overlap on the device.  Returns PIH_ERR_UNSUPPORTED for a head_dim that has no
 // tensor-core instance (the caller then uses the generic kernel).
-extern "C" int pih_paged_attention_mma(const void* q, int q_stride, void* out, const void* cache,
-                                       const int* block_table, int table_width, const int* cu_q,
-                                       const int* q_start, int rows, int num_requests, int tile_max_q,
-                                       int dec_tok_cap, int dec_max_ctx, int heads, int kv_heads, int head_dim,
-                                       int page_size, int num_pages, float scale, int window, int split,
-                                       int max_splits, const int* max_ctx_ptr, float* scratch,
-                                       const void* kv_tensor_map, uint32_t* error, void* stream) {
+namespace pih {
+struct QkFusion {                      // what the split kernel needs to norm and rotate q and k itself
+  const void* q_norm_w;
+  const void* k_norm_w;
+  int norm_w_f32;
+  float eps;
+  const float* rope;
+  int max_pos;
+  int write_kv;
+};
+}  // namespace pih
+
+static int paged_attention_mma(const void* q, int q_stride, void* out, const void* cache,
+                               const int* block_table, int table_width, const int* cu_q,
+                               const int* q_start, int rows, int num_requests, int tile_max_q,
+                               int dec_tok_cap, int dec_max_ctx, int heads, int kv_heads, int head_dim,
+                               int page_size, int num_pages, float scale, int window, int split,
+                               int max_splits, const int* max_ctx_ptr, float* scratch,
+                               const void* kv_tensor_map, uint32_t* error, void* stream, const QkFusion* fusion) {
   if (rows <= 0) return 0;
   if (heads <= 0 || kv_heads <= 0 || heads % kv_heads || page_size <= 0 || table_width <= 0 || window < 0 ||
       split < 0 || split % BN || (split == 0 && dec_tok_cap > 0 && (max_splits <= 0 || max_ctx_ptr == nullptr)) ||
@@ -1004,6 +1129,27 @@ extern "C" int pih_paged_attention_mma(const void* q, int q_stride, void* out, c
   p.part_o = scratch + tickets;
   p.part_ml = p.part_o + static_cast<size_t>(num_requests) * dec_tok_cap * heads * p.max_splits * head_dim;
   p.error = error;
+  p.fused = 0;
+  p.q_norm_w = p.k_norm_w = nullptr;
+  p.rope = nullptr;
+  p.norm_w_f32 = p.max_pos = p.write_kv = 0;
+  p.norm_eps = 0.0f;
+  p.cache_w = nullptr;
+  if (fusion != nullptr) {
+    // only the TMA split kernel does the q/k work itself: every request decode-like, a head on 32 lanes
+    if (tile_max_q > 0 || dec_tok_cap <= 0 || kv_tensor_map == nullptr || head_dim % 64 || p.page_shift < 3 ||
+        page_size > BN || (fusion->rope != nullptr && fusion->max_pos <= 0))
+      return PIH_ERR_UNSUPPORTED;
+    p.fused = 1;
+    p.q_norm_w = fusion->q_norm_w;
+    p.k_norm_w = fusion->k_norm_w;
+    p.norm_w_f32 = fusion->norm_w_f32;
+    p.norm_eps = fusion->eps;
+    p.rope = fusion->rope;
+    p.max_pos = fusion->max_pos;
+    p.write_kv = fusion->write_kv;
+    p.cache_w = static_cast<__nv_bfloat16*>(const_cast<void*>(cache));
+  }
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   CUtensorMap map_storage;
   const CUtensorMap* kv_map = nullptr;
@@ -1021,4 +1167,37 @@ extern "C" int pih_paged_attention_mma(const void* q, int q_stride, void* out, c
     case 256: return launch_both<256>(p, num_requests, tile_max_q, kv_map, s);
     default: return PIH_ERR_UNSUPPORTED;
   }
+}
+
+extern "C" int pih_paged_attention_mma(const void* q, int q_stride, void* out, const void* cache,
+                                       const int* block_table, int table_width, const int* cu_q,
+                                       const int* q_start, int rows, int num_requests, int tile_max_q,
+                                       int dec_tok_cap, int dec_max_ctx, int heads, int kv_heads, int head_dim,
+                                       int page_size, int num_pages, float scale, int window, int split,
+                                       int max_splits, const int* max_ctx_ptr, float* scratch,
+                                       const void* kv_tensor_map, uint32_t* error, void* stream) {
+  return paged_attention_mma(q, q_stride, out, cache, block_table, table_width, cu_q, q_start, rows, num_requests,
+                             tile_max_q, dec_tok_cap, dec_max_ctx, heads, kv_heads, head_dim, page_size, num_pages,
+                             scale, window, split, max_splits, max_ctx_ptr, scratch, kv_tensor_map, error, stream,
+                             nullptr);
+}
+
+// Decode attention that also does what pih_qk_norm_rope_kv_write does: qkv holds the raw rows [q | k | v] of the
+// q/k/v product (row stride q_stride); q and the new tokens' k get the per-head RMSNorm (weights q_norm_w, k_norm_w
+// of dtype norm_dtype, nullable) and the rotation (rope [max_pos, head_dim / 2, 2], nullable, over the whole head),
+// and with write_kv the new k and v are appended to the cache.  qkv itself is left as it is.  For steps whose
+// requests are all decode-like and shapes that the TMA split kernel takes; PIH_ERR_UNSUPPORTED otherwise, with
+// nothing launched (the caller runs the two kernels).
+extern "C" int pih_qk_attention_fused(const void* qkv, int q_stride, void* out, void* cache, const int* block_table,
+                                      int table_width, const int* cu_q, const int* q_start, int rows, int num_requests,
+                                      int dec_tok_cap, int dec_max_ctx, int heads, int kv_heads, int head_dim,
+                                      int page_size, int num_pages, float scale, int window, int split, int max_splits,
+                                      const int* max_ctx_ptr, float* scratch, const void* kv_tensor_map,
+                                      int norm_dtype, const void* q_norm_w, const void* k_norm_w, float eps,
+                                      const float* rope, int max_pos, int write_kv, uint32_t* error, void* stream) {
+  if (norm_dtype != PIH_BF16 && norm_dtype != PIH_F32) return PIH_ERR_BAD_ARGUMENT;
+  QkFusion f = {q_norm_w, k_norm_w, norm_dtype == PIH_F32 ? 1 : 0, eps, rope, max_pos, write_kv};
+  return paged_attention_mma(qkv, q_stride, out, cache, block_table, table_width, cu_q, q_start, rows, num_requests, 0,
+                             dec_tok_cap, dec_max_ctx, heads, kv_heads, head_dim, page_size, num_pages, scale, window,
+                             split, max_splits, max_ctx_ptr, scratch, kv_tensor_map, error, stream, &f);
 }

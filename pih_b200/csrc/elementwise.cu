@@ -3,6 +3,7 @@
 // template over the storage type (float for the true 32-bit path,
 // __nv_bfloat16 for serving) and takes every size as an argument.
 #include "common.cuh"
+#include "qk_math.cuh"
 
 namespace pih {
 
@@ -238,32 +239,12 @@ __global__ void qk_norm_rope_kv_fast_kernel(T* __restrict__ qkv, int row_stride,
     }
     const bool normed = is_q ? q_w != nullptr : k_w != nullptr;
     float v[EPL];
-    float ss = 0.0f;
 #pragma unroll
-    for (int j = 0; j < EPL; ++j) {
-      v[j] = to_float<T>(in[i].e[j]);
-      ss += v[j] * v[j];
-    }
-    if (normed) {
-      ss = warp_sum(ss);
-      const float scale = 1.0f / sqrtf(ss / static_cast<float>(D) + eps);
-#pragma unroll
-      for (int j = 0; j < EPL; ++j)
-        v[j] = round_to<T>((v[j] * scale) * to_float<W>(is_q ? wq.e[j] : wk.e[j]));
-    }
+    for (int j = 0; j < EPL; ++j) v[j] = to_float<T>(in[i].e[j]);
+    head_norm_rotate<T, W, EPL>(v, normed ? (is_q ? wq.e : wk.e) : nullptr, eps, rope != nullptr ? cs.e : nullptr, lane);
     Pack outp;
-    if (rope != nullptr) {
 #pragma unroll
-      for (int j = 0; j < EPL; ++j) {
-        const float other = __shfl_xor_sync(0xffffffffu, v[j], 16);
-        const float c = cs.e[j].x, sn = cs.e[j].y;
-        const float r = lane < 16 ? v[j] * c - other * sn : v[j] * c + other * sn;
-        outp.e[j] = from_float<T>(r);
-      }
-    } else {
-#pragma unroll
-      for (int j = 0; j < EPL; ++j) outp.e[j] = from_float<T>(v[j]);
-    }
+    for (int j = 0; j < EPL; ++j) outp.e[j] = from_float<T>(v[j]);
     *reinterpret_cast<Pack*>(row + static_cast<size_t>(slot) * D) = outp;
     if (dst_cache != nullptr) *reinterpret_cast<Pack*>(dst_cache) = outp;
   }

@@ -60,6 +60,7 @@ class CudaOps:
         self._kv_maps = {}                 # cache tensor (address, shape) -> 128-byte TMA descriptor
         self.tma_attention = True          # False: the split kernel gathers with cp.async instead of TMA
         self.tcgen05_attention = True      # False: prompt portions use the mma.sync tile kernel
+        self.fused_qk_attention = True     # decode-only steps: q/k norm, rotation and cache append inside the attention kernel
         self.cluster_attention = True      # False: splits always merge through scratch memory and tickets
         self.attention_split = 0           # keys per split of the decode attention kernel; 0: from the context, on the device
         self.tensor_core_attention = True  # False: bf16 attention runs on the generic kernel too
@@ -78,7 +79,8 @@ class CudaOps:
                      "pih_gather_rows", "pih_gemm_simt", "pih_paged_attention_generic", "pih_argmax",
                      "pih_sample", "pih_paged_attention_mma", "pih_gemm_tcgen05", "pih_make_kv_tensor_map",
                      "pih_attention_prefill_tcgen05", "pih_gemm_skinny", "pih_set_dependent_launch", "pih_set_attention_cluster_merge",
-                     "pih_gemm_skinny_f32out", "pih_block_tail_chain", "pih_block_tail_chain_reset"):
+                     "pih_gemm_skinny_f32out", "pih_block_tail_chain", "pih_block_tail_chain_reset",
+                     "pih_qk_attention_fused"):
             getattr(lib, name).restype = c_int
         lib.pih_attention_scratch_floats.restype = c_ll
 
@@ -380,6 +382,47 @@ class CudaOps:
             kv_map if (self.tma_attention and dec_cap > 0) else None,
             self._err(), self._stream())
         self._check(rc, "paged_attention_mma")
+        return out
+
+    def qk_attention_fused(self, qkv, *, heads, kv_heads, head_dim, q_norm, k_norm, eps, rope_table, rotary_dim,
+                           kv_cache, block_table, step, scale, window, write_kv):
+        """``qk_norm_rope_kv_write`` and ``paged_attention`` as one kernel, for steps whose requests are all
+        decode-like (bf16, the TMA split kernel's shapes, rotation over the whole head).  ``qkv`` stays raw.
+        Returns the attention output, or None when the separate kernels have to run."""
+        if (not self.fused_qk_attention or qkv.dtype != torch.bfloat16 or not self.tensor_core_attention
+                or not self.tma_attention or (rope_table is not None and rotary_dim != head_dim)
+                or (q_norm is not None and k_norm is not None and q_norm.dtype != k_norm.dtype)):
+            return None
+        group = heads // kv_heads
+        plans = getattr(step, "attention_plans", None)
+        plan = plans[group] if plans is not None and group in plans else None
+        if plan is None:
+            plan = self.attention_plan(step.host_cu_q, step.host_q_start, group)
+            if plans is not None:
+                plans[group] = plan
+        tile_max_q, dec_cap, dec_ctx = plan
+        max_ctx_ptr = getattr(step, "meta", None)
+        if tile_max_q > 0 or dec_cap <= 0 or (self.attention_split == 0 and max_ctx_ptr is None):
+            return None
+        kv_map = self.kv_tensor_map(kv_cache)
+        if kv_map is None:
+            return None
+        rows = qkv.shape[0]
+        num_pages, page_size = kv_cache.shape[0], kv_cache.shape[3]
+        nsplits = self.splits_for(step.num_requests, kv_heads)
+        self.reserve_attention_scratch(step.num_requests, dec_cap, heads, kv_heads, head_dim, dec_ctx)
+        out = torch.empty(rows, heads * head_dim, dtype=qkv.dtype, device=qkv.device)
+        norm = q_norm if q_norm is not None else k_norm
+        rc = self.lib.pih_qk_attention_fused(
+            _ptr(qkv), qkv.stride(0), _ptr(out), _ptr(kv_cache), _ptr(block_table), block_table.shape[1],
+            _ptr(step.cu_q), _ptr(step.q_start), rows, step.num_requests, dec_cap, dec_ctx, heads, kv_heads, head_dim,
+            page_size, num_pages, c_float(scale), int(window), self.attention_split, nsplits, _ptr(max_ctx_ptr),
+            _ptr(self._attn_scratch), kv_map, _DT[norm.dtype] if norm is not None else 1, _ptr(q_norm), _ptr(k_norm),
+            c_float(eps), _ptr(rope_table), rope_table.shape[0] if rope_table is not None else 0,
+            1 if write_kv else 0, self._err(), self._stream())
+        if rc == -2:
+            return None
+        self._check(rc, "qk_attention_fused")
         return out
 
     def paged_attention_generic(self, qkv, *, heads, kv_heads, head_dim, kv_cache, block_table,

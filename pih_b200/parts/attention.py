@@ -87,13 +87,18 @@ class PagedAttention:
         s, ops = self.spec, self.rt.ops
         table = self.position.rotation_table() if self.position is not None else None
         rotary = self.position.rotary_dim if self.position is not None else 0
-        ops.qk_norm_rope_kv_write(
-            qkv, heads=s.heads, kv_heads=s.kv_heads, head_dim=s.head_dim,
-            q_norm=self.q_norm, k_norm=self.k_norm, eps=s.qk_norm_eps or 0.0,
-            rope_table=table, rotary_dim=rotary, positions=step.positions,
-            slot_mapping=cache.slot_mapping, kv_cache=cache.kv, write_kv=cache.writable)
-        attn = ops.paged_attention(
-            qkv, heads=s.heads, kv_heads=s.kv_heads, head_dim=s.head_dim,
-            kv_cache=cache.kv, block_table=cache.block_table, step=step,
-            scale=s.scale, window=s.window or 0)
+        qk = dict(heads=s.heads, kv_heads=s.kv_heads, head_dim=s.head_dim, q_norm=self.q_norm, k_norm=self.k_norm,
+                  eps=s.qk_norm_eps or 0.0, rope_table=table, rotary_dim=rotary)
+        attn = None
+        if hasattr(ops, "qk_attention_fused"):
+            # a decode step: one kernel norms and rotates q and k, appends to the cache and attends
+            attn = ops.qk_attention_fused(qkv, kv_cache=cache.kv, block_table=cache.block_table, step=step,
+                                          scale=s.scale, window=s.window or 0, write_kv=cache.writable, **qk)
+        if attn is None:
+            ops.qk_norm_rope_kv_write(qkv, positions=step.positions, slot_mapping=cache.slot_mapping,
+                                      kv_cache=cache.kv, write_kv=cache.writable, **qk)
+            attn = ops.paged_attention(
+                qkv, heads=s.heads, kv_heads=s.kv_heads, head_dim=s.head_dim,
+                kv_cache=cache.kv, block_table=cache.block_table, step=step,
+                scale=s.scale, window=s.window or 0)
         return ops.linear(attn, self.w_o) if project else attn

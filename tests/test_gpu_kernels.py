@@ -568,3 +568,80 @@ def _check_block_tail_chain(ops, M, x, h, w_o, nw, eps, gate, up, w_gu, w_d):
         alone = ops.block_tail_chain(x[M - 1:].contiguous(), w_o, h[M - 1:].contiguous(), nw, eps, w_gu, w_d)
         assert torch.equal(alone[1][0], y[M - 1])
     ops.check_errors()
+
+
+FUSED_QK_CASES = [
+    # heads, kv_heads, D, page, lens, new, window, norms, rope, write_kv
+    (16, 8, 128, 16, [2048] * 8, [1] * 8, None, True, True, True),          # the decode step of the benchmark
+    (16, 8, 128, 16, [1, 64, 65, 130, 2047, 513], [1, 1, 1, 2, 8, 3], None, True, True, True),   # tile edges, small portions
+    (16, 8, 128, 16, [700, 300, 64], [1, 4, 2], 200, True, True, True),     # window
+    (8, 2, 64, 8, [90, 40, 33], [1, 2, 1], None, True, True, True),         # head_dim 64, G = 4, pages of 8
+    (4, 4, 256, 64, [200, 50], [1, 3], None, True, True, True),             # head_dim 256, G = 1, pages of 64
+    (16, 8, 128, 32, [300, 129], [1, 1], None, False, True, True),          # no q/k norm
+    (16, 8, 128, 16, [300, 129], [2, 1], None, True, False, True),          # no rotation
+    (16, 8, 128, 16, [300, 129], [1, 1], None, True, True, False),          # another entry's cache: nothing appended
+]
+
+
+@pytest.mark.parametrize("splits", [0, 64])
+@pytest.mark.parametrize("case", FUSED_QK_CASES, ids=[f"h{c[0]}kv{c[1]}d{c[2]}p{c[3]}w{c[6]}n{max(c[5])}{'' if c[7] else '-nonorm'}{'' if c[8] else '-norope'}{'' if c[9] else '-nowrite'}" for c in FUSED_QK_CASES])
+def test_qk_attention_fused_matches_the_two_kernels(ops, case, splits):
+    """The decode attention that norms and rotates q and k and appends to the cache itself gives the bits of
+    the q/k kernel followed by the attention kernel — output and cache — with the splits merged as a cluster
+    (automatic cut) and through tickets (64-key splits: more than eight of them)."""
+    heads, kv_heads, D, page, lens, new, window, norms, rope, write_kv = case
+    s = _paged_setup(torch.bfloat16, lens, new, heads, kv_heads, D, page, seed=31)
+    T = sum(new)
+    g = torch.Generator().manual_seed(32)
+    kv_new = torch.randn(T, 2 * kv_heads * D, generator=g).to(torch.bfloat16).to(DEV)
+    qkv = torch.cat([s["q"], kv_new], dim=1).contiguous()
+    qw = (1 + 0.2 * torch.randn(D, generator=g)).to(torch.bfloat16).to(DEV) if norms else None
+    kw = (1 + 0.2 * torch.randn(D, generator=g)).to(torch.bfloat16).to(DEV) if norms else None
+    table = _rope_table(2100, D, 10000.0) if rope else None
+    step = _step_of(lens, new)
+    slots = []
+    for r, (L, n) in enumerate(zip(lens, new)):
+        for pos in range(L - n, L):
+            slots.append(int(s["table"][r, pos // page]) * page + pos % page)
+    slots = torch.tensor(slots, dtype=torch.int32, device=DEV)
+    kw_args = dict(heads=heads, kv_heads=kv_heads, head_dim=D, q_norm=qw, k_norm=kw, eps=1e-6, rope_table=table,
+                   rotary_dim=D if rope else 0)
+    ops.attention_split = splits
+    try:
+        # the two kernels
+        qkv_a, cache_a = qkv.clone(), s["cache"].clone()
+        ops.qk_norm_rope_kv_write(qkv_a, positions=s["positions"], slot_mapping=slots, kv_cache=cache_a,
+                                  write_kv=write_kv, **kw_args)
+        out_a = ops.paged_attention_mma(qkv_a, heads=heads, kv_heads=kv_heads, head_dim=D, kv_cache=cache_a,
+                                        block_table=s["table"], step=step, scale=1.0 / math.sqrt(D), window=window or 0)
+        # one kernel
+        qkv_b, cache_b = qkv.clone(), s["cache"].clone()
+        step_b = _step_of(lens, new)
+        out_b = ops.qk_attention_fused(qkv_b, kv_cache=cache_b, block_table=s["table"], step=step_b,
+                                       scale=1.0 / math.sqrt(D), window=window or 0, write_kv=write_kv, **kw_args)
+    finally:
+        ops.attention_split = 0
+    ops.check_errors()
+    assert out_b is not None
+    assert torch.equal(qkv_b, qkv)                                   # the raw rows are left as they were
+    assert torch.equal(cache_b, cache_a)
+    assert torch.equal(out_b, out_a)
+    if not write_kv:
+        assert torch.equal(cache_b, s["cache"])
+
+
+def test_qk_attention_fused_declines_what_it_does_not_take(ops):
+    heads, kv_heads, D, page = 16, 8, 128, 16
+    lens, new = [300, 40], [1, 40]                                   # a prompt portion in the step
+    s = _paged_setup(torch.bfloat16, lens, new, heads, kv_heads, D, page, seed=33)
+    qkv = torch.cat([s["q"], torch.zeros(sum(new), 2 * kv_heads * D, dtype=torch.bfloat16, device=DEV)], dim=1).contiguous()
+    kw_args = dict(heads=heads, kv_heads=kv_heads, head_dim=D, q_norm=None, k_norm=None, eps=1e-6, rope_table=None,
+                   rotary_dim=0, kv_cache=s["cache"], block_table=s["table"], scale=0.1, window=0, write_kv=True)
+    assert ops.qk_attention_fused(qkv, step=_step_of(lens, new), **kw_args) is None
+    lens, new = [300, 40], [1, 1]
+    table = _rope_table(400, D, 10000.0)
+    s = _paged_setup(torch.bfloat16, lens, new, heads, kv_heads, D, page, seed=34)
+    qkv = torch.cat([s["q"], torch.zeros(2, 2 * kv_heads * D, dtype=torch.bfloat16, device=DEV)], dim=1).contiguous()
+    kw_args.update(kv_cache=s["cache"], block_table=s["table"], rope_table=table, rotary_dim=D // 2)   # partial rotation
+    assert ops.qk_attention_fused(qkv, step=_step_of(lens, new), **kw_args) is None
+    ops.check_errors()
