@@ -61,6 +61,7 @@ class CudaOps:
         self.tma_attention = True          # False: the split kernel gathers with cp.async instead of TMA
         self.tcgen05_attention = True      # False: prompt portions use the mma.sync tile kernel
         self.fused_qk_attention = True     # decode-only steps: q/k norm, rotation and cache append inside the attention kernel
+        self.fused_qk_max_requests = 32    # ... up to this batch (measured: 16 requests +4 %, 32 even, 64 -1.6 %)
         self.cluster_attention = True      # False: splits always merge through scratch memory and tickets
         self.attention_split = 0           # keys per split of the decode attention kernel; 0: from the context, on the device
         self.tensor_core_attention = True  # False: bf16 attention runs on the generic kernel too
@@ -402,7 +403,8 @@ class CudaOps:
                 plans[group] = plan
         tile_max_q, dec_cap, dec_ctx = plan
         max_ctx_ptr = getattr(step, "meta", None)
-        if tile_max_q > 0 or dec_cap <= 0 or (self.attention_split == 0 and max_ctx_ptr is None):
+        if (tile_max_q > 0 or dec_cap <= 0 or (self.attention_split == 0 and max_ctx_ptr is None)
+                or step.num_requests > self.fused_qk_max_requests):
             return None
         kv_map = self.kv_tensor_map(kv_cache)
         if kv_map is None:
