@@ -15,9 +15,9 @@
 //              sum formed with the same reference);
 //   warps 8, 10  producers: lane p looks up page p of the key tile and issues its TMA boxes; warp 8 feeds the
 //              K ring (three stages), warp 10 the V ring (two);
-//   warp 9     one thread issues the MMAs: S_j = Q K_j^T (8 x K=16) into one of two S buffers, then
-//              O += P_{j-1} V_{j-1} from one of two P buffers; S_j therefore overlaps the softmax of tile j-1,
-//              and the softmax of tile j never waits for the P V product of tile j-1.
+//   warps 9, 11  a thread each issues the MMAs: warp 9 S_j = Q K_j^T (8 x K=16) into one of two S buffers, warp 11
+//              O += P_j V_j from one of two P buffers; S_j overlaps the softmax of tile j-1, and the softmax of
+//              tile j never waits for the P V product of tile j-1.
 //   A CTA takes a late row tile (many keys) and then its early mirror image (few keys), so CTAs are balanced.
 //
 // Tensor memory: S0 [0,128) S1 [128,256) O [256, 256 + D) P0 [384,448) P1 [448,512).  Every mbarrier wait is bounded.
@@ -181,13 +181,14 @@ template <int THREADS> __device__ __forceinline__ void row_group_sync(int quarte
 // One CTA works through up to two row tiles of its (request, kv head): a long one (late rows, many keys)
 // and its short mirror image, so that every CTA has about the same number of key tiles.
 template <int D, int SPLIT>
-__global__ void __launch_bounds__(128 * SPLIT + 96)
+__global__ void __launch_bounds__(128 * SPLIT + 128)
 attn_prefill_tcgen05_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap kv_map) {
   wait_for_prior_kernels();
   using Smem = PrefillSmem<D, SPLIT>;
   constexpr int kSoftmaxThreads = 128 * SPLIT;
   constexpr int kSoftmaxWarps = 4 * SPLIT;
   constexpr int kProducerWarp = 4 * SPLIT, kMmaWarp = 4 * SPLIT + 1, kProducerWarpV = 4 * SPLIT + 2;
+  constexpr int kMmaWarpPV = 4 * SPLIT + 3;
   constexpr int CW = TK / SPLIT;                                  // key columns of a softmax thread
   constexpr int OW = D / SPLIT;                                   // output columns of a softmax thread
   static_assert(CW == 64 || CW == 32, "a thread reads its scores with one tcgen05.ld of 32 or 64 columns");
@@ -323,43 +324,56 @@ attn_prefill_tcgen05_kernel(const PrefillParams p, const __grid_constant__ CUten
         }
       }
     } else if (warp == kMmaWarp) {
-      // ---------------- MMA issuer ----------------
+      // ---------------- MMA issuer of S_j = Q K_j^T ----------------
+      // The S products and the P V products are issued by a thread each.  One thread for both was the block's
+      // bottleneck: a tcgen05.mma costs its issuer about 80 cycles, a satisfied barrier wait with its fence
+      // about 270, so sixteen MMAs and four waits a tile came to 2750 cycles against 1900 of softmax.
       if (lane == 0) {
         constexpr uint32_t idesc_s = idesc_bf16(TQ, TK, false);
-        constexpr uint32_t idesc_o = idesc_bf16(TQ, D, true);
-        const uint32_t q_addr = smem_u32(sm.q);
+        // Operand descriptors are made once; a descriptor's low bits hold the address in units of 16 bytes, so
+        // a step to another k slice, panel or stage is one 64-bit addition.
+        uint64_t q_desc[D / 16];
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk)
+          q_desc[kk] = desc_kmajor(smem_u32(sm.q) + (kk / 4) * PANEL_BYTES + (kk % 4) * 32);
+        const uint64_t k_desc0 = desc_kmajor(smem_u32(sm.k[0]));
+        constexpr uint64_t kStageUnits = (PANELS * KV_PANEL_BYTES) >> 4;
         bool alive = mbar_wait(&sm.q_full, 0, p.error);
         tc_fence_after();
-        for (int j = 0; j <= ntiles && alive; ++j) {
-          if (j < ntiles) {
-            const int b = j & 1, use = j >> 1, s = j % K_STAGES;
-            if (use > 0 && !mbar_wait(&sm.s_empty[b], (use - 1) & 1, p.error)) break;
-            if (!mbar_wait(&sm.k_full[s], (j / K_STAGES) & 1, p.error)) break;
-            tc_fence_after();
-            const uint32_t k_addr = smem_u32(sm.k[s]);
+        for (int j = 0; j < ntiles && alive; ++j) {
+          const int b = j & 1, use = j >> 1, s = j % K_STAGES;
+          if (use > 0 && !mbar_wait(&sm.s_empty[b], (use - 1) & 1, p.error)) break;
+          if (!mbar_wait(&sm.k_full[s], (j / K_STAGES) & 1, p.error)) break;
+          tc_fence_after();
+          const uint64_t k_desc = k_desc0 + static_cast<uint64_t>(s) * kStageUnits;
+          const uint32_t tmem_s = tmem + b * TK;
 #pragma unroll
-            for (int kk = 0; kk < D / 16; ++kk)
-              umma(tmem + b * TK, desc_kmajor(q_addr + (kk / 4) * PANEL_BYTES + (kk % 4) * 32),
-                   desc_kmajor(k_addr + (kk / 4) * KV_PANEL_BYTES + (kk % 4) * 32), idesc_s, kk > 0 ? 1u : 0u);
-            umma_commit(&sm.k_empty[s]);
-            umma_commit(&sm.s_full[b]);
-          }
-          if (j >= 1) {
-            const int i = j - 1, s = i % V_STAGES;
-            if (!mbar_wait(&sm.p_full[i % P_BUFS], (i / P_BUFS) & 1, p.error)) break;
-            if (!mbar_wait(&sm.v_full[s], (i / V_STAGES) & 1, p.error)) break;
-            tc_fence_after();
-            const uint32_t v_addr = smem_u32(sm.v[s]);
-            const uint32_t tmem_p = tmem + 384 + (i % P_BUFS) * (TK / 2);
+          for (int kk = 0; kk < D / 16; ++kk)
+            umma(tmem_s, q_desc[kk], k_desc + (((kk / 4) * KV_PANEL_BYTES + (kk % 4) * 32) >> 4), idesc_s,
+                 kk > 0 ? 1u : 0u);
+          umma_commit(&sm.k_empty[s]);
+          umma_commit(&sm.s_full[b]);
+        }
+      }
+    } else if (warp == kMmaWarpPV) {
+      // ---------------- MMA issuer of O += P_i V_i ----------------
+      if (lane == 0) {
+        constexpr uint32_t idesc_o = idesc_bf16(TQ, D, true);
+        const uint64_t v_desc0 = desc_mnmajor(smem_u32(sm.v[0]), KV_PANEL_BYTES);
+        constexpr uint64_t kStageUnits = (PANELS * KV_PANEL_BYTES) >> 4;
+        for (int i = 0; i < ntiles; ++i) {
+          const int s = i % V_STAGES;
+          if (!mbar_wait(&sm.p_full[i % P_BUFS], (i / P_BUFS) & 1, p.error)) break;
+          if (!mbar_wait(&sm.v_full[s], (i / V_STAGES) & 1, p.error)) break;
+          tc_fence_after();
+          const uint64_t v_desc = v_desc0 + static_cast<uint64_t>(s) * kStageUnits;
+          const uint32_t tmem_p = tmem + 384 + (i % P_BUFS) * (TK / 2);
 #pragma unroll
-            for (int kk = 0; kk < TK / 16; ++kk) {
-              const uint64_t bdesc = desc_mnmajor(v_addr + kk * 16 * 128, KV_PANEL_BYTES);
-              umma_a_tmem(tmem_o, tmem_p + kk * 8, bdesc, idesc_o, (i > 0 || kk > 0) ? 1u : 0u);
-            }
-            umma_commit(&sm.v_empty[s]);
-            umma_commit(&sm.p_empty[i % P_BUFS]);
-            if (i == ntiles - 1) umma_commit(&sm.o_ready);
-          }
+          for (int kk = 0; kk < TK / 16; ++kk)
+            umma_a_tmem(tmem_o, tmem_p + kk * 8, v_desc + ((kk * 16 * 128) >> 4), idesc_o, (i > 0 || kk > 0) ? 1u : 0u);
+          umma_commit(&sm.v_empty[s]);
+          umma_commit(&sm.p_empty[i % P_BUFS]);
+          if (i == ntiles - 1) umma_commit(&sm.o_ready);
         }
       }
     } else {
@@ -569,7 +583,7 @@ extern "C" int pih_attention_prefill_tcgen05(const void* q, int q_stride, void* 
       if (e != cudaSuccess) return static_cast<int>(e);
       configured[0] = true;
     }
-    launch_kernel(attn_prefill_tcgen05_kernel<128, SPLIT>, dim3(grid), dim3(128 * SPLIT + 96), smem, s, p, map);
+    launch_kernel(attn_prefill_tcgen05_kernel<128, SPLIT>, dim3(grid), dim3(128 * SPLIT + 128), smem, s, p, map);
   } else {
     const int smem = static_cast<int>(sizeof(PrefillSmem<64, 2>)) + 1024;
     if (!configured[1]) {
@@ -577,7 +591,7 @@ extern "C" int pih_attention_prefill_tcgen05(const void* q, int q_stride, void* 
       if (e != cudaSuccess) return static_cast<int>(e);
       configured[1] = true;
     }
-    launch_kernel(attn_prefill_tcgen05_kernel<64, 2>, dim3(grid), dim3(352), smem, s, p, map);
+    launch_kernel(attn_prefill_tcgen05_kernel<64, 2>, dim3(grid), dim3(384), smem, s, p, map);
   }
   PIH_LAUNCH_CHECK();
   return 0;
