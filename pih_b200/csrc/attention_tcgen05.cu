@@ -138,6 +138,14 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&v)[32
       "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31])
       : "memory");
 }
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&v)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};\n" ::"r"(taddr),
+      "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]), "r"(v[9]),
+      "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15])
+      : "memory");
+}
 __device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory"); }
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory"); }
 
@@ -403,7 +411,6 @@ attn_prefill_tcgen05_kernel(const PrefillParams p, const __grid_constant__ CUten
       const int first = (row_valid && p.window > 0) ? max(0, pos - p.window + 1) : 0;
       const float sl = p.scale * kLog2e5;
       float m_ref = -INFINITY, l = 0.0f;
-      static_assert(CW == 64, "a thread stores its 32 packed pairs of P with one tcgen05.st");
       bool ok = true;
 
       for (int j = 0; j < ntiles; ++j) {
@@ -485,7 +492,8 @@ attn_prefill_tcgen05_kernel(const PrefillParams p, const __grid_constant__ CUten
           __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
           pk[e] = *reinterpret_cast<uint32_t*>(&h);
         }
-        tmem_st32(tmem + 384 + pb * (TK / 2) + lane_base + part * (CW / 2), pk);
+        if constexpr (CW == 64) tmem_st32(tmem + 384 + pb * (TK / 2) + lane_base + part * (CW / 2), pk);
+        else tmem_st16(tmem + 384 + pb * (TK / 2) + lane_base + part * (CW / 2), pk);
         tmem_wait_st();
         l = l * alpha + sum;
         tc_fence_before();
@@ -576,6 +584,8 @@ extern "C" int pih_attention_prefill_tcgen05(const void* q, int q_stride, void* 
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   static bool configured[2] = {false, false};
   if (head_dim == 128) {
+    // two threads per row; four (sixteen softmax warps) were measured no faster once the MMA issue was off the
+    // critical path: the exponentials are bound by the special-function unit, not by latency
     constexpr int SPLIT = 2;
     const int smem = static_cast<int>(sizeof(PrefillSmem<128, SPLIT>)) + 1024;
     if (!configured[0]) {
