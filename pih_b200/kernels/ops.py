@@ -310,21 +310,27 @@ class CudaOps:
                 tile_max_q = max(tile_max_q, n)
         return tile_max_q, dec_cap, dec_ctx
 
-    def splits_for(self, num_requests: int, kv_heads: int) -> int:
+    def splits_for(self, num_requests: int, kv_heads: int, max_ctx: int = 0) -> int:
         """Splits per request of the decode attention: as many as fill the 2 x 148 CTA slots of the GPU in
         one wave (small batches are cut finely so that enough CTAs pull bandwidth, large ones not at all).
-        A function of the batch size only; the keys per split follow the context on the device."""
+        Up to eight splits merge as a thread-block cluster, which is what a short context wants (the merge
+        is most of its time); a long context wants every slot pulling (one request of 32768 keys: 69 us with
+        8 splits, 34 us with 37), so beyond ``CLUSTER_MAX_KEYS`` keys per split the finer cut with the merge
+        through scratch memory is taken.  A function of the batch size and the longest context that the
+        step's block tables can hold, not of the contexts themselves: a captured step keeps its grid."""
         slots = (2 * 148) // max(1, num_requests * kv_heads)
-        if self.cluster_attention and self.tma_attention and slots > 8:
+        if self.cluster_attention and self.tma_attention and slots > 8 and max_ctx <= 8 * self.CLUSTER_MAX_KEYS:
             return 8                                   # one portable cluster per (request, kv head)
         return max(1, min(64, slots))
+
+    CLUSTER_MAX_KEYS = 768
 
     def reserve_attention_scratch(self, num_requests, dec_tok_cap, heads, kv_heads, head_dim, max_ctx) -> None:
         """Make the split kernel's scratch large enough (before a CUDA graph that uses it is
         captured: an allocation cannot happen under capture).  A buffer that is outgrown is kept
         alive, because captured graphs hold its address."""
         splits = (-(-max_ctx // self.attention_split) if self.attention_split
-                  else self.splits_for(num_requests, kv_heads))
+                  else self.splits_for(num_requests, kv_heads, max_ctx))
         need = self.lib.pih_attention_scratch_floats(num_requests, dec_tok_cap, heads, kv_heads, head_dim, splits)
         if self._attn_scratch is None or self._attn_scratch.numel() < need:
             if self._attn_scratch is not None:
@@ -357,7 +363,7 @@ class CudaOps:
         out = torch.empty(rows, heads * head_dim, dtype=qkv.dtype, device=qkv.device)
         num_pages, page_size = kv_cache.shape[0], kv_cache.shape[3]
         split = self.attention_split                       # 0: cut on the device into `nsplits` parts
-        nsplits = self.splits_for(step.num_requests, kv_heads)
+        nsplits = self.splits_for(step.num_requests, kv_heads, dec_ctx)
         max_ctx_ptr = getattr(step, "meta", None)
         if split == 0 and max_ctx_ptr is None:              # a caller without a packed batch: fix the cut here
             split = max(64, -(-(-(-max(dec_ctx, 1) // nsplits)) // 64) * 64)
@@ -411,7 +417,7 @@ class CudaOps:
             return None
         rows = qkv.shape[0]
         num_pages, page_size = kv_cache.shape[0], kv_cache.shape[3]
-        nsplits = self.splits_for(step.num_requests, kv_heads)
+        nsplits = self.splits_for(step.num_requests, kv_heads, dec_ctx)
         self.reserve_attention_scratch(step.num_requests, dec_cap, heads, kv_heads, head_dim, dec_ctx)
         out = torch.empty(rows, heads * head_dim, dtype=qkv.dtype, device=qkv.device)
         norm = q_norm if q_norm is not None else k_norm
