@@ -37,14 +37,16 @@ class _InFlight:
     """A step that has been queued on the device: its plan and the ids it samples, on the device and — by a
     copy queued right behind the sampler, before any later step — in pinned host memory."""
 
-    def __init__(self, out, tokens):
+    def __init__(self, out, tokens, landing=None):
         self.out = out
         self.tokens = tokens
         self.host = self.copied = None
         if tokens is not None and tokens.device.type == "cuda":
-            self.host = torch.empty(tokens.shape, dtype=tokens.dtype, pin_memory=True)
+            # `landing`: a pinned buffer and its event, owned by the engine and free again (two steps at most
+            # are in flight, the engine rotates three)
+            buffer, self.copied = landing
+            self.host = buffer[:tokens.shape[0]]
             self.host.copy_(tokens, non_blocking=True)
-            self.copied = torch.cuda.Event()
             self.copied.record()
 
     def token_list(self) -> List[int]:
@@ -81,6 +83,8 @@ class Engine:
         self.run_ahead = run_ahead       # plan and queue the next decode step before this one's ids are read
         self._inflight: Optional[_InFlight] = None
         self.steps_planned_ahead = 0
+        self._landings = None            # pinned buffers for the sampled ids, made at the first step on a GPU
+        self._landing_turn = 0
 
     # -- the reference client's small calls ---------------------------------------
     def ready(self) -> bool:
@@ -133,7 +137,15 @@ class Engine:
             tokens = self.sampler.sample_on_device(
                 logits, [r.params for r in sampling], [len(r.outputs) + pending for r in sampling],
                 [self.scheduler.suppressed_ids(r, pending) for r in sampling])
-        return _InFlight(out, tokens)
+        return _InFlight(out, tokens, self._landing() if tokens is not None and tokens.device.type == "cuda" else None)
+
+    def _landing(self):
+        if self._landings is None:
+            rows = self.scheduler.max_batch_sequences
+            self._landings = [(torch.empty(rows, dtype=torch.int32, pin_memory=True), torch.cuda.Event())
+                              for _ in range(3)]
+        self._landing_turn = (self._landing_turn + 1) % len(self._landings)
+        return self._landings[self._landing_turn]
 
     def _collect(self, flight: "_InFlight") -> List[Request]:
         out = flight.out
