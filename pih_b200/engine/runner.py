@@ -35,6 +35,28 @@ class _FixedPlans(dict):
         return self._plan
 
 
+class _BoundedPlans(dict):
+    """Attention plans of a captured step of several requests: computed per group size from the rows that
+    each request brings (the step's key fixes them), with the longest context that the step's block tables
+    can hold in place of the contexts themselves."""
+
+    def __init__(self, counts, max_ctx: int):
+        super().__init__()
+        self._counts, self._max_ctx = list(counts), max_ctx
+
+    def __contains__(self, key):
+        return True
+
+    def __getitem__(self, group):
+        tile_max_q = dec_cap = 0
+        for n in self._counts:
+            if n * group <= 16:
+                dec_cap = max(dec_cap, n)
+            else:
+                tile_max_q = max(tile_max_q, n)
+        return tile_max_q, dec_cap, self._max_ctx if dec_cap else 0
+
+
 class ModelRunner:
     def __init__(self, model, cache: CacheManager, cuda_graphs: bool = False):
         self.cuda_graphs = cuda_graphs
@@ -108,10 +130,14 @@ class ModelRunner:
     # the attention plan); which request owns which row is data in the step's device buffer.  So a step
     # can be captured once per such key and replayed with fresh data written into the same buffer:
     #   * decode steps (every request one token that wants its logits): captured at first sight;
-    #   * a prompt portion of one request with at least GRAPH_MIN_PORTION rows (chunked prefill repeats
-    #     its chunk size): captured when its key is seen the second time.
+    #   * any other step of at least GRAPH_MIN_ROWS rows — a prompt portion, or portions beside decode
+    #     tokens — whose requests each want nothing or their last row: keyed by the rows that each
+    #     request brings, in order, and captured when that key is seen the second time (chunked prefill
+    #     under a token budget repeats its shapes: the same decode rows beside the same portion).  The
+    #     GRAPH_LIMIT most recently used of these are kept.
     GRAPH_WIDTH_STEP = 64           # block-table widths are rounded up to a multiple of this many pages
-    GRAPH_MIN_PORTION = 128
+    GRAPH_MIN_ROWS = 128
+    GRAPH_LIMIT = 48
 
     def _graphable(self, entries) -> bool:
         return self._graph_key(entries) is not None
@@ -121,11 +147,9 @@ class ModelRunner:
             return None
         if all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries):
             return ("decode", len(entries))
-        if len(entries) == 1 and len(entries[0].tokens) >= self.GRAPH_MIN_PORTION:
-            e = entries[0]
-            want = list(e.want)
-            if want in ([], [len(e.tokens) - 1]):
-                return ("portion", len(e.tokens), len(want))
+        counts = tuple(len(e.tokens) for e in entries)
+        if sum(counts) >= self.GRAPH_MIN_ROWS and all(list(e.want) in ([], [len(e.tokens) - 1]) for e in entries):
+            return ("step", counts, tuple(len(e.want) for e in entries))
         return None
 
     @staticmethod
@@ -155,8 +179,8 @@ class ModelRunner:
         key = kind + (width,)
         state = self._graphs.get(key)
         try:
-            if state is None and kind[0] == "portion" and self._sightings.get(key, 0) == 0:
-                # first sight of this portion shape: run it as it is; capture if it comes again
+            if state is None and kind[0] == "step" and self._sightings.get(key, 0) == 0:
+                # first sight of this shape: run it as it is; capture if it comes again
                 self._sightings[key] = 1
                 batch = self.builder.build(entries, self.cache)
                 self._feed(batch, token_feed)
@@ -167,6 +191,8 @@ class ModelRunner:
             else:
                 batch = self.builder.build(entries, self.cache, width=width, device_buffer=state["buffer"])
                 self._feed(batch, token_feed)
+                if key[0] == "step":
+                    self._graphs[key] = self._graphs.pop(key)     # most recently used last
                 state["graph"].replay()
                 self._count_launches(state["launches"])
                 logits = state["logits"]
@@ -194,14 +220,18 @@ class ModelRunner:
         self._feed(batch, token_feed)
         max_ctx = width * self.cache.page_size
         ops = self.model.rt.ops
+        # the attention plans of the graph cover every context that fits the table width
         if key[0] == "decode":
-            # the attention plan of the graph covers every context that fits the table width
             batch.attention_plans = _FixedPlans((0, 1, max_ctx))
-        if key[0] == "decode" and hasattr(ops, "reserve_attention_scratch"):
+        else:
+            batch.attention_plans = _BoundedPlans(key[1], max_ctx)
+        if hasattr(ops, "reserve_attention_scratch"):
             for block in self.model.blocks:
                 spec = getattr(block.mixer, "spec", None)
                 if spec is not None and hasattr(spec, "heads"):
-                    ops.reserve_attention_scratch(B, 1, spec.heads, spec.kv_heads, spec.head_dim, max_ctx)
+                    dec_cap = batch.attention_plans[spec.heads // spec.kv_heads][1]
+                    if dec_cap > 0:
+                        ops.reserve_attention_scratch(B, dec_cap, spec.heads, spec.kv_heads, spec.head_dim, max_ctx)
         caches = [self.cache.view(i, batch.block_tables, batch.slot_mappings) for i in range(self.num_entries)]
         # once eagerly on a side stream (lazy initialisations must not happen under capture) ...
         side = torch.cuda.Stream(self.device)
@@ -222,6 +252,9 @@ class ModelRunner:
         self._count_launches(launches)
         state = {"graph": graph, "buffer": buffer, "logits": logits, "batch": batch, "launches": launches}
         self._graphs[key] = state
+        steps = [k for k in self._graphs if k[0] == "step"]
+        if len(steps) > self.GRAPH_LIMIT:                 # dicts keep insertion order; a replay re-inserts its key
+            del self._graphs[steps[0]]
         return state
 
     def finish(self, rid: Hashable) -> None:

@@ -138,7 +138,7 @@ def test_steps_replayed_from_cuda_graphs_match(model_dirs, tiny_configs, dtype):
         got[rid] = torch.cat(rows)
         runner.finish(rid)
     model.rt.ops.check_errors()
-    assert any(k[0] == "portion" for k in runner._graphs), "no prompt portion was replayed from a graph"
+    assert any(k[0] == "step" for k in runner._graphs), "no prompt portion was replayed from a graph"
     cfg, w = load_plain_weights(model_dirs[name])
     for rid, toks in reqs.items():
         lead = len(toks) - 300
@@ -146,6 +146,51 @@ def test_steps_replayed_from_cuda_graphs_match(model_dirs, tiny_configs, dtype):
         truth = plain_impl.forward(cfg, w, toks)[places]
         plain = plain_impl.forward(cfg, w, toks, "bf16")[places] if dtype == "bfloat16" else None
         compare({rid: got[rid]}, {rid: truth}, dtype, f"graph {rid}", {rid: plain} if plain is not None else None)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_mixed_steps_replayed_from_cuda_graphs_match(model_dirs, tiny_configs, name, dtype):
+    """Steps that hold decode tokens of two requests beside a prompt portion of a third repeat their shape
+    (chunked prefill under a token budget does): the second sighting is captured, later ones are replayed
+    with other requests in the rows — every logit still matches the plain implementation."""
+    from pih_b200.engine import StepEntry
+    from pih_b200.engine.factory import create_runner
+    vocab = tiny_configs[name]["vocab_size"]
+    decoders = traces.make_requests(vocab, [60, 45], seed=41)                       # d0, d1: 20 decode steps each
+    arrivals = {f"p{i}": t for i, t in enumerate(traces.make_requests(vocab, [260] * 4, seed=42).values())}
+    _, model, cache, runner = create_runner(model_dirs[name], dtype, page_size=16 if name == "A" else 8,
+                                            max_cache_tokens=1536, max_requests=4, cuda_graphs=True)
+    got = {rid: [] for rid in list(decoders) + list(arrivals)}
+    places = {rid: [] for rid in got}
+    lead = {rid: len(t) - 8 for rid, t in decoders.items()}
+    for rid, toks in decoders.items():                                                # prompts, whole
+        got[rid].append(runner.step([StepEntry(rid, toks[:lead[rid]], [lead[rid] - 1])]).float().cpu())
+        places[rid].append(lead[rid] - 1)
+    fed = dict(lead)
+    for i, (rid, toks) in enumerate(arrivals.items()):
+        for lo in (0, 130):                                                           # two portions of 130 rows
+            entries = []
+            for d, dt in decoders.items():
+                entries.append(StepEntry(d, [dt[fed[d]]], [0]))
+            entries.append(StepEntry(rid, toks[lo:lo + 130], [129] if lo else []))
+            out = runner.step(entries).float().cpu()
+            for k, d in enumerate(decoders):
+                got[d].append(out[k:k + 1])
+                places[d].append(fed[d])
+                fed[d] += 1
+            if lo:
+                got[rid].append(out[len(decoders):])
+                places[rid].append(259)
+        runner.finish(rid)
+    model.rt.ops.check_errors()
+    assert any(k[0] == "step" and len(k[1]) == 3 for k in runner._graphs), "no mixed step was replayed from a graph"
+    cfg, w = load_plain_weights(model_dirs[name])
+    for rid, toks in {**decoders, **arrivals}.items():
+        truth = plain_impl.forward(cfg, w, toks)[places[rid]]
+        plain = plain_impl.forward(cfg, w, toks, "bf16")[places[rid]] if dtype == "bfloat16" else None
+        compare({rid: torch.cat(got[rid])}, {rid: truth}, dtype, f"mixed graph {rid}", {rid: plain} if plain is not None else None)
+    cache.check()
 
 
 def _run_trace_run(model_dir, dtype, steps, out_dir, max_tokens, env=None):
