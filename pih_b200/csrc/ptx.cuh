@@ -25,21 +25,26 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(bar)) : "memory");
 }
+// One try for the phase with the given parity (the instruction itself may block for a short, bounded time).
+__device__ __forceinline__ bool mbar_try(uint32_t addr, uint32_t parity) {
+  uint32_t done;
+  asm volatile(
+      "{\n.reg .pred p;\n"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      "selp.b32 %0, 1, 0, p;\n}\n"
+      : "=r"(done)
+      : "r"(addr), "r"(parity)
+      : "memory");
+  return done != 0;
+}
 // Bounded wait for the phase with the given parity; false (and kWaitTimedOut recorded) when the bound was hit.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint32_t* error) {
   const uint32_t addr = smem_u32(bar);
+  if (mbar_try(addr, parity)) return true;              // the usual case costs no clock read
   const long long t0 = clock64();
   for (uint32_t spin = 0;; ++spin) {
     if ((spin & 1023u) == 1023u && clock64() - t0 > kWaitCycles) break;
-    uint32_t done;
-    asm volatile(
-        "{\n.reg .pred p;\n"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
-        "selp.b32 %0, 1, 0, p;\n}\n"
-        : "=r"(done)
-        : "r"(addr), "r"(parity)
-        : "memory");
-    if (done) return true;
+    if (mbar_try(addr, parity)) return true;
   }
   publish_error(error, kWaitTimedOut);
   return false;
