@@ -308,11 +308,24 @@ __global__ void qk_norm_rope_kv_wide_kernel(T* __restrict__ qkv, int row_stride,
     }
     cs = *reinterpret_cast<const CsPack*>(rope + (static_cast<size_t>(pos) * HALF + (l16 & 7) * EPL) * 2);
   }
-  WPack wq, wk;
+  // the lane's norm weights as floats, and its sines with the rotation's sign, once for all slots
+  float wq[EPL], wk[EPL];
 #pragma unroll
-  for (int j = 0; j < EPL; ++j) wq.e[j] = wk.e[j] = from_float<W>(1.0f);
-  if (q_w != nullptr) wq = *reinterpret_cast<const WPack*>(q_w + l16 * EPL);
-  if (k_w != nullptr) wk = *reinterpret_cast<const WPack*>(k_w + l16 * EPL);
+  for (int j = 0; j < EPL; ++j) wq[j] = wk[j] = 1.0f;
+  if (q_w != nullptr) {
+    const WPack w = *reinterpret_cast<const WPack*>(q_w + l16 * EPL);
+#pragma unroll
+    for (int j = 0; j < EPL; ++j) wq[j] = to_float<W>(w.e[j]);
+  }
+  if (k_w != nullptr) {
+    const WPack w = *reinterpret_cast<const WPack*>(k_w + l16 * EPL);
+#pragma unroll
+    for (int j = 0; j < EPL; ++j) wk[j] = to_float<W>(w.e[j]);
+  }
+  if (l16 < 8) {
+#pragma unroll
+    for (int j = 0; j < EPL; ++j) cs.e[j].y = -cs.e[j].y;       // first half: x cos - y sin; second: x cos + y sin
+  }
 #pragma unroll
   for (int i = 0; i < SPW; ++i) {
     const int slot = slot0 + 2 * i + sub;
@@ -333,17 +346,14 @@ __global__ void qk_norm_rope_kv_wide_kernel(T* __restrict__ qkv, int row_stride,
     if (normed) {
 #pragma unroll
       for (int j = 0; j < EPL; ++j)
-        v[j] = round_to<T>((v[j] * scale) * to_float<W>(is_q ? wq.e[j] : wk.e[j]));
+        v[j] = round_to<T>((v[j] * scale) * (is_q ? wq[j] : wk[j]));
     }
     Pack outp;
 #pragma unroll
     for (int j = 0; j < EPL; ++j) {
       const float other = __shfl_xor_sync(0xffffffffu, v[j], 8);
       float r = v[j];
-      if (rope != nullptr) {
-        const float c = cs.e[j].x, sn = cs.e[j].y;
-        r = l16 < 8 ? v[j] * c - other * sn : v[j] * c + other * sn;
-      }
+      if (rope != nullptr) r = __fadd_rn(__fmul_rn(v[j], cs.e[j].x), __fmul_rn(other, cs.e[j].y));
       outp.e[j] = from_float<T>(r);
     }
     if (!live) continue;
