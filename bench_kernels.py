@@ -141,7 +141,11 @@ def main() -> int:
             w = torch.randn(args.n, args.k, device=dev).to(bf)
             rates.update(flops=2 * args.m * args.n * args.k, m=args.m, n=args.n, k=args.k,
                          bytes=2 * (args.m * args.k + args.n * args.k + args.m * args.n))
-            if args.impl == "tcgen05":
+            if args.impl == "tcgen05" and args.fused == "swiglu":
+                fn = lambda: ops.linear_tcgen05_swiglu(x, w, tile_n=args.tile_n)
+            elif args.impl == "library" and args.fused == "swiglu":
+                fn = lambda: ops.silu_mul(torch.mm(x, w.t()), 8)
+            elif args.impl == "tcgen05":
                 fn = lambda: ops.linear_tcgen05(x, w, tile_n=args.tile_n)
             elif args.impl == "skinny" and args.fused != "none":
                 d = torch.randn(args.m, args.k, device=dev).to(bf)

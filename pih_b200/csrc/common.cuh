@@ -49,6 +49,15 @@ template <typename T> __device__ __forceinline__ float round_to(float v) {
   return to_float<T>(from_float<T>(v));
 }
 
+// silu(g) * u in 32-bit.  The 32-bit stream uses expf and a true division, as the reference's kernel does
+// (kernels/cuda/qwen_bf16_primitives.cu:274-283); the bf16 stream uses the special-function unit's exp2 and
+// reciprocal, whose two-ulp error in 32-bit is a five-hundredth of a bf16 rounding step.
+template <typename T> __device__ __forceinline__ float silu_times(float g, float u);
+template <> __device__ __forceinline__ float silu_times<float>(float g, float u) { return (g / (1.0f + expf(-g))) * u; }
+template <> __device__ __forceinline__ float silu_times<__nv_bfloat16>(float g, float u) {
+  return __fdividef(g, 1.0f + __expf(-g)) * u;
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
   for (int d = 16; d > 0; d >>= 1) v += __shfl_xor_sync(0xffffffffu, v, d);

@@ -626,16 +626,8 @@ extern "C" int pih_qk_norm_rope_kv_write(int dtype, int weight_dtype, void* qkv,
   return PIH_ERR_BAD_ARGUMENT;
 }
 
-// silu(g) * u in 32-bit.  The 32-bit stream uses expf and a true division, as the reference's kernel does
-// (qwen_bf16_primitives.cu:274-283); the bf16 stream uses the special-function unit's exp2 and reciprocal, whose
-// two-ulp error in 32-bit is a five-hundredth of a bf16 rounding step (the exact forms made the kernel
-// instruction-bound: 11 us for 2048 x 3072 outputs).
-template <typename T> __device__ __forceinline__ float silu_times(float g, float u);
-template <> __device__ __forceinline__ float silu_times<float>(float g, float u) { return (g / (1.0f + expf(-g))) * u; }
-template <> __device__ __forceinline__ float silu_times<__nv_bfloat16>(float g, float u) {
-  return __fdividef(g, 1.0f + __expf(-g)) * u;
-}
-
+// (silu_times: common.cuh.  The exact forms made this kernel instruction-bound on the bf16 stream: 11 us for
+// 2048 x 3072 outputs against 7.7.)
 // 16 bytes per thread and row, two rows per thread with their loads issued together; needs
 // inter * sizeof(T) % 16 == 0 and il a multiple of the vector length.  grid (column vectors / 256, row pairs)
 template <typename T>

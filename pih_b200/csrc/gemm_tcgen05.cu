@@ -67,7 +67,11 @@ struct GemmSmem {
 // Persistent: CTA b computes tiles b, b + gridDim.x, ... (tile t = (t % tiles_m, t / tiles_m), so that the
 // CTAs that run together share a panel of W in L2).  Two accumulators in tensor memory alternate, so the
 // epilogue of one tile overlaps the products of the next.
-template <typename TC, int BN, int NSTAGES>
+// SWIGLU: the rows of W (columns of the product) come in blocks of 16 = 8 gate columns + their 8 up columns, and
+// the epilogue writes out[m, 8 b + i] = round(silu(round(g)) * round(u)) for block b — C is [M, N / 2] — with the
+// roundings of the separate kernels (the product's bf16 output, then SiLU-mul): the gate/up product of a prompt
+// portion never writes its [M, 2 I] result to memory.
+template <typename TC, int BN, int NSTAGES, bool SWIGLU>
 __global__ void __launch_bounds__(192)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                     TC* __restrict__ C, int M, int N, int K, long long ldc, uint32_t* error) {
@@ -188,7 +192,36 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
               "=r"(v[30]), "=r"(v[31])
             : "r"(taddr));
         asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
-        if (row < M && n0 + c0 < N) {
+        if (SWIGLU) {
+          if constexpr (sizeof(TC) == 2) {
+            if (row < M && n0 + c0 < N) {                   // N is a multiple of 16, so is c0: whole blocks
+              TC* dst = C + static_cast<long long>(row) * ldc + (n0 + c0) / 2;
+              uint32_t packed[8];
+#pragma unroll
+              for (int blk = 0; blk < 2; ++blk) {
+#pragma unroll
+                for (int i = 0; i < 8; i += 2) {
+                  float o[2];
+#pragma unroll
+                  for (int e = 0; e < 2; ++e) {
+                    const float g = round_to<TC>(__uint_as_float(v[16 * blk + i + e]));
+                    const float u = round_to<TC>(__uint_as_float(v[16 * blk + 8 + i + e]));
+                    o[e] = silu_times<TC>(g, u);
+                  }
+                  __nv_bfloat162 h = __floats2bfloat162_rn(o[0], o[1]);
+                  packed[4 * blk + i / 2] = *reinterpret_cast<uint32_t*>(&h);
+                }
+              }
+              const int live = min(2, (N - (n0 + c0)) / 16);  // blocks of this chunk that exist
+              if (live == 2 && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+                reinterpret_cast<uint4*>(dst)[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+                reinterpret_cast<uint4*>(dst)[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+              } else {
+                for (int j = 0; j < 4 * live; ++j) reinterpret_cast<uint32_t*>(dst)[j] = packed[j];
+              }
+            }
+          }
+        } else if (row < M && n0 + c0 < N) {
           TC* dst = C + static_cast<long long>(row) * ldc + n0 + c0;
           const bool full = n0 + c0 + 32 <= N && (reinterpret_cast<uintptr_t>(dst) & 15) == 0;
           if (full) {
@@ -247,20 +280,20 @@ using namespace pih;
 // out_dtype: PIH_BF16 or PIH_F32.  Returns PIH_ERR_UNSUPPORTED when the operands cannot be described
 // to TMA (K or a row stride not a multiple of 8 elements, a base not 16-byte aligned): the caller then
 // uses another product.
-template <typename TC, int BN, int NSTAGES>
+template <typename TC, int BN, int NSTAGES, bool SWIGLU = false>
 static int launch_gemm(const CUtensorMap& map_a, const CUtensorMap& map_w, void* C, int M, int N, int K,
                        long long ldc, uint32_t* error, int sms, cudaStream_t s) {
   const int smem = static_cast<int>(sizeof(GemmSmem<BN, NSTAGES>)) + 1024;
   static bool configured = false;                     // per instance
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<TC, BN, NSTAGES>,
+    cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<TC, BN, NSTAGES, SWIGLU>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return static_cast<int>(e);
     configured = true;
   }
   const long long tiles = static_cast<long long>((M + GM - 1) / GM) * ((N + BN - 1) / BN);
   const int grid = static_cast<int>(tiles < sms ? tiles : sms);
-  launch_kernel(gemm_tcgen05_kernel<TC, BN, NSTAGES>, dim3(grid), dim3(192), smem, s, map_a, map_w, static_cast<TC*>(C), M, N, K, ldc, error);
+  launch_kernel(gemm_tcgen05_kernel<TC, BN, NSTAGES, SWIGLU>, dim3(grid), dim3(192), smem, s, map_a, map_w, static_cast<TC*>(C), M, N, K, ldc, error);
   PIH_LAUNCH_CHECK();
   return 0;
 }
@@ -311,4 +344,28 @@ extern "C" int pih_gemm_tcgen05(int out_dtype, const void* A, const void* W, voi
   if (out_dtype == PIH_BF16) return launch_gemm_bn<__nv_bfloat16>(bn, map_a, map_w, C, M, N, K, ldc, error, sms, s);
   if (out_dtype == PIH_F32) return launch_gemm_bn<float>(bn, map_a, map_w, C, M, N, K, ldc, error, sms, s);
   return PIH_ERR_BAD_ARGUMENT;
+}
+
+// The gate/up product of a SwiGLU feed-forward with SiLU-mul in its epilogue (bf16): W [N, K] holds blocks of 8
+// gate rows followed by their 8 up rows (N a multiple of 16), C is [M, N / 2] with row stride ldc.
+extern "C" int pih_gemm_tcgen05_swiglu(const void* A, const void* W, void* C, int M, int N, int K, long long lda,
+                                       long long ldw, long long ldc, int tile_n, uint32_t* error, void* stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if (K <= 0 || (tile_n != 0 && tile_n != 128 && tile_n != 256)) return PIH_ERR_BAD_ARGUMENT;
+  if (N % 16 || K % 8 || lda % 8 || ldw % 8 || (reinterpret_cast<uintptr_t>(A) & 15) ||
+      (reinterpret_cast<uintptr_t>(W) & 15) || (reinterpret_cast<uintptr_t>(C) & 3) || ldc % 2)
+    return PIH_ERR_UNSUPPORTED;
+  static int sms = 0;
+  if (sms == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (sms <= 0) sms = 148;
+  }
+  const int bn = tile_n != 0 ? tile_n : 256;
+  CUtensorMap map_a, map_w;
+  if (!make_map(&map_a, A, M, K, lda, GM) || !make_map(&map_w, W, N, K, ldw, bn)) return PIH_ERR_UNSUPPORTED;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (bn == 256) return launch_gemm<__nv_bfloat16, 256, 4, true>(map_a, map_w, C, M, N, K, ldc, error, sms, s);
+  return launch_gemm<__nv_bfloat16, 128, 6, true>(map_a, map_w, C, M, N, K, ldc, error, sms, s);
 }

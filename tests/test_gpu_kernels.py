@@ -645,3 +645,29 @@ def test_qk_attention_fused_declines_what_it_does_not_take(ops):
     kw_args.update(kv_cache=s["cache"], block_table=s["table"], rope_table=table, rotary_dim=D // 2)   # partial rotation
     assert ops.qk_attention_fused(qkv, step=_step_of(lens, new), **kw_args) is None
     ops.check_errors()
+
+
+@pytest.mark.parametrize("M,I,K", [(300, 264, 200), (2048, 3072, 1024), (130, 8, 64), (129, 1000, 1032)])
+def test_linear_tcgen05_swiglu(ops, M, I, K):
+    """The tcgen05 product with SiLU-mul in its epilogue against the plain parts: gate and up rounded to bf16, then
+    silu(g) * u rounded — each element within what one rounding flip per stage can do (see the few-rows test)."""
+    x = _rand((M, K), torch.bfloat16, 51)
+    gate = _rand((I, K), torch.bfloat16, 52, 0.05)
+    up = _rand((I, K), torch.bfloat16, 53, 0.05)
+    w = torch.stack([gate.reshape(-1, 8, K), up.reshape(-1, 8, K)], dim=1).reshape(2 * I, K).contiguous()
+    act = ops.linear_tcgen05_swiglu(x, w)
+    ops.check_errors()
+    assert act is not None and act.shape == (M, I)
+    g_ref = plain_impl.linear(x.cpu(), gate.cpu(), "bf16")
+    u_ref = plain_impl.linear(x.cpu(), up.cpu(), "bf16")
+    act_ref = plain_impl.silu_mul(g_ref, u_ref, "bf16")
+    ulp = lambda t: torch.exp2(torch.floor(torch.log2(t.abs().clamp_min(1e-30))) - 7)
+    sig = torch.sigmoid(g_ref)
+    silu, dsilu = g_ref * sig, sig * (1 + g_ref * (1 - sig))
+    bound = ulp(g_ref) * (dsilu * u_ref).abs() + ulp(u_ref) * silu.abs() + ulp(act_ref) + 1e-6
+    err = (act.cpu().double() - act_ref).abs()
+    assert bool((err <= 1.05 * bound).all()), float((err / bound).max())
+    # and the separate kernels of the pack
+    act2 = ops.silu_mul(ops.linear(x, w), 8)
+    err2 = (act2.cpu().double() - act.cpu().double()).abs()
+    assert bool((err2 <= 2.1 * bound).all()), float((err2 / bound).max())
