@@ -43,9 +43,29 @@ TINY_B = {
     # layers 1 and 2 see only the last 24 keys: a second cache group with a window
     "use_sliding_window": True, "sliding_window": 24, "max_window_layers": 1,
 }
+# Two more with the head sizes that the TMA-fed, tcgen05 and cluster kernels take (64 and 128), small otherwise:
+# C has a windowed layer, a hidden size that the few-rows product takes and an intermediate size that it refuses;
+# D has one query head per kv head.
+TINY_C = {
+    "architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3", "torch_dtype": "bfloat16",
+    "hidden_act": "silu", "use_cache": True, "tie_word_embeddings": False,
+    "hidden_size": 160, "intermediate_size": 272, "num_hidden_layers": 2,
+    "num_attention_heads": 4, "num_key_value_heads": 2, "head_dim": 64, "vocab_size": 1000,
+    "max_position_embeddings": 2048, "rope_theta": 50000.0, "rms_norm_eps": 1e-6,
+    "bos_token_id": 3, "eos_token_id": 4, "attention_bias": False,
+    "use_sliding_window": True, "sliding_window": 40, "max_window_layers": 1,
+}
+TINY_D = {
+    "architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3", "torch_dtype": "bfloat16",
+    "hidden_act": "silu", "use_cache": True, "tie_word_embeddings": True,
+    "hidden_size": 96, "intermediate_size": 160, "num_hidden_layers": 2,
+    "num_attention_heads": 2, "num_key_value_heads": 2, "head_dim": 128, "vocab_size": 300,
+    "max_position_embeddings": 1024, "rope_theta": 1000000.0, "rms_norm_eps": 1e-6,
+    "bos_token_id": 0, "eos_token_id": 1, "attention_bias": False, "use_sliding_window": False,
+}
 # sigma and seed of the random weights (BASELINE configs: 0.02 / seed 0 and 0.05 / seed 1)
-TINY_INIT = {"A": (0.02, 0), "B": (0.05, 1)}
-TINY = {"A": TINY_A, "B": TINY_B}
+TINY_INIT = {"A": (0.02, 0), "B": (0.05, 1), "C": (0.06, 2), "D": (0.08, 3)}
+TINY = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D}
 
 
 @pytest.fixture(scope="session")

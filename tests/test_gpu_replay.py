@@ -18,8 +18,9 @@ from conftest import ROOT, load_plain_weights
 
 pytestmark = pytest.mark.gpu
 
-LENGTHS = {"A": [70, 45, 90, 33, 61, 50, 77, 40], "B": [64, 33, 97, 41, 80, 55, 35, 66]}
-PAGE = {"A": 16, "B": 8}
+LENGTHS = {"A": [70, 45, 90, 33, 61, 50, 77, 40], "B": [64, 33, 97, 41, 80, 55, 35, 66],
+           "C": [130, 45, 257, 64, 33, 150, 65, 90], "D": [129, 40, 200, 64, 35, 70, 128, 50]}
+PAGE = {"A": 16, "B": 8, "C": 16, "D": 32}
 FAMILIES = ["whole", "tail_decode", "portions", "mixed"]
 
 # 32-bit: accumulation-order noise only (logits are O(1)).
@@ -73,11 +74,11 @@ def compare_with_plain(got, model_dir, name, requests, dtype, what):
 
 @pytest.fixture(scope="module")
 def requests_of(tiny_configs):
-    return {n: traces.make_requests(tiny_configs[n]["vocab_size"], LENGTHS[n], seed=11) for n in ("A", "B")}
+    return {n: traces.make_requests(tiny_configs[n]["vocab_size"], LENGTHS[n], seed=11) for n in ("A", "B", "C", "D")}
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 @pytest.mark.parametrize("family", FAMILIES)
 def test_replay_families(model_dirs, requests_of, name, dtype, family):
     from pih_b200.engine.factory import create_runner
@@ -149,7 +150,7 @@ def test_steps_replayed_from_cuda_graphs_match(model_dirs, tiny_configs, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_mixed_steps_replayed_from_cuda_graphs_match(model_dirs, tiny_configs, name, dtype):
     """Steps that hold decode tokens of two requests beside a prompt portion of a third repeat their shape
     (chunked prefill under a token budget does): the second sighting is captured, later ones are replayed
@@ -159,7 +160,7 @@ def test_mixed_steps_replayed_from_cuda_graphs_match(model_dirs, tiny_configs, n
     vocab = tiny_configs[name]["vocab_size"]
     decoders = traces.make_requests(vocab, [60, 45], seed=41)                       # d0, d1: 20 decode steps each
     arrivals = {f"p{i}": t for i, t in enumerate(traces.make_requests(vocab, [260] * 4, seed=42).values())}
-    _, model, cache, runner = create_runner(model_dirs[name], dtype, page_size=16 if name == "A" else 8,
+    _, model, cache, runner = create_runner(model_dirs[name], dtype, page_size=PAGE[name],
                                             max_cache_tokens=1536, max_requests=4, cuda_graphs=True)
     got = {rid: [] for rid in list(decoders) + list(arrivals)}
     places = {rid: [] for rid in got}
