@@ -3,9 +3,11 @@
 // This is the matrix product of the true 32-bit path (no tensor cores, no
 // TF32, no split tricks) and the plain twin of the tensor-core products.  It
 // also takes bf16 inputs and writes bf16 or fp32.  Every output element is
-// accumulated by one thread in ascending k, so a row's result does not
-// depend on how many other rows the call holds: cutting a prompt into
-// portions or batching it with other requests cannot change a bit.
+// accumulated by one thread in ascending k — sixteen products into a partial
+// sum, the partial sums into the total, which keeps the rounding error of a
+// long sum (k of a thousand and more) near that of a short one — so a row's
+// result does not depend on how many other rows the call holds: cutting a
+// prompt into portions or batching it with other requests cannot change a bit.
 //
 // The reference runs all products through a library
 // (src/backend/cuda/gemm_plan.cpp:83-199: row-major A[m,k], W[n,k] with
@@ -44,6 +46,11 @@ gemm_simt_kernel(const TA* __restrict__ A, const TA* __restrict__ W, TC* __restr
       Ws[c][r] = (gn < N && gk < K) ? to_float<TA>(W[static_cast<long long>(gn) * ldw + gk]) : 0.0f;
     }
     __syncthreads();
+    float part[TM][TN];
+#pragma unroll
+    for (int i = 0; i < TM; ++i)
+#pragma unroll
+      for (int j = 0; j < TN; ++j) part[i][j] = 0.0f;
 #pragma unroll
     for (int k = 0; k < BK; ++k) {
       float a[TM], w[TN];
@@ -54,8 +61,12 @@ gemm_simt_kernel(const TA* __restrict__ A, const TA* __restrict__ W, TC* __restr
 #pragma unroll
       for (int i = 0; i < TM; ++i)
 #pragma unroll
-        for (int j = 0; j < TN; ++j) acc[i][j] = fmaf(a[i], w[j], acc[i][j]);
+        for (int j = 0; j < TN; ++j) part[i][j] = fmaf(a[i], w[j], part[i][j]);
     }
+#pragma unroll
+    for (int i = 0; i < TM; ++i)
+#pragma unroll
+      for (int j = 0; j < TN; ++j) acc[i][j] += part[i][j];
     __syncthreads();
   }
 #pragma unroll
