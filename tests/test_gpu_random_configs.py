@@ -58,3 +58,32 @@ def test_a_random_configuration(tmp_path, seed):
             model.rt.ops.check_errors()
             compare(got, truth, dtype, f"{what}: {dtype} {family}", plain)
             cache.check()
+
+
+@pytest.mark.parametrize("seed", range(4))
+def test_greedy_generation_on_a_random_configuration(tmp_path, seed):
+    """Scheduler, run-ahead, sampler and step function together, in 32-bit: the tokens of the plain implementation."""
+    import torch
+    from pih_b200.config import config_from_dict
+    from pih_b200.engine import Engine
+    from pih_b200.weights import write_random_model
+    rng = random.Random(2000 + seed)
+    raw, page = _random_config(rng)
+    d = str(tmp_path)
+    write_random_model(d, config_from_dict(raw), seed=seed, sigma=0.08)
+    cfg, w = load_plain_weights(d)
+    prompts = list(traces.make_requests(raw["vocab_size"], [rng.randrange(1, 70) for _ in range(5)], seed=seed).values())
+    engine = Engine(d, "float32", page_size=page, max_cache_tokens=1024, maximum_batch_sequences=3,
+                    maximum_batch_tokens=rng.choice([8, 32, 200]))
+    results = engine.complete_batch(prompts, max_tokens=7, ignore_eos=True)
+    engine.rt.ops.check_errors()
+    for prompt, res in zip(prompts, results):
+        ids = list(prompt)
+        for tok in res["token_ids"]:
+            logits = plain_impl.forward(cfg, w, ids)[-1]
+            best = int(torch.argmax(logits))
+            assert tok == best or float(logits[best] - logits[tok]) < 1e-4, (ids[len(prompt):], tok, best)
+            ids.append(tok)
+        assert res["completion_tokens"] == 7 and res["finish_reason"] == "length"
+    engine.cache.check()
+    assert all(f == engine.cache.num_pages for f in engine.cache.num_free_pages())
