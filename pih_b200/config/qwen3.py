@@ -60,7 +60,7 @@ class Qwen3Config:
     sliding_window: Optional[int] = None
     max_window_layers: Optional[int] = None
     bos_token_id: Optional[int] = None
-    eos_token_id: Optional[int] = None
+    eos_token_id: Optional[object] = None     # an id, or a tuple of ids
     model_type: str = "qwen3"
 
     # -- reading ---------------------------------------------------------
@@ -102,7 +102,10 @@ class Qwen3Config:
         ids = {}
         for k in ("bos_token_id", "eos_token_id"):
             v = raw.get(k)
-            if v is not None and (isinstance(v, bool) or not isinstance(v, int)):
+            if k == "eos_token_id" and isinstance(v, (list, tuple)) and v and \
+                    all(isinstance(i, int) and not isinstance(i, bool) for i in v):
+                v = tuple(v)                       # some checkpoints list several end-of-sequence ids
+            elif v is not None and (isinstance(v, bool) or not isinstance(v, int)):
                 raise ValueError(f"config.json: {k} must be an integer or null")
             ids[k] = v
         cfg = cls(head_dim=head_dim, rope_theta=_as_number(raw, "rope_theta"),
@@ -120,11 +123,14 @@ class Qwen3Config:
             raise ValueError(f"head_dim must be even for rotate-half RoPE, got {self.head_dim}")
         for k in ("bos_token_id", "eos_token_id"):
             v = getattr(self, k)
-            if v is not None and not 0 <= v < self.vocab_size:
-                raise ValueError(f"{k}={v} is outside the vocabulary of {self.vocab_size}")
+            for i in (v if isinstance(v, tuple) else () if v is None else (v,)):
+                if not 0 <= i < self.vocab_size:
+                    raise ValueError(f"{k}={i} is outside the vocabulary of {self.vocab_size}")
 
     def to_dict(self) -> dict:
         d = asdict(self)
+        if isinstance(d["eos_token_id"], tuple):
+            d["eos_token_id"] = list(d["eos_token_id"])
         d["architectures"] = [self.architecture]
         d["use_cache"] = True
         d["attention_bias"] = False
@@ -168,7 +174,8 @@ class Qwen3Config:
                              activation=self.hidden_act)
             blocks.append(BlockSpec(prefix=f"model.layers.{i}.", mixer=attn, ffn=ffn,
                                     norm_in=norm, norm_post=norm))
-        eos: Tuple[int, ...] = () if self.eos_token_id is None else (self.eos_token_id,)
+        eos: Tuple[int, ...] = () if self.eos_token_id is None else (
+            tuple(self.eos_token_id) if isinstance(self.eos_token_id, tuple) else (self.eos_token_id,))
         spec = ModelSpec(vocab=self.vocab_size, hidden=self.hidden_size, blocks=tuple(blocks),
                          schedule=tuple(ScheduleEntry(i) for i in range(self.num_hidden_layers)),
                          final_norm=norm, tie_embeddings=self.tie_word_embeddings,
