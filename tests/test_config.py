@@ -58,6 +58,8 @@ def test_roundtrip_through_a_folder(tmp_path, tiny_configs):
     ({"rms_norm_eps": -1.0}, "rms_norm_eps"),
     ({"torch_dtype": "float16"}, "torch_dtype"),
     ({"eos_token_id": 100000}, "outside the vocabulary"),
+    ({"eos_token_id": [2, 100000]}, "outside the vocabulary"),
+    ({"eos_token_id": [2, "x"]}, "eos_token_id"),
     ({"use_sliding_window": True}, "sliding_window"),
 ])
 def test_bad_configurations_are_refused(tiny_configs, change, match):
@@ -65,6 +67,15 @@ def test_bad_configurations_are_refused(tiny_configs, change, match):
     raw.update(change)
     with pytest.raises(ValueError, match=match):
         config_from_dict(raw)
+
+
+def test_several_end_of_sequence_ids(tmp_path, tiny_configs):
+    cfg = config_from_dict(dict(tiny_configs["A"], eos_token_id=[2, 5]))
+    assert cfg.model_spec().eos_token_ids == (2, 5)
+    (tmp_path / "config.json").write_text(json.dumps(cfg.to_dict()))
+    assert load_config(str(tmp_path)) == cfg
+    one = config_from_dict(dict(tiny_configs["A"], eos_token_id=7))
+    assert one.model_spec().eos_token_ids == (7,)
 
 
 def test_missing_key_is_an_error(tiny_configs):
