@@ -302,7 +302,7 @@ def main() -> int:
     if not args.skip_points:
         for b in (1, 64):
             points[f"decode_b{b}"] = round(decode_run(model, b, max(8, args.steps // 2), 3)["tok_s"], 1)
-    pre = {"ms": float("nan"), "tok_s": float("nan"), "flops": 0.0} if args.skip_prefill else prefill_run(model, PREFILL_TOKENS)
+    pre = None if args.skip_prefill else prefill_run(model, PREFILL_TOKENS)
     e2e = None
     if not args.skip_e2e:
         from pih_b200.weights import write_random_model
@@ -313,20 +313,23 @@ def main() -> int:
             e2e = e2e_run(config, d, args.batch, args.steps, args.warmup)
     achieved = main_run["bytes"] / (main_run["ms"] * 1e-3) / 1e9
     line = {
-        "metric": METRIC, "value": round(main_run["tok_s"], 1), "unit": "tok/s", "n_gpus": 1,
+        "metric": METRIC.replace("batch 8", f"batch {args.batch}"), "value": round(main_run["tok_s"], 1), "unit": "tok/s", "n_gpus": 1,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(main_run["ms"], 4),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "impl": "ours",
         "config": {"model": "Qwen3-0.6B random weights seed 2", "layers": args.layers, "layers_of_config": 28,
-                   "hidden": 1024, "heads": 16, "kv_heads": 8, "head_dim": 128, "intermediate": 3072,
-                   "vocab": 151936, "tied_embeddings": True, "global_batch": args.batch, "seq_len": CONTEXT,
+                   "hidden": config.hidden_size, "heads": config.num_attention_heads,
+                   "kv_heads": config.num_key_value_heads, "head_dim": config.head_dim,
+                   "intermediate": config.intermediate_size, "vocab": config.vocab_size,
+                   "tied_embeddings": config.tie_word_embeddings, "global_batch": args.batch, "seq_len": CONTEXT,
                    "context_window": 4096, "page_size": PAGE, "prefill_tokens": PREFILL_TOKENS,
                    "parallelism": "single GPU", "l2": "inputs larger than L2", "peaks": peak_src},
         "e2e": e2e,
         "gpu_launches": main_run["launches"],
         "clocks": clock_summary,
-        "prefill": {"value": round(pre["tok_s"], 1), "tokens": PREFILL_TOKENS, "ms": round(pre["ms"], 3),
-                    "frac": round(pre["flops"] / (pre["ms"] * 1e-3) / (bf16_tflops * 1e12), 4)},
+        "prefill": None if args.skip_prefill else {
+            "value": round(pre["tok_s"], 1), "tokens": PREFILL_TOKENS, "ms": round(pre["ms"], 3),
+            "frac": round(pre["flops"] / (pre["ms"] * 1e-3) / (bf16_tflops * 1e12), 4)},
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": hbm_gbs, "unit": "GB/s",
                      "frac": round(achieved / hbm_gbs, 4)},
         "points": points,

@@ -250,21 +250,118 @@ __global__ void qk_norm_rope_kv_fast_kernel(T* __restrict__ qkv, int row_stride,
   }
 }
 
-// The same for many rows, with a head on 16 lanes (head_dim = 16 * EPL, EPL in {4, 8, 16}): a warp works on two
-// head slots at a time, SPW times, so the per-slot work — the reduction, the reciprocal square root, the
-// address arithmetic — is spread over twice the elements, and a lane's loads are 16 bytes for bf16 heads of 128.
-// Rotation partner: lane ^ 8.  Every lane runs every shuffle; what a lane keeps depends on its slot's kind.
+// The same for many rows, with a head on 16 lanes (head_dim = 16 * EPL, EPL in {4, 8, 16}).  A lane holds EPL / 2
+// elements of the head's first half and the EPL / 2 elements that rotate with them from the second half, so
+// the rotation needs no exchange between lanes; the only shuffles are the four of the sum of squares (a shuffle
+// costs the issue slots of four arithmetic instructions).  A warp works on two head slots at a time, SPW times.
+// A group of slots that holds only V heads is copied to the cache and nothing else; a group of one kind (only q
+// or only k heads: the usual case) reads one set of norm weights and selects nothing per element.
+template <typename T, int N>
+struct alignas(N * sizeof(T) > 16 ? 16 : N * sizeof(T)) VecPack {
+  T e[N];
+};
+
+template <typename T, typename W, int EPL, int SPW, bool MIXED>
+__device__ __forceinline__ void qk_wide_slots(const VecPack<T, EPL / 2> (&lo)[SPW], const VecPack<T, EPL / 2> (&hi)[SPW],
+                                              T* __restrict__ row, T* __restrict__ cache, size_t cache_k,
+                                              size_t head_stride, int m, int slot0, int sub, int slots, int heads,
+                                              int kv_heads, const W* __restrict__ q_w, const W* __restrict__ k_w,
+                                              int l16, float eps, const VecPack<float2, EPL / 2>& cs, bool has_rope) {
+  constexpr int D = 16 * EPL, HALF = D / 2, E2 = EPL / 2;
+  // wa: the weights of the group's first kind; wb (mixed groups only): the k weights behind q slots
+  const bool first_is_q = slot0 < heads;
+  const W* wa_src = first_is_q ? q_w : k_w;
+  float wa_lo[E2], wa_hi[E2], wb_lo[E2], wb_hi[E2];
+#pragma unroll
+  for (int j = 0; j < E2; ++j) wa_lo[j] = wa_hi[j] = wb_lo[j] = wb_hi[j] = 1.0f;
+  if (wa_src != nullptr) {
+    const VecPack<W, E2> l = *reinterpret_cast<const VecPack<W, E2>*>(wa_src + l16 * E2);
+    const VecPack<W, E2> h = *reinterpret_cast<const VecPack<W, E2>*>(wa_src + HALF + l16 * E2);
+#pragma unroll
+    for (int j = 0; j < E2; ++j) {
+      wa_lo[j] = to_float<W>(l.e[j]);
+      wa_hi[j] = to_float<W>(h.e[j]);
+    }
+  }
+  if (MIXED && first_is_q && k_w != nullptr) {
+    const VecPack<W, E2> l = *reinterpret_cast<const VecPack<W, E2>*>(k_w + l16 * E2);
+    const VecPack<W, E2> h = *reinterpret_cast<const VecPack<W, E2>*>(k_w + HALF + l16 * E2);
+#pragma unroll
+    for (int j = 0; j < E2; ++j) {
+      wb_lo[j] = to_float<W>(l.e[j]);
+      wb_hi[j] = to_float<W>(h.e[j]);
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < SPW; ++i) {
+    const int slot = slot0 + 2 * i + sub;
+    const bool live = slot < slots;
+    const bool is_q = MIXED ? slot < heads : first_is_q;
+    const bool is_k = MIXED ? (!is_q && slot < heads + kv_heads) : !first_is_q;
+    const bool second = MIXED && first_is_q && !is_q;      // a k slot of a group that began with q slots
+    const bool normed = is_q ? q_w != nullptr : (is_k && k_w != nullptr);
+    float x[E2], y[E2];
+    float ss = 0.0f;
+#pragma unroll
+    for (int j = 0; j < E2; ++j) {
+      x[j] = to_float<T>(lo[i].e[j]);
+      y[j] = to_float<T>(hi[i].e[j]);
+      ss += x[j] * x[j];
+      ss += y[j] * y[j];
+    }
+#pragma unroll
+    for (int d = 8; d > 0; d >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, d);      // over the head's 16 lanes
+    if (normed) {
+      const float scale = 1.0f / sqrtf(ss / static_cast<float>(D) + eps);
+#pragma unroll
+      for (int j = 0; j < E2; ++j) {
+        x[j] = round_to<T>((x[j] * scale) * (second ? wb_lo[j] : wa_lo[j]));
+        y[j] = round_to<T>((y[j] * scale) * (second ? wb_hi[j] : wa_hi[j]));
+      }
+    }
+    VecPack<T, E2> out_lo, out_hi;
+#pragma unroll
+    for (int j = 0; j < E2; ++j) {
+      float a = x[j], b = y[j];
+      if (has_rope) {
+        a = __fsub_rn(__fmul_rn(x[j], cs.e[j].x), __fmul_rn(y[j], cs.e[j].y));
+        b = __fadd_rn(__fmul_rn(y[j], cs.e[j].x), __fmul_rn(x[j], cs.e[j].y));
+      }
+      out_lo.e[j] = from_float<T>(a);
+      out_hi.e[j] = from_float<T>(b);
+    }
+    if (!live) continue;
+    T* dst_cache = (!is_q && m >= 0) ? cache + cache_k + static_cast<size_t>(slot - heads) * head_stride : nullptr;
+    if (MIXED && !is_q && !is_k) {                         // a V head: copied as it is
+      if (dst_cache != nullptr) {
+        *reinterpret_cast<VecPack<T, E2>*>(dst_cache) = lo[i];
+        *reinterpret_cast<VecPack<T, E2>*>(dst_cache + HALF) = hi[i];
+      }
+      continue;
+    }
+    T* dst = row + static_cast<size_t>(slot) * D;
+    *reinterpret_cast<VecPack<T, E2>*>(dst) = out_lo;
+    *reinterpret_cast<VecPack<T, E2>*>(dst + HALF) = out_hi;
+    if (dst_cache != nullptr) {
+      *reinterpret_cast<VecPack<T, E2>*>(dst_cache) = out_lo;
+      *reinterpret_cast<VecPack<T, E2>*>(dst_cache + HALF) = out_hi;
+    }
+  }
+}
+
+// Blocks of four warps, at most 64 registers a thread for heads of up to 128: the kernel waits on memory, and
+// what helps it is many resident warps (measured at 2048 rows of 16 + 8 + 8 heads of 128: 13.8 us against 15.2
+// to 17 with eight slots per warp in blocks of eight warps; 256 rows: 3.7 against 4.6).
+constexpr int QK_WIDE_SPW = 2, QK_WIDE_WARPS = 4;
 template <typename T, typename W, int EPL, int SPW>
-__global__ void qk_norm_rope_kv_wide_kernel(T* __restrict__ qkv, int row_stride, int rows, int heads,
-                                            int kv_heads, const W* __restrict__ q_w,
-                                            const W* __restrict__ k_w, float eps,
-                                            const float* __restrict__ rope, int max_pos,
-                                            const int* __restrict__ positions,
-                                            const int* __restrict__ slot_mapping, T* __restrict__ cache,
-                                            int page_size, int num_pages, int write_kv, uint32_t* error) {
+__global__ void __launch_bounds__(QK_WIDE_WARPS * 32, (EPL <= 8 && sizeof(T) == 2) ? 8 : 4)
+qk_norm_rope_kv_wide_kernel(T* __restrict__ qkv, int row_stride, int rows, int heads, int kv_heads,
+                            const W* __restrict__ q_w, const W* __restrict__ k_w, float eps,
+                            const float* __restrict__ rope, int max_pos, const int* __restrict__ positions,
+                            const int* __restrict__ slot_mapping, T* __restrict__ cache, int page_size,
+                            int num_pages, int write_kv, uint32_t* error) {
   wait_for_prior_kernels();
-  constexpr int D = 16 * EPL;
-  constexpr int HALF = D / 2;
+  constexpr int D = 16 * EPL, HALF = D / 2, E2 = EPL / 2;
   const int warps_per_block = blockDim.x >> 5;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int sub = lane >> 4, l16 = lane & 15;
@@ -274,97 +371,58 @@ __global__ void qk_norm_rope_kv_wide_kernel(T* __restrict__ qkv, int row_stride,
   if (item >= static_cast<long long>(rows) * groups) return;
   const int t = static_cast<int>(item / groups);
   const int slot0 = static_cast<int>(item % groups) * 2 * SPW;
-  struct alignas(EPL * sizeof(T) > 16 ? 16 : EPL * sizeof(T)) Pack { T e[EPL]; };
-  struct alignas(EPL * sizeof(W) > 16 ? 16 : EPL * sizeof(W)) WPack { W e[EPL]; };
-  struct alignas(16) CsPack { float2 e[EPL]; };
-  T* row = qkv + static_cast<size_t>(t) * row_stride + l16 * EPL;
-  Pack in[SPW];
+  const int slot_end = min(slot0 + 2 * SPW, slots);        // past the group's last live slot
+  T* row = qkv + static_cast<size_t>(t) * row_stride + l16 * E2;
+  VecPack<T, E2> lo[SPW], hi[SPW];
 #pragma unroll
   for (int i = 0; i < SPW; ++i) {
     const int slot = min(slot0 + 2 * i + sub, slots - 1);
-    in[i] = *reinterpret_cast<const Pack*>(row + static_cast<size_t>(slot) * D);
+    lo[i] = *reinterpret_cast<const VecPack<T, E2>*>(row + static_cast<size_t>(slot) * D);
+    hi[i] = *reinterpret_cast<const VecPack<T, E2>*>(row + static_cast<size_t>(slot) * D + HALF);
   }
   int m = -1;
   size_t cache_k = 0;
-  if (slot0 + 2 * SPW > heads) {
+  if (slot_end > heads) {
     m = slot_mapping[t];
     if (m < 0 || m >= num_pages * page_size) {
       if (lane == 0) publish_error(error, kRowWithoutPage);
       m = -1;
     } else {
       const int page = m / page_size, off = m % page_size;
-      cache_k = static_cast<size_t>(page) * 2 * kv_heads * page_size * D + static_cast<size_t>(off) * D + l16 * EPL;
+      cache_k = static_cast<size_t>(page) * 2 * kv_heads * page_size * D + static_cast<size_t>(off) * D + l16 * E2;
     }
   }
   const size_t head_stride = static_cast<size_t>(page_size) * D;
-  CsPack cs;
+  if (slot0 >= heads + kv_heads) {                         // only V heads: a copy
+    if (m < 0) return;
 #pragma unroll
-  for (int j = 0; j < EPL; ++j) cs.e[j] = make_float2(1.0f, 0.0f);
-  if (rope != nullptr && slot0 < heads + kv_heads) {
+    for (int i = 0; i < SPW; ++i) {
+      const int slot = slot0 + 2 * i + sub;
+      if (slot >= slots) continue;
+      T* dst = cache + cache_k + static_cast<size_t>(slot - heads) * head_stride;
+      *reinterpret_cast<VecPack<T, E2>*>(dst) = lo[i];
+      *reinterpret_cast<VecPack<T, E2>*>(dst + HALF) = hi[i];
+    }
+    return;
+  }
+  VecPack<float2, E2> cs;
+#pragma unroll
+  for (int j = 0; j < E2; ++j) cs.e[j] = make_float2(1.0f, 0.0f);
+  if (rope != nullptr) {
     int pos = positions[t];
     if (pos < 0 || pos >= max_pos) {
       if (lane == 0) publish_error(error, kBadPosition);
       pos = 0;
     }
-    cs = *reinterpret_cast<const CsPack*>(rope + (static_cast<size_t>(pos) * HALF + (l16 & 7) * EPL) * 2);
+    cs = *reinterpret_cast<const VecPack<float2, E2>*>(rope + (static_cast<size_t>(pos) * HALF + l16 * E2) * 2);
   }
-  // the lane's norm weights as floats, and its sines with the rotation's sign, once for all slots
-  float wq[EPL], wk[EPL];
-#pragma unroll
-  for (int j = 0; j < EPL; ++j) wq[j] = wk[j] = 1.0f;
-  if (q_w != nullptr) {
-    const WPack w = *reinterpret_cast<const WPack*>(q_w + l16 * EPL);
-#pragma unroll
-    for (int j = 0; j < EPL; ++j) wq[j] = to_float<W>(w.e[j]);
-  }
-  if (k_w != nullptr) {
-    const WPack w = *reinterpret_cast<const WPack*>(k_w + l16 * EPL);
-#pragma unroll
-    for (int j = 0; j < EPL; ++j) wk[j] = to_float<W>(w.e[j]);
-  }
-  if (l16 < 8) {
-#pragma unroll
-    for (int j = 0; j < EPL; ++j) cs.e[j].y = -cs.e[j].y;       // first half: x cos - y sin; second: x cos + y sin
-  }
-#pragma unroll
-  for (int i = 0; i < SPW; ++i) {
-    const int slot = slot0 + 2 * i + sub;
-    const bool live = slot < slots;
-    const bool is_q = slot < heads;
-    const bool is_k = !is_q && slot < heads + kv_heads;
-    const bool normed = is_q ? q_w != nullptr : (is_k && k_w != nullptr);
-    float v[EPL];
-    float ss = 0.0f;
-#pragma unroll
-    for (int j = 0; j < EPL; ++j) {
-      v[j] = to_float<T>(in[i].e[j]);
-      ss += v[j] * v[j];
-    }
-#pragma unroll
-    for (int d = 8; d > 0; d >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, d);      // over the head's 16 lanes
-    const float scale = 1.0f / sqrtf(ss / static_cast<float>(D) + eps);
-    if (normed) {
-#pragma unroll
-      for (int j = 0; j < EPL; ++j)
-        v[j] = round_to<T>((v[j] * scale) * (is_q ? wq[j] : wk[j]));
-    }
-    Pack outp;
-#pragma unroll
-    for (int j = 0; j < EPL; ++j) {
-      const float other = __shfl_xor_sync(0xffffffffu, v[j], 8);
-      float r = v[j];
-      if (rope != nullptr) r = __fadd_rn(__fmul_rn(v[j], cs.e[j].x), __fmul_rn(other, cs.e[j].y));
-      outp.e[j] = from_float<T>(r);
-    }
-    if (!live) continue;
-    T* dst_cache = (!is_q && m >= 0) ? cache + cache_k + static_cast<size_t>(slot - heads) * head_stride : nullptr;
-    if (!is_q && !is_k) {                                  // a V head: copied as it is
-      if (dst_cache != nullptr) *reinterpret_cast<Pack*>(dst_cache) = in[i];
-      continue;
-    }
-    *reinterpret_cast<Pack*>(row + static_cast<size_t>(slot) * D) = outp;
-    if (dst_cache != nullptr) *reinterpret_cast<Pack*>(dst_cache) = outp;
-  }
+  const bool one_kind = slot_end <= heads || (slot0 >= heads && slot_end <= heads + kv_heads);
+  if (one_kind)
+    qk_wide_slots<T, W, EPL, SPW, false>(lo, hi, row, cache, cache_k, head_stride, m, slot0, sub, slots, heads,
+                                         kv_heads, q_w, k_w, l16, eps, cs, rope != nullptr);
+  else
+    qk_wide_slots<T, W, EPL, SPW, true>(lo, hi, row, cache, cache_k, head_stride, m, slot0, sub, slots, heads,
+                                        kv_heads, q_w, k_w, l16, eps, cs, rope != nullptr);
 }
 
 // ---------------------------------------------------------------------------
@@ -555,8 +613,9 @@ static int launch_qk(void* qkv, int row_stride, int rows, int heads, int kv_head
     const int slots = heads + (write_kv ? 2 * kv_heads : 0);
     // with few rows (a decode step) one slot per warp is the shortest chain
     if (rows >= 64) {
-      // many rows: a head on 16 lanes, eight head slots per warp
-      constexpr int SPW = 4;
+      // many rows: a head on 16 lanes, four head slots per warp
+      constexpr int SPW = QK_WIDE_SPW;
+      const int warps = QK_WIDE_WARPS;
       const long long work = static_cast<long long>(rows) * ((slots + 2 * SPW - 1) / (2 * SPW));
       const unsigned blocks = static_cast<unsigned>((work + warps - 1) / warps);
 #define PIH_QK_WIDE(EPL)                                                                                   \
