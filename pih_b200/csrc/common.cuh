@@ -100,7 +100,10 @@ __device__ __forceinline__ float block_sum(float v, float* scratch /* >= 33 floa
 // (Qwen3-0.6B shapes, batch 8, 2048-token contexts, CUDA graph), plain launches took 1.483 ms, the
 // attribute alone 1.406 ms, and the attribute with an early signal — at the top of every kernel, or only
 // before the epilogue of the two large ones — 1.63 and 1.50 ms: blocks that sit in the wait while the
-// earlier kernel still runs cost more than their early residency gains.  The reference launches every
+// earlier kernel still runs cost more than their early residency gains.  Without an early signal a kernel's
+// blocks start only when the kernel before it has ended, so work placed before the wait overlaps just that
+// kernel's flush: the decode attention fetching its first K/V tiles before its wait changed nothing
+// (1.1233 against 1.1239 ms).  The reference launches every
 // kernel with full serialisation (kernels/cuda/qwen_bf16_primitives.cu, all launches).
 __device__ __forceinline__ void wait_for_prior_kernels() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
