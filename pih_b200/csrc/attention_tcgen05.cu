@@ -160,6 +160,44 @@ __device__ __forceinline__ void cp16(void* smem, const void* gmem, int bytes) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(smem_u32(smem)), "l"(gmem), "r"(bytes));
 }
 
+// Packed row i of a (request, kv head) is token i / G, head g G + i % G.  A thread that walks rows i, i + step, ...
+// keeps the pair up to date with additions: the two divisions are done once (a walk with a division per row
+// made one warp's fetch of a Q tile take about ten thousand cycles).
+struct PackedRowWalk {
+  int i, tok, hd, step, tok_step, hd_step, G;
+  __device__ __forceinline__ PackedRowWalk(int first, int step_, int G_)
+      : i(first), tok(first / G_), hd(first % G_), step(step_), tok_step(step_ / G_), hd_step(step_ % G_), G(G_) {}
+  __device__ __forceinline__ void next() {
+    i += step;
+    tok += tok_step;
+    hd += hd_step;
+    if (hd >= G) {
+      hd -= G;
+      ++tok;
+    }
+  }
+};
+
+// A query tile (TQ packed rows) into shared memory as D / 64 panels of 128 rows x 128 bytes with the 128-byte
+// swizzle, by threads t of nthreads (a multiple of D / 8: a thread keeps its 16-byte column); rows past `packed`
+// are zero.
+template <int D>
+__device__ __forceinline__ void load_q_tile(unsigned char* q_smem, const PrefillParams& p, int row0, int g, int G,
+                                            int packed, int tile_row0, int t, int nthreads) {
+  constexpr int PANEL_BYTES = TQ * 128;
+  constexpr int CPR = D / 8;                                     // 16-byte chunks of a row
+  const int ch = t % CPR, row_step = nthreads / CPR;
+  PackedRowWalk w(tile_row0 + t / CPR, row_step, G);
+  unsigned char* col = q_smem + (ch >> 3) * PANEL_BYTES;
+  for (int qrow = t / CPR; qrow < TQ; qrow += row_step, w.next()) {
+    const bool valid = w.i < packed;
+    const __nv_bfloat16* src = p.q;
+    if (valid)
+      src = p.q + static_cast<size_t>(row0 + w.tok) * p.q_stride + static_cast<size_t>(g * G + w.hd) * D + ch * 8;
+    cp16(col + qrow * 128 + (((ch & 7) ^ (qrow & 7)) << 4), src, valid ? 16 : 0);
+  }
+}
+
 template <int D, int SPLIT>
 struct PrefillSmem {
   static constexpr int PANELS = D / 64;
@@ -331,6 +369,18 @@ attn_prefill_tcgen05_kernel(const PrefillParams p, const __grid_constant__ CUten
             tma_load_3d(dst + pn * KV_PANEL_BYTES, &kv_map, pn * 64, 0, z, &full[s]);
         }
       }
+      if (item == 0 && items == 2) {
+        // The mirror tile's Q rows, fetched by the two producer warps while this tile's last steps and its
+        // epilogue run (a block of a 2048-token prompt spent 3.3 of its 59 thousand cycles waiting for them).
+        // Q is free once the last S product has read it: that product's completion is the last arrival on its
+        // K stage's barrier.
+        const int jl = ntiles - 1;
+        if (alive) alive = mbar_wait(&sm.k_empty[jl % K_STAGES], (jl / K_STAGES) & 1, p.error);
+        __syncwarp();
+        load_q_tile<D>(sm.q, p, row0, g, G, packed, bx * TQ, (is_v ? 32 : 0) + lane, 64);
+        asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;\n" ::: "memory");
+        proxy_fence();                                           // before the barrier that ends the item
+      }
     } else if (warp == kMmaWarp) {
       // ---------------- MMA issuer of S_j = Q K_j^T ----------------
       // The S products and the P V products are issued by a thread each.  One thread for both was the block's
@@ -346,7 +396,9 @@ attn_prefill_tcgen05_kernel(const PrefillParams p, const __grid_constant__ CUten
           q_desc[kk] = desc_kmajor(smem_u32(sm.q) + (kk / 4) * PANEL_BYTES + (kk % 4) * 32);
         const uint64_t k_desc0 = desc_kmajor(smem_u32(sm.k[0]));
         constexpr uint64_t kStageUnits = (PANELS * KV_PANEL_BYTES) >> 4;
-        bool alive = mbar_wait(&sm.q_full, 0, p.error);
+        // item 1: its Q tile was in place, and fenced for the tensor core's reads, before the barrier that
+        // ended item 0
+        bool alive = item > 0 || mbar_wait(&sm.q_full, 0, p.error);
         tc_fence_after();
         for (int j = 0; j < ntiles && alive; ++j) {
           const int b = j & 1, use = j >> 1, s = j % K_STAGES;
@@ -390,20 +442,14 @@ attn_prefill_tcgen05_kernel(const PrefillParams p, const __grid_constant__ CUten
       const int part = warp >> 2;                                // which CW of the 128 key columns (and OW of D)
       const int row = (warp & 3) * 32 + lane;                    // tensor-memory lane
       const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
-      for (int c = t; c < TQ * (D / 8); c += kSoftmaxThreads) {
-        const int qrow = c / (D / 8), ch = c % (D / 8);
-        const int i = tile_row0 + qrow;
-        const bool valid = i < packed;
-        const __nv_bfloat16* src = p.q;
-        if (valid)
-          src = p.q + static_cast<size_t>(row0 + i / G) * p.q_stride + static_cast<size_t>(g * G + i % G) * D + ch * 8;
-        unsigned char* dst = sm.q + (ch >> 3) * PANEL_BYTES + qrow * 128 + (((ch & 7) ^ (qrow & 7)) << 4);
-        cp16(dst, src, valid ? 16 : 0);
+      if (item == 0) {
+        // (the mirror tile's rows were fetched by the K producer while the first tile's last steps ran)
+        load_q_tile<D>(sm.q, p, row0, g, G, packed, tile_row0, t, kSoftmaxThreads);
+        asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;\n" ::: "memory");
+        proxy_fence();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&sm.q_full);
       }
-      asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;\n" ::: "memory");
-      proxy_fence();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&sm.q_full);
 
       const int i_row = tile_row0 + row;
       const bool row_valid = i_row < packed;
@@ -506,31 +552,42 @@ attn_prefill_tcgen05_kernel(const PrefillParams p, const __grid_constant__ CUten
       float l_row = 0.0f;
 #pragma unroll
       for (int o = 0; o < SPLIT; ++o) l_row += sm.xsum[o][row];
+      // O leaves through shared memory (the K ring is idle: every product has finished), so that the stores to
+      // global memory are whole rows — 16 lanes a row — instead of 16 bytes a lane to 32 different rows, which
+      // took 2.8 of a block's 59 thousand cycles per tile.
+      constexpr int STAGE_STRIDE = D * 2 + 16;                   // bytes a staged row; the pad spreads rows over banks
+      unsigned char* stage = sm.k[0];
+      static_assert(TQ * STAGE_STRIDE <= K_STAGES * PANELS * KV_PANEL_BYTES, "the staged tile fits the K ring");
       if (ok && mbar_wait(&sm.o_ready, 0, p.error)) {
         tc_fence_after();
         const float inv = (l_row > 0.0f) ? 1.0f / l_row : 0.0f;
         if (row_valid && part == 0 && (!(l_row > 0.0f) || !isfinite(l_row))) publish_error(p.error, kAttentionDenominator);
-        __nv_bfloat16* orow = nullptr;
-        if (row_valid)
-          orow = p.out + (static_cast<size_t>(row0 + i_row / G) * p.heads + g * G + i_row % G) * D + part * OW;
 #pragma unroll 1
         for (int c = 0; c < OW / 32; ++c) {
           uint32_t ov[32];
           tmem_ld32(tmem_o + lane_base + part * OW + c * 32, ov);
           tmem_wait_ld();
-          if (row_valid) {
-            uint32_t pk[16];
+          uint32_t pk[16];
 #pragma unroll
-            for (int e = 0; e < 16; ++e) {
-              __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(ov[2 * e]) * inv, __uint_as_float(ov[2 * e + 1]) * inv);
-              pk[e] = *reinterpret_cast<uint32_t*>(&h);
-            }
-#pragma unroll
-            for (int e = 0; e < 4; ++e)
-              reinterpret_cast<uint4*>(orow + c * 32)[e] = make_uint4(pk[4 * e], pk[4 * e + 1], pk[4 * e + 2], pk[4 * e + 3]);
+          for (int e = 0; e < 16; ++e) {
+            __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(ov[2 * e]) * inv, __uint_as_float(ov[2 * e + 1]) * inv);
+            pk[e] = *reinterpret_cast<uint32_t*>(&h);
           }
+          uint4* dst = reinterpret_cast<uint4*>(stage + row * STAGE_STRIDE + (part * OW + c * 32) * 2);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) dst[e] = make_uint4(pk[4 * e], pk[4 * e + 1], pk[4 * e + 2], pk[4 * e + 3]);
         }
       }
+      softmax_sync<kSoftmaxThreads>();                           // every softmax thread, whatever its waits said
+      {
+        constexpr int CPR = D / 8;
+        const int ch = t % CPR;
+        PackedRowWalk w(tile_row0 + t / CPR, kSoftmaxThreads / CPR, G);
+        for (int r_out = t / CPR; r_out < TQ && w.i < packed; r_out += kSoftmaxThreads / CPR, w.next())
+          *reinterpret_cast<uint4*>(p.out + (static_cast<size_t>(row0 + w.tok) * p.heads + g * G + w.hd) * D + ch * 8) =
+              *reinterpret_cast<const uint4*>(stage + r_out * STAGE_STRIDE + ch * 16);
+      }
+      proxy_fence();                                             // the next item's TMA boxes land where these rows lay
     }
     tc_fence_before();
     __syncthreads();                                             // the item is finished everywhere
