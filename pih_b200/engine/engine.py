@@ -27,7 +27,7 @@ import torch
 from ..sampling.params import SamplingParams
 from ..sampling.sampler import Sampler
 from .batch import StepEntry
-from .factory import create_runner
+from .factory import create_runner, runner_for
 from .scheduler import Request, Scheduler
 
 RESULT_SCHEMA = "pih.token-generation-result.v1"
@@ -62,17 +62,29 @@ class Engine:
                  page_size: int = 16, max_cache_tokens: Optional[int] = None,
                  maximum_batch_sequences: int = 32, maximum_batch_tokens: int = 4096,
                  maximum_context_tokens: Optional[int] = None, cuda_graphs: bool = True,
-                 run_ahead: bool = True, ops: Optional[object] = None):
+                 run_ahead: bool = True, ops: Optional[object] = None, model: Optional[tuple] = None):
+        """``model_dir``: a folder with config.json and model.safetensors.  ``model``: instead of loading that
+        folder, a ``(configuration, model)`` pair that is already built on its device (``model_dir`` is then
+        only a name; ``dtype`` and ``device`` are the model's own)."""
         from ..config.registry import load_config
         self.model_dir = model_dir
-        self.device = torch.device(device)
-        max_positions = load_config(model_dir).model_spec().max_positions
+        if model is not None:
+            self.config, self.model = model
+            self.device = self.model.rt.device
+            max_positions = self.model.spec.max_positions
+        else:
+            self.device = torch.device(device)
+            max_positions = load_config(model_dir).model_spec().max_positions
         self.max_context = min(maximum_context_tokens or max_positions, max_positions)
         if max_cache_tokens is None:
             max_cache_tokens = min(maximum_batch_sequences * self.max_context, 1 << 20)
-        self.config, self.model, self.cache, self.runner = create_runner(
-            model_dir, dtype, device=device, page_size=page_size, max_cache_tokens=max_cache_tokens,
-            max_requests=maximum_batch_sequences, cuda_graphs=cuda_graphs, ops=ops)
+        if model is not None:
+            self.cache, self.runner = runner_for(self.model, page_size=page_size, max_cache_tokens=max_cache_tokens,
+                                                 max_requests=maximum_batch_sequences, cuda_graphs=cuda_graphs)
+        else:
+            self.config, self.model, self.cache, self.runner = create_runner(
+                model_dir, dtype, device=device, page_size=page_size, max_cache_tokens=max_cache_tokens,
+                max_requests=maximum_batch_sequences, cuda_graphs=cuda_graphs, ops=ops)
         self.rt = self.model.rt
         spec = self.model.spec
         self.scheduler = Scheduler(self.cache, max_batch_sequences=maximum_batch_sequences,

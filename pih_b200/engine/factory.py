@@ -28,7 +28,16 @@ def create_runner(model_dir: str, dtype: str = "bfloat16", *, device: str = "cud
     dev = torch.device(device)
     rt = Runtime(device=dev, dtype=DTYPES[dtype], ops=ops if ops is not None else get_ops(dev))
     config, model = load_model(model_dir, rt)
+    cache, runner = runner_for(model, page_size=page_size, max_cache_tokens=max_cache_tokens,
+                               max_requests=max_requests, cuda_graphs=cuda_graphs)
+    return config, model, cache, runner
+
+
+def runner_for(model, *, page_size: int = 16, max_cache_tokens: int = 4096, max_requests: int = 32,
+               cuda_graphs: bool = False):
+    """A cache and a step function for a model that is already built; returns ``(cache, runner)``."""
+    rt = model.rt
     cache = CacheManager(model.cache_needs(), [e.reads_cache_of for e in model.spec.schedule],
                          page_size=page_size, num_pages=-(-max_cache_tokens // page_size),
-                         max_requests=max_requests, device=dev, dtype=rt.dtype)
-    return config, model, cache, ModelRunner(model, cache, cuda_graphs=cuda_graphs)
+                         max_requests=max_requests, device=rt.device, dtype=rt.dtype)
+    return cache, ModelRunner(model, cache, cuda_graphs=cuda_graphs)

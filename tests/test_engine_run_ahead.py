@@ -80,3 +80,18 @@ def test_run_ahead_with_late_arrival_cancel_and_preemption(model_dirs, tiny_conf
     got, preempted_ahead, planned = run(True)
     assert preempted > 0 and planned > 0
     assert got == want
+
+
+def test_an_engine_around_a_model_that_is_already_built(model_dirs, tiny_configs):
+    """``Engine(model=(configuration, model))`` gives the tokens of the engine that loads the folder itself."""
+    import torch
+    from pih_b200.models import load_model
+    from pih_b200.parts import Runtime
+    prompts = _prompts(tiny_configs["A"]["vocab_size"], [5, 11, 17], seed=2)
+    want = _engine(model_dirs["A"], True, page_size=16).complete_batch(prompts, max_tokens=8, ignore_eos=True)
+    rt = Runtime(torch.device("cpu"), torch.float32, FakeOps())
+    config, model = load_model(model_dirs["A"], rt)
+    built = Engine("tiny-a", model=(config, model), page_size=16, max_cache_tokens=1024, maximum_batch_sequences=4,
+                   maximum_batch_tokens=16)
+    assert built.complete_batch(prompts, max_tokens=8, ignore_eos=True) == want
+    assert built.models()["data"][0]["id"] == "tiny-a"
