@@ -53,12 +53,22 @@ METRIC = "decode tok/s at batch 8 (Qwen3-0.6B, 2048-token contexts)"
 def peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     hbm, flops, src = 6650.0, 1590.0, "fallback"
+    def number(v, default):
+        if isinstance(v, dict):                      # {"value": ...} or the like
+            v = next((v[k] for k in ("value", "median", "mean") if k in v), None)
+        try:
+            v = float(v)
+        except (TypeError, ValueError):
+            return default
+        return v if v > 0 else default
+
     try:
         with open(path) as f:
             p = json.load(f)
-        hbm = float(p.get("hbm_gbs", hbm))
-        flops = float(p.get("bf16_tflops", flops))
-        src = "measured"
+        if isinstance(p, dict):
+            measured_hbm, measured_flops = number(p.get("hbm_gbs"), None), number(p.get("bf16_tflops"), None)
+            if measured_hbm is not None and measured_flops is not None:
+                hbm, flops, src = measured_hbm, measured_flops, "measured"
     except (OSError, ValueError):
         pass
     return hbm, flops, src
