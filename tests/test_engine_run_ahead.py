@@ -95,3 +95,56 @@ def test_an_engine_around_a_model_that_is_already_built(model_dirs, tiny_configs
                    maximum_batch_tokens=16)
     assert built.complete_batch(prompts, max_tokens=8, ignore_eos=True) == want
     assert built.models()["data"][0]["id"] == "tiny-a"
+
+
+@pytest.mark.parametrize("seed", range(6))
+def test_random_workloads_give_the_same_tokens_with_and_without_run_ahead(model_dirs, tiny_configs, seed):
+    """Seeded random workloads — arrivals over time, lengths, limits, temperatures, a stop id, cancellations, a pool
+    that forces preemptions in some of them: after every step the cache's books are right and no step holds
+    more tokens or requests than allowed; at the end every page is free; and planning ahead changes no token."""
+    import random
+    name = "AB"[seed % 2]
+    vocab = tiny_configs[name]["vocab_size"]
+    rng = random.Random(100 + seed)
+    n = rng.randint(4, 7)
+    lengths = [rng.randint(1, 40) for _ in range(n)]
+    prompts = _prompts(vocab, lengths, seed=seed)
+    arrive = sorted(rng.randint(0, 12) for _ in range(n))
+    limits = [rng.randint(1, 20) for _ in range(n)]
+    temps = [rng.choice([0.0, 0.0, 0.7]) for _ in range(n)]
+    stop_id = rng.randrange(vocab)
+    cancel_at = {rng.randint(3, 25): rng.randrange(n) for _ in range(rng.randint(0, 2))}
+    budget, seqs = rng.choice([8, 16, 32]), rng.choice([2, 3, 4])
+    pool_tokens = rng.choice([96, 160, 1024])
+    longest = max(a + b for a, b in zip(lengths, limits))
+    pool_tokens = max(pool_tokens, -(-longest // 8) * 8 + 8)       # the longest request fits alone
+
+    def run(run_ahead):
+        e = _engine(model_dirs[name], run_ahead, max_cache_tokens=pool_tokens, maximum_batch_tokens=budget,
+                    maximum_batch_sequences=seqs)
+        reqs, cancelled = {}, set()
+        step = 0
+        while step < 400 and (e.has_work() or len(reqs) < n):
+            for i in range(n):
+                if i not in reqs and arrive[i] <= step:
+                    params = SamplingParams(max_tokens=limits[i], temperature=temps[i], seed=seed + i,
+                                            stop_token_ids=(stop_id,), ignore_eos=True)
+                    reqs[i] = e._live[e.submit(prompts[i], params)]
+            if step in cancel_at and cancel_at[step] in reqs and reqs[cancel_at[step]].status != "finished":
+                cancelled.add(cancel_at[step])
+                e.cancel(reqs[cancel_at[step]].rid)
+            if e.has_work():
+                e.step()
+            e.cache.check()
+            step += 1
+        assert not e.has_work() and len(reqs) == n
+        assert all(f == e.cache.num_pages for f in e.cache.num_free_pages())
+        for i, r in reqs.items():
+            if i not in cancelled:
+                assert r.status == "finished" and 1 <= len(r.outputs) <= limits[i]
+                assert r.finish_reason in ("length", "stop")
+                assert (r.finish_reason == "stop") == (r.outputs[-1] == stop_id and len(r.outputs) <= limits[i]) \
+                    or len(r.outputs) == limits[i]
+        return {i: (r.outputs, r.finish_reason) for i, r in reqs.items() if i not in cancelled}
+
+    assert run(True) == run(False)
