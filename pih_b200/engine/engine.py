@@ -62,10 +62,14 @@ class Engine:
                  page_size: int = 16, max_cache_tokens: Optional[int] = None,
                  maximum_batch_sequences: int = 32, maximum_batch_tokens: int = 4096,
                  maximum_context_tokens: Optional[int] = None, cuda_graphs: bool = True,
-                 run_ahead: bool = True, ops: Optional[object] = None, model: Optional[tuple] = None):
+                 run_ahead: bool = True, ops: Optional[object] = None, model: Optional[tuple] = None,
+                 decode_batch_multiple: int = 1):
         """``model_dir``: a folder with config.json and model.safetensors.  ``model``: instead of loading that
         folder, a ``(configuration, model)`` pair that is already built on its device (``model_dir`` is then
-        only a name; ``dtype`` and ``device`` are the model's own)."""
+        only a name; ``dtype`` and ``device`` are the model's own).  ``decode_batch_multiple``: with CUDA graphs,
+        decode steps are brought to a multiple of this many requests by stand-in requests, so that a few graphs
+        serve every batch size (1, the default: never — the stand-ins are tested with the stand-in kernels on the
+        CPU and have not yet run on a GPU)."""
         from ..config.registry import load_config
         self.model_dir = model_dir
         if model is not None:
@@ -78,13 +82,15 @@ class Engine:
         self.max_context = min(maximum_context_tokens or max_positions, max_positions)
         if max_cache_tokens is None:
             max_cache_tokens = min(maximum_batch_sequences * self.max_context, 1 << 20)
+        pad = decode_batch_multiple if cuda_graphs else 1
         if model is not None:
             self.cache, self.runner = runner_for(self.model, page_size=page_size, max_cache_tokens=max_cache_tokens,
-                                                 max_requests=maximum_batch_sequences, cuda_graphs=cuda_graphs)
+                                                 max_requests=maximum_batch_sequences, cuda_graphs=cuda_graphs,
+                                                 pad_decode_to=pad)
         else:
             self.config, self.model, self.cache, self.runner = create_runner(
                 model_dir, dtype, device=device, page_size=page_size, max_cache_tokens=max_cache_tokens,
-                max_requests=maximum_batch_sequences, cuda_graphs=cuda_graphs, ops=ops)
+                max_requests=maximum_batch_sequences, cuda_graphs=cuda_graphs, ops=ops, pad_decode_to=pad)
         self.rt = self.model.rt
         spec = self.model.spec
         self.scheduler = Scheduler(self.cache, max_batch_sequences=maximum_batch_sequences,

@@ -57,9 +57,26 @@ class _BoundedPlans(dict):
         return tile_max_q, dec_cap, self._max_ctx if dec_cap else 0
 
 
+class _Pad:
+    """Owner of a stand-in request (no caller's request id can be equal to it)."""
+
+    def __init__(self, k: int):
+        self.k = k
+
+    def __repr__(self):
+        return f"<stand-in request {self.k}>"
+
+
 class ModelRunner:
-    def __init__(self, model, cache: CacheManager, cuda_graphs: bool = False):
+    def __init__(self, model, cache: CacheManager, cuda_graphs: bool = False, pad_decode_to: int = 1):
         self.cuda_graphs = cuda_graphs
+        # Decode steps are brought to a multiple of this many requests by stand-in requests (one token at
+        # position 0 in a page that they hold for the step only; their logits are dropped).  A decode graph is
+        # keyed by its number of requests, and a batch whose requests end one after the other would otherwise
+        # show a new key — an eager step or a capture — every step or two.
+        self.pad_decode_to = pad_decode_to
+        self._pad_ids = []
+        self.stand_ins_used = 0            # over the runner's life
         self.model = model
         self.cache = cache
         self.device = model.rt.device
@@ -109,6 +126,36 @@ class ModelRunner:
 
         The returned tensor may be reused by the next step: use it (or queue the kernel that does) before
         calling ``step`` again."""
+        pads = self._stand_ins(entries)
+        if not pads:
+            return self._step(entries, token_feed)
+        self.stand_ins_used += len(pads)
+        try:
+            logits = self._step(list(entries) + pads, token_feed)
+        finally:
+            for p in pads:
+                if self.cache.has_request(p.rid):
+                    self.cache.release(p.rid)              # its page and its slot, held for this step only
+        return logits[:len(entries)]
+
+    def _stand_ins(self, entries: Sequence[StepEntry]):
+        m = self.pad_decode_to
+        if m <= 1 or self.cache.state_tensors or not entries:
+            return []
+        if not all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries):
+            return []
+        n = -len(entries) % m
+        if n == 0 or len(entries) < m:                      # the smallest batches keep their own graphs: the
+            return []                                      # decode attention cuts a lone long request finer
+        # only with slots and pages to spare: a stand-in must never be the reason for a step to fail
+        new = sum(1 for e in entries if not self.cache.has_request(e.rid))
+        pages = sum(max(self.cache.pages_needed(e.rid, 1)) if self.cache.has_request(e.rid) else 1 for e in entries)
+        n = min(n, self.cache.slots.num_free - new, min(self.cache.num_free_pages()) - pages)
+        while len(self._pad_ids) < n:
+            self._pad_ids.append(_Pad(len(self._pad_ids)))
+        return [StepEntry(self._pad_ids[k], [0], [0]) for k in range(max(n, 0))]
+
+    def _step(self, entries: Sequence[StepEntry], token_feed: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
         if self._graphable(entries):
             return self._graph_step(entries, token_feed)
         batch = self.prepare(entries)
@@ -155,9 +202,11 @@ class ModelRunner:
     @staticmethod
     def _feed(batch: StepBatch, token_feed: Optional[torch.Tensor]) -> None:
         if token_feed is not None:
-            if token_feed.shape != batch.token_ids.shape or token_feed.dtype != batch.token_ids.dtype:
+            # (a step with stand-in requests has more rows than the feed: theirs come last and keep their ids)
+            if (token_feed.dim() != 1 or token_feed.shape[0] > batch.token_ids.shape[0]
+                    or token_feed.dtype != batch.token_ids.dtype):
                 raise ValueError("token_feed needs one int32 id per row of the step")
-            batch.token_ids.copy_(token_feed)          # queued behind the batch's own copy to the device
+            batch.token_ids[:token_feed.shape[0]].copy_(token_feed)   # queued behind the batch's own copy to the device
 
     def _graph_step(self, entries, token_feed=None) -> Optional[torch.Tensor]:
         kind = self._graph_key(entries)
