@@ -131,7 +131,7 @@ class ModelRunner:
             return self._step(entries, token_feed)
         self.stand_ins_used += len(pads)
         try:
-            logits = self._step(list(entries) + pads, token_feed)
+            logits = self._step(list(entries) + pads, token_feed, stand_in_rows=len(pads))
         finally:
             for p in pads:
                 if self.cache.has_request(p.rid):
@@ -155,12 +155,13 @@ class ModelRunner:
             self._pad_ids.append(_Pad(len(self._pad_ids)))
         return [StepEntry(self._pad_ids[k], [0], [0]) for k in range(max(n, 0))]
 
-    def _step(self, entries: Sequence[StepEntry], token_feed: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
+    def _step(self, entries: Sequence[StepEntry], token_feed: Optional[torch.Tensor] = None,
+              stand_in_rows: int = 0) -> Optional[torch.Tensor]:
         if self._graphable(entries):
-            return self._graph_step(entries, token_feed)
+            return self._graph_step(entries, token_feed, stand_in_rows)
         batch = self.prepare(entries)
         try:
-            self._feed(batch, token_feed)
+            self._feed(batch, token_feed, stand_in_rows)
             logits = self.run(batch)
         except Exception:
             for e in entries:
@@ -200,15 +201,15 @@ class ModelRunner:
         return None
 
     @staticmethod
-    def _feed(batch: StepBatch, token_feed: Optional[torch.Tensor]) -> None:
+    def _feed(batch: StepBatch, token_feed: Optional[torch.Tensor], stand_in_rows: int = 0) -> None:
         if token_feed is not None:
-            # (a step with stand-in requests has more rows than the feed: theirs come last and keep their ids)
-            if (token_feed.dim() != 1 or token_feed.shape[0] > batch.token_ids.shape[0]
+            # (the rows of stand-in requests come last and keep their own ids)
+            if (token_feed.dim() != 1 or token_feed.shape[0] + stand_in_rows != batch.token_ids.shape[0]
                     or token_feed.dtype != batch.token_ids.dtype):
                 raise ValueError("token_feed needs one int32 id per row of the step")
             batch.token_ids[:token_feed.shape[0]].copy_(token_feed)   # queued behind the batch's own copy to the device
 
-    def _graph_step(self, entries, token_feed=None) -> Optional[torch.Tensor]:
+    def _graph_step(self, entries, token_feed=None, stand_in_rows: int = 0) -> Optional[torch.Tensor]:
         kind = self._graph_key(entries)
         for e in entries:
             if not self.cache.has_request(e.rid):
@@ -232,14 +233,14 @@ class ModelRunner:
                 # first sight of this shape: run it as it is; capture if it comes again
                 self._sightings[key] = 1
                 batch = self.builder.build(entries, self.cache)
-                self._feed(batch, token_feed)
+                self._feed(batch, token_feed, stand_in_rows)
                 logits = self.run(batch)
             elif state is None:
-                state = self._capture(entries, key, width, token_feed)
+                state = self._capture(entries, key, width, token_feed, stand_in_rows)
                 logits = state["logits"]
             else:
                 batch = self.builder.build(entries, self.cache, width=width, device_buffer=state["buffer"])
-                self._feed(batch, token_feed)
+                self._feed(batch, token_feed, stand_in_rows)
                 if key[0] == "step":
                     self._graphs[key] = self._graphs.pop(key)     # most recently used last
                 state["graph"].replay()
@@ -259,14 +260,14 @@ class ModelRunner:
         if hasattr(ops, "launches"):
             ops.launches += n
 
-    def _capture(self, entries, key, width, token_feed=None):
+    def _capture(self, entries, key, width, token_feed=None, stand_in_rows: int = 0):
         G = len(self.cache.groups)
         T = sum(len(e.tokens) for e in entries)
         B = len(entries)
         S = sum(len(e.want) for e in entries)
         buffer = torch.empty(self.builder.buffer_size(T, B, S, G, width), dtype=torch.int32, device=self.device)
         batch = self.builder.build(entries, self.cache, width=width, device_buffer=buffer)
-        self._feed(batch, token_feed)
+        self._feed(batch, token_feed, stand_in_rows)
         max_ctx = width * self.cache.page_size
         ops = self.model.rt.ops
         # the attention plans of the graph cover every context that fits the table width
