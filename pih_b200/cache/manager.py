@@ -23,7 +23,18 @@ What is here instead:
 * **State slots.**  Every live request holds one slot; mixers that ask for
   ``StateNeed`` get a tensor ``[slots, *shape]`` per entry, zeroed for the
   slot when a request takes it.  Qwen3 has no such mixer; the slots exist so
-  that one can be added.
+  that one can be added.  ``append`` keeps a copy of the request's slot as it
+  is before the step, and ``rollback`` puts it back: a step that did not run
+  to its end leaves no half-advanced state.
+* **Lengths that count only once the step was seen to succeed.**  The
+  reference advances a block table only after the step has completed without
+  an error (qwen3_bf16_packed_batch_transaction.cpp:118-167).  A caller that
+  queues steps on the device without waiting for them commits with
+  ``confirmed=False``: the next step starts behind the queued tokens, but
+  ``confirmed_tokens`` — and with it what a windowed group gives back —
+  advances only at ``confirm``, after the step's error word has been read as
+  zero.  ``rollback`` then returns the request to its confirmed length, pages
+  and state.
 
 Page ids in a block table are indexed by ``position // page_size``; an entry
 of a windowed group that was given back reads -1.
@@ -108,8 +119,12 @@ class PageList:
 class RequestCache:
     rid: Hashable
     slot: int
-    num_tokens: int = 0                               # committed length
+    num_tokens: int = 0                               # committed length: where the next step starts
     pending: int = 0                                  # tokens appended, not yet committed
+    confirmed_tokens: int = 0                         # length whose steps were seen to succeed (<= num_tokens)
+    unconfirmed: List[int] = field(default_factory=list)   # token counts of committed steps not yet confirmed, oldest first
+    state_before: List[Dict[int, torch.Tensor]] = field(default_factory=list)   # state slot before each of those steps
+    state_pending: Optional[Dict[int, torch.Tensor]] = None   # ... and before the step being appended
     pages: List[PageList] = field(default_factory=list)    # per group: page id per page index, -1 = given back
     first_live: List[int] = field(default_factory=list)    # per group: first page index still held
 
@@ -226,26 +241,65 @@ class CacheManager:
                                  f"{self.groups[g].pool.num_free} free")
         for g, c in enumerate(need):
             rc.pages[g].extend(self.groups[g].pool.allocate(c, rid))
+        if rc.pending == 0 and self.state_tensors:
+            # the state as it is before this step (copies queued on the current stream, ahead of the step)
+            rc.state_pending = {e: t[rc.slot].clone() for e, t in self.state_tensors.items()}
         rc.pending += n_new
 
-    def rollback(self, rid: Hashable) -> None:
-        """Undo appends that were not committed (the step did not run)."""
+    def rollback(self, rid: Hashable, unconfirmed: bool = False) -> None:
+        """Undo appends that were not committed (the step did not run): their pages go back, and the state
+        slot is as it was before the step.  With ``unconfirmed`` also the committed steps that were not
+        confirmed: the request returns to its confirmed length, pages and state."""
         rc = self.requests[rid]
+        saved = rc.state_pending
+        if unconfirmed:
+            if rc.state_before:
+                saved = rc.state_before[0]
+            rc.num_tokens = rc.confirmed_tokens
+            rc.unconfirmed.clear()
+            rc.state_before.clear()
         keep = -(-rc.num_tokens // self.page_size)
         for g, grp in enumerate(self.groups):
             grp.pool.free([p for p in rc.pages[g].truncate(keep) if p >= 0], rid)
+        if saved is not None:
+            for e, t in saved.items():
+                self.state_tensors[e][rc.slot].copy_(t)
+        rc.pending = 0
+        rc.state_pending = None
+
+    def commit(self, rid: Hashable, confirmed: bool = True) -> None:
+        """The step was run (``confirmed``) or queued on the device (not ``confirmed``): the appended tokens
+        count for where the next step starts.  Once confirmed, pages that no later query can reach (windowed
+        groups) go back to their pool."""
+        rc = self.requests[rid]
+        if confirmed and rc.unconfirmed:
+            raise ValueError(f"request {rid!r} has queued steps to confirm before a confirmed commit")
+        rc.num_tokens += rc.pending
+        if confirmed:
+            rc.confirmed_tokens = rc.num_tokens
+            self._give_back(rc)
+        else:
+            rc.unconfirmed.append(rc.pending)
+            if self.state_tensors:
+                rc.state_before.append(rc.state_pending)
+        rc.state_pending = None
         rc.pending = 0
 
-    def commit(self, rid: Hashable) -> None:
-        """The step ran: the appended tokens count, and pages that no later
-        query can reach (windowed groups) go back to their pool."""
+    def confirm(self, rid: Hashable) -> None:
+        """The oldest queued step of ``rid`` was seen to succeed."""
         rc = self.requests[rid]
-        rc.num_tokens += rc.pending
-        rc.pending = 0
+        if not rc.unconfirmed:
+            raise ValueError(f"request {rid!r} has no queued step to confirm")
+        rc.confirmed_tokens += rc.unconfirmed.pop(0)
+        if rc.state_before:
+            rc.state_before.pop(0)
+        self._give_back(rc)
+
+    def _give_back(self, rc: RequestCache) -> None:
         for g, grp in enumerate(self.groups):
-            first = self._first_needed_page(grp, rc.num_tokens)
+            first = self._first_needed_page(grp, rc.confirmed_tokens)
             if first > rc.first_live[g]:
-                grp.pool.free(rc.pages[g].give_back(rc.first_live[g], first), rid)
+                grp.pool.free(rc.pages[g].give_back(rc.first_live[g], first), rc.rid)
                 rc.first_live[g] = first
 
     def release(self, rid: Hashable) -> None:
@@ -262,8 +316,11 @@ class CacheManager:
             grp.pool.free(rc.pages[g].held(), rid)
             rc.pages[g] = PageList()
             rc.first_live[g] = 0
-        rc.num_tokens = 0
+        rc.num_tokens = rc.confirmed_tokens = 0
         rc.pending = 0
+        rc.unconfirmed.clear()
+        rc.state_before.clear()
+        rc.state_pending = None
         for t in self.state_tensors.values():
             t[rc.slot].zero_()
 

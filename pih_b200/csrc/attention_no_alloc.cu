@@ -31,6 +31,12 @@ void explain(char* message, int capacity, const char* text) {
 
 }  // namespace
 
+extern "C" void* pih_no_alloc_scratch_address(void) {
+  int device = -1;
+  if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= kMaxDevices) return nullptr;
+  return g_scratch_address[device];
+}
+
 extern "C" int pih_paged_attention_mma_no_alloc(const void* q, int q_stride, void* out, const void* cache,
                                                 const int* block_table, int table_width, const int* cu_q,
                                                 const int* q_start, int rows, int num_requests, int tile_max_q,

@@ -1,9 +1,10 @@
 // Decode attention for callers that must not allocate device memory.
 //
 // This entry point has no counterpart in the reference project: it exists for programs that embed the
-// kernel pack where cudaMalloc is off limits — inside a CUDA-graph capture, under a host that owns all
-// device memory and hands out none (a game engine, another inference runtime's plugin slot), or in a
-// real-time loop where an allocation's latency or failure cannot be tolerated.
+// kernel pack where cudaMalloc is off limits — under a host that owns all device memory and hands out
+// none (a game engine, another inference runtime's plugin slot), after a set-up phase whose end freezes
+// the process's device allocations, or in a real-time loop where an allocation's latency or failure
+// cannot be tolerated.
 //
 // It is the split-KV paged attention of pih_paged_attention_mma (attention_mma.cu) with one difference:
 // the scratch memory that the kernel needs for its per-split partial results and tickets is not passed
@@ -39,6 +40,10 @@ extern "C" {
 // Arguments as pih_paged_attention_mma, without `scratch`; `split` must be > 0 (keys per split, a multiple
 // of 64) so that the scratch need is known on the host.  `message` (nullable) receives a zero-terminated
 // explanation when the return value is not 0.  Returns 0, a negative PIH_* code, or a cudaError_t (> 0).
+// For tests and diagnostics: the device address of the built-in array on the current device, or null
+// before the first call of pih_paged_attention_mma_no_alloc on that device.  It allocates nothing.
+void* pih_no_alloc_scratch_address(void);
+
 int pih_paged_attention_mma_no_alloc(const void* q, int q_stride, void* out, const void* cache,
                                      const int* block_table, int table_width, const int* cu_q,
                                      const int* q_start, int rows, int num_requests, int tile_max_q,

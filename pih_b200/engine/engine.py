@@ -20,77 +20,120 @@ from __future__ import annotations
 
 import itertools
 import os
-from typing import Dict, Hashable, Iterator, List, Optional, Sequence
+from collections import deque
+from typing import Deque, Dict, Hashable, Iterator, List, Optional, Sequence
 
 import torch
 
+from ..kernels.ops import KernelError, error_text
 from ..sampling.params import SamplingParams
 from ..sampling.sampler import Sampler
+from ..cache import OutOfPages
 from .batch import StepEntry
-from .factory import create_runner, runner_for
+from ..kernels import get_ops
+from .factory import runner_for
 from .scheduler import Request, Scheduler
 
 RESULT_SCHEMA = "pih.token-generation-result.v1"
 
 
-class _InFlight:
-    """A step that has been queued on the device: its plan and the ids it samples, on the device and — by a
-    copy queued right behind the sampler, before any later step — in pinned host memory."""
+class _Landing:
+    """Pinned host memory for what one step reports back: the ids it sampled and, behind them, the device's
+    error word as it stood after the step; with the event that says both have arrived."""
 
-    def __init__(self, out, tokens, landing=None):
+    def __init__(self, rows: int):
+        self.buffer = torch.empty(rows + 1, dtype=torch.int32, pin_memory=True)
+        self.event = torch.cuda.Event()
+
+
+class _InFlight:
+    """A step that has been queued on the device: its plan, the ids it samples, and the error word after it —
+    both copied to pinned host memory right behind the step, before any later step."""
+
+    def __init__(self, out, tokens, error_word=None, landing: Optional[_Landing] = None):
         self.out = out
         self.tokens = tokens
-        self.host = self.copied = None
-        if tokens is not None and tokens.device.type == "cuda":
-            # `landing`: a pinned buffer and its event, owned by the engine and free again (two steps at most
-            # are in flight, the engine rotates three)
-            buffer, self.copied = landing
-            self.host = buffer[:tokens.shape[0]]
-            self.host.copy_(tokens, non_blocking=True)
-            self.copied.record()
+        self.landing = landing
+        self.error_word = error_word
+        self.rows = 0 if tokens is None else int(tokens.shape[0])
+        self.holders = []                   # (request id, its cache record) of the step's requests
+        # kernels that run on the host have finished by now: the word is read as it stands
+        self._code = int(error_word) if landing is None and error_word is not None else None
+        if landing is not None:
+            if tokens is not None:
+                landing.buffer[:self.rows].copy_(tokens, non_blocking=True)
+            landing.buffer[-1:].copy_(error_word, non_blocking=True)
+            landing.event.record()
+
+    def done(self) -> bool:
+        return self.landing is None or self.landing.event.query()
+
+    def wait(self) -> None:
+        if self.landing is not None:
+            self.landing.event.synchronize()
+
+    def error_code(self) -> int:
+        """The error word after this step (call after ``wait`` or a true ``done``)."""
+        if self.landing is not None:
+            return int(self.landing.buffer[-1])
+        return self._code or 0
 
     def token_list(self) -> List[int]:
         """The sampled ids; waits for this step only, not for steps queued after it."""
-        if self.host is None:
+        if self.tokens is None:
+            return []
+        if self.landing is None:
             return self.tokens.tolist()
-        self.copied.synchronize()
-        return self.host.tolist()
+        self.wait()
+        return self.landing.buffer[:self.rows].tolist()
 
 
 class Engine:
     def __init__(self, model_dir: str, dtype: str = "bfloat16", *, device: str = "cuda:0",
-                 page_size: int = 16, max_cache_tokens: Optional[int] = None,
+                 page_size: int = 16, max_cache_tokens: Optional[int] = None, memory_fraction: float = 0.9,
                  maximum_batch_sequences: int = 32, maximum_batch_tokens: int = 4096,
                  maximum_context_tokens: Optional[int] = None, cuda_graphs: bool = True,
                  run_ahead: bool = True, ops: Optional[object] = None, model: Optional[tuple] = None,
                  decode_batch_multiple: int = 1):
         """``model_dir``: a folder with config.json and model.safetensors.  ``model``: instead of loading that
         folder, a ``(configuration, model)`` pair that is already built on its device (``model_dir`` is then
-        only a name; ``dtype`` and ``device`` are the model's own).  ``decode_batch_multiple``: with CUDA graphs,
-        decode steps are brought to a multiple of this many requests by stand-in requests, so that a few graphs
-        serve every batch size (1, the default: never — the stand-ins are tested with the stand-in kernels on the
-        CPU and have not yet run on a GPU)."""
-        from ..config.registry import load_config
+        only a name; ``dtype`` and ``device`` are the model's own).
+
+        ``max_cache_tokens``: the size of every cache group's pool.  None (the default): what the device has
+        left once the weights are on it, so that at most ``memory_fraction`` of its memory is in use — but no
+        more than ``maximum_batch_sequences`` requests of ``maximum_context_tokens`` need (see
+        ``factory.cache_tokens_for_memory``; the chosen size is ``engine.cache_tokens``).
+
+        ``decode_batch_multiple``: with CUDA graphs, decode steps are brought to a multiple of this many requests
+        by stand-in requests, so that a few graphs serve every batch size (1: never)."""
+        from ..models import load_model
+        from ..parts.registry import Runtime
+        from .factory import DTYPES, cache_tokens_for_memory
         self.model_dir = model_dir
         if model is not None:
             self.config, self.model = model
-            self.device = self.model.rt.device
-            max_positions = self.model.spec.max_positions
         else:
-            self.device = torch.device(device)
-            max_positions = load_config(model_dir).model_spec().max_positions
+            if dtype not in DTYPES:
+                raise ValueError(f"dtype must be one of {sorted(DTYPES)}, got {dtype!r}")
+            dev = torch.device(device)
+            rt = Runtime(device=dev, dtype=DTYPES[dtype], ops=ops if ops is not None else get_ops(dev))
+            self.config, self.model = load_model(model_dir, rt)
+        self.device = self.model.rt.device
+        max_positions = self.model.spec.max_positions
         self.max_context = min(maximum_context_tokens or max_positions, max_positions)
         if max_cache_tokens is None:
-            max_cache_tokens = min(maximum_batch_sequences * self.max_context, 1 << 20)
+            if self.device.type == "cuda":
+                max_cache_tokens = cache_tokens_for_memory(
+                    self.model, page_size=page_size, max_requests=maximum_batch_sequences,
+                    max_batch_tokens=maximum_batch_tokens, max_context=self.max_context,
+                    memory_fraction=memory_fraction)
+            else:
+                max_cache_tokens = min(maximum_batch_sequences * self.max_context, 1 << 16)
+        self.cache_tokens = max_cache_tokens
         pad = decode_batch_multiple if cuda_graphs else 1
-        if model is not None:
-            self.cache, self.runner = runner_for(self.model, page_size=page_size, max_cache_tokens=max_cache_tokens,
-                                                 max_requests=maximum_batch_sequences, cuda_graphs=cuda_graphs,
-                                                 pad_decode_to=pad)
-        else:
-            self.config, self.model, self.cache, self.runner = create_runner(
-                model_dir, dtype, device=device, page_size=page_size, max_cache_tokens=max_cache_tokens,
-                max_requests=maximum_batch_sequences, cuda_graphs=cuda_graphs, ops=ops, pad_decode_to=pad)
+        self.cache, self.runner = runner_for(self.model, page_size=page_size, max_cache_tokens=max_cache_tokens,
+                                             max_requests=maximum_batch_sequences, cuda_graphs=cuda_graphs,
+                                             pad_decode_to=pad)
         self.rt = self.model.rt
         spec = self.model.spec
         self.scheduler = Scheduler(self.cache, max_batch_sequences=maximum_batch_sequences,
@@ -101,8 +144,8 @@ class Engine:
         self.run_ahead = run_ahead       # plan and queue the next decode step before this one's ids are read
         self._inflight: Optional[_InFlight] = None
         self.steps_planned_ahead = 0
-        self._landings = None            # pinned buffers for the sampled ids, made at the first step on a GPU
-        self._landing_turn = 0
+        self._unconfirmed: Deque[_InFlight] = deque()   # queued steps whose error word has not been seen, oldest first
+        self._free_landings: List[_Landing] = []
 
     # -- the reference client's small calls ---------------------------------------
     def ready(self) -> bool:
@@ -136,6 +179,11 @@ class Engine:
     def has_work(self) -> bool:
         return self._inflight is not None or self.scheduler.has_work()
 
+    def drain(self) -> None:
+        """Wait for every queued step and see its error word (raises ``KernelError`` as ``step`` does)."""
+        if self._unconfirmed:
+            self._settle(self._unconfirmed[-1])
+
     # -- one step ---------------------------------------------------------------------
     # A step's sampled ids are needed on the host only to book them and to see who stops.  So while
     # step N runs, step N + 1 is planned (Scheduler.plan_ahead: every request decodes one more token),
@@ -144,32 +192,86 @@ class Engine:
     # batch builder or the copy of the ids.  A request that N's token stops has one token too many
     # computed in N + 1; it is dropped.  Whenever the plain path has a decision to make (admission, a
     # request at its length limit, pages that run out) nothing is planned ahead.
+    #
+    # What a step did counts only once it has been seen to succeed (the reference advances its block tables
+    # only after the step completed without an error, qwen3_bf16_packed_batch_transaction.cpp:118-167).  The
+    # kernels never trap: they record the first fault in one word on the device.  A copy of that word travels
+    # to pinned host memory behind every step, with the sampled ids and under the same event, so seeing it
+    # costs no wait of its own.  Until then the cache holds the step's tokens as queued, not confirmed.  A
+    # non-zero word fails every request that took part in a step not yet confirmed: no token of such a step
+    # is booked, the requests go back to their confirmed state, end with reason "error" and free what they
+    # hold, the word is cleared, and ``step`` raises ``KernelError``; requests outside those steps go on.
     def _launch(self, out, feed=None) -> "_InFlight":
         pending = 1 if feed is not None else 0
         entries = [StepEntry(s.request.rid, s.tokens, [len(s.tokens) - 1] if s.samples else [])
                    for s in out.scheduled]
-        logits = self.runner.step(entries, token_feed=feed)
+        logits = self.runner.step(entries, token_feed=feed, confirm=False)
         sampling = [s.request for s in out.scheduled if s.samples]
         tokens = None
         if sampling:
             tokens = self.sampler.sample_on_device(
                 logits, [r.params for r in sampling], [len(r.outputs) + pending for r in sampling],
                 [self.scheduler.suppressed_ids(r, pending) for r in sampling])
-        return _InFlight(out, tokens, self._landing() if tokens is not None and tokens.device.type == "cuda" else None)
+        word = getattr(self.rt.ops, "error_word", None)
+        on_gpu = self.device.type == "cuda" and word is not None
+        flight = _InFlight(out, tokens, word, self._landing() if on_gpu else None)
+        flight.holders = [(s.request.rid, self.cache.requests[s.request.rid]) for s in out.scheduled]
+        self._unconfirmed.append(flight)
+        return flight
 
-    def _landing(self):
-        if self._landings is None:
-            rows = self.scheduler.max_batch_sequences
-            self._landings = [(torch.empty(rows, dtype=torch.int32, pin_memory=True), torch.cuda.Event())
-                              for _ in range(3)]
-        self._landing_turn = (self._landing_turn + 1) % len(self._landings)
-        return self._landings[self._landing_turn]
+    def _landing(self) -> _Landing:
+        if self._free_landings:
+            return self._free_landings.pop()
+        return _Landing(self.scheduler.max_batch_sequences)
+
+    def _settle(self, upto: Optional["_InFlight"]) -> None:
+        """See the error words of queued steps, oldest first: those up to ``upto`` (waiting for it), or, with
+        None, those that the device has finished.  A step seen to succeed is confirmed in the cache."""
+        while self._unconfirmed:
+            flight = self._unconfirmed[0]
+            if upto is None and not flight.done():
+                return
+            flight.wait()
+            code = flight.error_code()
+            if code:
+                self._fail(code)
+            self._unconfirmed.popleft()
+            for rid, held in flight.holders:
+                if self.cache.requests.get(rid) is held and held.unconfirmed:
+                    self.cache.confirm(rid)
+            if flight.landing is not None:
+                self._free_landings.append(flight.landing)
+            if flight is upto:
+                return
+
+    def _fail(self, code: int) -> None:
+        flights = list(self._unconfirmed)
+        self._unconfirmed.clear()
+        self._inflight = None                       # a step planned ahead is among the flights: dropped with them
+        affected: Dict[int, Request] = {}
+        for flight in flights:
+            for (rid, held), s in zip(flight.holders, flight.out.scheduled):
+                if self.cache.requests.get(rid) is held:
+                    self.cache.rollback(rid, unconfirmed=True)
+                if s.request.status != "finished":
+                    affected[id(s.request)] = s.request
+            if flight.landing is not None:
+                self._free_landings.append(flight.landing)
+        for req in affected.values():
+            self.scheduler.cancel(req.rid, reason="error")
+            self._live.pop(req.rid, None)
+        clear = getattr(self.rt.ops, "clear_errors", None)
+        if clear is not None:
+            clear()                                 # queued behind every step in flight
+        raise KernelError(f"a kernel reported: {error_text(code)}; the requests of the steps not yet seen to "
+                          f"succeed were ended with reason 'error': {[r.rid for r in affected.values()]}")
 
     def _collect(self, flight: "_InFlight") -> List[Request]:
+        self._settle(flight if flight.tokens is not None else None)
         out = flight.out
         sampled: List[Optional[int]] = [None] * len(out.scheduled)
         if flight.tokens is not None:
-            it = iter(flight.token_list())             # waits for this step
+            it = iter(flight.token_list())
             for i, s in enumerate(out.scheduled):
                 if s.samples:
                     sampled[i] = next(it)
@@ -183,21 +285,28 @@ class Engine:
 
     def step(self) -> List[Request]:
         """One scheduler turn and one model step; returns the requests that
-        produced a token in it (finished ones have ``status == 'finished'``)."""
+        produced a token in it (finished ones have ``status == 'finished'``).  Raises ``KernelError`` when a
+        kernel of a queued step reported a fault (see above)."""
         flight = self._inflight
         self._inflight = None
         if flight is None:
+            self._settle(None)
             out = self.scheduler.schedule()
             for req in out.failed:
                 self._live.pop(req.rid, None)
             if not out.scheduled:
+                if self._unconfirmed:
+                    self._settle(self._unconfirmed[-1])
                 return list(out.failed)
             flight = self._launch(out)
         if self.run_ahead and flight.tokens is not None:
             plan = self.scheduler.plan_ahead(flight.out)
             if plan is not None:
-                self._inflight = self._launch(plan, feed=flight.tokens)
-                self.steps_planned_ahead += 1
+                try:
+                    self._inflight = self._launch(plan, feed=flight.tokens)
+                    self.steps_planned_ahead += 1
+                except OutOfPages:
+                    pass                            # nothing was queued or kept: the plain path decides next turn
         return self._collect(flight)
 
     # -- whole generations ------------------------------------------------------------
@@ -227,8 +336,14 @@ class Engine:
             mt = extra.pop("max_tokens", max_tokens)
             rid = self.submit(p, self._params(mt, extra))
             reqs.append(self._live[rid])
-        while any(r.status != "finished" for r in reqs):
-            self.step()
+        try:
+            while any(r.status != "finished" for r in reqs):
+                self.step()
+        except Exception:
+            for r in reqs:                           # nothing of this call stays behind in the engine
+                if r.status != "finished":
+                    self.cancel(r.rid)
+            raise
         return [self._result(r) for r in reqs]
 
     def stream_complete(self, prompt_token_ids: Sequence[int], *, max_tokens: int = 128,

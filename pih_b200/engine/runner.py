@@ -84,8 +84,9 @@ class ModelRunner:
         self.num_entries = len(model.spec.schedule)
         self.steps_run = 0
         self._graphs = {}
-        self._sightings = {}
+        self._sightings = {}               # shapes seen once and not captured yet; bounded like the graphs
         self._graph_pool = None
+        self._confirm = True
 
     def prepare(self, entries: Sequence[StepEntry]) -> StepBatch:
         """Allocate cache room for every entry (all or none) and pack the batch."""
@@ -116,7 +117,8 @@ class ModelRunner:
                   for i in range(self.num_entries)]
         return self.model.forward(batch, caches)
 
-    def step(self, entries: Sequence[StepEntry], token_feed: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
+    def step(self, entries: Sequence[StepEntry], token_feed: Optional[torch.Tensor] = None,
+             confirm: bool = True) -> Optional[torch.Tensor]:
         """Run ``entries`` as one batch; returns fp32 logits ``[wanted, vocab]``
         in the order of the entries and of their ``want`` lists, or None.
 
@@ -124,8 +126,14 @@ class ModelRunner:
         entries' token ids on the device — the ids that an earlier step sampled and that the host has not
         read yet.
 
+        ``confirm``: the step's tokens count as soon as its kernels are queued (for a caller that reads the
+        device's error word itself before it goes on, as the replay program does).  With False the cache
+        only notes them as queued: the caller calls ``confirm(rids)`` once it has seen the step's error
+        word as zero, or ``discard(rids)`` when it was not.
+
         The returned tensor may be reused by the next step: use it (or queue the kernel that does) before
         calling ``step`` again."""
+        self._confirm = confirm
         pads = self._stand_ins(entries)
         if not pads:
             return self._step(entries, token_feed)
@@ -138,9 +146,25 @@ class ModelRunner:
                     self.cache.release(p.rid)              # its page and its slot, held for this step only
         return logits[:len(entries)]
 
+    def confirm(self, rids) -> None:
+        """The oldest queued step of each of these requests was seen to succeed."""
+        for rid in rids:
+            if self.cache.has_request(rid):
+                self.cache.confirm(rid)
+
+    def discard(self, rids) -> None:
+        """A queued step of these requests failed: they return to their confirmed length, pages and state."""
+        for rid in rids:
+            if self.cache.has_request(rid):
+                self.cache.rollback(rid, unconfirmed=True)
+
+    def _commit(self, rid) -> None:
+        # a stand-in request lives for one step and is never confirmed by anyone
+        self.cache.commit(rid, confirmed=self._confirm or isinstance(rid, _Pad))
+
     def _stand_ins(self, entries: Sequence[StepEntry]):
         m = self.pad_decode_to
-        if m <= 1 or self.cache.state_tensors or not entries:
+        if m <= 1 or not entries:
             return []
         if not all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries):
             return []
@@ -168,7 +192,7 @@ class ModelRunner:
                 self.cache.rollback(e.rid)
             raise
         for e in entries:
-            self.cache.commit(e.rid)
+            self._commit(e.rid)
         self.steps_run += 1
         return logits
 
@@ -191,7 +215,7 @@ class ModelRunner:
         return self._graph_key(entries) is not None
 
     def _graph_key(self, entries):
-        if not (self.cuda_graphs and self.device.type == "cuda") or self.cache.state_tensors:
+        if not (self.cuda_graphs and self.device.type == "cuda"):
             return None
         if all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries):
             return ("decode", len(entries))
@@ -232,12 +256,14 @@ class ModelRunner:
             if state is None and kind[0] == "step" and self._sightings.get(key, 0) == 0:
                 # first sight of this shape: run it as it is; capture if it comes again
                 self._sightings[key] = 1
+                if len(self._sightings) > 4 * self.GRAPH_LIMIT:           # dicts keep insertion order: oldest out
+                    del self._sightings[next(iter(self._sightings))]
                 batch = self.builder.build(entries, self.cache)
                 self._feed(batch, token_feed, stand_in_rows)
                 logits = self.run(batch)
             elif state is None:
-                state = self._capture(entries, key, width, token_feed, stand_in_rows)
-                logits = state["logits"]
+                self._sightings.pop(key, None)
+                logits = self._capture(entries, key, width, token_feed, stand_in_rows)
             else:
                 batch = self.builder.build(entries, self.cache, width=width, device_buffer=state["buffer"])
                 self._feed(batch, token_feed, stand_in_rows)
@@ -251,7 +277,7 @@ class ModelRunner:
                 self.cache.rollback(rid)
             raise
         for rid in rids:
-            self.cache.commit(rid)
+            self._commit(rid)
         self.steps_run += 1
         return logits
 
@@ -275,22 +301,18 @@ class ModelRunner:
             batch.attention_plans = _FixedPlans((0, 1, max_ctx))
         else:
             batch.attention_plans = _BoundedPlans(key[1], max_ctx)
-        if hasattr(ops, "reserve_attention_scratch"):
-            for block in self.model.blocks:
-                spec = getattr(block.mixer, "spec", None)
-                if spec is not None and hasattr(spec, "heads"):
-                    dec_cap = batch.attention_plans[spec.heads // spec.kv_heads][1]
-                    if dec_cap > 0:
-                        ops.reserve_attention_scratch(B, dec_cap, spec.heads, spec.kv_heads, spec.head_dim, max_ctx)
         caches = [self.cache.view(i, batch.block_tables, batch.slot_mappings) for i in range(self.num_entries)]
-        # once eagerly on a side stream (lazy initialisations must not happen under capture) ...
+        # This step itself runs eagerly, on a side stream, from the buffer and with the plans that the graph
+        # will have: whatever a kernel or a part sets up or allocates at its first call with these shapes (shared
+        # memory limits, tensor maps, scratch sized by the plans, library handles) happens here and not under
+        # capture.  The capture that follows records the same launches and executes nothing, so the step's
+        # work — a mixer's update of its state slot included — is done exactly once.
         side = torch.cuda.Stream(self.device)
         side.wait_stream(torch.cuda.current_stream(self.device))
         with torch.cuda.stream(side):
-            self.model.forward(batch, caches)
+            eager_logits = self.model.forward(batch, caches)
         torch.cuda.current_stream(self.device).wait_stream(side)
         torch.cuda.synchronize(self.device)
-        # ... then captured; the eager run already did this step's work (cache writes are idempotent)
         graph = torch.cuda.CUDAGraph()
         before = getattr(ops, "launches", 0)
         with torch.cuda.graph(graph, pool=self._graph_pool):
@@ -298,14 +320,12 @@ class ModelRunner:
         launches = getattr(ops, "launches", 0) - before        # the pack's kernels inside the graph
         if self._graph_pool is None:
             self._graph_pool = graph.pool()
-        graph.replay()
-        self._count_launches(launches)
         state = {"graph": graph, "buffer": buffer, "logits": logits, "batch": batch, "launches": launches}
         self._graphs[key] = state
         steps = [k for k in self._graphs if k[0] == "step"]
         if len(steps) > self.GRAPH_LIMIT:                 # dicts keep insertion order; a replay re-inserts its key
             del self._graphs[steps[0]]
-        return state
+        return eager_logits
 
     def finish(self, rid: Hashable) -> None:
         """The request has ended: everything it holds goes back to the pools."""

@@ -57,7 +57,7 @@ class Request:
     outputs: List[int] = field(default_factory=list)
     num_computed: int = 0
     status: str = "waiting"              # waiting | running | finished
-    finish_reason: Optional[str] = None  # stop | length | capacity | cancelled
+    finish_reason: Optional[str] = None  # stop | length | capacity | cancelled | error
     arrival: int = 0
     preemptions: int = 0
 
@@ -277,18 +277,19 @@ class Scheduler:
                 finished.append(req)
         return finished
 
-    def cancel(self, rid: Hashable) -> Optional[Request]:
-        """Cooperative cancel at a step boundary (controller_runtime.cpp: cancel -> draining)."""
+    def cancel(self, rid: Hashable, reason: str = "cancelled") -> Optional[Request]:
+        """Cooperative cancel at a step boundary (controller_runtime.cpp: cancel -> draining).  ``reason``
+        "error": a step that the request took part in failed."""
         for req in list(self.running):
             if req.rid == rid:
                 self.running.remove(req)
                 self.cache.release(rid)
-                req.status, req.finish_reason = "finished", "cancelled"
+                req.status, req.finish_reason = "finished", reason
                 return req
         for req in list(self.waiting):
             if req.rid == rid:
                 self.waiting.remove(req)
-                req.status, req.finish_reason = "finished", "cancelled"
+                req.status, req.finish_reason = "finished", reason
                 return req
         return None
 

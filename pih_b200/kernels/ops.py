@@ -32,6 +32,11 @@ class KernelError(RuntimeError):
     pass
 
 
+def error_text(code: int) -> str:
+    """What a value of the device's error word means."""
+    return _ERRORS.get(code, f"error code {code}")
+
+
 class CudaOps:
     def __init__(self, device=None):
         if not torch.cuda.is_available():
@@ -71,10 +76,6 @@ class CudaOps:
         # it takes 30.9 against 29.3 us at 2048 rows, 53.6 against 52.9 at 4096 and far more below
         self.tcgen05_swiglu_min_rows = None
         self.tcgen05_min_rows = None       # bf16 products with at least this many rows use the pack's tcgen05 kernel
-        # few rows: output projection + feed-forward of a block as ONE kernel with grid barriers between its three
-        # products.  Off: measured slower than the three kernels it replaces (batch 8: 1.342 against 1.197 ms a
-        # step) — a barrier of 296 blocks costs about what a kernel boundary costs under programmatic launch
-        self.chain_block_tail = False
         self.skinny_max_rows = 16          # bf16 products with at most this many rows use the fused few-rows kernel
         self._declare()
 
@@ -85,7 +86,7 @@ class CudaOps:
                      "pih_gather_rows", "pih_gemm_simt", "pih_paged_attention_generic", "pih_argmax",
                      "pih_sample", "pih_paged_attention_mma", "pih_gemm_tcgen05", "pih_make_kv_tensor_map",
                      "pih_attention_prefill_tcgen05", "pih_gemm_skinny", "pih_set_dependent_launch", "pih_set_attention_cluster_merge",
-                     "pih_gemm_skinny_f32out", "pih_block_tail_chain", "pih_block_tail_chain_reset",
+                     "pih_gemm_skinny_f32out",
                      "pih_qk_attention_fused", "pih_gemm_tcgen05_swiglu"):
             getattr(lib, name).restype = c_int
         lib.pih_attention_scratch_floats.restype = c_ll
@@ -118,13 +119,21 @@ class CudaOps:
             raise KernelError(f"{what}: this size is not supported by the kernel")
         raise KernelError(f"{what}: CUDA error {rc}")
 
+    @property
+    def error_word(self) -> torch.Tensor:
+        """int32 [1] on the device: 0, or the code of the first fault that a kernel reported since it was cleared."""
+        return self._error
+
+    def clear_errors(self) -> None:
+        """Zero the error word (queued on the current stream, behind the kernels already queued there)."""
+        self._error.zero_()
+
     def check_errors(self) -> None:
         """Read the device error word (synchronises); raise if a kernel reported something."""
         code = int(self._error.item())
         if code:
-            self._error.zero_()
-            self.lib.pih_block_tail_chain_reset()          # a barrier that gave up may have left its words dirty
-            raise KernelError(f"a kernel reported: {_ERRORS.get(code, f'error code {code}')}")
+            self.clear_errors()
+            raise KernelError(f"a kernel reported: {error_text(code)}")
 
     def _err(self):
         return c_void_p(self._error.data_ptr())
@@ -217,32 +226,6 @@ class CudaOps:
             return None
         self._check(rc, "gemm_tcgen05_swiglu")
         return out
-
-    def block_tail_chain(self, x: torch.Tensor, w_proj: torch.Tensor, h: torch.Tensor, norm_weight: torch.Tensor,
-                         eps: float, w_gate_up: torch.Tensor, w_down: torch.Tensor):
-        """The tail of a pre-norm block for few rows as ONE kernel: ``o = x . w_proj^T``, ``h' = h + o``,
-        ``y = SwiGLU-FFN(rmsnorm(h'))`` with gate/up rows interleaved in blocks of 8.  Returns ``(h', y)``, or
-        None when the chain kernel does not take the shapes (the caller runs the separate kernels)."""
-        M, Ka = x.shape
-        H = w_proj.shape[0]
-        I = w_down.shape[1]
-        if (not self.chain_block_tail or x.dtype != torch.bfloat16 or M > self.skinny_max_rows
-                or w_gate_up.shape != (2 * I, H) or w_down.shape[0] != H or h.shape != (M, H)
-                or x.stride(1) != 1 or not h.is_contiguous()
-                or any(w.stride(1) != 1 for w in (w_proj, w_gate_up, w_down))):
-            return None
-        o = torch.empty(M, H, dtype=torch.bfloat16, device=x.device)
-        h_out = torch.empty_like(o)
-        act = torch.empty(M, I, dtype=torch.bfloat16, device=x.device)
-        y = torch.empty_like(o)
-        rc = self.lib.pih_block_tail_chain(
-            _ptr(x), c_ll(x.stride(0)), Ka, _ptr(w_proj), c_ll(w_proj.stride(0)), _ptr(h), _ptr(o), _ptr(h_out),
-            _DT[norm_weight.dtype], _ptr(norm_weight), c_float(eps), _ptr(w_gate_up), c_ll(w_gate_up.stride(0)), I,
-            _ptr(act), _ptr(w_down), c_ll(w_down.stride(0)), _ptr(y), M, H, self._err(), self._stream())
-        if rc == -2:
-            return None
-        self._check(rc, "block_tail_chain")
-        return h_out, y
 
     def norm_linear(self, h: torch.Tensor, delta: Optional[torch.Tensor], norm_weight: torch.Tensor, eps: float,
                     w: torch.Tensor, swiglu_interleave: int = 0):

@@ -75,15 +75,7 @@ class PagedAttention:
         h, qkv = ops.norm_linear(h, delta, norm.weight, norm.spec.eps, w)
         return h, self._attend(qkv, step, cache)
 
-    def forward_prenorm_unprojected(self, h, delta, norm, step, cache):
-        """As ``forward_prenorm`` without the output projection: returns ``(h', a, w)`` with the mixer's
-        output ``a . w^T`` left to the caller, who may fuse that product with what follows it."""
-        s, ops = self.spec, self.rt.ops
-        w = self.w_qkv if cache.writable else self.w_qkv[:s.q_size]
-        h, qkv = ops.norm_linear(h, delta, norm.weight, norm.spec.eps, w)
-        return h, self._attend(qkv, step, cache, project=False), self.w_o
-
-    def _attend(self, qkv, step, cache, project=True):
+    def _attend(self, qkv, step, cache):
         s, ops = self.spec, self.rt.ops
         table = self.position.rotation_table() if self.position is not None else None
         rotary = self.position.rotary_dim if self.position is not None else 0
@@ -101,4 +93,4 @@ class PagedAttention:
                 qkv, heads=s.heads, kv_heads=s.kv_heads, head_dim=s.head_dim,
                 kv_cache=cache.kv, block_table=cache.block_table, step=step,
                 scale=s.scale, window=s.window or 0)
-        return ops.linear(attn, self.w_o) if project else attn
+        return ops.linear(attn, self.w_o)

@@ -50,15 +50,6 @@ class PreNormBlock:
         # any other part gets the normed rows
         fused_in = getattr(self.norm_in, "fusable", False)
         fused_post = getattr(self.norm_post, "fusable", False)
-        if (fused_in and fused_post and hasattr(self.mixer, "forward_prenorm_unprojected")
-                and hasattr(self.ffn, "forward_prenorm_projected")):
-            # the mixer leaves its output projection to the feed-forward, which may run it, the add, the norm
-            # and itself as one kernel
-            h, a, w = self.mixer.forward_prenorm_unprojected(h, delta, self.norm_in, step, cache)
-            done = self.ffn.forward_prenorm_projected(h, a, w, self.norm_post)
-            if done is not None:
-                return done
-            return self.ffn.forward_prenorm(h, self.rt.ops.linear(a, w), self.norm_post)
         if fused_in and hasattr(self.mixer, "forward_prenorm"):
             h, a = self.mixer.forward_prenorm(h, delta, self.norm_in, step, cache)
         else:

@@ -53,12 +53,3 @@ class SwiGLU:
         h, act = ops.norm_linear(h, delta, norm.weight, norm.spec.eps, self.w_gate_up,
                                  swiglu_interleave=self.interleave)
         return h, ops.linear(act, self.w_down)
-
-    def forward_prenorm_projected(self, h, x, w_proj, norm):
-        """``delta = x . w_proj^T; h' = h + delta; y = ffn(norm(h'))``: the product that the part before left
-        undone, the add, the norm and this feed-forward as one kernel, where the kernels have one for these
-        shapes; returns ``(h', y)`` or None."""
-        ops = self.rt.ops
-        if self.interleave != 8 or not hasattr(ops, "block_tail_chain"):
-            return None
-        return ops.block_tail_chain(x, w_proj, h, norm.weight, norm.spec.eps, self.w_gate_up, self.w_down)

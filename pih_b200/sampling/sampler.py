@@ -20,22 +20,47 @@ from __future__ import annotations
 
 from typing import List, Sequence
 
+import numpy as np
 import torch
 
 from .params import SamplingParams
 
 MAX_SUPPRESSED = 17          # include/pih/model/qwen3_sampler.h:18
+_INT_COLUMNS = 6 + MAX_SUPPRESSED
 
 
 class Sampler:
+    """Per-row parameters reach the device in one copy from pinned memory that does not wait (a copy from
+    pageable memory would stall the host until the device has caught up, in every step)."""
+
+    STAGES = 4                # pinned buffers in rotation: a buffer is reused only after its copy has left it
+
     def __init__(self, ops, vocab: int, device: torch.device):
         self.ops = ops
         self.vocab = vocab
         self.device = device
+        self._stages = []
+        self._turn = 0
 
     def sample(self, logits: torch.Tensor, params: Sequence[SamplingParams], ordinals: Sequence[int],
                suppressed: Sequence[Sequence[int]]) -> List[int]:
         return self.sample_on_device(logits, params, ordinals, suppressed).tolist()
+
+    def _stage(self, rows: int):
+        """(host int32 buffer, event or None) with room for ``rows`` rows of parameters."""
+        need = rows * (2 + _INT_COLUMNS)
+        pin = self.device.type == "cuda"
+        if len(self._stages) < self.STAGES:
+            self._stages.append([torch.empty(max(need, 64 * (2 + _INT_COLUMNS)), dtype=torch.int32, pin_memory=pin),
+                                 torch.cuda.Event() if pin else None, False])
+        self._turn = (self._turn + 1) % len(self._stages)
+        stage = self._stages[self._turn]
+        if stage[2]:
+            stage[1].synchronize()
+            stage[2] = False
+        if stage[0].numel() < need:
+            stage[0] = torch.empty(2 * need, dtype=torch.int32, pin_memory=pin)
+        return stage
 
     def sample_on_device(self, logits: torch.Tensor, params: Sequence[SamplingParams], ordinals: Sequence[int],
                          suppressed: Sequence[Sequence[int]]) -> torch.Tensor:
@@ -45,15 +70,24 @@ class Sampler:
             raise ValueError("one set of sampling parameters per row of logits is needed")
         if all(p.greedy for p in params) and not any(suppressed):
             return self.ops.argmax(logits)
-        fl = torch.empty(S, 2, dtype=torch.float32)
-        it = torch.empty(S, 6 + MAX_SUPPRESSED, dtype=torch.int32)
+        stage = self._stage(S)
+        host = stage[0][:S * (2 + _INT_COLUMNS)]
+        view = host.numpy()
+        fl = view[:2 * S].view(np.float32).reshape(S, 2)
+        it = view[2 * S:].view(np.uint32).reshape(S, _INT_COLUMNS)
         for i, (p, o, sup) in enumerate(zip(params, ordinals, suppressed)):
             if len(sup) > MAX_SUPPRESSED or len(sup) >= self.vocab:
                 raise ValueError("too many suppressed token ids")
             fl[i, 0] = p.temperature
             fl[i, 1] = p.top_p
             k = 0 if p.top_k is None or p.top_k >= self.vocab else p.top_k
-            row = [k, p.seed & 0xFFFFFFFF, (p.seed >> 32) & 0xFFFFFFFF, o & 0xFFFFFFFF, (o >> 32) & 0xFFFFFFFF,
-                   len(sup)] + list(sup) + [-1] * (MAX_SUPPRESSED - len(sup))
-            it[i] = torch.tensor([v - (1 << 32) if v >= (1 << 31) else v for v in row], dtype=torch.int32)
-        return self.ops.sample(logits, fl.to(self.device), it.to(self.device))
+            it[i, :6] = (k, p.seed & 0xFFFFFFFF, (p.seed >> 32) & 0xFFFFFFFF, o & 0xFFFFFFFF,
+                         (o >> 32) & 0xFFFFFFFF, len(sup))
+            it[i, 6:6 + len(sup)] = list(sup)
+            it[i, 6 + len(sup):] = 0xFFFFFFFF
+        dev = torch.empty(host.numel(), dtype=torch.int32, device=self.device)
+        dev.copy_(host, non_blocking=True)
+        if stage[1] is not None:
+            stage[1].record()
+            stage[2] = True
+        return self.ops.sample(logits, dev[:2 * S].view(torch.float32).view(S, 2), dev[2 * S:].view(S, _INT_COLUMNS))

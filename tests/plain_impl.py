@@ -153,6 +153,28 @@ def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float,
     return _rounder(rounding)(out)
 
 
+def attention_rows(q: torch.Tensor, positions, k: torch.Tensor, v: torch.Tensor, scale: float,
+                   window: int | None = None) -> torch.Tensor:
+    """``attention`` for some rows only: q [n, heads, D] are the queries at ``positions`` (row i sees keys
+    0..positions[i], or the last ``window`` of them) of a sequence whose keys and values are k, v [L, kv_heads, D].
+    Same formula (plugins/model-qwen3/qwen3_gqa_oracle.cpp:59-103), without the L x L score matrix."""
+    n, heads, D = q.shape
+    L, kv_heads = k.shape[0], k.shape[1]
+    group = heads // kv_heads
+    q, k, v = q.to(F64), k.to(F64), v.to(F64)
+    pos = torch.as_tensor(positions, dtype=torch.long)[:, None]
+    keys = torch.arange(L)[None, :]
+    visible = keys <= pos
+    if window is not None:
+        visible &= keys > pos - window
+    out = torch.zeros(n, heads, D, dtype=F64)
+    for h in range(heads):
+        g = h // group
+        scores = ((q[:, h, :] @ k[:, g, :].T) * scale).masked_fill(~visible, float("-inf"))
+        out[:, h, :] = torch.softmax(scores, dim=-1) @ v[:, g, :]
+    return out
+
+
 def silu_mul(gate: torch.Tensor, up: torch.Tensor, rounding="none") -> torch.Tensor:
     """(g / (1 + exp(-g))) * u, rounded once.
 

@@ -166,3 +166,123 @@ def test_block_table_rows_and_slot_mapping():
     pages = list(m.requests["a"].pages[0])
     assert m.block_table_rows(0, ["a"], 3) == [pages + [-1]]
     assert m.slot_mapping(0, "a", 0, 6) == [pages[0] * 4 + i for i in range(4)] + [pages[1] * 4, pages[1] * 4 + 1]
+
+
+def test_queued_steps_count_for_the_next_step_but_only_confirmed_ones_give_pages_back():
+    m = manager([FULL, WIN], page_size=4, num_pages=8)
+    m.add_request("a")
+    m.append("a", 9)
+    m.commit("a", confirmed=False)                         # queued on the device, its error word not seen yet
+    rc = m.requests["a"]
+    assert rc.num_tokens == 9 and rc.confirmed_tokens == 0 and rc.unconfirmed == [9]
+    assert m.num_free_pages() == [5, 5]                    # the window group keeps page 0 until the step is confirmed
+    m.append("a", 1)                                       # the next step starts behind the queued tokens
+    assert m.slot_mapping(1, "a", 9, 1) == [rc.pages[1][2] * 4 + 1]
+    m.commit("a", confirmed=False)
+    m.confirm("a")
+    assert rc.confirmed_tokens == 9 and m.num_free_pages() == [5, 6] and rc.pages[1][0] == -1
+    m.confirm("a")
+    assert rc.confirmed_tokens == 10 and rc.unconfirmed == []
+    with pytest.raises(ValueError, match="no queued step"):
+        m.confirm("a")
+    m.check()
+
+
+def test_rollback_of_queued_steps_returns_to_the_confirmed_length():
+    m = manager([FULL, WIN], page_size=4, num_pages=8)
+    m.add_request("a")
+    m.append("a", 6)
+    m.commit("a")
+    held = [list(pl) for pl in m.requests["a"].pages]
+    for n in (5, 1):
+        m.append("a", n)
+        m.commit("a", confirmed=False)
+    m.append("a", 3)                                       # a third step, not even queued
+    m.rollback("a")                                        # plain rollback: only the append is undone
+    rc = m.requests["a"]
+    assert rc.num_tokens == 12 and rc.unconfirmed == [5, 1] and rc.pending == 0
+    m.rollback("a", unconfirmed=True)                      # ... and now the queued steps too
+    assert rc.num_tokens == rc.confirmed_tokens == 6 and rc.unconfirmed == []
+    assert [list(pl) for pl in rc.pages] == held
+    m.check()
+    m.append("a", 2)
+    with pytest.raises(ValueError, match="queued steps to confirm"):
+        m.commit("a", confirmed=False), m.append("a", 1), m.commit("a")
+    m.release("a")
+    m.check()
+    assert m.num_free_pages() == [8, 8]
+
+
+def test_rollback_puts_the_state_slot_back_as_it_was_before_the_step():
+    m = manager([FULL, StateNeed((3,), torch.float32)], max_requests=2)
+    slot = m.add_request("a").slot
+    state = m.state_tensors[1]
+    m.append("a", 2)
+    state[slot] = 1.0                                      # the step's mixer advanced the state
+    m.commit("a")
+    m.append("a", 1)
+    state[slot] = 2.0
+    m.rollback("a")                                        # the step failed half-way: the old state is back
+    assert state[slot].tolist() == [1.0] * 3
+    # queued steps: the state goes back to what it was at the confirmed length
+    for value in (3.0, 4.0):
+        m.append("a", 1)
+        state[slot] = value
+        m.commit("a", confirmed=False)
+    m.confirm("a")                                         # the step that wrote 3.0 succeeded
+    m.append("a", 1)
+    state[slot] = 5.0
+    m.rollback("a", unconfirmed=True)
+    assert state[slot].tolist() == [3.0] * 3 and m.requests["a"].num_tokens == 3
+
+
+def test_random_orders_with_queued_steps_keep_the_books():
+    rnd = random.Random(7)
+    m = manager([FULL, WIN], page_size=4, num_pages=24, max_requests=4)
+    live, serial = {}, 0                                   # rid -> [confirmed length, queued counts]
+    for _ in range(3000):
+        op = rnd.random()
+        if op < 0.15 and len(live) < 4:
+            rid = f"r{serial}"
+            serial += 1
+            m.add_request(rid)
+            live[rid] = [0, []]
+        elif op < 0.6 and live:
+            rid = rnd.choice(list(live))
+            n = rnd.choice([1, 1, 2, 5, 11])
+            try:
+                m.append(rid, n)
+            except OutOfPages:
+                continue
+            if len(live[rid][1]) < 2 and rnd.random() < 0.7:
+                m.commit(rid, confirmed=False)
+                live[rid][1].append(n)
+            elif not live[rid][1]:
+                m.commit(rid)
+                live[rid][0] += n
+            else:
+                m.rollback(rid)
+        elif op < 0.8 and live:
+            rid = rnd.choice(list(live))
+            if live[rid][1]:
+                m.confirm(rid)
+                live[rid][0] += live[rid][1].pop(0)
+        elif op < 0.9 and live:
+            rid = rnd.choice(list(live))
+            m.rollback(rid, unconfirmed=True)
+            live[rid][1] = []
+        elif live:
+            rid = rnd.choice(list(live))
+            m.release(rid)
+            del live[rid]
+        for rid, (confirmed, queued) in live.items():
+            rc = m.requests[rid]
+            assert rc.confirmed_tokens == confirmed and rc.num_tokens == confirmed + sum(queued)
+            # every key that a query from the confirmed length on may read is still held
+            for j in range(max(0, confirmed - 5), rc.num_tokens):
+                assert rc.pages[1][j // 4] >= 0
+        m.check()
+    for rid in list(live):
+        m.release(rid)
+    m.check()
+    assert m.num_free_pages() == [24, 24]

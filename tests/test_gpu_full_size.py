@@ -33,7 +33,7 @@ def full_size(tmp_path_factory):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("family", ["whole", "tail_decode", "mixed"])
+@pytest.mark.parametrize("family", ["whole", "tail_decode", "portions", "mixed"])
 def test_replay_at_full_layer_sizes(full_size, dtype, family):
     from pih_b200.engine.factory import create_runner
     d, requests, truth, plain_bf16 = full_size

@@ -182,16 +182,23 @@ def test_a_toy_mixer_with_state_of_its_own(model_dirs, tiny_configs):
         def cache_need(self):
             return StateNeed((self.spec.hidden,), torch.float32)
 
+        fail_after_writing = False
+
         def forward(self, x, step, cache):
+            # no value leaves the device here (a captured step could not wait for one): the requests' slots are
+            # gathered and scattered by index tensors, the row ranges come from the host's copy of cu_q
             out = torch.empty_like(x)
+            slots = step.state_slots.long()
+            s = cache.state.index_select(0, slots)
             for r in range(step.num_requests):
-                lo, hi = step.host_cu_q[r], step.host_cu_q[r + 1]
-                slot = int(step.state_slots[r])
-                s = cache.state[slot].clone()
-                for t in range(lo, hi):
-                    s = self.spec.decay * s + x[t].float()
-                    out[t] = (x[t].float() * self.gain + s).to(x.dtype)
-                cache.state[slot] = s
+                sr = s[r]
+                for t in range(step.host_cu_q[r], step.host_cu_q[r + 1]):
+                    sr = self.spec.decay * sr + x[t].float()
+                    out[t] = (x[t].float() * self.gain + sr).to(x.dtype)
+                s[r] = sr
+            cache.state.index_copy_(0, slots, s)
+            if DecayMixer.fail_after_writing:
+                raise RuntimeError("the toy mixer fails after it has advanced its state")
             return out
 
     try:
@@ -212,6 +219,31 @@ def test_a_toy_mixer_with_state_of_its_own(model_dirs, tiny_configs):
         mixed = traces.replay(runner, traces.mixed(reqs, seed=1, max_live=3))
         for rid in reqs:
             assert float((whole[rid] - mixed[rid]).abs().max()) < 1e-5
+        # the same under CUDA graphs: decode steps are captured and replayed, and the state advances once a step
+        cache_g = CacheManager(model.cache_needs(), [None, None], page_size=16, num_pages=16, max_requests=3,
+                               device=rt.device, dtype=rt.dtype)
+        graphed = ModelRunner(model, cache_g, cuda_graphs=True)
+        tail = traces.replay(graphed, traces.tail_decode(reqs, tail=12))
+        mixed_g = traces.replay(graphed, traces.mixed(reqs, seed=2, max_live=3))
+        assert any(k[0] == "decode" for k in graphed._graphs)
+        for rid in reqs:
+            assert float((whole[rid] - tail[rid]).abs().max()) < 1e-5
+            assert float((whole[rid] - mixed_g[rid]).abs().max()) < 1e-5
+        # a step that fails after the mixer wrote its state leaves the old state behind, and runs again as new
+        toks = reqs["r0"]
+        runner.step([StepEntry("x", toks[:10], [9])])
+        slot = cache.requests["x"].slot
+        state_before = cache.state_tensors[1][slot].clone()
+        DecayMixer.fail_after_writing = True
+        with pytest.raises(RuntimeError, match="toy mixer fails"):
+            runner.step([StepEntry("x", toks[10:14], [3])])
+        DecayMixer.fail_after_writing = False
+        assert cache.requests["x"].num_tokens == 10 and cache.requests["x"].pending == 0
+        assert torch.equal(cache.state_tensors[1][slot], state_before)
+        again = runner.step([StepEntry("x", toks[10:14], [3])])
+        assert float((again[0].cpu() - whole["r0"][13]).abs().max()) < 1e-5
+        runner.finish("x")
+        cache.check()
         # state matters: another decay gives other logits after the first token
         blocks[1] = replace(blocks[1], mixer=DecaySpec(hidden=base.hidden, decay=0.0))
         model0 = CausalLM(replace(base, blocks=tuple(blocks)), weights, rt)
