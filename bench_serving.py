@@ -44,6 +44,8 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=None, help="run this many layers of the shape")
     ap.add_argument("--requests", type=int, default=None)
     ap.add_argument("--new-tokens", type=int, default=None)
+    ap.add_argument("--decode-multiple", type=int, default=1,
+                    help="decode batches are brought to a multiple of this many requests by stand-in requests")
     args = ap.parse_args()
 
     import torch
@@ -78,9 +80,11 @@ def main() -> int:
     lengths = [rng.randint(lo, hi) for _ in range(work["requests"])]
     g = torch.Generator().manual_seed(seed)
     prompts = [torch.randint(0, config.vocab_size, (n,), generator=g).tolist() for n in lengths]
-    cache_tokens = sum(n + work["new_tokens"] + 32 for n in lengths)
-    engine = Engine(f"Qwen3-{args.shape}-random", model=(config, model), page_size=16, max_cache_tokens=cache_tokens,
-                    maximum_batch_sequences=work["requests"], maximum_batch_tokens=work["budget"])
+    # no pool size given: the engine takes what the device has left beside the weights, up to what this many
+    # requests of the longest context could hold
+    engine = Engine(f"Qwen3-{args.shape}-random", model=(config, model), page_size=16,
+                    maximum_batch_sequences=work["requests"], maximum_batch_tokens=work["budget"],
+                    maximum_context_tokens=hi + work["new_tokens"] + 32, decode_batch_multiple=args.decode_multiple)
     reqs = []
     for i, prompt in enumerate(prompts):
         sampled = i < work["sampled"] * work["requests"]
@@ -113,7 +117,8 @@ def main() -> int:
         "decode_only": {"steps": decode_only["steps"],
                         "tok_s": round(decode_only["tokens"] / decode_only["seconds"], 1) if decode_only["seconds"] else None},
         "preemptions": sum(r.preemptions for r in reqs),
-        "steps_planned_ahead": engine.steps_planned_ahead,
+        "steps_planned_ahead": engine.steps_planned_ahead, "cache_tokens": engine.cache_tokens,
+        "stand_ins_used": engine.runner.stand_ins_used, "decode_batch_multiple": args.decode_multiple,
         "config": {"shape": args.shape, "layers": config.num_hidden_layers, "layers_of_shape": layers_of_shape,
                    "hidden": config.hidden_size, "intermediate": config.intermediate_size,
                    "heads": config.num_attention_heads, "kv_heads": config.num_key_value_heads,
