@@ -509,8 +509,15 @@ def test_sampler_matches_the_plain_definition(ops, vocab):
 
 def test_sampler_at_the_full_vocabulary(ops):
     """The vocabulary that serving samples from (151 936): the radix selection's two-level counts and the
-    fixed-point mass over 150 000 terms, against the plain sampler.  Temperature alone, top-k 50, top-p 0.9,
-    both, a suppressed arg-max, greedy with a suppressed arg-max."""
+    fixed-point mass over 150 000 terms.  Temperature alone, top-k 50, top-p 0.9, both, a suppressed arg-max,
+    greedy with a suppressed arg-max, a plateau of equal logits.
+
+    The kernel adds masses exactly (2^-44 fixed point); the definition adds them one after the other in
+    float32 (plugins/model-qwen3/qwen3_sampler.cpp:140-170), which over 150 000 terms loses up to a few
+    thousandths of the total — every term below half an ulp of the running sum is dropped.  So the kernel is
+    held to the definition evaluated without that loss (float64: its choice is the first place where the
+    cumulative share exceeds u, to 2e-6), and its distance from the plain float32 sampler's choice may be no
+    more than the mass that float32 summation can lose.  Where few terms are summed (top-k) the two agree."""
     import numpy as np
     vocab = 151936
     g = torch.Generator().manual_seed(19)
@@ -527,23 +534,24 @@ def test_sampler_at_the_full_vocabulary(ops):
         ref, _, word = plain_impl.sample(logits[i].tolist(), temperature=t, top_p=p, top_k=k, seed=seed,
                                          ordinal=ordinal, suppressed=sup)
         assert got[i] not in sup
-        if got[i] == ref:
+        if t == 0.0 or (k is not None and k <= 50):
+            assert got[i] == ref, (i, rows[i], got[i], ref)
             continue
-        # the kernel adds the masses in another order than the sequential sums of the definition: a draw within
-        # rounding of the boundary between two neighbours of the sorted order may fall to either
-        scaled = (logits[i].numpy() / np.float32(t)).astype(np.float64)
-        scaled[list(sup)] = -np.inf
-        order = np.lexsort((np.arange(vocab), -scaled))
+        scaled = (logits[i].numpy() / np.float32(t)).astype(np.float32)
+        order = np.lexsort((np.arange(vocab), -scaled.astype(np.float64)))
+        order = order[~np.isin(order, sup)]
         if k is not None:
             order = order[:k]
-        w = np.exp(scaled[order] - scaled[order[0]])
+        w = np.exp((scaled[order] - scaled[order[0]]).astype(np.float64))
         share = np.cumsum(w) / w.sum()
-        kept = int(np.searchsorted(share, p - 1e-7)) + 1
-        cum = np.cumsum(w[:kept]) / w[:kept].sum()
-        at = {int(tok): j for j, tok in enumerate(order[:kept + 1])}
+        kept = min(len(order), int(np.searchsorted(share, p, side="left")) + 1)
+        cum = np.concatenate([[0.0], np.cumsum(w[:kept]) / w[:kept].sum()])
+        at = {int(tok): j for j, tok in enumerate(order)}
         u = (word + 0.5) / 2.0 ** 32
-        assert got[i] in at and abs(at[got[i]] - at[ref]) == 1, (i, rows[i], got[i], ref)
-        assert abs(cum[min(at[got[i]], at[ref])] - u) < 1e-5, (i, rows[i], got[i], ref)
+        j = at[got[i]]
+        assert j < kept and cum[j] - 2e-6 <= u < cum[j + 1] + 2e-6, (i, rows[i], got[i], j, kept, u)
+        jr = min(at[ref], kept - 1)
+        assert abs(cum[j + 1] - cum[jr + 1]) < 1e-2, (i, rows[i], got[i], ref)
 
 
 def test_sampler_draws_follow_the_distribution(ops):
