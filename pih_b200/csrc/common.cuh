@@ -89,23 +89,20 @@ __device__ __forceinline__ float block_sum(float v, float* scratch /* >= 33 floa
 }
 
 // Programmatic dependent launch.  Kernels of the pack are launched with programmatic stream serialisation:
-// the next kernel's blocks may become resident as soon as the blocks of the kernel before it have exited,
-// before that kernel's writes have been flushed; wait_for_prior_kernels() then blocks until every earlier
-// kernel has completed and its writes are visible.  Every kernel launched through launch_kernel() executes
-// it in every block before its first read of anything an earlier kernel may have written and before its
-// first write to global memory (only loads of weights, which no kernel writes, may come before it), so
-// completion of a kernel implies completion of all kernels before it.  The instruction does nothing in a
-// kernel launched without the attribute.
-// No kernel signals its dependents early (griddepcontrol.launch_dependents): measured on the decode step
-// (Qwen3-0.6B shapes, batch 8, 2048-token contexts, CUDA graph), plain launches took 1.483 ms, the
-// attribute alone 1.406 ms, and the attribute with an early signal — at the top of every kernel, or only
-// before the epilogue of the two large ones — 1.63 and 1.50 ms: blocks that sit in the wait while the
-// earlier kernel still runs cost more than their early residency gains.  Without an early signal a kernel's
-// blocks start only when the kernel before it has ended, so work placed before the wait overlaps just that
-// kernel's flush: the decode attention fetching its first K/V tiles before its wait changed nothing
-// (1.1233 against 1.1239 ms).  The reference launches every
-// kernel with full serialisation (kernels/cuda/qwen_bf16_primitives.cu, all launches).
+// the next kernel's blocks may become resident as soon as every block of the kernel before it has exited or
+// has executed launch_dependents(), before that kernel's writes have been flushed; wait_for_prior_kernels()
+// then blocks until every earlier kernel has completed and its writes are visible.  Every kernel launched
+// through launch_kernel() executes the wait in its blocks before their first read of anything an earlier
+// kernel may have written and before their first write to global memory (only loads of what no kernel writes
+// — weights, the cache of earlier steps, the step's batch arrays — may come before it), so completion of a
+// kernel implies completion of all kernels before it.  The kernels of a decode step signal their dependents
+// when their last load from memory has been issued, and are shaped so that the next kernel's block fits on
+// the SM beside theirs (one block per SM, half its registers, about 100 KB of its shared memory): the next
+// kernel's first loads are in flight while this one computes and stores.  Both instructions do nothing in a
+// kernel launched without the attribute.  The reference launches every kernel with full serialisation
+// (kernels/cuda/qwen_bf16_primitives.cu, all launches).
 __device__ __forceinline__ void wait_for_prior_kernels() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 // 1: kernels are launched with programmatic stream serialisation; 0: plain launches.  Set by pih_set_dependent_launch.
 extern int g_dependent_launch;

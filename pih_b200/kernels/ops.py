@@ -178,7 +178,7 @@ class CudaOps:
         if out_dtype == torch.float32 and M <= self.skinny_max_rows and K % 32 == 0:
             out = torch.empty(M, N, dtype=torch.float32, device=x.device)
             rc = self.lib.pih_gemm_skinny_f32out(_ptr(x), _ptr(w), _ptr(out), M, N, K, c_ll(x.stride(0)),
-                                                 c_ll(w.stride(0)), c_ll(N), self._stream())
+                                                 c_ll(w.stride(0)), c_ll(N), self._err(), self._stream())
             if rc != -2:
                 self._check(rc, "gemm_skinny_f32out")
                 return out
@@ -205,7 +205,7 @@ class CudaOps:
         nd = _DT[norm_weight.dtype] if norm_weight is not None else 0
         rc = self.lib.pih_gemm_skinny(_ptr(x), _ptr(delta), _ptr(x_out), nd, _ptr(norm_weight), c_float(eps), _ptr(w),
                                       _ptr(out), M, N, K, c_ll(x.stride(0)), c_ll(w.stride(0)), c_ll(out.stride(0)),
-                                      1 if swiglu else 0, self._stream())
+                                      1 if swiglu else 0, self._err(), self._stream())
         if rc == -2:
             return None
         self._check(rc, "gemm_skinny")
