@@ -858,60 +858,67 @@ attn_split_tma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap kv
       float wq[EPL], wk[EPL];
       if (p.q_norm_w != nullptr) weights(p.q_norm_w, wq);
       if (p.k_norm_w != nullptr) weights(p.k_norm_w, wk);
+      // The block's tasks: its query rows, then the new tokens whose positions lie in its key range (their k is
+      // normed and rotated, their v kept, both appended to the cache and held for the tile that the TMA boxes may
+      // have filled from the cache's old contents).  Task t goes to warp t % 4, so the tasks' loads — one trip to
+      // the L2 each — run side by side; rows beyond the request's are zero.  The first task's rotation angles
+      // depend on the position alone: they are fetched before the wait.
+      const int nk = (p.write_kv && has_keys) ? n_tok : 0;
+      const int ntasks = packed + nk;
+      auto position_of = [&](int t) { return t < packed ? start + t / G : start + (t - packed); };
+      for (int row = packed + warp; row < 16; row += 4) {
+        Pack zero;
+#pragma unroll
+        for (int j = 0; j < EPL; ++j) zero.e[j] = __float2bfloat16_rn(0.0f);
+        *reinterpret_cast<Pack*>(Qs + row * LD + lane * EPL) = zero;
+      }
+      float2 cs_first[EPL];
+      if (p.rope != nullptr && warp < ntasks) angles(position_of(warp), cs_first);
       wait_for_prior_kernels();                            // q and the new k and v are the kernel before's output
       ASTAMP(1);
-      for (int row = warp; row < 16; row += 4) {           // a row per warp at a time
-        Pack outp;
-        if (row < packed) {
-          const Pack in = *reinterpret_cast<const Pack*>(
-              p.q + static_cast<size_t>(row0 + row / G) * p.q_stride + static_cast<size_t>(g * G + row % G) * D + lane * EPL);
-          float v[EPL];
-          float2 cs[EPL];
+      for (int t = warp; t < ntasks; t += 4) {
+        const bool is_q = t < packed;
+        const int tt = is_q ? t / G : t - packed;          // the token of the step
+        const int j = start + tt;                          // its position
+        if (!is_q && (j < kmin || j > kmax)) continue;
+        const __nv_bfloat16* src = p.q + static_cast<size_t>(row0 + tt) * p.q_stride +
+                                   static_cast<size_t>(is_q ? g * G + t % G : p.heads + g) * D + lane * EPL;
+        const Pack in = *reinterpret_cast<const Pack*>(src);
+        Pack vin;
+        if (!is_q) vin = *reinterpret_cast<const Pack*>(src + static_cast<size_t>(p.kv_heads) * D);
+        float v[EPL];
+        float2 cs[EPL];
 #pragma unroll
-          for (int j = 0; j < EPL; ++j) v[j] = __bfloat162float(in.e[j]);
-          if (p.rope != nullptr) angles(start + row / G, cs);
-          head_norm_rotate<__nv_bfloat16, float, EPL>(v, p.q_norm_w != nullptr ? wq : nullptr, p.norm_eps,
-                                                      p.rope != nullptr ? cs : nullptr, lane);
+        for (int e = 0; e < EPL; ++e) v[e] = __bfloat162float(in.e[e]);
+        if (p.rope != nullptr) {
+          if (t == warp) {
 #pragma unroll
-          for (int j = 0; j < EPL; ++j) outp.e[j] = __float2bfloat16_rn(v[j]);
-        } else {
-#pragma unroll
-          for (int j = 0; j < EPL; ++j) outp.e[j] = __float2bfloat16_rn(0.0f);
-        }
-        *reinterpret_cast<Pack*>(Qs + row * LD + lane * EPL) = outp;
-      }
-      // the new tokens whose positions lie in this block's key range: k normed and rotated, v as it is; both go
-      // to the cache and are kept for the tile that the TMA boxes may have filled from the cache's old contents
-      if (p.write_kv && has_keys) {
-        for (int tt = warp; tt < n_tok; tt += 4) {
-          const int j = start + tt;
-          if (j < kmin || j > kmax) continue;
-          const __nv_bfloat16* krow = p.q + static_cast<size_t>(row0 + tt) * p.q_stride +
-                                      static_cast<size_t>(p.heads + g) * D + lane * EPL;
-          const Pack kin = *reinterpret_cast<const Pack*>(krow);
-          const Pack vin = *reinterpret_cast<const Pack*>(krow + static_cast<size_t>(p.kv_heads) * D);
-          float v[EPL];
-          float2 cs[EPL];
-#pragma unroll
-          for (int e = 0; e < EPL; ++e) v[e] = __bfloat162float(kin.e[e]);
-          if (p.rope != nullptr) angles(j, cs);
-          head_norm_rotate<__nv_bfloat16, float, EPL>(v, p.k_norm_w != nullptr ? wk : nullptr, p.norm_eps,
-                                                      p.rope != nullptr ? cs : nullptr, lane);
-          Pack kout;
-#pragma unroll
-          for (int e = 0; e < EPL; ++e) kout.e[e] = __float2bfloat16_rn(v[e]);
-          int page = table[j >> p.page_shift];
-          if (page < 0 || page >= p.num_pages) {
-            if (lane == 0) publish_error(p.error, kRowWithoutPage);
+            for (int e = 0; e < EPL; ++e) cs[e] = cs_first[e];
           } else {
-            __nv_bfloat16* dst = p.cache_w + (static_cast<size_t>(page) * 2 * p.kv_heads + g) * p.page_size * D +
-                                 static_cast<size_t>(j & (p.page_size - 1)) * D + lane * EPL;
-            *reinterpret_cast<Pack*>(dst) = kout;
-            *reinterpret_cast<Pack*>(dst + static_cast<size_t>(p.kv_heads) * p.page_size * D) = vin;
+            angles(j, cs);
           }
-          *reinterpret_cast<Pack*>(NewK + tt * D + lane * EPL) = kout;
-          *reinterpret_cast<Pack*>(NewV + tt * D + lane * EPL) = vin;
         }
+        const void* nw = is_q ? p.q_norm_w : p.k_norm_w;
+        head_norm_rotate<__nv_bfloat16, float, EPL>(v, nw != nullptr ? (is_q ? wq : wk) : nullptr, p.norm_eps,
+                                                    p.rope != nullptr ? cs : nullptr, lane);
+        Pack outp;
+#pragma unroll
+        for (int e = 0; e < EPL; ++e) outp.e[e] = __float2bfloat16_rn(v[e]);
+        if (is_q) {
+          *reinterpret_cast<Pack*>(Qs + t * LD + lane * EPL) = outp;
+          continue;
+        }
+        int page = table[j >> p.page_shift];
+        if (page < 0 || page >= p.num_pages) {
+          if (lane == 0) publish_error(p.error, kRowWithoutPage);
+        } else {
+          __nv_bfloat16* dst = p.cache_w + (static_cast<size_t>(page) * 2 * p.kv_heads + g) * p.page_size * D +
+                               static_cast<size_t>(j & (p.page_size - 1)) * D + lane * EPL;
+          *reinterpret_cast<Pack*>(dst) = outp;
+          *reinterpret_cast<Pack*>(dst + static_cast<size_t>(p.kv_heads) * p.page_size * D) = vin;
+        }
+        *reinterpret_cast<Pack*>(NewK + tt * D + lane * EPL) = outp;
+        *reinterpret_cast<Pack*>(NewV + tt * D + lane * EPL) = vin;
       }
     } else {
       for (int c = threadIdx.x; c < 16 * (D / 8); c += 128) {
@@ -982,7 +989,15 @@ static int launch_split_tma(const AttnParams& p, int R, const CUtensorMap* kv_ma
     dim3 grid(p.max_splits, p.kv_heads, R);
 #define PIH_SPLIT_TMA(CLUSTER, FUSE)                                                                              \
   do {                                                                                                            \
-    static int smem_done = 0;                                                                                     \
+    static int smem_done = -1;                                                                                    \
+    if (smem_done < 0) {                                                                                          \
+      /* the same preference as the products of a decode step: their blocks may then be resident beside these */  \
+      cudaError_t e = cudaFuncSetAttribute(attn_split_tma_kernel<D, CLUSTER, FUSE>,                               \
+                                           cudaFuncAttributePreferredSharedMemoryCarveout,                        \
+                                           cudaSharedmemCarveoutMaxShared);                                       \
+      if (e != cudaSuccess) return static_cast<int>(e);                                                           \
+      smem_done = 0;                                                                                              \
+    }                                                                                                             \
     if (smem_done < smem) {                                                                                       \
       cudaError_t e = cudaFuncSetAttribute(attn_split_tma_kernel<D, CLUSTER, FUSE>,                               \
                                            cudaFuncAttributeMaxDynamicSharedMemorySize, smem);                    \

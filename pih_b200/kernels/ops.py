@@ -77,6 +77,7 @@ class CudaOps:
         self.tcgen05_swiglu_min_rows = None
         self.tcgen05_min_rows = None       # bf16 products with at least this many rows use the pack's tcgen05 kernel
         self.skinny_max_rows = 16          # bf16 products with at most this many rows use the fused few-rows kernel
+        self.fused_residual = True         # ... and add the residual in the epilogue of output projections
         self._declare()
 
     # -- plumbing ---------------------------------------------------------------
@@ -191,25 +192,34 @@ class CudaOps:
         return torch.mm(x, w.t())
 
     def linear_skinny(self, x: torch.Tensor, w: torch.Tensor, *, delta=None, norm_weight=None, eps: float = 0.0,
-                      swiglu: bool = False):
+                      swiglu: bool = False, residual: Optional[torch.Tensor] = None):
         """The few-rows product (bf16, at most 16 rows) with its optional fused residual add, RMSNorm and
-        SwiGLU.  Returns ``out`` — or ``(x + delta, out)`` when ``delta`` is given — or None when the kernel
-        does not take the shape."""
+        SwiGLU in front and behind.  ``residual``: the result is ``round(round(x . w^T) + residual)``.  Returns
+        ``out`` — or ``(x + delta, out)`` when ``delta`` is given — or None when the kernel does not take the shape."""
         M, K = x.shape
         N = w.shape[0]
         if (x.dtype != torch.bfloat16 or M > 16 or K % 32 or K > 16384 or x.stride(1) != 1 or w.stride(1) != 1
-                or (swiglu and N % 16)):
+                or (swiglu and (N % 16 or residual is not None))
+                or (residual is not None and (residual.shape != (M, N) or not residual.is_contiguous()))):
             return None
         out = torch.empty(M, N // 2 if swiglu else N, dtype=torch.bfloat16, device=x.device)
         x_out = torch.empty_like(x) if delta is not None else None
         nd = _DT[norm_weight.dtype] if norm_weight is not None else 0
         rc = self.lib.pih_gemm_skinny(_ptr(x), _ptr(delta), _ptr(x_out), nd, _ptr(norm_weight), c_float(eps), _ptr(w),
-                                      _ptr(out), M, N, K, c_ll(x.stride(0)), c_ll(w.stride(0)), c_ll(out.stride(0)),
-                                      1 if swiglu else 0, self._err(), self._stream())
+                                      _ptr(out), _ptr(residual), M, N, K, c_ll(x.stride(0)), c_ll(w.stride(0)),
+                                      c_ll(out.stride(0)), 1 if swiglu else 0, self._err(), self._stream())
         if rc == -2:
             return None
         self._check(rc, "gemm_skinny")
         return out if delta is None else (x_out, out)
+
+    def linear_add(self, x: torch.Tensor, w: torch.Tensor, residual: torch.Tensor):
+        """``round(round(x . w^T) + residual)`` as one kernel — an output projection with the residual add that
+        follows it — or None when only the separate kernels can do it (the caller then passes the product on and
+        the next norm adds it)."""
+        if x.shape[0] > self.skinny_max_rows or not self.fused_residual:
+            return None
+        return self.linear_skinny(x, w, residual=residual)
 
     def linear_tcgen05_swiglu(self, x: torch.Tensor, w: torch.Tensor, tile_n: int = 0):
         """``SwiGLU(x . w^T)`` with the pack's tcgen05 product and SiLU-mul in its epilogue: ``w`` holds blocks

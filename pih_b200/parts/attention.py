@@ -73,9 +73,11 @@ class PagedAttention:
         s, ops = self.spec, self.rt.ops
         w = self.w_qkv if cache.writable else self.w_qkv[:s.q_size]
         h, qkv = ops.norm_linear(h, delta, norm.weight, norm.spec.eps, w)
-        return h, self._attend(qkv, step, cache)
+        return self._attend(qkv, step, cache, residual=h)
 
-    def _attend(self, qkv, step, cache):
+    def _attend(self, qkv, step, cache, residual=None):
+        """Attention and the output projection.  With ``residual`` (the stream ``h``) returns ``(h', delta)``: either
+        ``(h + projection, None)`` when one kernel did both, or ``(h, projection)`` for the next norm to add."""
         s, ops = self.spec, self.rt.ops
         table = self.position.rotation_table() if self.position is not None else None
         rotary = self.position.rotary_dim if self.position is not None else 0
@@ -93,4 +95,10 @@ class PagedAttention:
                 qkv, heads=s.heads, kv_heads=s.kv_heads, head_dim=s.head_dim,
                 kv_cache=cache.kv, block_table=cache.block_table, step=step,
                 scale=s.scale, window=s.window or 0)
-        return ops.linear(attn, self.w_o)
+        if residual is None:
+            return ops.linear(attn, self.w_o)
+        if hasattr(ops, "linear_add"):
+            h_new = ops.linear_add(attn, self.w_o, residual)
+            if h_new is not None:
+                return h_new, None
+        return residual, ops.linear(attn, self.w_o)

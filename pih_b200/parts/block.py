@@ -5,7 +5,8 @@
 passes on the residual stream ``h`` together with ``delta``, the last
 sub-layer's output that is not yet added, so that the add fuses with the
 next norm wherever that norm lives (the next block's, or the model's final
-norm).
+norm).  ``delta`` is None when the last sub-layer has added its output itself
+(for few rows the output projections add the residual in their epilogue).
 """
 from __future__ import annotations
 

@@ -48,8 +48,13 @@ class SwiGLU:
 
     def forward_prenorm(self, h, delta, norm):
         """``h' = h + delta; y = ffn(norm(h'))`` with the add, the norm and SiLU-mul fused into the
-        gate-up product where the kernels can; returns ``(h', y)``."""
+        gate-up product where the kernels can; returns ``(h', y)`` — or ``(h' + y, None)`` when the down product
+        added the residual itself."""
         ops = self.rt.ops
         h, act = ops.norm_linear(h, delta, norm.weight, norm.spec.eps, self.w_gate_up,
                                  swiglu_interleave=self.interleave)
+        if hasattr(ops, "linear_add"):
+            h_new = ops.linear_add(act, self.w_down, h)      # the down product and the residual add as one kernel
+            if h_new is not None:
+                return h_new, None
         return h, ops.linear(act, self.w_down)

@@ -141,8 +141,27 @@ def test_linear_skinny(ops, M, N, K):
     assert out is not None and out.shape == (M, N)
     ref = x.cpu().double() @ w.cpu().double().T
     torch.testing.assert_close(out.cpu().double(), ref, rtol=8e-3, atol=1e-3 * max(1.0, float(ref.abs().max()) / 4))
-    # a row alone gives the same bits as among others
-    assert torch.equal(ops.linear_skinny(x[M - 1:].contiguous(), w)[0], out[M - 1])
+    # a row gives the same bits alone as among others (up to 8 rows and 9 to 16 rows are cut differently: a row
+    # among 9 to 16 is compared with itself among 9)
+    few = x[M - 1:] if M <= 8 else x[M - 9:]
+    assert torch.equal(ops.linear_skinny(few.contiguous(), w)[-1], out[M - 1])
+
+
+@pytest.mark.parametrize("M", [1, 8, 13])
+@pytest.mark.parametrize("N,K", [(1024, 2048), (1024, 3072), (151, 96), (1000, 1024)])
+def test_linear_skinny_adds_the_residual_in_its_epilogue(ops, M, N, K):
+    """``round(round(x . w^T) + residual)``: the bits of the separate product followed by the separate add."""
+    x = _rand((M, K), torch.bfloat16, 3)
+    w = _rand((N, K), torch.bfloat16, 4, 0.1)
+    h = _rand((M, N), torch.bfloat16, 5, 2.0)
+    fused = ops.linear_add(x, w, h)
+    assert fused is not None and fused.shape == (M, N)
+    product = ops.linear_skinny(x, w)
+    want = (product.float() + h.float()).to(torch.bfloat16)
+    assert torch.equal(fused, want)
+    ref = plain_impl.residual_add(h.cpu(), plain_impl.linear(x.cpu(), w.cpu(), "bf16"), "bf16")
+    torch.testing.assert_close(fused.cpu().double(), ref, rtol=1.6e-2, atol=2e-2)
+    ops.check_errors()
 
 
 @pytest.mark.parametrize("M", [1, 8, 13])
