@@ -73,15 +73,7 @@ struct AttnParams {
   int write_kv;                        // append the new tokens' k and v to the cache (and use them)
   __nv_bfloat16* cache_w;              // the cache, writable
   int fused;                           // host: launch the FUSE variant
-  int knob;                            // bit 0: signal dependents after the last load; bit 1: loads before the wait
-  unsigned long long* stamps;
 };
-__device__ __forceinline__ unsigned long long gtime() {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-  return t;
-}
-#define ASTAMP(k) do { if (p.stamps != nullptr && (threadIdx.x == 0 || threadIdx.x == 128)) p.stamps[((blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) * 16 + (k)] = gtime(); } while (0)
 
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem, int src_bytes) {
   const uint32_t s = static_cast<uint32_t>(__cvta_generic_to_shared(smem));
@@ -733,8 +725,7 @@ attn_split_tma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap kv
   // still running; the consumers wait just before they read q and the new k and v.  (The new tokens' own keys,
   // which the boxes may bring in their old state, are put into the landed tile from registers anyway.)
   // Without FUSE the kernel before this one has written the new keys into the cache: everything waits for it.
-  if (threadIdx.x == 0) ASTAMP(0);
-  if (!FUSE || !(p.knob & 2)) wait_for_prior_kernels();
+  if (!FUSE) wait_for_prior_kernels();
   constexpr int LD = D + 8;
   constexpr int PANELS = D / 64;
   constexpr int TILE_BYTES = BN * D * 2;               // K (or V) of one tile: PANELS panels of BN x 128 bytes
@@ -832,8 +823,7 @@ attn_split_tma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap kv
     }
     // the block's last load is on its way: once every block says so, the next kernel's blocks may become resident
     // and start streaming their weights
-    if (lane == 0 && (p.knob & 1)) launch_dependents();
-    ASTAMP(6);
+    if (lane == 0) launch_dependents();
   } else {
     // consumers: the query rows arrive while the first tiles are on their way
     if (FUSE) {
@@ -875,7 +865,6 @@ attn_split_tma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap kv
       float2 cs_first[EPL];
       if (p.rope != nullptr && warp < ntasks) angles(position_of(warp), cs_first);
       wait_for_prior_kernels();                            // q and the new k and v are the kernel before's output
-      ASTAMP(1);
       for (int t = warp; t < ntasks; t += 4) {
         const bool is_q = t < packed;
         const int tt = is_q ? t / G : t - packed;          // the token of the step
@@ -933,12 +922,9 @@ attn_split_tma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap kv
       cp_async_wait<0>();
     }
     asm volatile("bar.sync 1, 128;\n" ::: "memory");   // the four consumer warps only
-    ASTAMP(2);
     for (int i = 0; i < ntiles; ++i) {
       const int s = i % kSplitStages;
       mbar_wait(&full[s], (i / kSplitStages) & 1, p.error);
-      if (i == 0) ASTAMP(3);
-      if (i == ntiles - 1) ASTAMP(4);
       const __nv_bfloat16* Ks = reinterpret_cast<const __nv_bfloat16*>(KV + s * 2 * TILE_BYTES);
       const __nv_bfloat16* Vs = reinterpret_cast<const __nv_bfloat16*>(KV + s * 2 * TILE_BYTES + TILE_BYTES);
       if (FUSE && p.write_kv) {
@@ -969,13 +955,11 @@ attn_split_tma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap kv
     cluster_finish<D>(p, g, static_cast<int>(gridDim.x), packed, G, row0, m, l, o, reinterpret_cast<float*>(KV));
   else
     split_finish<D>(p, r, g, sp, s_lo, s_hi, packed, G, row0, m, l, o, reinterpret_cast<float*>(KV), &s_last);
-  if (threadIdx.x == 0) ASTAMP(5);
 }
 
 // 1: the splits of one (request, kv head) are a thread-block cluster when there are 2 to kMaxCluster of them
 int g_cluster_merge = 1;
-int g_attn_knob = 3;
-extern unsigned long long* g_stamps;
+
 
 template <int D>
 static int launch_split_tma(const AttnParams& p, int R, const CUtensorMap* kv_map, cudaStream_t s) {
@@ -1061,17 +1045,10 @@ static int launch_both(const AttnParams& p, int R, int tile_max_q, const CUtenso
 }  // namespace pih
 
 using namespace pih;
-extern "C" int pih_debug_stamp_next();
 
 // 1 (the default): 2 to 8 splits of one (request, kv head) run as a thread-block cluster and merge through
 // distributed shared memory; 0: every split count merges through scratch memory and tickets.  Returns the
 // previous setting.
-extern "C" int pih_debug_attn_knob(int value) {
-  const int before = pih::g_attn_knob;
-  pih::g_attn_knob = value;
-  return before;
-}
-
 extern "C" int pih_set_attention_cluster_merge(int on) {
   const int before = pih::g_cluster_merge;
   pih::g_cluster_merge = on ? 1 : 0;
@@ -1178,8 +1155,6 @@ static int paged_attention_mma(const void* q, int q_stride, void* out, const voi
   p.part_o = scratch + tickets;
   p.part_ml = p.part_o + static_cast<size_t>(num_requests) * dec_tok_cap * heads * p.max_splits * head_dim;
   p.error = error;
-  p.knob = pih::g_attn_knob;
-  p.stamps = pih::g_stamps ? pih::g_stamps + static_cast<size_t>(pih_debug_stamp_next()) * 512 * 16 : nullptr;
   p.fused = 0;
   p.q_norm_w = p.k_norm_w = nullptr;
   p.rope = nullptr;
