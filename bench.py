@@ -221,11 +221,12 @@ def prefill_run(model, tokens_n: int, reps: int = 6):
     runner = ModelRunner(model, cache, cuda_graphs=True)    # a repeated portion shape is replayed from a graph
     g = torch.Generator().manual_seed(6)
     toks = torch.randint(0, spec.vocab, (tokens_n,), generator=g).tolist()
-    # a prompt of another length first: what the kernels and the library set up at their first call is not part
-    # of "the first sight of a shape"
-    runner.step([StepEntry("w", toks[:tokens_n - 48], [tokens_n - 49])])
-    torch.cuda.synchronize()
-    runner.finish("w")
+    # prompts of other lengths first: what the kernels and the library set up or load at their first calls with
+    # rows of about this number is not part of "the first sight of a shape" in a process that has served before
+    for cut in (48, 112, 16, 80):
+        runner.step([StepEntry("w", toks[:tokens_n - cut], [tokens_n - cut - 1])])
+        torch.cuda.synchronize()
+        runner.finish("w")
     times = []
     first_sight = None
     for i in range(reps + 2):
@@ -258,7 +259,8 @@ def e2e_run(config, model_dir_weights, batch: int, steps: int, warmup: int):
     from pih_b200.sampling import SamplingParams
 
     engine = Engine(model_dir_weights, "bfloat16", page_size=PAGE, maximum_batch_sequences=batch,
-                    maximum_batch_tokens=4096, maximum_context_tokens=2 * CONTEXT)    # the pool: sized by the engine
+                    maximum_batch_tokens=4096, maximum_context_tokens=2 * CONTEXT,    # the pool: sized by the engine
+                    capture_decode_after=0)        # the batch never changes: its graph is captured at once
     g = torch.Generator().manual_seed(7)
     # long enough that no request finishes inside the timed region (prompts finish prefill on different steps)
     params = SamplingParams(max_tokens=steps + warmup + batch + 16, ignore_eos=True)

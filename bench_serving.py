@@ -44,8 +44,8 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=None, help="run this many layers of the shape")
     ap.add_argument("--requests", type=int, default=None)
     ap.add_argument("--new-tokens", type=int, default=None)
-    ap.add_argument("--decode-multiple", type=int, default=1,
-                    help="decode batches are brought to a multiple of this many requests by stand-in requests")
+    ap.add_argument("--capture-decode-after", type=int, default=None,
+                    help="uncaptured runs of a decode shape before it is captured into a CUDA graph")
     args = ap.parse_args()
 
     import torch
@@ -84,7 +84,9 @@ def main() -> int:
     # requests of the longest context could hold
     engine = Engine(f"Qwen3-{args.shape}-random", model=(config, model), page_size=16,
                     maximum_batch_sequences=work["requests"], maximum_batch_tokens=work["budget"],
-                    maximum_context_tokens=hi + work["new_tokens"] + 32, decode_batch_multiple=args.decode_multiple)
+                    maximum_context_tokens=hi + work["new_tokens"] + 32)
+    if args.capture_decode_after is not None:
+        engine.runner.capture_decode_after = args.capture_decode_after
     reqs = []
     for i, prompt in enumerate(prompts):
         sampled = i < work["sampled"] * work["requests"]
@@ -118,7 +120,7 @@ def main() -> int:
                         "tok_s": round(decode_only["tokens"] / decode_only["seconds"], 1) if decode_only["seconds"] else None},
         "preemptions": sum(r.preemptions for r in reqs),
         "steps_planned_ahead": engine.steps_planned_ahead, "cache_tokens": engine.cache_tokens,
-        "stand_ins_used": engine.runner.stand_ins_used, "decode_batch_multiple": args.decode_multiple,
+
         "config": {"shape": args.shape, "layers": config.num_hidden_layers, "layers_of_shape": layers_of_shape,
                    "hidden": config.hidden_size, "intermediate": config.intermediate_size,
                    "heads": config.num_attention_heads, "kv_heads": config.num_key_value_heads,

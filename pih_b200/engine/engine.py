@@ -94,7 +94,7 @@ class Engine:
                  maximum_batch_sequences: int = 32, maximum_batch_tokens: int = 4096,
                  maximum_context_tokens: Optional[int] = None, cuda_graphs: bool = True,
                  run_ahead: bool = True, ops: Optional[object] = None, model: Optional[tuple] = None,
-                 decode_batch_multiple: int = 1):
+                 capture_decode_after: int = 8):
         """``model_dir``: a folder with config.json and model.safetensors.  ``model``: instead of loading that
         folder, a ``(configuration, model)`` pair that is already built on its device (``model_dir`` is then
         only a name; ``dtype`` and ``device`` are the model's own).
@@ -104,8 +104,10 @@ class Engine:
         more than ``maximum_batch_sequences`` requests of ``maximum_context_tokens`` need (see
         ``factory.cache_tokens_for_memory``; the chosen size is ``engine.cache_tokens``).
 
-        ``decode_batch_multiple``: with CUDA graphs, decode steps are brought to a multiple of this many requests
-        by stand-in requests, so that a few graphs serve every batch size (1: never)."""
+        ``capture_decode_after``: with CUDA graphs, a decode step's shape is captured into a graph once it has been
+        run this many times as it is (a capture costs about ten such steps; with requests that end one after the
+        other a shape lasts a few steps only: measured on 32 requests of the 1.7B shape, 8 gave 6.1 thousand
+        generated tokens a second against 5.6 with captures at first sight)."""
         from ..models import load_model
         from ..parts.registry import Runtime
         from .factory import DTYPES, cache_tokens_for_memory
@@ -130,10 +132,9 @@ class Engine:
             else:
                 max_cache_tokens = min(maximum_batch_sequences * self.max_context, 1 << 16)
         self.cache_tokens = max_cache_tokens
-        pad = decode_batch_multiple if cuda_graphs else 1
         self.cache, self.runner = runner_for(self.model, page_size=page_size, max_cache_tokens=max_cache_tokens,
                                              max_requests=maximum_batch_sequences, cuda_graphs=cuda_graphs,
-                                             pad_decode_to=pad)
+                                             capture_decode_after=capture_decode_after)
         self.rt = self.model.rt
         spec = self.model.spec
         self.scheduler = Scheduler(self.cache, max_batch_sequences=maximum_batch_sequences,

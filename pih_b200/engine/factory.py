@@ -16,7 +16,7 @@ DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.f
 
 def create_runner(model_dir: str, dtype: str = "bfloat16", *, device: str = "cuda:0", page_size: int = 16,
                   max_cache_tokens: int = 4096, max_requests: int = 32, cuda_graphs: bool = False,
-                  ops: Optional[object] = None, pad_decode_to: int = 1):
+                  ops: Optional[object] = None, capture_decode_after: int = 0):
     """Returns ``(config, model, cache, runner)``.
 
     ``max_cache_tokens`` sizes every cache group's pool: ``ceil(max_cache_tokens
@@ -29,7 +29,8 @@ def create_runner(model_dir: str, dtype: str = "bfloat16", *, device: str = "cud
     rt = Runtime(device=dev, dtype=DTYPES[dtype], ops=ops if ops is not None else get_ops(dev))
     config, model = load_model(model_dir, rt)
     cache, runner = runner_for(model, page_size=page_size, max_cache_tokens=max_cache_tokens,
-                               max_requests=max_requests, cuda_graphs=cuda_graphs, pad_decode_to=pad_decode_to)
+                               max_requests=max_requests, cuda_graphs=cuda_graphs,
+                               capture_decode_after=capture_decode_after)
     return config, model, cache, runner
 
 
@@ -72,10 +73,10 @@ def cache_tokens_for_memory(model, *, page_size: int, max_requests: int, max_bat
 
 
 def runner_for(model, *, page_size: int = 16, max_cache_tokens: int = 4096, max_requests: int = 32,
-               cuda_graphs: bool = False, pad_decode_to: int = 1):
+               cuda_graphs: bool = False, capture_decode_after: int = 0):
     """A cache and a step function for a model that is already built; returns ``(cache, runner)``."""
     rt = model.rt
     cache = CacheManager(model.cache_needs(), [e.reads_cache_of for e in model.spec.schedule],
                          page_size=page_size, num_pages=-(-max_cache_tokens // page_size),
                          max_requests=max_requests, device=rt.device, dtype=rt.dtype)
-    return cache, ModelRunner(model, cache, cuda_graphs=cuda_graphs, pad_decode_to=pad_decode_to)
+    return cache, ModelRunner(model, cache, cuda_graphs=cuda_graphs, capture_decode_after=capture_decode_after)

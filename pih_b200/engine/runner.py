@@ -57,32 +57,19 @@ class _BoundedPlans(dict):
         return tile_max_q, dec_cap, self._max_ctx if dec_cap else 0
 
 
-class _Pad:
-    """Owner of a stand-in request (no caller's request id can be equal to it)."""
-
-    def __init__(self, k: int):
-        self.k = k
-
-    def __repr__(self):
-        return f"<stand-in request {self.k}>"
-
-
 class ModelRunner:
-    def __init__(self, model, cache: CacheManager, cuda_graphs: bool = False, pad_decode_to: int = 1):
+    def __init__(self, model, cache: CacheManager, cuda_graphs: bool = False, capture_decode_after: int = 0):
         self.cuda_graphs = cuda_graphs
-        # Decode steps are brought to a multiple of this many requests by stand-in requests (one token at
-        # position 0 in a page that they hold for the step only; their logits are dropped).  A decode graph is
-        # keyed by its number of requests, and a batch whose requests end one after the other would otherwise
-        # show a new key — an eager step or a capture — every step or two.
-        self.pad_decode_to = pad_decode_to
-        self._pad_ids = []
-        self.stand_ins_used = 0            # over the runner's life
         self.model = model
         self.cache = cache
         self.device = model.rt.device
         self.builder = BatchBuilder(self.device)
         self.num_entries = len(model.spec.schedule)
         self.steps_run = 0
+        # A decode step is captured when its shape (requests, table width) has been run this many times uncaptured.
+        # A capture costs about as much as ten uncaptured steps; a batch whose requests end one after the other
+        # shows a shape for a few steps only.
+        self.capture_decode_after = capture_decode_after
         self._graphs = {}
         self._sightings = {}               # shapes seen once and not captured yet; bounded like the graphs
         self._graph_pool = None
@@ -134,17 +121,7 @@ class ModelRunner:
         The returned tensor may be reused by the next step: use it (or queue the kernel that does) before
         calling ``step`` again."""
         self._confirm = confirm
-        pads = self._stand_ins(entries)
-        if not pads:
-            return self._step(entries, token_feed)
-        self.stand_ins_used += len(pads)
-        try:
-            logits = self._step(list(entries) + pads, token_feed, stand_in_rows=len(pads))
-        finally:
-            for p in pads:
-                if self.cache.has_request(p.rid):
-                    self.cache.release(p.rid)              # its page and its slot, held for this step only
-        return logits[:len(entries)]
+        return self._step(entries, token_feed)
 
     def confirm(self, rids) -> None:
         """The oldest queued step of each of these requests was seen to succeed."""
@@ -159,33 +136,14 @@ class ModelRunner:
                 self.cache.rollback(rid, unconfirmed=True)
 
     def _commit(self, rid) -> None:
-        # a stand-in request lives for one step and is never confirmed by anyone
-        self.cache.commit(rid, confirmed=self._confirm or isinstance(rid, _Pad))
+        self.cache.commit(rid, confirmed=self._confirm)
 
-    def _stand_ins(self, entries: Sequence[StepEntry]):
-        m = self.pad_decode_to
-        if m <= 1 or not entries:
-            return []
-        if not all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries):
-            return []
-        n = -len(entries) % m
-        if n == 0 or len(entries) < m:                      # the smallest batches keep their own graphs: the
-            return []                                      # decode attention cuts a lone long request finer
-        # only with slots and pages to spare: a stand-in must never be the reason for a step to fail
-        new = sum(1 for e in entries if not self.cache.has_request(e.rid))
-        pages = sum(max(self.cache.pages_needed(e.rid, 1)) if self.cache.has_request(e.rid) else 1 for e in entries)
-        n = min(n, self.cache.slots.num_free - new, min(self.cache.num_free_pages()) - pages)
-        while len(self._pad_ids) < n:
-            self._pad_ids.append(_Pad(len(self._pad_ids)))
-        return [StepEntry(self._pad_ids[k], [0], [0]) for k in range(max(n, 0))]
-
-    def _step(self, entries: Sequence[StepEntry], token_feed: Optional[torch.Tensor] = None,
-              stand_in_rows: int = 0) -> Optional[torch.Tensor]:
+    def _step(self, entries: Sequence[StepEntry], token_feed: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
         if self._graphable(entries):
-            return self._graph_step(entries, token_feed, stand_in_rows)
+            return self._graph_step(entries, token_feed)
         batch = self.prepare(entries)
         try:
-            self._feed(batch, token_feed, stand_in_rows)
+            self._feed(batch, token_feed)
             logits = self.run(batch)
         except Exception:
             for e in entries:
@@ -210,6 +168,7 @@ class ModelRunner:
     GRAPH_WIDTH_STEP = 64           # block-table widths are rounded up to a multiple of this many pages
     GRAPH_MIN_ROWS = 128
     GRAPH_LIMIT = 48
+    CAPTURE_AFTER_STEP = 1          # a mixed step is captured when its shape is seen the second time
 
     def _graphable(self, entries) -> bool:
         return self._graph_key(entries) is not None
@@ -225,15 +184,14 @@ class ModelRunner:
         return None
 
     @staticmethod
-    def _feed(batch: StepBatch, token_feed: Optional[torch.Tensor], stand_in_rows: int = 0) -> None:
+    def _feed(batch: StepBatch, token_feed: Optional[torch.Tensor]) -> None:
         if token_feed is not None:
-            # (the rows of stand-in requests come last and keep their own ids)
-            if (token_feed.dim() != 1 or token_feed.shape[0] + stand_in_rows != batch.token_ids.shape[0]
+            if (token_feed.dim() != 1 or token_feed.shape[0] != batch.token_ids.shape[0]
                     or token_feed.dtype != batch.token_ids.dtype):
                 raise ValueError("token_feed needs one int32 id per row of the step")
-            batch.token_ids[:token_feed.shape[0]].copy_(token_feed)   # queued behind the batch's own copy to the device
+            batch.token_ids.copy_(token_feed)                # queued behind the batch's own copy to the device
 
-    def _graph_step(self, entries, token_feed=None, stand_in_rows: int = 0) -> Optional[torch.Tensor]:
+    def _graph_step(self, entries, token_feed=None) -> Optional[torch.Tensor]:
         kind = self._graph_key(entries)
         for e in entries:
             if not self.cache.has_request(e.rid):
@@ -253,20 +211,21 @@ class ModelRunner:
         key = kind + (width,)
         state = self._graphs.get(key)
         try:
-            if state is None and kind[0] == "step" and self._sightings.get(key, 0) == 0:
-                # first sight of this shape: run it as it is; capture if it comes again
-                self._sightings[key] = 1
+            seen = self._sightings.get(key, 0)
+            if state is None and seen < (self.CAPTURE_AFTER_STEP if kind[0] == "step" else self.capture_decode_after):
+                # this shape has not been seen often enough to be worth a capture: run it as it is
+                self._sightings[key] = seen + 1
                 if len(self._sightings) > 4 * self.GRAPH_LIMIT:           # dicts keep insertion order: oldest out
                     del self._sightings[next(iter(self._sightings))]
                 batch = self.builder.build(entries, self.cache)
-                self._feed(batch, token_feed, stand_in_rows)
+                self._feed(batch, token_feed)
                 logits = self.run(batch)
             elif state is None:
                 self._sightings.pop(key, None)
-                logits = self._capture(entries, key, width, token_feed, stand_in_rows)
+                logits = self._capture(entries, key, width, token_feed)
             else:
                 batch = self.builder.build(entries, self.cache, width=width, device_buffer=state["buffer"])
-                self._feed(batch, token_feed, stand_in_rows)
+                self._feed(batch, token_feed)
                 if key[0] == "step":
                     self._graphs[key] = self._graphs.pop(key)     # most recently used last
                 state["graph"].replay()
@@ -286,14 +245,14 @@ class ModelRunner:
         if hasattr(ops, "launches"):
             ops.launches += n
 
-    def _capture(self, entries, key, width, token_feed=None, stand_in_rows: int = 0):
+    def _capture(self, entries, key, width, token_feed=None):
         G = len(self.cache.groups)
         T = sum(len(e.tokens) for e in entries)
         B = len(entries)
         S = sum(len(e.want) for e in entries)
         buffer = torch.empty(self.builder.buffer_size(T, B, S, G, width), dtype=torch.int32, device=self.device)
         batch = self.builder.build(entries, self.cache, width=width, device_buffer=buffer)
-        self._feed(batch, token_feed, stand_in_rows)
+        self._feed(batch, token_feed)
         max_ctx = width * self.cache.page_size
         ops = self.model.rt.ops
         # the attention plans of the graph cover every context that fits the table width

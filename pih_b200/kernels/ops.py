@@ -78,6 +78,8 @@ class CudaOps:
         self.tcgen05_min_rows = None       # bf16 products with at least this many rows use the pack's tcgen05 kernel
         self.skinny_max_rows = 16          # bf16 products with at most this many rows use the fused few-rows kernel
         self.fused_residual = True         # ... and add the residual in the epilogue of output projections
+        self.native_blocks = True          # blocks of the built-in parts are issued by one native call each
+        self._native = None
         self._declare()
 
     # -- plumbing ---------------------------------------------------------------
@@ -91,6 +93,20 @@ class CudaOps:
                      "pih_qk_attention_fused", "pih_gemm_tcgen05_swiglu"):
             getattr(lib, name).restype = c_int
         lib.pih_attention_scratch_floats.restype = c_ll
+
+    def _native_supports(self, block) -> bool:
+        from .native_block import NativeBlocks
+        return NativeBlocks.supports(block)
+
+    def native_block(self, block, h, delta, step, cache):
+        """A pre-norm block of the built-in parts through one native call (``native_block.NativeBlocks``); None when
+        that path is off or does not take the block."""
+        if not self.native_blocks:
+            return None
+        if self._native is None:
+            from .native_block import NativeBlocks
+            self._native = NativeBlocks(self)
+        return self._native.run(block, h, delta, step, cache)
 
     def set_dependent_launch(self, on: bool) -> bool:
         """Whether the pack's kernels are launched so that each may begin while the one before it drains

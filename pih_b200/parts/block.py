@@ -45,8 +45,18 @@ class PreNormBlock:
             spec.norm_post, _sub(weights, norm_post_cls.expected_tensors(spec.norm_post), n["norm_post"]), rt)
         self.mixer = mixer_cls(spec.mixer, _sub(weights, mixer_cls.expected_tensors(spec.mixer)), rt)
         self.ffn = ffn_cls(spec.ffn, _sub(weights, ffn_cls.expected_tensors(spec.ffn)), rt)
+        self._native_ok = None             # decided at the first step
 
     def forward(self, h, delta, step, cache):
+        # kernels that can issue a whole block of these parts from one native call get it (the same kernels in the
+        # same order as below; what they do not take comes back as None)
+        if self._native_ok is None:
+            native = getattr(self.rt.ops, "native_block", None)
+            self._native_ok = native is not None and self.rt.ops._native_supports(self)
+        if self._native_ok:
+            done = self.rt.ops.native_block(self, h, delta, step, cache)
+            if done is not None:
+                return done
         # a part that can take "add, norm, then me" as one call gets it (fewer kernels for few rows);
         # any other part gets the normed rows
         fused_in = getattr(self.norm_in, "fusable", False)

@@ -149,29 +149,3 @@ def test_random_workloads_give_the_same_tokens_with_and_without_run_ahead(model_
         return {i: (r.outputs, r.finish_reason) for i, r in reqs.items() if i not in cancelled}
 
     assert run(True) == run(False)
-
-
-@pytest.mark.parametrize("run_ahead", [False, True])
-def test_stand_in_requests_change_no_token_and_keep_no_page(model_dirs, tiny_configs, run_ahead):
-    """Decode steps brought to a multiple of four requests by stand-in requests: the same tokens as without
-    them, the cache's books right after every step, no page and no slot kept; and when slots or pages are
-    short the step runs without them."""
-    prompts = _prompts(tiny_configs["B"]["vocab_size"], [3, 20, 9, 33, 5], seed=21)
-    per_prompt = [dict(max_tokens=m) for m in (14, 5, 9, 2, 11)]
-    kw = dict(temperature=0.0, ignore_eos=True, parameters_per_prompt=per_prompt)
-    plain = _engine(model_dirs["B"], run_ahead, maximum_batch_sequences=8, decode_batch_multiple=1)
-    padded = _engine(model_dirs["B"], run_ahead, maximum_batch_sequences=8, decode_batch_multiple=4)
-    want = plain.complete_batch(prompts, **kw)
-    reqs = [padded._live[padded.submit(p, SamplingParams(max_tokens=m["max_tokens"], ignore_eos=True))]
-            for p, m in zip(prompts, per_prompt)]
-    while padded.has_work():
-        padded.step()
-        padded.cache.check()
-        assert padded.cache.slots.num_free >= 8 - len(prompts)
-    assert [r.outputs for r in reqs] == [w["token_ids"] for w in want]
-    assert plain.runner.stand_ins_used == 0 and padded.runner.stand_ins_used > 0
-    assert all(f == padded.cache.num_pages for f in padded.cache.num_free_pages())
-    assert padded.cache.slots.num_free == 8
-    # five requests in five slots: no slot to spare, so no stand-in, and the same tokens again
-    tight = _engine(model_dirs["B"], run_ahead, maximum_batch_sequences=5, decode_batch_multiple=4)
-    assert tight.complete_batch(prompts, **kw) == want
