@@ -78,8 +78,9 @@ def main() -> int:
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--no-flush", action="store_true")
     ap.add_argument("--impl", default="default", choices=["default", "tcgen05", "skinny", "library"])
-    ap.add_argument("--fused", default="none", choices=["none", "norm", "swiglu"],
-                    help="linear --impl skinny: with the fused residual add + RMSNorm prologue (and SwiGLU epilogue)")
+    ap.add_argument("--fused", default="none", choices=["none", "norm", "addnorm", "swiglu", "residual"],
+                    help="linear --impl skinny: with the RMSNorm prologue (addnorm: and the residual add before it; "
+                         "swiglu: and the SwiGLU epilogue), or with the residual add in the epilogue")
     ap.add_argument("--tile-n", type=int, default=0)
     ap.add_argument("--chain", action="store_true", help="many calls on different inputs back to back in a CUDA graph: the time of one call inside a step")
     ap.add_argument("--chain-mb", type=float, default=200.0,
@@ -147,8 +148,11 @@ def main() -> int:
                 fn = lambda: ops.silu_mul(torch.mm(x, w.t()), 8)
             elif args.impl == "tcgen05":
                 fn = lambda: ops.linear_tcgen05(x, w, tile_n=args.tile_n)
+            elif args.impl == "skinny" and args.fused == "residual":
+                r = torch.randn(args.m, args.n, device=dev).to(bf)
+                fn = lambda: ops.linear_skinny(x, w, residual=r)
             elif args.impl == "skinny" and args.fused != "none":
-                d = torch.randn(args.m, args.k, device=dev).to(bf)
+                d = torch.randn(args.m, args.k, device=dev).to(bf) if args.fused == "addnorm" else None
                 nw = torch.ones(args.k, device=dev).to(bf)
                 fn = lambda: ops.linear_skinny(x, w, delta=d, norm_weight=nw, eps=1e-6, swiglu=args.fused == "swiglu")
             elif args.impl == "skinny":
