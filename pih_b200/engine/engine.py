@@ -300,6 +300,7 @@ class Engine:
                     self._settle(self._unconfirmed[-1])
                 return list(out.failed)
             flight = self._launch(out)
+        ahead_failed = None
         if self.run_ahead and flight.tokens is not None:
             plan = self.scheduler.plan_ahead(flight.out)
             if plan is not None:
@@ -308,7 +309,12 @@ class Engine:
                     self.steps_planned_ahead += 1
                 except OutOfPages:
                     pass                            # nothing was queued or kept: the plain path decides next turn
-        return self._collect(flight)
+                except Exception as error:          # the step that already ran is still collected, then this is raised
+                    ahead_failed = error
+        done = self._collect(flight)
+        if ahead_failed is not None:
+            raise ahead_failed
+        return done
 
     # -- whole generations ------------------------------------------------------------
     @staticmethod
