@@ -82,6 +82,7 @@ def main() -> int:
                     help="linear --impl skinny: with the RMSNorm prologue (addnorm: and the residual add before it; "
                          "swiglu: and the SwiGLU epilogue), or with the residual add in the epilogue")
     ap.add_argument("--tile-n", type=int, default=0)
+    ap.add_argument("--out-f32", action="store_true", help="linear: 32-bit output, as the output head has")
     ap.add_argument("--chain", action="store_true", help="many calls on different inputs back to back in a CUDA graph: the time of one call inside a step")
     ap.add_argument("--chain-mb", type=float, default=200.0,
                     help="--chain: total size of the distinct weights (below the L2 size they stay resident)")
@@ -159,6 +160,9 @@ def main() -> int:
                 fn = lambda: ops.linear_skinny(x, w)
             elif args.impl == "library":
                 fn = lambda: torch.mm(x, w.t())
+            elif args.out_f32:
+                rates["bytes"] += 2 * args.m * args.n
+                fn = lambda: ops.linear(x, w, out_dtype=torch.float32)
             else:
                 fn = (lambda: ops.linear_plain(x, w)) if args.plain else (lambda: ops.linear(x, w))
             return fn, (x.numel() + w.numel()) * 2

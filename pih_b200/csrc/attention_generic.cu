@@ -28,6 +28,7 @@ __global__ void paged_attention_generic_kernel(
     const int* __restrict__ positions, int rows, int heads, int kv_heads, int head_dim, int page_size,
     int num_pages, float scale, int window, uint32_t* error) {
   wait_for_prior_kernels();
+  launch_dependents();                                   // (the next kernel's blocks may become resident and wait)
   extern __shared__ float smem[];
   const int warps_per_block = blockDim.x >> 5;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;

@@ -261,6 +261,7 @@ template <int D>
 __global__ void __launch_bounds__(128)
 attn_tile_kernel(const AttnParams p) {
   wait_for_prior_kernels();
+  launch_dependents();                                   // (the next kernel's blocks may become resident and wait)
   constexpr int LD = D + 8;
   constexpr int BM = 64;
   constexpr int THREADS = 128;
@@ -626,6 +627,7 @@ template <int D>
 __global__ void __launch_bounds__(128)
 attn_split_kernel(const AttnParams p) {
   wait_for_prior_kernels();
+  launch_dependents();                                   // (the next kernel's blocks may become resident and wait)
   constexpr int LD = D + 8;
   constexpr int THREADS = 128;
   extern __shared__ __align__(16) unsigned char smem_raw[];

@@ -230,6 +230,7 @@ template <int D, int SPLIT>
 __global__ void __launch_bounds__(128 * SPLIT + 128)
 attn_prefill_tcgen05_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap kv_map) {
   wait_for_prior_kernels();
+  launch_dependents();                                   // (the next kernel's blocks may become resident and wait)
   using Smem = PrefillSmem<D, SPLIT>;
   constexpr int kSoftmaxThreads = 128 * SPLIT;
   constexpr int kSoftmaxWarps = 4 * SPLIT;

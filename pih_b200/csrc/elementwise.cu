@@ -16,6 +16,7 @@ __global__ void embedding_kernel(const T* __restrict__ table, const int* __restr
                                  T* __restrict__ out, int rows, int hidden, int vocab,
                                  uint32_t* error) {
   wait_for_prior_kernels();
+  launch_dependents();                                   // (the next kernel's blocks may become resident and wait)
   const int t = blockIdx.x;
   if (t >= rows) return;
   int id = ids[t];
@@ -49,6 +50,7 @@ __global__ void rmsnorm_kernel(T* __restrict__ x, const T* __restrict__ delta,
                                const W* __restrict__ weight, T* __restrict__ out,
                                const int* __restrict__ rows, int width, float eps) {
   wait_for_prior_kernels();
+  launch_dependents();                                   // (the next kernel's blocks may become resident and wait)
   __shared__ float scratch[33];
   const int o = blockIdx.x;
   const size_t r = rows != nullptr ? static_cast<size_t>(rows[o]) : static_cast<size_t>(o);
@@ -93,6 +95,7 @@ __global__ void qk_norm_rope_kv_kernel(T* __restrict__ qkv, int row_stride, int 
                                        const int* __restrict__ slot_mapping, T* __restrict__ cache,
                                        int page_size, int num_pages, int write_kv, uint32_t* error) {
   wait_for_prior_kernels();
+  launch_dependents();                                   // (the next kernel's blocks may become resident and wait)
   extern __shared__ float smem[];
   const int warps_per_block = blockDim.x >> 5;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -179,6 +182,7 @@ __global__ void qk_norm_rope_kv_fast_kernel(T* __restrict__ qkv, int row_stride,
                                             const int* __restrict__ slot_mapping, T* __restrict__ cache,
                                             int page_size, int num_pages, int write_kv, uint32_t* error) {
   wait_for_prior_kernels();
+  launch_dependents();                                   // (the next kernel's blocks may become resident and wait)
   constexpr int D = 32 * EPL;
   constexpr int HALF = D / 2;
   const int warps_per_block = blockDim.x >> 5;
@@ -361,6 +365,7 @@ qk_norm_rope_kv_wide_kernel(T* __restrict__ qkv, int row_stride, int rows, int h
                             const int* __restrict__ slot_mapping, T* __restrict__ cache, int page_size,
                             int num_pages, int write_kv, uint32_t* error) {
   wait_for_prior_kernels();
+  launch_dependents();                                   // (the next kernel's blocks may become resident and wait)
   constexpr int D = 16 * EPL, HALF = D / 2, E2 = EPL / 2;
   const int warps_per_block = blockDim.x >> 5;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -435,6 +440,7 @@ template <typename T>
 __global__ void silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ out, long long rows,
                                 int inter, int il) {
   wait_for_prior_kernels();
+  launch_dependents();                                   // (the next kernel's blocks may become resident and wait)
   const long long total = rows * inter;
   for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
        i += static_cast<long long>(gridDim.x) * blockDim.x) {
@@ -452,6 +458,7 @@ template <typename T>
 __global__ void gather_rows_kernel(const T* __restrict__ in, const int* __restrict__ rows,
                                    T* __restrict__ out, int width) {
   wait_for_prior_kernels();
+  launch_dependents();                                   // (the next kernel's blocks may become resident and wait)
   const T* s = in + static_cast<size_t>(rows[blockIdx.x]) * width;
   T* d = out + static_cast<size_t>(blockIdx.x) * width;
   for (int c = threadIdx.x; c < width; c += blockDim.x) d[c] = s[c];
@@ -497,6 +504,7 @@ __global__ void rmsnorm_vec_kernel(T* __restrict__ x, const T* __restrict__ delt
                                    const W* __restrict__ weight, T* __restrict__ out,
                                    const int* __restrict__ rows, int width, float eps) {
   wait_for_prior_kernels();
+  launch_dependents();                                   // (the next kernel's blocks may become resident and wait)
   constexpr int VEC = 16 / sizeof(T);
   __shared__ float scratch[33];
   const int o = blockIdx.x;
@@ -693,6 +701,7 @@ template <typename T>
 __global__ void silu_mul_vec_kernel(const T* __restrict__ gate_up, T* __restrict__ out, long long rows,
                                     int inter, int il) {
   wait_for_prior_kernels();
+  launch_dependents();                                   // (the next kernel's blocks may become resident and wait)
   constexpr int VEC = 16 / sizeof(T);
   const int per_row = inter / VEC;
   const int c = blockIdx.x * blockDim.x + threadIdx.x;

@@ -433,6 +433,132 @@ static int dispatch_skinny(bool swiglu, const SkinnyParams& p, cudaStream_t s) {
   return launch_skinny<MR, 1, NORM, false, NW>(p, s);
 }
 
+// ---- the same product for a LONG job: many weight rows per SM (the output head: a vocabulary of rows) -----------
+//
+// The kernel above is made for a block that owns a few units and lives for a few microseconds.  The output head
+// gives every SM a megabyte of weights; what counts there is only how many bytes an SM keeps in flight, and a
+// stage ring with a block-wide meeting per unit does not keep enough.  Here nothing is staged and no warp ever
+// waits for another: a warp owns 8-row granules of W (granule g of warp w of block b: w * blocks + b + g * warps),
+// loads a granule's rows straight into registers in the MMA's operand layout — a lane's 16 bytes of a row per 32-wide
+// k block are the 8-column operand of two MMAs, as above — eight k blocks at a time into one of two register sets,
+// the next set's loads issued before this set's MMAs.  Sixteen warps an SM with up to 8 KB each on the way cover the
+// memory's latency.  The tokens (up to 16 rows, padded rows as above) lie in shared memory and are the 16-row
+// operand.  A warp's sums are complete in its own accumulators: it stores them, 32 bytes a token.
+constexpr int SH_WARPS = 8;
+constexpr int SH_CHUNK = 8;                                  // k blocks of a register set
+
+template <int MR, typename OT>
+__global__ void __launch_bounds__(SH_WARPS * 32, 2) skinny_stream_kernel(const SkinnyParams p) {
+  extern __shared__ __align__(128) unsigned char smem[];
+  const int K = p.K, N = p.N, M = p.M;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int gid = lane >> 2, q = lane & 3;
+  const int row_bytes = K * 2 + 64;
+  const int KB = K / 32;
+  const int chunks = (KB + SH_CHUNK - 1) / SH_CHUNK;        // register sets of a granule
+  const int granules = (N + 7) / 8;
+  const int warps = gridDim.x * SH_WARPS;
+  const int gw = warp * gridDim.x + blockIdx.x;              // (the granules left over go to different SMs)
+  const int my_granules = gw < granules ? (granules - 1 - gw) / warps + 1 : 0;
+  const int items = my_granules * chunks;
+
+  // the next set to load: granule and chunk of it
+  int lg = gw, lc = 0;
+  auto load_set = [&](uint4 (&set)[SH_CHUNK]) {
+    const int row = min(lg * 8 + gid, N - 1);                // (rows beyond the last are loaded twice and not stored)
+    const unsigned char* src = reinterpret_cast<const unsigned char*>(p.W + static_cast<long long>(row) * p.ldw) +
+                               q * 16 + lc * (SH_CHUNK * 64);
+#pragma unroll
+    for (int j = 0; j < SH_CHUNK; ++j)
+      if (lc * SH_CHUNK + j < KB) set[j] = ldg_nc16(src + j * 64);
+    if (++lc == chunks) lc = 0, lg += warps;
+  };
+
+  uint4 set_a[SH_CHUNK], set_b[SH_CHUNK];
+  if (items > 0) load_set(set_a);                            // weights: nobody writes them, so before the wait
+  wait_for_prior_kernels();
+  launch_dependents();                                       // (what follows the head is small: it may wait beside it)
+
+  // the token rows, padded so that the eight rows a warp reads at once lie in different banks; rows beyond M zero
+  const int chunks16 = K / 8;
+  for (int i = threadIdx.x; i < MR * chunks16; i += SH_WARPS * 32) {
+    const int row = i / chunks16, c = i - row * chunks16;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (row < M) v = *reinterpret_cast<const uint4*>(p.x + row * p.ldx + c * 8);
+    *reinterpret_cast<uint4*>(smem + row * row_bytes + c * 16) = v;
+  }
+  __syncthreads();
+
+  OT* out = static_cast<OT*>(p.out);
+  const unsigned char* xa = smem + gid * row_bytes + q * 16;
+  float acc[2][4];
+  int cg = gw, cc = 0;                                       // the set to use: granule and chunk of it
+  auto use_set = [&](const uint4 (&set)[SH_CHUNK]) {
+    if (cc == 0) {
+#pragma unroll
+      for (int a = 0; a < 2; ++a) acc[a][0] = acc[a][1] = acc[a][2] = acc[a][3] = 0.0f;
+    }
+#pragma unroll
+    for (int j = 0; j < SH_CHUNK; ++j) {
+      const int kb = cc * SH_CHUNK + j;
+      if (kb < KB) {
+        const uint4 xlo = *reinterpret_cast<const uint4*>(xa + kb * 64);
+        uint4 xhi = make_uint4(0, 0, 0, 0);
+        if (MR == 16) xhi = *reinterpret_cast<const uint4*>(xa + 8 * row_bytes + kb * 64);
+        mma16816(acc[j & 1], xlo.x, xhi.x, xlo.y, xhi.y, set[j].x, set[j].y);
+        mma16816(acc[j & 1], xlo.z, xhi.z, xlo.w, xhi.w, set[j].z, set[j].w);
+      }
+    }
+    if (++cc == chunks) {
+      // register r of lane (gid, q): token gid + 8 (r / 2), weight row 2 q + (r & 1) of the granule
+      const int col = cg * 8 + 2 * q;
+#pragma unroll
+      for (int h = 0; h < MR / 8; ++h) {
+        const int tok = gid + 8 * h;
+        if (tok < M) {
+          OT* o = out + tok * p.ldo + col;
+          if (col < N) o[0] = from_float<OT>(acc[0][2 * h] + acc[1][2 * h]);
+          if (col + 1 < N) o[1] = from_float<OT>(acc[0][2 * h + 1] + acc[1][2 * h + 1]);
+        }
+      }
+      cc = 0, cg += warps;
+    }
+  };
+
+  for (int i = 0; i < items; i += 2) {
+    if (i + 1 < items) load_set(set_b);
+    use_set(set_a);
+    if (i + 2 < items) load_set(set_a);
+    if (i + 1 < items) use_set(set_b);
+  }
+}
+
+// Takes the job when every warp of a full grid gets at least four granules; returns PIH_ERR_UNSUPPORTED otherwise.
+template <int MR, typename OT>
+static int launch_stream(const SkinnyParams& p, cudaStream_t s) {
+  static int sms = 0;
+  if (sms == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (sms <= 0) sms = 148;
+  }
+  const int smem = MR * (p.K * 2 + 64);
+  const int per_sm = smem <= 100 * 1024 ? 2 : 1;
+  if (smem > 200 * 1024) return PIH_ERR_UNSUPPORTED;
+  const int grid = sms * per_sm;
+  if ((p.N + 7) / 8 < 4 * grid * SH_WARPS) return PIH_ERR_UNSUPPORTED;
+  static int smem_set = 0;
+  if (smem > 48 * 1024 && smem_set < smem) {
+    cudaError_t e = cudaFuncSetAttribute(skinny_stream_kernel<MR, OT>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    smem_set = smem;
+  }
+  launch_kernel(skinny_stream_kernel<MR, OT>, dim3(grid), dim3(SH_WARPS * 32), smem, s, p);
+  PIH_LAUNCH_CHECK();
+  return 0;
+}
+
 static bool skinny_takes(const void* x, const void* W, int M, int K, long long ldx, long long ldw) {
   return M <= 16 && K > 0 && K % 32 == 0 && ldx % 8 == 0 && ldw % 8 == 0 &&
          (reinterpret_cast<uintptr_t>(x) & 15) == 0 && (reinterpret_cast<uintptr_t>(W) & 15) == 0;
@@ -495,6 +621,9 @@ extern "C" int pih_gemm_skinny_f32out(const void* x, const void* W, void* out, i
   p.M = M, p.N = N, p.K = K;
   p.ldx = ldx, p.ldw = ldw, p.ldo = ldo;
   p.error = error;
+  // a vocabulary of rows: the kernel for long jobs, if the job is long enough for it
+  const int rc = M <= 8 ? launch_stream<8, float>(p, s) : launch_stream<16, float>(p, s);
+  if (rc != PIH_ERR_UNSUPPORTED) return rc;
   if (M <= 8)
     return N >= 148 * 16 ? launch_skinny<8, 2, false, false, float, float>(p, s)
                          : launch_skinny<8, 1, false, false, float, float>(p, s);

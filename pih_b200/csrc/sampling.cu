@@ -231,6 +231,7 @@ __global__ void __launch_bounds__(kSampleThreads)
 sample_kernel(const float* __restrict__ logits, int vocab, const float* __restrict__ fparams,
               const int* __restrict__ iparams, int* __restrict__ out_tokens, uint32_t* error) {
   wait_for_prior_kernels();
+  launch_dependents();                                   // (the next kernel's blocks may become resident and wait)
   __shared__ int s_sup[kMaxSuppressed];
   __shared__ unsigned long long s_hist[256];
   __shared__ unsigned long long s_scratch[40];
@@ -337,6 +338,7 @@ sample_kernel(const float* __restrict__ logits, int vocab, const float* __restri
 __global__ void __launch_bounds__(kSampleThreads)
 argmax_kernel(const float* __restrict__ logits, int vocab, int* __restrict__ out_tokens, uint32_t* error) {
   wait_for_prior_kernels();
+  launch_dependents();                                   // (the next kernel's blocks may become resident and wait)
   __shared__ float s_val[32];
   __shared__ int s_idx[32];
   const float* row = logits + static_cast<size_t>(blockIdx.x) * vocab;
@@ -389,6 +391,7 @@ __global__ void __launch_bounds__(256)
 argmax_slices_kernel(const float* __restrict__ logits, int vocab, int slices, float* __restrict__ part_val,
                      int* __restrict__ part_idx, uint32_t* error) {
   wait_for_prior_kernels();
+  launch_dependents();                                   // (the next kernel's blocks may become resident and wait)
   __shared__ float s_val[8];
   __shared__ int s_idx[8];
   const int row = blockIdx.y, slice = blockIdx.x;
@@ -436,6 +439,7 @@ argmax_slices_kernel(const float* __restrict__ logits, int vocab, int slices, fl
 __global__ void argmax_final_kernel(const float* __restrict__ part_val, const int* __restrict__ part_idx,
                                     int slices, int* __restrict__ out_tokens) {
   wait_for_prior_kernels();
+  launch_dependents();                                   // (the next kernel's blocks may become resident and wait)
   const int row = blockIdx.x, lane = threadIdx.x;
   float best = -INFINITY;
   int best_id = 0x7fffffff;
