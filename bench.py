@@ -6,7 +6,7 @@ A "step" is one decode step of the batch.  The default run has the layer
 sizes of the Qwen3-0.6B configuration (28 layers, hidden 1024, 16/8 heads of
 128, intermediate 3072, vocabulary 151 936, tied embeddings) with random
 weights (N(0, 0.02), seed 2), a batch of 8 requests each holding 2 048
-context tokens, page size 16.  It prints ONE JSON line:
+context tokens, page size 64.  It prints ONE JSON line:
 
 * ``value``      decoded tokens per second, timed on the device with CUDA events around K
                  steps of the step function plus device sampling (no host transfer inside);
@@ -48,7 +48,7 @@ QWEN3_0_6B = {
 }
 CONTEXT = 2048
 PREFILL_TOKENS = 2048
-PAGE = 16
+PAGE = 64
 METRIC = "decode tok/s at batch 8 (Qwen3-0.6B, 2048-token contexts)"
 
 

@@ -66,6 +66,7 @@ def main() -> int:
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--ctx", type=int, default=2048)
     ap.add_argument("--tokens", type=int, default=2048)
+    ap.add_argument("--start", type=int, default=0, help="attn_prefill: tokens of the request already in the cache")
     ap.add_argument("--heads", type=int, default=16)
     ap.add_argument("--kv-heads", type=int, default=8)
     ap.add_argument("--head-dim", type=int, default=128)
@@ -115,7 +116,7 @@ def main() -> int:
             if k == "attn_decode":
                 lens, new = [args.ctx] * args.batch, [1] * args.batch
             else:
-                lens, new = [args.tokens], [args.tokens]
+                lens, new = [args.start + args.tokens], [args.tokens]      # a portion that starts at --start
             pages_per = [-(-n // P) for n in lens]
             num_pages = sum(pages_per)
             cache = torch.randn(num_pages, 2, KV, P, D, device=dev).to(bf)
@@ -129,7 +130,8 @@ def main() -> int:
             if k == "attn_decode":
                 rates.update(bytes=sum(lens) * 2 * KV * D * 2, batch=args.batch, ctx=args.ctx)
             else:
-                rates.update(flops=4 * H * D * args.tokens * (args.tokens + 1) // 2, tokens=args.tokens)
+                rates.update(flops=4 * H * D * (args.tokens * (args.tokens + 1) // 2 + args.tokens * args.start),
+                             tokens=args.tokens, start=args.start)
             if args.plain:
                 fn = lambda: ops.paged_attention_generic(q, heads=H, kv_heads=KV, head_dim=D, kv_cache=cache,
                                                          block_table=table, request_of_row=step.request_of_row,

@@ -9,7 +9,7 @@
 Random weights of the named architecture (seeded), seeded uniform-random prompt ids, one GPU.  Requests are all
 submitted at once; the scheduler admits them, cuts their prompts under the token budget beside the decode
 tokens of the others, and frees what finishes.  Prints one JSON line: generated tokens a second over the whole
-run (wall clock, host in the loop), the same over the part of the run in which every live request decodes,
+run (wall clock, host in the loop; the engine's warm-up before the first request is timed apart), the same over the part of the run in which every live request decodes,
 prompt tokens, steps, preemptions.  `--layers` runs fewer layers of the shape (both numbers are in the line).
 """
 from __future__ import annotations
@@ -42,8 +42,11 @@ def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--shape", choices=sorted(SHAPES), default="1.7b")
     ap.add_argument("--layers", type=int, default=None, help="run this many layers of the shape")
+    ap.add_argument("--page-size", type=int, default=64)
     ap.add_argument("--requests", type=int, default=None)
     ap.add_argument("--new-tokens", type=int, default=None)
+    ap.add_argument("--no-warm-up", action="store_true",
+                    help="first request on a cold engine: what a process sets up and captures once falls into the run")
     ap.add_argument("--capture-decode-after", type=int, default=None,
                     help="uncaptured runs of a decode shape before it is captured into a CUDA graph")
     args = ap.parse_args()
@@ -82,11 +85,13 @@ def main() -> int:
     prompts = [torch.randint(0, config.vocab_size, (n,), generator=g).tolist() for n in lengths]
     # no pool size given: the engine takes what the device has left beside the weights, up to what this many
     # requests of the longest context could hold
-    engine = Engine(f"Qwen3-{args.shape}-random", model=(config, model), page_size=16,
+    engine = Engine(f"Qwen3-{args.shape}-random", model=(config, model), page_size=args.page_size,
                     maximum_batch_sequences=work["requests"], maximum_batch_tokens=work["budget"],
                     maximum_context_tokens=hi + work["new_tokens"] + 32)
     if args.capture_decode_after is not None:
         engine.runner.capture_decode_after = args.capture_decode_after
+    # as a server does before it opens: the shapes that its limits make likely are run and captured once
+    warm = None if args.no_warm_up else engine.warm_up()
     reqs = []
     for i, prompt in enumerate(prompts):
         sampled = i < work["sampled"] * work["requests"]
@@ -120,6 +125,7 @@ def main() -> int:
                         "tok_s": round(decode_only["tokens"] / decode_only["seconds"], 1) if decode_only["seconds"] else None},
         "preemptions": sum(r.preemptions for r in reqs),
         "steps_planned_ahead": engine.steps_planned_ahead, "cache_tokens": engine.cache_tokens,
+        "warm_up": None if warm is None else {"seconds": warm["seconds"], "graphs": warm["graphs"]},
 
         "config": {"shape": args.shape, "layers": config.num_hidden_layers, "layers_of_shape": layers_of_shape,
                    "hidden": config.hidden_size, "intermediate": config.intermediate_size,

@@ -87,13 +87,14 @@ def main(argv=None) -> int:
         if not opts["--max-tokens"].isdigit() or not 1 <= int(opts["--max-tokens"]) <= 65536:
             raise ValueError("maximum_tokens_invalid")
         maximum = int(opts["--max-tokens"])
+        from ..cache import DEFAULT_PAGE_SIZE
         from ..engine import Engine
         params = {"temperature": float(opts.get("--temperature", 0.0)), "top_p": float(opts.get("--top-p", 1.0)),
                   "seed": int(opts.get("--seed", 7)), "ignore_eos": bool(opts.get("--ignore-eos", False))}
         if "--top-k" in opts:
             params["top_k"] = int(opts["--top-k"])
         engine = Engine(opts["--model"], opts.get("--dtype", "bfloat16"),
-                        page_size=int(opts.get("--page-size", 16)),
+                        page_size=int(opts.get("--page-size", DEFAULT_PAGE_SIZE)),
                         max_cache_tokens=int(opts["--max-cache-tokens"]) if "--max-cache-tokens" in opts
                         else len(tokens) + maximum + 64,
                         maximum_batch_sequences=1)

@@ -38,6 +38,7 @@ __global__ void paged_attention_generic_kernel(
   const int h = static_cast<int>(item % heads);
   const int g = h / (heads / kv_heads);
   const int r = request_of_row[t];
+  if (r < 0) return;                                   // a row of padding
   const int p = positions[t];
   const int first = window > 0 ? max(0, p - window + 1) : 0;
   const int* table = block_table + static_cast<size_t>(r) * table_width;

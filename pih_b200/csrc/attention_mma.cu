@@ -640,7 +640,7 @@ attn_split_kernel(const AttnParams p) {
   const int row0 = p.cu_q[r];
   const int n_tok = p.cu_q[r + 1] - row0;
   const int packed = n_tok * G;
-  if (packed > 16) return;                           // the tile kernel's
+  if (packed > 16 || n_tok <= 0) return;             // the tile kernel's; a request of padding
   const int start = p.q_start[r];
   // keys that any row of the request sees, and the splits that hold them
   const int req_kmin = p.window > 0 ? max(0, start - p.window + 1) : 0;
@@ -746,7 +746,7 @@ attn_split_tma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap kv
   const int row0 = p.cu_q[r];
   const int n_tok = p.cu_q[r + 1] - row0;
   const int packed = n_tok * G;
-  if (packed > 16) return;
+  if (packed > 16 || n_tok <= 0) return;               // the tile kernel's; a request of padding (a whole cluster leaves)
   const int start = p.q_start[r];
   const int req_kmin = p.window > 0 ? max(0, start - p.window + 1) : 0;
   const int req_kmax = start + n_tok - 1;

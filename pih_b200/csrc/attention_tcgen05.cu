@@ -45,6 +45,8 @@ struct PrefillParams {
   const int* cu_q;
   const int* q_start;
   int heads, kv_heads, page_size, page_shift, num_pages;
+  int num_requests;
+  int pair_above;                      // row tiles x kv heads beyond which a block takes two row tiles
   float scale;
   int window;
   uint32_t* error;
@@ -208,34 +210,42 @@ struct PrefillSmem {
   alignas(1024) unsigned char v[V_STAGES][PANELS * KV_PANEL_BYTES];
   alignas(8) uint64_t q_full, o_ready, p_full[P_BUFS], p_empty[P_BUFS];
   alignas(8) uint64_t k_full[K_STAGES], k_empty[K_STAGES], v_full[V_STAGES], v_empty[V_STAGES];
-  alignas(8) uint64_t s_full[2], s_empty[2];
-  float xmax[2][SPLIT][128];                                    // [tile parity][column part][row] maxima
-  float xsum[SPLIT][128];                                       // row sums of the column parts
+  alignas(8) uint64_t s_full[2], s_empty[2], r_full[2];
+  float xmax[2][2][SPLIT][128];                                 // [set][parity of the set's tile][column part][row] maxima
+  float mref[2][128];                                           // [tile parity][row] the reference maximum after that tile
+  float xsum[2 * SPLIT][128];                                   // row sums of the sets' column parts
   uint32_t tmem_base;
 };
 
-// SPLIT threads share a row (= tensor-memory lane), each with 128 / SPLIT of the key columns and D / SPLIT of
-// the output columns: warps 0 .. 4 SPLIT - 1 are softmax warps, then the producer warp, then the MMA warp.
+// Two SETS of softmax warps take the key tiles in turn (set = tile & 1); in a set, SPLIT threads share a row
+// (= tensor-memory lane), each with 128 / SPLIT of the key columns and D / SPLIT of the output columns.  Warps
+// 0 .. 8 SPLIT - 1 are softmax warps (set 0 first), then the producer and MMA warps.
 template <int THREADS> __device__ __forceinline__ void softmax_sync() {
   asm volatile("bar.sync 1, %0;\n" ::"n"(THREADS) : "memory");
 }
-// the SPLIT softmax warps (w, w + 4, ...) that share tensor-memory lanes 32 quarter .. 32 quarter + 31
-template <int THREADS> __device__ __forceinline__ void row_group_sync(int quarter) {
-  asm volatile("bar.sync %0, %1;\n" ::"r"(2 + quarter), "n"(THREADS) : "memory");
+// the SPLIT warps of a set (w, w + 4, ...) that share tensor-memory lanes 32 quarter .. 32 quarter + 31
+template <int THREADS> __device__ __forceinline__ void row_group_sync(int set, int quarter) {
+  asm volatile("bar.sync %0, %1;\n" ::"r"(2 + 4 * set + quarter), "n"(THREADS) : "memory");
+}
+// set 0 alone (the epilogue)
+template <int THREADS> __device__ __forceinline__ void first_set_sync() {
+  asm volatile("bar.sync 10, %0;\n" ::"n"(THREADS) : "memory");
 }
 
 // One CTA works through up to two row tiles of its (request, kv head): a long one (late rows, many keys)
 // and its short mirror image, so that every CTA has about the same number of key tiles.
 template <int D, int SPLIT>
-__global__ void __launch_bounds__(128 * SPLIT + 128)
+__global__ void __launch_bounds__(256 * SPLIT + 128)
 attn_prefill_tcgen05_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap kv_map) {
   wait_for_prior_kernels();
   launch_dependents();                                   // (the next kernel's blocks may become resident and wait)
   using Smem = PrefillSmem<D, SPLIT>;
-  constexpr int kSoftmaxThreads = 128 * SPLIT;
-  constexpr int kSoftmaxWarps = 4 * SPLIT;
-  constexpr int kProducerWarp = 4 * SPLIT, kMmaWarp = 4 * SPLIT + 1, kProducerWarpV = 4 * SPLIT + 2;
-  constexpr int kMmaWarpPV = 4 * SPLIT + 3;
+  constexpr int kSetThreads = 128 * SPLIT;                        // softmax threads of a set
+  constexpr int kSetWarps = 4 * SPLIT;
+  constexpr int kSoftmaxThreads = 2 * kSetThreads;
+  constexpr int kSoftmaxWarps = 2 * kSetWarps;
+  constexpr int kProducerWarp = kSoftmaxWarps, kMmaWarp = kSoftmaxWarps + 1, kProducerWarpV = kSoftmaxWarps + 2;
+  constexpr int kMmaWarpPV = kSoftmaxWarps + 3;
   constexpr int CW = TK / SPLIT;                                  // key columns of a softmax thread
   constexpr int OW = D / SPLIT;                                   // output columns of a softmax thread
   static_assert(CW == 64 || CW == 32, "a thread reads its scores with one tcgen05.ld of 32 or 64 columns");
@@ -246,16 +256,37 @@ attn_prefill_tcgen05_kernel(const PrefillParams p, const __grid_constant__ CUten
   extern __shared__ unsigned char smem_raw[];
   Smem& sm = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
 
-  const int r = blockIdx.z, g = blockIdx.y;
+  // Which rows are this block's: the row tiles of all requests that bring more than 16 packed rows are numbered
+  // through, from the step's row ranges on the device (a step's make-up is data, not launch geometry: the grid is
+  // an upper bound, and a captured graph serves every make-up).  With many tiles a block takes a late tile and its
+  // early mirror image; with few — a portion of a few hundred tokens beside decoding requests — a tile each, so
+  // that twice as many SMs work.
+  const int g = blockIdx.y;
   const int G = p.heads / p.kv_heads;
+  int total_tiles = 0;
+  for (int q = 0; q < p.num_requests; ++q) {
+    const int pk = (p.cu_q[q + 1] - p.cu_q[q]) * G;
+    if (pk > 16) total_tiles += (pk + TQ - 1) / TQ;
+  }
+  const bool paired = total_tiles * p.kv_heads > p.pair_above;
+  int r = -1, bx = static_cast<int>(blockIdx.x);
+  for (int q = 0; q < p.num_requests; ++q) {
+    const int pk = (p.cu_q[q + 1] - p.cu_q[q]) * G;
+    if (pk <= 16) continue;                                     // decode-like: the split kernel's
+    const int t = (pk + TQ - 1) / TQ;
+    const int mine = paired ? (t + 1) / 2 : t;
+    if (bx < mine) {
+      r = q;
+      break;
+    }
+    bx -= mine;
+  }
+  if (r < 0) return;
   const int row0 = p.cu_q[r];
   const int n_tok = p.cu_q[r + 1] - row0;
   const int packed = n_tok * G;
-  if (packed <= 16) return;                                     // decode-like: the split kernel's
   const int tiles_q = (packed + TQ - 1) / TQ;
-  const int bx = static_cast<int>(blockIdx.x);
-  if (2 * bx > tiles_q - 1) return;
-  const int items = (2 * bx < tiles_q - 1) ? 2 : 1;              // the middle tile of an odd count stands alone
+  const int items = (paired && 2 * bx < tiles_q - 1) ? 2 : 1;    // the middle tile of an odd count stands alone
   const int start = p.q_start[r];
   const int* table = p.block_table + static_cast<size_t>(r) * p.table_width;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -296,6 +327,7 @@ attn_prefill_tcgen05_kernel(const PrefillParams p, const __grid_constant__ CUten
         for (int b = 0; b < 2; ++b) {
           inval(&sm.s_full[b]);
           inval(&sm.s_empty[b]);
+          inval(&sm.r_full[b]);
         }
         for (int b = 0; b < P_BUFS; ++b) {
           inval(&sm.p_full[b]);
@@ -307,7 +339,7 @@ attn_prefill_tcgen05_kernel(const PrefillParams p, const __grid_constant__ CUten
       mbar_init(&sm.q_full, kSoftmaxWarps);
       mbar_init(&sm.o_ready, 1);
       for (int b = 0; b < P_BUFS; ++b) {
-        mbar_init(&sm.p_full[b], kSoftmaxWarps);
+        mbar_init(&sm.p_full[b], kSetWarps);                     // buffer b is set b's
         mbar_init(&sm.p_empty[b], 1);
       }
       for (int s = 0; s < K_STAGES; ++s) {
@@ -320,7 +352,8 @@ attn_prefill_tcgen05_kernel(const PrefillParams p, const __grid_constant__ CUten
       }
       for (int b = 0; b < 2; ++b) {
         mbar_init(&sm.s_full[b], 1);
-        mbar_init(&sm.s_empty[b], kSoftmaxWarps);
+        mbar_init(&sm.s_empty[b], kSetWarps);
+        mbar_init(&sm.r_full[b], 4);                             // the set's warps of column part 0 publish the reference
       }
       mbar_init_fence();
     }
@@ -438,9 +471,17 @@ attn_prefill_tcgen05_kernel(const PrefillParams p, const __grid_constant__ CUten
         }
       }
     } else {
-      // ---------------- softmax / epilogue: SPLIT threads per row ----------------
+      // ---------------- softmax / epilogue: two sets of SPLIT threads per row ----------------
+      // Set s takes the key tiles j = s, s + 2, ... with S buffer s and P buffer s.  A tile's softmax is a chain of
+      // phases (wait for S, read it, maximum, exchange in the row, exponentials, store of P), and only the
+      // exponentials use the special-function unit that bounds the tile: with one set all warps are in the same
+      // phase and the unit idles half of the time; with two, one set's other phases run under the other set's
+      // exponentials.  What the sets share is the row's running reference maximum (a chain through shared memory,
+      // published early in a tile) and O, which a set rescales — rarely — between the P V products of the tile
+      // before and of its own; each thread keeps its own part of the row sum until the end.
       const int t = threadIdx.x;                                 // 0 .. kSoftmaxThreads - 1
-      const int part = warp >> 2;                                // which CW of the 128 key columns (and OW of D)
+      const int set = warp / kSetWarps;
+      const int part = (warp >> 2) % SPLIT;                      // which CW of the 128 key columns (and OW of D)
       const int row = (warp & 3) * 32 + lane;                    // tensor-memory lane
       const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
       if (item == 0) {
@@ -457,102 +498,135 @@ attn_prefill_tcgen05_kernel(const PrefillParams p, const __grid_constant__ CUten
       const int pos = row_valid ? start + i_row / G : -1;
       const int first = (row_valid && p.window > 0) ? max(0, pos - p.window + 1) : 0;
       const float sl = p.scale * kLog2e5;
-      float m_ref = -INFINITY, l = 0.0f;
+      float m_ref = -INFINITY, l = 0.0f;                         // l is this thread's sum relative to m_ref
       bool ok = true;
+      const int b = set;                                         // the set's S and P buffer
 
-      for (int j = 0; j < ntiles; ++j) {
-        const int b = j & 1;
-        if (!mbar_wait(&sm.s_full[b], (j >> 1) & 1, p.error)) { ok = false; break; }
+      for (int j = set; j < ntiles; j += 2) {
+        const int use = j >> 1;
+        if (!mbar_wait(&sm.s_full[b], use & 1, p.error)) { ok = false; break; }
         tc_fence_after();
         const uint32_t s_addr = tmem + lane_base + b * TK + part * CW;
         const int j0 = (t_first + j) * TK + part * CW;
         // a tile that lies wholly inside every row's visible range needs no mask (the usual case)
         const bool unmasked = __all_sync(0xffffffffu, j0 + CW - 1 <= pos && j0 >= first);
-        // this thread's scores, read once
-        uint32_t sv[CW];
-        if constexpr (CW == 64) tmem_ld64(s_addr, sv);
-        else tmem_ld32(s_addr, sv);
-        tmem_wait_ld();
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&sm.s_empty[b]);              // S_b is in registers: the next-but-one S may land
+        // first pass over this thread's scores: their maximum
         float m_part = -INFINITY;
-        if (unmasked) {
-          float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};   // four chains instead of one
+        {
+          uint32_t sv[CW];
+          if constexpr (CW == 64) tmem_ld64(s_addr, sv);
+          else tmem_ld32(s_addr, sv);
+          tmem_wait_ld();
+          if (unmasked) {
+            float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};   // four chains instead of one
 #pragma unroll
-          for (int e = 0; e < CW; ++e) m4[e & 3] = fmaxf(m4[e & 3], __uint_as_float(sv[e]));
-          m_part = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
-        } else {
+            for (int e = 0; e < CW; ++e) m4[e & 3] = fmaxf(m4[e & 3], __uint_as_float(sv[e]));
+            m_part = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
+          } else {
 #pragma unroll
-          for (int e = 0; e < CW; ++e) {
-            const int key = j0 + e;
-            if (key <= pos && key >= first) m_part = fmaxf(m_part, __uint_as_float(sv[e]));
-            else sv[e] = 0xff800000u;                            // -inf: masked for good
+            for (int e = 0; e < CW; ++e) {
+              const int key = j0 + e;
+              if (key <= pos && key >= first) m_part = fmaxf(m_part, __uint_as_float(sv[e]));
+            }
           }
         }
         m_part *= sl;                                            // scale > 0
-        sm.xmax[b][part][row] = m_part;
-        row_group_sync<32 * SPLIT>(warp & 3);                    // the warps that share these 32 rows
+        sm.xmax[set][use & 1][part][row] = m_part;
+        row_group_sync<32 * SPLIT>(set, warp & 3);               // the warps of the set that share these 32 rows
         float m_tile = m_part;
 #pragma unroll
-        for (int o = 0; o < SPLIT; ++o) m_tile = fmaxf(m_tile, sm.xmax[b][o][row]);
-        float alpha = 1.0f;
+        for (int o = 0; o < SPLIT; ++o) m_tile = fmaxf(m_tile, sm.xmax[set][use & 1][o][row]);
+        // the reference after the tile before, which the other set has published
+        float m_prev = -INFINITY;
+        if (j > 0) {
+          if (!mbar_wait(&sm.r_full[b ^ 1], ((j - 1) >> 1) & 1, p.error)) { ok = false; break; }
+          m_prev = sm.mref[(j - 1) & 1][row];
+        }
+        float m_new = m_prev;
         bool grow = false;
-        if (m_tile > m_ref + kRescaleThreshold || (m_ref == -INFINITY && m_tile > -INFINITY)) {
-          alpha = m_ref == -INFINITY ? 0.0f : exp2f(m_ref - m_tile);
-          m_ref = m_tile;
+        if (m_tile > m_prev + kRescaleThreshold || (m_prev == -INFINITY && m_tile > -INFINITY)) {
+          m_new = m_tile;
           grow = true;
         }
-        const float m_use = m_ref == -INFINITY ? 0.0f : m_ref;
-        // this tile's P buffer is free once the P V product that read it last has finished; O may only be
-        // rescaled while no P V product is running, so a (rare) rescale waits for the latest one
-        const int pb = j % P_BUFS;
-        if (j >= P_BUFS) {
-          if (!mbar_wait(&sm.p_empty[pb], (j / P_BUFS - 1) & 1, p.error)) { ok = false; break; }
+        if (part == 0) {
+          // (the slot's last reader, the other set at tile j - 1, read it before it published what was waited for above)
+          sm.mref[j & 1][row] = m_new;
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&sm.r_full[b]);
         }
-        if (j > 0) {
-          if (__any_sync(0xffffffffu, grow)) {
-            if (!mbar_wait(&sm.p_empty[(j - 1) % P_BUFS], ((j - 1) / P_BUFS) & 1, p.error)) { ok = false; break; }
-            tc_fence_after();
-#pragma unroll 1
-            for (int c = 0; c < OW / 32; ++c) {                  // this thread's part of the O columns
-              uint32_t ov[32];
-              const uint32_t o_addr = tmem_o + lane_base + part * OW + c * 32;
-              tmem_ld32(o_addr, ov);
-              tmem_wait_ld();
+        const float m_use = m_new == -INFINITY ? 0.0f : m_new;
+        // this thread's sum refers to the reference of its set's last tile
+        const float alpha_l = m_new == m_ref ? 1.0f : (m_ref == -INFINITY ? 0.0f : exp2f(m_ref - m_new));
+        // the set's P buffer is free once the P V product of the set's last tile has finished
+        if (use > 0) {
+          if (!mbar_wait(&sm.p_empty[b], (use - 1) & 1, p.error)) { ok = false; break; }
+        }
+        // second pass, 32 scores at a time: exponentials; the probabilities go to tensor memory as packed pairs,
+        // where the P V product reads them as its A operand (a masked score counts as -inf and gives 0)
+        float sum = 0.0f;
 #pragma unroll
-              for (int e = 0; e < 32; ++e) ov[e] = __float_as_uint(__uint_as_float(ov[e]) * alpha);
-              tmem_st32(o_addr, ov);
+        for (int c = 0; c < CW / 32; ++c) {
+          uint32_t sv[32];
+          tmem_ld32(s_addr + c * 32, sv);
+          tmem_wait_ld();
+          if (c == CW / 32 - 1) {
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&sm.s_empty[b]);          // S_b has been read: the set's next S may land
+          }
+          if (!unmasked) {
+#pragma unroll
+            for (int e = 0; e < 32; ++e) {
+              const int key = j0 + c * 32 + e;
+              if (!(key <= pos && key >= first)) sv[e] = 0xff800000u;   // -inf
             }
-            tmem_wait_st();
+          }
+          uint32_t pk[16];
+#pragma unroll
+          for (int e = 0; e < 16; ++e) {
+            const float p0 = fast_exp2(fmaf(__uint_as_float(sv[2 * e]), sl, -m_use));
+            const float p1 = fast_exp2(fmaf(__uint_as_float(sv[2 * e + 1]), sl, -m_use));
+            sum += p0 + p1;
+            __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
+            pk[e] = *reinterpret_cast<uint32_t*>(&h);
+          }
+          tmem_st16(tmem + 384 + b * (TK / 2) + lane_base + part * (CW / 2) + c * 16, pk);
+        }
+        // O may only be rescaled while no P V product is running: after the product of the tile before (the other
+        // set's) and before this tile's, which waits for the arrival below
+        if (j > 0 && __any_sync(0xffffffffu, grow)) {
+          if (!mbar_wait(&sm.p_empty[b ^ 1], ((j - 1) >> 1) & 1, p.error)) { ok = false; break; }
+          tc_fence_after();
+          const float alpha = m_new == m_prev ? 1.0f : (m_prev == -INFINITY ? 0.0f : exp2f(m_prev - m_new));
+#pragma unroll 1
+          for (int c = 0; c < OW / 32; ++c) {                    // this thread's part of the O columns
+            uint32_t ov[32];
+            const uint32_t o_addr = tmem_o + lane_base + part * OW + c * 32;
+            tmem_ld32(o_addr, ov);
+            tmem_wait_ld();
+#pragma unroll
+            for (int e = 0; e < 32; ++e) ov[e] = __float_as_uint(__uint_as_float(ov[e]) * alpha);
+            tmem_st32(o_addr, ov);
           }
         }
-        // exponentials; the thread's 64 probabilities go to tensor memory as 32 packed pairs, where the P V
-        // product reads them as its A operand (a masked score is -inf and gives 0)
-        float sum = 0.0f;
-        uint32_t pk[CW / 2];
-#pragma unroll
-        for (int e = 0; e < CW / 2; ++e) {
-          const float p0 = fast_exp2(fmaf(__uint_as_float(sv[2 * e]), sl, -m_use));
-          const float p1 = fast_exp2(fmaf(__uint_as_float(sv[2 * e + 1]), sl, -m_use));
-          sum += p0 + p1;
-          __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
-          pk[e] = *reinterpret_cast<uint32_t*>(&h);
-        }
-        if constexpr (CW == 64) tmem_st32(tmem + 384 + pb * (TK / 2) + lane_base + part * (CW / 2), pk);
-        else tmem_st16(tmem + 384 + pb * (TK / 2) + lane_base + part * (CW / 2), pk);
         tmem_wait_st();
-        l = l * alpha + sum;
+        l = l * alpha_l + sum;
+        m_ref = m_new;
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(&sm.p_full[pb]);
+        if (lane == 0) mbar_arrive(&sm.p_full[b]);
       }
-      // epilogue: the parts of a row share the row sum
-      sm.xsum[part][row] = l;
+      // epilogue: the row's sums, each brought to the last reference
+      softmax_sync<kSoftmaxThreads>();                           // the last tile's reference is published
+      {
+        const float m_final = sm.mref[(ntiles - 1) & 1][row];
+        sm.xsum[set * SPLIT + part][row] = (l > 0.0f && m_ref != m_final) ? l * exp2f(m_ref - m_final) : l;
+      }
       softmax_sync<kSoftmaxThreads>();
+      if (set == 0) {
       float l_row = 0.0f;
 #pragma unroll
-      for (int o = 0; o < SPLIT; ++o) l_row += sm.xsum[o][row];
+      for (int o = 0; o < 2 * SPLIT; ++o) l_row += sm.xsum[o][row];
       // O leaves through shared memory (the K ring is idle: every product has finished), so that the stores to
       // global memory are whole rows — 16 lanes a row — instead of 16 bytes a lane to 32 different rows, which
       // took 2.8 of a block's 59 thousand cycles per tile.
@@ -579,16 +653,17 @@ attn_prefill_tcgen05_kernel(const PrefillParams p, const __grid_constant__ CUten
           for (int e = 0; e < 4; ++e) dst[e] = make_uint4(pk[4 * e], pk[4 * e + 1], pk[4 * e + 2], pk[4 * e + 3]);
         }
       }
-      softmax_sync<kSoftmaxThreads>();                           // every softmax thread, whatever its waits said
+      first_set_sync<kSetThreads>();                             // every thread of the set, whatever its waits said
       {
         constexpr int CPR = D / 8;
         const int ch = t % CPR;
-        PackedRowWalk w(tile_row0 + t / CPR, kSoftmaxThreads / CPR, G);
-        for (int r_out = t / CPR; r_out < TQ && w.i < packed; r_out += kSoftmaxThreads / CPR, w.next())
+        PackedRowWalk w(tile_row0 + t / CPR, kSetThreads / CPR, G);
+        for (int r_out = t / CPR; r_out < TQ && w.i < packed; r_out += kSetThreads / CPR, w.next())
           *reinterpret_cast<uint4*>(p.out + (static_cast<size_t>(row0 + w.tok) * p.heads + g * G + w.hd) * D + ch * 8) =
               *reinterpret_cast<const uint4*>(stage + r_out * STAGE_STRIDE + ch * 16);
       }
       proxy_fence();                                             // the next item's TMA boxes land where these rows lay
+      }
     }
     tc_fence_before();
     __syncthreads();                                             // the item is finished everywhere
@@ -604,14 +679,15 @@ using namespace pih;
 
 // Attention of the requests that bring more than 16 packed rows (prompt portions); rows of other requests
 // are left untouched.  head_dim 64 or 128, page_size 8..64 (a power of two), kv_tensor_map from
-// pih_make_kv_tensor_map.  tile_max_q: the most rows of such a request.  PIH_ERR_UNSUPPORTED otherwise.
-extern "C" int pih_attention_prefill_tcgen05(const void* q, int q_stride, void* out, const int* block_table,
+// pih_make_kv_tensor_map.  rows: the rows of the step (of q); tile_max_q: the most rows of such a request — the two
+// bound the grid, which rows are whose is read from cu_q on the device.  PIH_ERR_UNSUPPORTED otherwise.
+extern "C" int pih_attention_prefill_tcgen05(const void* q, int q_stride, int rows, void* out, const int* block_table,
                                              int table_width, const int* cu_q, const int* q_start, int num_requests,
                                              int tile_max_q, int heads, int kv_heads, int head_dim, int page_size,
                                              int num_pages, float scale, int window, const void* kv_tensor_map,
                                              uint32_t* error, void* stream) {
   if (tile_max_q <= 0) return 0;
-  if (heads <= 0 || kv_heads <= 0 || heads % kv_heads || num_requests <= 0 || num_requests > 65535 ||
+  if (heads <= 0 || kv_heads <= 0 || heads % kv_heads || num_requests <= 0 || rows <= 0 ||
       kv_heads > 65535 || q_stride % 8 || window < 0 || table_width <= 0)
     return PIH_ERR_BAD_ARGUMENT;
   int shift = -1;
@@ -631,14 +707,29 @@ extern "C" int pih_attention_prefill_tcgen05(const void* q, int q_stride, void* 
   p.page_size = page_size;
   p.page_shift = shift;
   p.num_pages = num_pages;
+  p.num_requests = num_requests;
   p.scale = scale;
   p.window = window;
   p.error = error;
   CUtensorMap map;
   memcpy(&map, kv_tensor_map, sizeof(CUtensorMap));
   const int G = heads / kv_heads;
-  const int tiles_q = (tile_max_q * G + TQ - 1) / TQ;
-  dim3 grid((tiles_q + 1) / 2, kv_heads, num_requests);
+  // row tiles of all requests together: no more than the step's packed rows hold, one partial tile a request
+  // more; and no more than every request at its longest
+  const long long by_rows = (static_cast<long long>(rows) * G + TQ - 1) / TQ + num_requests;
+  const long long by_requests = static_cast<long long>(num_requests) * ((tile_max_q * G + TQ - 1) / TQ);
+  const long long tiles = by_rows < by_requests ? by_rows : by_requests;
+  if (tiles > 0x7fffffffLL) return PIH_ERR_BAD_ARGUMENT;
+  static int sms = 0;
+  if (sms == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (sms <= 0) sms = 148;
+  }
+  p.pair_above = sms;                  // single tiles while every tile finds an SM of its own; beyond that, pairs
+                                       // (a 2048-token prompt: 256 single tiles in two uneven waves 40 us, 128 pairs 31 us)
+  dim3 grid(static_cast<unsigned>(tiles), kv_heads, 1);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   static bool configured[2] = {false, false};
   if (head_dim == 128) {
@@ -651,7 +742,7 @@ extern "C" int pih_attention_prefill_tcgen05(const void* q, int q_stride, void* 
       if (e != cudaSuccess) return static_cast<int>(e);
       configured[0] = true;
     }
-    launch_kernel(attn_prefill_tcgen05_kernel<128, SPLIT>, dim3(grid), dim3(128 * SPLIT + 128), smem, s, p, map);
+    launch_kernel(attn_prefill_tcgen05_kernel<128, SPLIT>, dim3(grid), dim3(256 * SPLIT + 128), smem, s, p, map);
   } else {
     const int smem = static_cast<int>(sizeof(PrefillSmem<64, 2>)) + 1024;
     if (!configured[1]) {
@@ -659,7 +750,7 @@ extern "C" int pih_attention_prefill_tcgen05(const void* q, int q_stride, void* 
       if (e != cudaSuccess) return static_cast<int>(e);
       configured[1] = true;
     }
-    launch_kernel(attn_prefill_tcgen05_kernel<64, 2>, dim3(grid), dim3(384), smem, s, p, map);
+    launch_kernel(attn_prefill_tcgen05_kernel<64, 2>, dim3(grid), dim3(640), smem, s, p, map);
   }
   PIH_LAUNCH_CHECK();
   return 0;

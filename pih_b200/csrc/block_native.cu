@@ -53,7 +53,7 @@ int pih_qk_attention_fused(const void* qkv, int q_stride, void* out, void* cache
                            float scale, int window, int split, int max_splits, const int* max_ctx_ptr, float* scratch,
                            const void* kv_tensor_map, int norm_dtype, const void* q_norm_w, const void* k_norm_w,
                            float eps, const float* rope, int max_pos, int write_kv, uint32_t* error, void* stream);
-int pih_attention_prefill_tcgen05(const void* q, int q_stride, void* out, const int* block_table, int table_width,
+int pih_attention_prefill_tcgen05(const void* q, int q_stride, int rows, void* out, const int* block_table, int table_width,
                                   const int* cu_q, const int* q_start, int num_requests, int tile_max_q, int heads,
                                   int kv_heads, int head_dim, int page_size, int num_pages, float scale, int window,
                                   const void* kv_tensor_map, uint32_t* error, void* stream);
@@ -259,7 +259,7 @@ extern "C" int pih_prenorm_attention_swiglu_block(const PihStepArgs* sp, const P
     if (a.tensor_cores) {
       int tile_max_q = a.tile_max_q;
       if (tile_max_q > 0 && a.tcgen05_prefill && b->kv_map != nullptr) {
-        PIH_TRY(pih_attention_prefill_tcgen05(b->qkv, b->qkv_cols, b->attn, a.block_table, a.table_width, s.cu_q, s.q_start,
+        PIH_TRY(pih_attention_prefill_tcgen05(b->qkv, b->qkv_cols, T, b->attn, a.block_table, a.table_width, s.cu_q, s.q_start,
                                               s.num_requests, tile_max_q, b->heads, b->kv_heads, D, a.page_size,
                                               a.num_pages, b->scale, b->window, b->kv_map, s.error, s.stream));
         tile_max_q = 0;

@@ -28,6 +28,10 @@ enum ErrorCode : uint32_t {
   kWaitTimedOut = 6,
 };
 
+// A step may be padded to a larger shape: a row of padding carries this cache slot (nothing is written for it) and
+// request -1; a request of padding has no rows.  Kernels leave both alone without reporting anything.
+constexpr int kPaddingSlot = -2;
+
 __device__ __forceinline__ void publish_error(uint32_t* flag, uint32_t code) {
   if (flag != nullptr) atomicCAS(flag, 0u, code);
 }

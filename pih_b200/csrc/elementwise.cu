@@ -114,7 +114,7 @@ __global__ void qk_norm_rope_kv_kernel(T* __restrict__ qkv, int row_stride, int 
   if (!is_q) {
     const int m = slot_mapping[t];
     if (m < 0 || m >= num_pages * page_size) {
-      if (lane == 0) publish_error(error, kRowWithoutPage);
+      if (lane == 0 && m != kPaddingSlot) publish_error(error, kRowWithoutPage);   // (a row of padding is left alone)
     } else {
       const int page = m / page_size, off = m % page_size;
       const int h = is_k ? slot - heads : slot - heads - kv_heads;
@@ -208,7 +208,7 @@ __global__ void qk_norm_rope_kv_fast_kernel(T* __restrict__ qkv, int row_stride,
   if (any_kv) {
     m = slot_mapping[t];
     if (m < 0 || m >= num_pages * page_size) {
-      if (lane == 0) publish_error(error, kRowWithoutPage);
+      if (lane == 0 && m != kPaddingSlot) publish_error(error, kRowWithoutPage);   // (a row of padding is left alone)
       m = -1;
     } else {
       const int page = m / page_size, off = m % page_size;
@@ -390,7 +390,7 @@ qk_norm_rope_kv_wide_kernel(T* __restrict__ qkv, int row_stride, int rows, int h
   if (slot_end > heads) {
     m = slot_mapping[t];
     if (m < 0 || m >= num_pages * page_size) {
-      if (lane == 0) publish_error(error, kRowWithoutPage);
+      if (lane == 0 && m != kPaddingSlot) publish_error(error, kRowWithoutPage);   // (a row of padding is left alone)
       m = -1;
     } else {
       const int page = m / page_size, off = m % page_size;

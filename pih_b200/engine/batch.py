@@ -16,6 +16,13 @@ Arrays (int32, on the device):
   q_start[R] (length before this step), ctx_len[R] (length after it),
   state_slots[R], and per cache group block_table[R, width] and
   slot_mapping[T].
+
+A step may be PADDED to larger counts of rows, requests and wanted rows, so that steps of different make-up have
+one shape (one set of launch geometries, one captured graph).  What is padding is marked in the data, and every
+kernel that reads it leaves padding alone: a padding row has token 0, position 0, request -1 and cache slot
+``PAD_SLOT`` (nothing is written for it); a padding request has no rows (cu_q stays at the number of real rows),
+length 0, state slot -1 and a block table of -1; a padding wanted row repeats row 0.  The rows of padding run
+through the row-wise kernels and the products like any other and are never read.
 """
 from __future__ import annotations
 
@@ -24,6 +31,9 @@ from typing import Hashable, List, Optional, Sequence
 
 import numpy as np
 import torch
+
+
+PAD_SLOT = -2          # slot_mapping of a row that belongs to no request (a negative slot otherwise is an error)
 
 
 @dataclass
@@ -35,7 +45,7 @@ class StepEntry:
 
 @dataclass
 class StepBatch:
-    num_rows: int
+    num_rows: int                      # with padding: the tensors' sizes, which the kernels' launches follow
     num_requests: int
     num_logit_rows: int
     max_q: int                         # most rows of one request
@@ -55,6 +65,10 @@ class StepBatch:
     host_cu_q: List[int] = field(default_factory=list)
     host_q_start: List[int] = field(default_factory=list)
     attention_plans: dict = field(default_factory=dict)     # filled by the attention op, per group size
+    padded: bool = False               # of a shape that other steps share (by padding, or by its nature)
+    real_rows: int = 0                 # without padding
+    real_requests: int = 0
+    real_logit_rows: int = 0
 
 
 def _align(n: int, a: int = 4) -> int:
@@ -80,14 +94,14 @@ class BatchBuilder:
         return self._pinned[:n]
 
     def build(self, entries: Sequence[StepEntry], cache, width: Optional[int] = None,
-              device_buffer: Optional[torch.Tensor] = None) -> StepBatch:
+              device_buffer: Optional[torch.Tensor] = None, pad=None) -> StepBatch:
         """``cache``: the CacheManager, after ``append`` was called for every entry.
 
         ``width`` fixes the block tables' row length (default: the longest table of the batch);
         ``device_buffer`` is an int32 device tensor to fill instead of a fresh one.  The layout is a
         function of (rows, requests, wanted rows, groups, width) alone, so a step of the same shape
         written into the same buffer puts every array at the same address — what a captured CUDA
-        graph needs.
+        graph needs.  ``pad``: (rows, requests, wanted rows) to pad the step to (each at least the real count).
         """
         R = len(entries)
         rids = [e.rid for e in entries]
@@ -109,7 +123,10 @@ class BatchBuilder:
                     raise ValueError(f"request {e.rid!r}: wanted place {w} is outside its {counts[r]} tokens")
                 logit_rows.append(cu_q[r] + int(w))
         S = len(logit_rows)
-        sizes = self._sizes(T, R, S, G, width)
+        Tp, Rp, Sp = (T, R, S) if pad is None else pad
+        if Tp < T or Rp < R or Sp < S:
+            raise ValueError("a step cannot be padded to less than it holds")
+        sizes = self._sizes(Tp, Rp, Sp, G, width)
         offsets, total = [], 0
         for n in sizes:
             offsets.append(total)
@@ -128,6 +145,15 @@ class BatchBuilder:
                 v[o[0] + lo:o[0] + hi] = e.tokens
                 v[o[1] + lo:o[1] + hi] = np.arange(starts[r], starts[r] + counts[r], dtype=np.int32)
                 v[o[2] + lo:o[2] + hi] = r
+        if pad is not None:
+            v[o[0] + T:o[0] + Tp] = 0
+            v[o[1] + T:o[1] + Tp] = 0
+            v[o[2] + T:o[2] + Tp] = -1
+            v[o[3] + S:o[3] + Sp] = 0
+            v[o[4] + R + 1:o[4] + Rp + 1] = T
+            v[o[5] + R:o[5] + Rp] = 0
+            v[o[6] + R:o[6] + Rp] = 0
+            v[o[7] + R:o[7] + Rp] = -1
         if S:
             v[o[3]:o[3] + S] = logit_rows
         v[o[4]:o[4] + R + 1] = cu_q
@@ -138,6 +164,9 @@ class BatchBuilder:
         for g in range(G):
             table = v[o[9 + 2 * g]:o[9 + 2 * g] + R * width].reshape(R, width)
             cache.fill_block_table(g, rids, table)
+            if pad is not None:
+                v[o[9 + 2 * g] + R * width:o[9 + 2 * g] + Rp * width] = -1
+                v[o[10 + 2 * g] + T:o[10 + 2 * g] + Tp] = PAD_SLOT
             sm = v[o[10 + 2 * g]:o[10 + 2 * g] + T]
             for r, rc in enumerate(reqs):
                 pages = rc.pages[g].arr
@@ -170,14 +199,16 @@ class BatchBuilder:
             return dev[offsets[i]:offsets[i] + n]
 
         batch = StepBatch(
-            num_rows=T, num_requests=R, num_logit_rows=S, max_q=max(counts),
+            num_rows=Tp, num_requests=Rp, num_logit_rows=Sp, max_q=max(counts),
             max_ctx=max(starts[r] + counts[r] for r in range(R)),
-            token_ids=part(0, T), positions=part(1, T), request_of_row=part(2, T),
-            logit_rows=part(3, S), cu_q=part(4, R + 1), q_start=part(5, R), ctx_len=part(6, R),
-            state_slots=part(7, R), meta=part(8, 4), host_cu_q=cu_q, host_q_start=starts)
+            token_ids=part(0, Tp), positions=part(1, Tp), request_of_row=part(2, Tp),
+            logit_rows=part(3, Sp), cu_q=part(4, Rp + 1), q_start=part(5, Rp), ctx_len=part(6, Rp),
+            state_slots=part(7, Rp), meta=part(8, 4), host_cu_q=cu_q + [T] * (Rp - R),
+            host_q_start=starts + [0] * (Rp - R), real_rows=T, real_requests=R, real_logit_rows=S,
+            padded=pad is not None)
         for g in range(G):
-            batch.block_tables.append(part(9 + 2 * g, R * width).view(R, width))
-            batch.slot_mappings.append(part(10 + 2 * g, T))
+            batch.block_tables.append(part(9 + 2 * g, Rp * width).view(Rp, width))
+            batch.slot_mappings.append(part(10 + 2 * g, Tp))
         return batch
 
     @staticmethod

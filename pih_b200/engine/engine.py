@@ -28,7 +28,7 @@ import torch
 from ..kernels.ops import KernelError, error_text
 from ..sampling.params import SamplingParams
 from ..sampling.sampler import Sampler
-from ..cache import OutOfPages
+from ..cache import DEFAULT_PAGE_SIZE, OutOfPages
 from .batch import StepEntry
 from ..kernels import get_ops
 from .factory import runner_for
@@ -90,7 +90,7 @@ class _InFlight:
 
 class Engine:
     def __init__(self, model_dir: str, dtype: str = "bfloat16", *, device: str = "cuda:0",
-                 page_size: int = 16, max_cache_tokens: Optional[int] = None, memory_fraction: float = 0.9,
+                 page_size: int = DEFAULT_PAGE_SIZE, max_cache_tokens: Optional[int] = None, memory_fraction: float = 0.9,
                  maximum_batch_sequences: int = 32, maximum_batch_tokens: int = 4096,
                  maximum_context_tokens: Optional[int] = None, cuda_graphs: bool = True,
                  run_ahead: bool = True, ops: Optional[object] = None, model: Optional[tuple] = None,
@@ -184,6 +184,73 @@ class Engine:
         """Wait for every queued step and see its error word (raises ``KernelError`` as ``step`` does)."""
         if self._unconfirmed:
             self._settle(self._unconfirmed[-1])
+
+    def warm_up(self, decode_batches: Optional[Sequence[int]] = None, rows: Optional[Sequence[int]] = None) -> dict:
+        """Run — and, with CUDA graphs, capture — the step shapes that serving under this engine's limits
+        meets most, before the first request: decode steps of every batch size that has a graph of its own,
+        and steps of the token budget's rows with every bucket of requests, with and without wanted rows.
+        What a process pays once (library handles and kernels loaded at their first launch, work areas,
+        captures) is then not paid between requests.  Stand-in requests hold a few pages for the duration of
+        the call; nothing of them remains.  Only with an engine that holds no request.  ``decode_batches`` /
+        ``rows``: other batch sizes / row counts than the default choice.  Returns what it did."""
+        import time
+        from .runner import _requests_bucket, _rows_bucket
+        if self._live or self._inflight is not None:
+            raise RuntimeError("warm_up needs an engine without requests")
+        runner, cache, ops = self.runner, self.cache, self.rt.ops
+        t0 = time.perf_counter()
+        limit = self.scheduler.max_batch_sequences
+        if decode_batches is None:
+            decode_batches = [n for n in range(1, limit + 1) if runner._graph_key_of_decode(n)[1] == n]
+        if rows is None:
+            rows = [min(self.scheduler.max_batch_tokens, self.max_context - 1)]
+        tag = ("warm-up", next(self._ids))
+        standing: List[Hashable] = []
+        done = {"decode_batches": [], "steps": [], "graphs_before": len(runner._graphs)}
+
+        def decoders(n):
+            while len(standing) < n:
+                rid = (tag, "d", len(standing))
+                runner.step([StepEntry(rid, [0], [])])
+                standing.append(rid)
+            return standing[:n]
+
+        try:
+            for n in sorted(set(int(b) for b in decode_batches if 1 <= int(b) <= limit)):
+                ids = decoders(n)
+                for _ in range(runner.capture_decode_after + 1):
+                    runner.step([StepEntry(r, [0], [0]) for r in ids])
+                done["decode_batches"].append(n)
+            while len(standing) > limit - 1:                       # (a slot for the request that brings the portion)
+                runner.finish(standing.pop())
+            for t in sorted(set(int(r) for r in rows if int(r) >= 2)):
+                buckets = sorted({_requests_bucket(n) for n in range(1, limit + 1)})
+                for requests in buckets:
+                    beside = min(requests, limit) - 1             # decode tokens beside one portion
+                    if t - beside < 2:
+                        continue
+                    for wanted in (True, False):
+                        ids = decoders(beside)
+                        rid = (tag, "p", t, requests, wanted)
+                        for _ in range(runner.CAPTURE_AFTER_STEP + 1):
+                            entries = [StepEntry(r, [0], [0] if wanted else []) for r in ids]
+                            entries.append(StepEntry(rid, [0] * (t - beside), [t - beside - 1] if wanted else []))
+                            runner.step(entries)
+                        runner.finish(rid)
+                        done["steps"].append((_rows_bucket(t), requests, wanted))
+        except OutOfPages:
+            done["stopped"] = "out of pages"
+        finally:
+            for rid in standing:
+                runner.finish(rid)
+            for rid in [r for r in cache.requests if isinstance(r, tuple) and r and r[0] == tag]:
+                runner.finish(rid)
+        if self.device.type == "cuda":
+            torch.cuda.synchronize(self.device)
+        ops.check_errors()
+        done["graphs"] = len(runner._graphs)
+        done["seconds"] = round(time.perf_counter() - t0, 3)
+        return done
 
     # -- one step ---------------------------------------------------------------------
     # A step's sampled ids are needed on the host only to book them and to see who stops.  So while

@@ -5,7 +5,7 @@ from typing import Optional
 
 import torch
 
-from ..cache import CacheManager
+from ..cache import DEFAULT_PAGE_SIZE, CacheManager
 from ..kernels import get_ops
 from ..models import load_model
 from ..parts.registry import Runtime
@@ -14,7 +14,7 @@ from .runner import ModelRunner
 DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32}
 
 
-def create_runner(model_dir: str, dtype: str = "bfloat16", *, device: str = "cuda:0", page_size: int = 16,
+def create_runner(model_dir: str, dtype: str = "bfloat16", *, device: str = "cuda:0", page_size: int = DEFAULT_PAGE_SIZE,
                   max_cache_tokens: int = 4096, max_requests: int = 32, cuda_graphs: bool = False,
                   ops: Optional[object] = None, capture_decode_after: int = 0):
     """Returns ``(config, model, cache, runner)``.
@@ -72,7 +72,7 @@ def cache_tokens_for_memory(model, *, page_size: int, max_requests: int, max_bat
     return int(tokens)
 
 
-def runner_for(model, *, page_size: int = 16, max_cache_tokens: int = 4096, max_requests: int = 32,
+def runner_for(model, *, page_size: int = DEFAULT_PAGE_SIZE, max_cache_tokens: int = 4096, max_requests: int = 32,
                cuda_graphs: bool = False, capture_decode_after: int = 0):
     """A cache and a step function for a model that is already built; returns ``(cache, runner)``."""
     rt = model.rt

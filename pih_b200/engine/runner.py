@@ -57,9 +57,40 @@ class _BoundedPlans(dict):
         return tile_max_q, dec_cap, self._max_ctx if dec_cap else 0
 
 
+class _PaddedPlans(dict):
+    """Attention plans of a step padded to ``rows`` rows: whatever its requests bring.  Any request may be a
+    portion of up to all the rows, or decode-like with as many rows as 16 packed rows hold."""
+
+    def __init__(self, rows: int, max_ctx: int):
+        super().__init__()
+        self._rows, self._max_ctx = rows, max_ctx
+
+    def __contains__(self, key):
+        return True
+
+    def __getitem__(self, group):
+        return (self._rows if self._rows * group > 16 else 0), max(1, min(self._rows, 16 // group)), self._max_ctx
+
+
+def _rows_bucket(n: int) -> int:
+    """Rows of a padded step: 16, 32, 64, then steps of a quarter to a half of the count."""
+    for b in (16, 32, 64, 128, 192, 256, 384, 512, 768, 1024, 1536, 2048, 3072, 4096):
+        if n <= b:
+            return b
+    return -(-n // 2048) * 2048
+
+
+def _requests_bucket(n: int) -> int:
+    return 1 << max(0, n - 1).bit_length()
+
+
 class ModelRunner:
-    def __init__(self, model, cache: CacheManager, cuda_graphs: bool = False, capture_decode_after: int = 0):
+    def __init__(self, model, cache: CacheManager, cuda_graphs: bool = False, capture_decode_after: int = 0,
+                 pad_steps: bool = True):
         self.cuda_graphs = cuda_graphs
+        # Steps of different make-up are padded to common shapes (see engine/batch.py), so that a serving run meets
+        # a handful of shapes and replays them from graphs, if every part of the model leaves padding alone.
+        self.pad_steps = pad_steps and cuda_graphs and bool(getattr(model, "pad_safe", False))
         self.model = model
         self.cache = cache
         self.device = model.rt.device
@@ -159,16 +190,20 @@ class ModelRunner:
     # launch geometry of every kernel depends only on (rows, requests, wanted rows, block-table width,
     # the attention plan); which request owns which row is data in the step's device buffer.  So a step
     # can be captured once per such key and replayed with fresh data written into the same buffer:
-    #   * decode steps (every request one token that wants its logits): captured at first sight;
-    #   * any other step of at least GRAPH_MIN_ROWS rows — a prompt portion, or portions beside decode
-    #     tokens — whose requests each want nothing or their last row: keyed by the rows that each
-    #     request brings, in order, and captured when that key is seen the second time (chunked prefill
-    #     under a token budget repeats its shapes: the same decode rows beside the same portion).  The
-    #     GRAPH_LIMIT most recently used of these are kept.
+    #   * decode steps (every request one token that wants its logits): keyed by the number of requests — beyond
+    #     PAD_DECODE_ABOVE of them, padded to a multiple of 8 — and captured when the key has been seen
+    #     ``capture_decode_after`` times;
+    #   * any other step — a prompt portion, or portions beside decode tokens — whose requests each want
+    #     nothing or their last row: padded to (rows bucket, requests bucket, wanted rows: none or one a request)
+    #     and captured when that shape is seen the second time.  What the kernels need to know about the step's
+    #     make-up is in its device buffer; the attention plans cover every make-up.  Without padding (a model
+    #     with a part that does not allow it): keyed by the rows that each request brings, in order, from
+    #     GRAPH_MIN_ROWS rows on.  The GRAPH_LIMIT most recently used of these are kept.
     GRAPH_WIDTH_STEP = 64           # block-table widths are rounded up to a multiple of this many pages
     GRAPH_MIN_ROWS = 128
     GRAPH_LIMIT = 48
     CAPTURE_AFTER_STEP = 1          # a mixed step is captured when its shape is seen the second time
+    PAD_DECODE_ABOVE = 16           # up to here every batch size of a decode step has a graph of its own
 
     def _graphable(self, entries) -> bool:
         return self._graph_key(entries) is not None
@@ -176,20 +211,47 @@ class ModelRunner:
     def _graph_key(self, entries):
         if not (self.cuda_graphs and self.device.type == "cuda"):
             return None
+        n = len(entries)
         if all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries):
-            return ("decode", len(entries))
+            return self._graph_key_of_decode(n)
         counts = tuple(len(e.tokens) for e in entries)
-        if sum(counts) >= self.GRAPH_MIN_ROWS and all(list(e.want) in ([], [len(e.tokens) - 1]) for e in entries):
+        if not all(list(e.want) in ([], [len(e.tokens) - 1]) for e in entries):
+            return None
+        if self.pad_steps:
+            requests = _requests_bucket(n)
+            return ("padded", _rows_bucket(sum(counts)), requests, requests if any(e.want for e in entries) else 0)
+        if sum(counts) >= self.GRAPH_MIN_ROWS:
             return ("step", counts, tuple(len(e.want) for e in entries))
         return None
+
+    def _graph_key_of_decode(self, n: int):
+        if self.pad_steps and n > self.PAD_DECODE_ABOVE:
+            return ("decode", -(-n // 8) * 8)
+        return ("decode", n)
+
+    @staticmethod
+    def _padding(kind, entries):
+        """(rows, requests, wanted rows) that a step of this key is padded to; None: as it is."""
+        if kind[0] == "padded":
+            return kind[1], kind[2], kind[3]
+        if kind[0] == "decode" and kind[1] != len(entries):
+            return kind[1], kind[1], kind[1]
+        return None
+
+    def _plans(self, kind, max_ctx: int):
+        if kind[0] == "decode":
+            return _FixedPlans((0, 1, max_ctx))
+        if kind[0] == "padded":
+            return _PaddedPlans(kind[1], max_ctx)
+        return _BoundedPlans(kind[1], max_ctx)
 
     @staticmethod
     def _feed(batch: StepBatch, token_feed: Optional[torch.Tensor]) -> None:
         if token_feed is not None:
-            if (token_feed.dim() != 1 or token_feed.shape[0] != batch.token_ids.shape[0]
-                    or token_feed.dtype != batch.token_ids.dtype):
+            rows = batch.real_rows
+            if token_feed.dim() != 1 or token_feed.shape[0] != rows or token_feed.dtype != batch.token_ids.dtype:
                 raise ValueError("token_feed needs one int32 id per row of the step")
-            batch.token_ids.copy_(token_feed)                # queued behind the batch's own copy to the device
+            batch.token_ids[:rows].copy_(token_feed)         # queued behind the batch's own copy to the device
 
     def _graph_step(self, entries, token_feed=None) -> Optional[torch.Tensor]:
         kind = self._graph_key(entries)
@@ -210,27 +272,38 @@ class ModelRunner:
         width = -(-self.cache.table_width(rids) // step_w) * step_w
         key = kind + (width,)
         state = self._graphs.get(key)
+        pad = self._padding(kind, entries)
+        wanted = sum(len(e.want) for e in entries)
         try:
             seen = self._sightings.get(key, 0)
-            if state is None and seen < (self.CAPTURE_AFTER_STEP if kind[0] == "step" else self.capture_decode_after):
-                # this shape has not been seen often enough to be worth a capture: run it as it is
+            if state is None and seen < (self.capture_decode_after if kind[0] == "decode" else self.CAPTURE_AFTER_STEP):
+                # this shape has not been seen often enough to be worth a capture: run it uncaptured (padded as
+                # its graph will be and with the graph's plans: the same kernels on the same shapes give the
+                # same logits whether replayed or not)
                 self._sightings[key] = seen + 1
                 if len(self._sightings) > 4 * self.GRAPH_LIMIT:           # dicts keep insertion order: oldest out
                     del self._sightings[next(iter(self._sightings))]
-                batch = self.builder.build(entries, self.cache)
+                if pad is None:
+                    batch = self.builder.build(entries, self.cache)
+                else:
+                    batch = self.builder.build(entries, self.cache, width=width, pad=pad)
+                    batch.attention_plans = self._plans(kind, width * self.cache.page_size)
+                batch.padded = True                               # (a shape that comes again, padded or not)
                 self._feed(batch, token_feed)
                 logits = self.run(batch)
             elif state is None:
                 self._sightings.pop(key, None)
                 logits = self._capture(entries, key, width, token_feed)
             else:
-                batch = self.builder.build(entries, self.cache, width=width, device_buffer=state["buffer"])
+                batch = self.builder.build(entries, self.cache, width=width, device_buffer=state["buffer"], pad=pad)
                 self._feed(batch, token_feed)
-                if key[0] == "step":
+                if key[0] != "decode":
                     self._graphs[key] = self._graphs.pop(key)     # most recently used last
                 state["graph"].replay()
                 self._count_launches(state["launches"])
                 logits = state["logits"]
+            if pad is not None and logits is not None:
+                logits = logits[:wanted] if wanted else None
         except Exception:
             for rid in rids:
                 self.cache.rollback(rid)
@@ -247,19 +320,18 @@ class ModelRunner:
 
     def _capture(self, entries, key, width, token_feed=None):
         G = len(self.cache.groups)
-        T = sum(len(e.tokens) for e in entries)
-        B = len(entries)
-        S = sum(len(e.want) for e in entries)
+        pad = self._padding(key, entries)
+        if pad is None:
+            T, B, S = sum(len(e.tokens) for e in entries), len(entries), sum(len(e.want) for e in entries)
+        else:
+            T, B, S = pad
         buffer = torch.empty(self.builder.buffer_size(T, B, S, G, width), dtype=torch.int32, device=self.device)
-        batch = self.builder.build(entries, self.cache, width=width, device_buffer=buffer)
+        batch = self.builder.build(entries, self.cache, width=width, device_buffer=buffer, pad=pad)
+        batch.padded = True
         self._feed(batch, token_feed)
-        max_ctx = width * self.cache.page_size
         ops = self.model.rt.ops
         # the attention plans of the graph cover every context that fits the table width
-        if key[0] == "decode":
-            batch.attention_plans = _FixedPlans((0, 1, max_ctx))
-        else:
-            batch.attention_plans = _BoundedPlans(key[1], max_ctx)
+        batch.attention_plans = self._plans(key, width * self.cache.page_size)
         caches = [self.cache.view(i, batch.block_tables, batch.slot_mappings) for i in range(self.num_entries)]
         # This step itself runs eagerly, on a side stream, from the buffer and with the plans that the graph
         # will have: whatever a kernel or a part sets up or allocates at its first call with these shapes (shared
@@ -281,7 +353,7 @@ class ModelRunner:
             self._graph_pool = graph.pool()
         state = {"graph": graph, "buffer": buffer, "logits": logits, "batch": batch, "launches": launches}
         self._graphs[key] = state
-        steps = [k for k in self._graphs if k[0] == "step"]
+        steps = [k for k in self._graphs if k[0] != "decode"]
         if len(steps) > self.GRAPH_LIMIT:                 # dicts keep insertion order; a replay re-inserts its key
             del self._graphs[steps[0]]
         return eager_logits

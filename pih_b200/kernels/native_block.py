@@ -186,12 +186,14 @@ class NativeBlocks:
         """``(h', delta')`` of the block, or None when this path does not take it (the parts then run it)."""
         if not h.is_contiguous() or (delta is not None and not delta.is_contiguous()) or h.dtype not in _DT:
             return None
-        # Steps of many rows in bfloat16 stay with the parts: their products are the library's, and called through
-        # torch a product of a row count not seen before costs far less host time than through cublasGemmEx (which
-        # searches and loads anew for every new shape: measured on a serving run whose portions all differ in
-        # length, 3.7 against 4.7 thousand generated tokens a second).  Few rows — decode steps, where the host time
-        # of an uncaptured step matters most — and the 32-bit path need no library product.
-        if h.dtype == torch.bfloat16 and h.shape[0] > self.ops.skinny_max_rows:
+        # Steps of many rows in bfloat16 whose row count is their own stay with the parts: their products are the
+        # library's, and called through torch a product of a row count not seen before costs far less host time
+        # than through cublasGemmEx (which searches and loads anew for every new shape: measured on a serving run
+        # whose portions all differ in length, 3.7 against 4.7 thousand generated tokens a second).  Few rows —
+        # decode steps, where the host time of an uncaptured step matters most —, the 32-bit path (no library
+        # product) and steps padded to a shape that comes again are issued from here.
+        if (h.dtype == torch.bfloat16 and h.shape[0] > self.ops.skinny_max_rows
+                and not getattr(step, "padded", False)):
             return None
         b = getattr(block, "_native_args", None)
         if b is None:

@@ -412,7 +412,7 @@ class CudaOps:
         if tile_max_q > 0 and self.tcgen05_attention and kv_map is not None and head_dim in (64, 128) \
                 and page_size in (8, 16, 32, 64):
             rc = self.lib.pih_attention_prefill_tcgen05(
-                _ptr(qkv), qkv.stride(0), _ptr(out), _ptr(block_table), block_table.shape[1], _ptr(step.cu_q),
+                _ptr(qkv), qkv.stride(0), rows, _ptr(out), _ptr(block_table), block_table.shape[1], _ptr(step.cu_q),
                 _ptr(step.q_start), step.num_requests, tile_max_q, heads, kv_heads, head_dim, page_size, num_pages,
                 c_float(scale), int(window), kv_map, self._err(), self._stream())
             self._check(rc, "attention_prefill_tcgen05")

@@ -58,6 +58,11 @@ class CausalLM:
             {name: weights[spec.final_norm_prefix + name] for name in norm_cls.expected_tensors(spec.final_norm)},
             rt)
 
+    @property
+    def pad_safe(self) -> bool:
+        """Whether a step may be padded to a larger shape: every mixer and feed-forward has to leave padding alone."""
+        return all(getattr(b.mixer, "pad_safe", False) and getattr(b.ffn, "pad_safe", False) for b in self.blocks)
+
     # -- what the cache manager must provide, per schedule entry -------------
     def cache_needs(self) -> List[Optional[object]]:
         needs = []

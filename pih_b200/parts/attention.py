@@ -26,6 +26,10 @@ from ._bind import bind_matrix, bind_vector
 
 @register_mixer("attention")
 class PagedAttention:
+    # A step may be padded (rows of no request, requests without rows: see engine/batch.py); the kernels of this
+    # part leave padding alone.  A mixer that does not say so is only given steps as they are.
+    pad_safe = True
+
     @classmethod
     def expected_tensors(cls, spec):
         n = spec.names

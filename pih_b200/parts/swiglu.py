@@ -18,6 +18,8 @@ from ._bind import bind_matrix
 
 @register_ffn("swiglu")
 class SwiGLU:
+    pad_safe = True                        # row-wise: rows of padding are computed and never read
+
     @classmethod
     def expected_tensors(cls, spec):
         n = spec.names

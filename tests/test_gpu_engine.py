@@ -176,3 +176,34 @@ def test_the_default_pool_comes_from_the_devices_memory(model_dirs, tiny_configs
     assert [len(r["token_ids"]) for r in got] == [4, 4]
     with pytest.raises(MemoryError, match="fewer than one request"):
         Engine(model_dirs["A"], "bfloat16", memory_fraction=1e-6)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_warm_up_captures_shapes_and_leaves_nothing_behind(model_dirs, tiny_configs, dtype):
+    """Before the first request the engine runs and captures the shapes that its limits make likely, with stand-in
+    requests; afterwards the pool is whole, and requests are answered with the tokens of an engine that was
+    not warmed up — now from graphs captured beforehand, padded to the shapes of the warm-up."""
+    vocab = tiny_configs["A"]["vocab_size"]
+    prompts = _prompts(vocab, [45, 9, 70, 23, 31], seed=17)
+
+    def run(warm):
+        e = _engine(model_dirs["A"], dtype, page_size=16, max_cache_tokens=2048, maximum_batch_sequences=6,
+                    maximum_batch_tokens=48, cuda_graphs=True, capture_decode_after=2)
+        done = e.warm_up() if warm else None
+        if warm:
+            assert done["decode_batches"] == [1, 2, 3, 4, 5, 6] and done["graphs"] >= 6 + 4, done
+            assert ("stopped" not in done) and not e.cache.requests
+            assert all(f == e.cache.num_pages for f in e.cache.num_free_pages())
+        before = len(e.runner._graphs)
+        got = e.complete_batch(prompts, max_tokens=12, ignore_eos=True)
+        _all_back(e)
+        return [r["token_ids"] for r in got], before, len(e.runner._graphs)
+
+    cold, _, _ = run(False)
+    warm, before, after = run(True)
+    assert warm == cold
+    assert after - before <= 4, "most shapes of the run should have been captured by the warm-up"
+    with pytest.raises(RuntimeError, match="without requests"):
+        e = _engine(model_dirs["A"], dtype, cuda_graphs=True)
+        e.submit(prompts[0])
+        e.warm_up()

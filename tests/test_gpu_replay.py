@@ -139,7 +139,7 @@ def test_steps_replayed_from_cuda_graphs_match(model_dirs, tiny_configs, dtype):
         got[rid] = torch.cat(rows)
         runner.finish(rid)
     model.rt.ops.check_errors()
-    assert any(k[0] == "step" for k in runner._graphs), "no prompt portion was replayed from a graph"
+    assert any(k[0] in ("step", "padded") for k in runner._graphs), "no prompt portion was replayed from a graph"
     cfg, w = load_plain_weights(model_dirs[name])
     for rid, toks in reqs.items():
         lead = len(toks) - 300
@@ -185,7 +185,8 @@ def test_mixed_steps_replayed_from_cuda_graphs_match(model_dirs, tiny_configs, n
                 places[rid].append(259)
         runner.finish(rid)
     model.rt.ops.check_errors()
-    assert any(k[0] == "step" and len(k[1]) == 3 for k in runner._graphs), "no mixed step was replayed from a graph"
+    assert any(k[0] == "padded" or (k[0] == "step" and len(k[1]) == 3) for k in runner._graphs), \
+        "no mixed step was replayed from a graph"
     cfg, w = load_plain_weights(model_dirs[name])
     for rid, toks in {**decoders, **arrivals}.items():
         truth = plain_impl.forward(cfg, w, toks)[places[rid]]
@@ -205,7 +206,7 @@ def _run_trace_run(model_dir, dtype, steps, out_dir, max_tokens, env=None):
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_trace_run_program(model_dirs, requests_of, tmp_path, dtype):
-    """bin/trace_run with its default page size of 16, mixed trace, pool = the peak of live tokens."""
+    """bin/trace_run with its default page size, mixed trace, pool = the peak of live tokens."""
     name = "B"
     requests = requests_of[name]
     steps = traces.mixed(requests, seed=3)
