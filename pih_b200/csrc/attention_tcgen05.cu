@@ -495,7 +495,10 @@ attn_prefill_tcgen05_kernel(const PrefillParams p, const __grid_constant__ CUten
 
       const int i_row = tile_row0 + row;
       const bool row_valid = i_row < packed;
-      const int pos = row_valid ? start + i_row / G : -1;
+      // A row past the request's last (the tile is not full) sees every key, like the tile's full rows far from the
+      // diagonal: nothing of it is stored, and it must not put its warp on the masked path in every key tile — the
+      // last tile of a portion is the one with the most keys, and it is seldom full.
+      const int pos = row_valid ? start + i_row / G : 0x7fffffff;
       const int first = (row_valid && p.window > 0) ? max(0, pos - p.window + 1) : 0;
       const float sl = p.scale * kLog2e5;
       float m_ref = -INFINITY, l = 0.0f;                         // l is this thread's sum relative to m_ref

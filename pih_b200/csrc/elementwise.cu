@@ -556,10 +556,93 @@ __global__ void rmsnorm_vec_kernel(T* __restrict__ x, const T* __restrict__ delt
   }
 }
 
+// A warp per row, for steps of many rows: a lane holds CHUNKS 16-byte pieces of the row (piece lane + 32 k), all
+// of their loads in flight at once, and the row's sum of squares needs shuffles only.  One block per row with a
+// block-wide sum (above) has two 16-byte loads a thread in flight and two barriers on every row's path: on 2048
+// rows of 1024 it ran at 2.7 TB/s out of the L2.  Needs width * sizeof(T) == 32 * CHUNKS * 16 and weights
+// aligned to 16 bytes.
+constexpr int NORM_ROWS_WARPS = 8;
+template <typename T, typename W, int CHUNKS>
+__global__ void __launch_bounds__(NORM_ROWS_WARPS * 32)
+rmsnorm_rows_kernel(T* __restrict__ x, const T* __restrict__ delta, const W* __restrict__ weight,
+                    T* __restrict__ out, const int* __restrict__ rows, int out_rows, int width, float eps) {
+  wait_for_prior_kernels();
+  launch_dependents();                                   // (the next kernel's blocks may become resident and wait)
+  constexpr int VEC = 16 / sizeof(T);
+  constexpr int WV = VEC * sizeof(W) / 16;               // 16-byte loads per VEC weights
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int o = blockIdx.x * NORM_ROWS_WARPS + warp;
+  if (o >= out_rows) return;
+  const size_t r = rows != nullptr ? static_cast<size_t>(rows[o]) : static_cast<size_t>(o);
+  uint4* xr = reinterpret_cast<uint4*>(x + r * width);
+  const uint4* dr = delta != nullptr ? reinterpret_cast<const uint4*>(delta + r * width) : nullptr;
+  const bool write_back = delta != nullptr && rows == nullptr;
+  uint4 h[CHUNKS], d[CHUNKS];
+#pragma unroll
+  for (int k = 0; k < CHUNKS; ++k) h[k] = xr[lane + 32 * k];
+  if (dr != nullptr) {
+#pragma unroll
+    for (int k = 0; k < CHUNKS; ++k) d[k] = dr[lane + 32 * k];
+  }
+  float ss = 0.0f;
+#pragma unroll
+  for (int k = 0; k < CHUNKS; ++k) {
+    T* e = reinterpret_cast<T*>(&h[k]);
+    if (dr != nullptr) {
+      const T* de = reinterpret_cast<const T*>(&d[k]);
+#pragma unroll
+      for (int j = 0; j < VEC; ++j) e[j] = from_float<T>(to_float<T>(e[j]) + to_float<T>(de[j]));
+      if (write_back) xr[lane + 32 * k] = h[k];
+    }
+#pragma unroll
+    for (int j = 0; j < VEC; ++j) {
+      const float f = to_float<T>(e[j]);
+      ss = fmaf(f, f, ss);
+    }
+  }
+  ss = warp_sum(ss);
+  const float scale = 1.0f / sqrtf(ss / static_cast<float>(width) + eps);
+  uint4* yr = reinterpret_cast<uint4*>(out + static_cast<size_t>(o) * width);
+#pragma unroll
+  for (int k = 0; k < CHUNKS; ++k) {
+    uint4 wq[WV];
+#pragma unroll
+    for (int u = 0; u < WV; ++u) wq[u] = reinterpret_cast<const uint4*>(weight)[(lane + 32 * k) * WV + u];
+    const W* we = reinterpret_cast<const W*>(wq);
+    T* e = reinterpret_cast<T*>(&h[k]);
+#pragma unroll
+    for (int j = 0; j < VEC; ++j) e[j] = from_float<T>((to_float<T>(e[j]) * scale) * to_float<W>(we[j]));
+    yr[lane + 32 * k] = h[k];
+  }
+}
+
 template <typename T, typename W>
 static int launch_rmsnorm(void* x, const void* delta, const void* weight, void* out, const int* rows,
                           int out_rows, int width, float eps, cudaStream_t s) {
   constexpr int VEC = 16 / sizeof(T);
+  // many rows: a warp each
+  if (out_rows >= 4 * NORM_ROWS_WARPS && width % (32 * VEC) == 0 && width / (32 * VEC) <= 8 &&
+      (reinterpret_cast<uintptr_t>(weight) & 15) == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0 &&
+      (reinterpret_cast<uintptr_t>(delta) & 15) == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0) {
+    const int chunks = width / (32 * VEC);
+    const dim3 grid((out_rows + NORM_ROWS_WARPS - 1) / NORM_ROWS_WARPS), block(NORM_ROWS_WARPS * 32);
+    T* xp = static_cast<T*>(x);
+    const T* dp = static_cast<const T*>(delta);
+    const W* wp = static_cast<const W*>(weight);
+    T* op = static_cast<T*>(out);
+    bool taken = true;
+    switch (chunks) {
+      case 1: launch_kernel(rmsnorm_rows_kernel<T, W, 1>, grid, block, 0, s, xp, dp, wp, op, rows, out_rows, width, eps); break;
+      case 2: launch_kernel(rmsnorm_rows_kernel<T, W, 2>, grid, block, 0, s, xp, dp, wp, op, rows, out_rows, width, eps); break;
+      case 4: launch_kernel(rmsnorm_rows_kernel<T, W, 4>, grid, block, 0, s, xp, dp, wp, op, rows, out_rows, width, eps); break;
+      case 8: launch_kernel(rmsnorm_rows_kernel<T, W, 8>, grid, block, 0, s, xp, dp, wp, op, rows, out_rows, width, eps); break;
+      default: taken = false;
+    }
+    if (taken) {
+      PIH_LAUNCH_CHECK();
+      return 0;
+    }
+  }
   if ((width * sizeof(T)) % 16 == 0) {
     const int nvec = width / VEC;
     int threads = 32;
