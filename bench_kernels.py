@@ -65,6 +65,7 @@ def main() -> int:
     ap.add_argument("kernel", choices=["attn_decode", "attn_prefill", "linear", "rmsnorm", "qk", "silu", "argmax"])
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--ctx", type=int, default=2048)
+    ap.add_argument("--ctx-min", type=int, default=0, help="attn_decode: the shortest context (default: all --ctx)")
     ap.add_argument("--tokens", type=int, default=2048)
     ap.add_argument("--start", type=int, default=0, help="attn_prefill: tokens of the request already in the cache")
     ap.add_argument("--heads", type=int, default=16)
@@ -78,7 +79,7 @@ def main() -> int:
     ap.add_argument("--width", type=int, default=1024)
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--no-flush", action="store_true")
-    ap.add_argument("--impl", default="default", choices=["default", "tcgen05", "skinny", "library"])
+    ap.add_argument("--impl", default="default", choices=["default", "tcgen05", "skinny", "midrows", "library"])
     ap.add_argument("--fused", default="none", choices=["none", "norm", "addnorm", "swiglu", "residual"],
                     help="linear --impl skinny: with the RMSNorm prologue (addnorm: and the residual add before it; "
                          "swiglu: and the SwiGLU epilogue), or with the residual add in the epilogue")
@@ -114,7 +115,9 @@ def main() -> int:
         k = args.kernel
         if k in ("attn_decode", "attn_prefill"):
             if k == "attn_decode":
-                lens, new = [args.ctx] * args.batch, [1] * args.batch
+                lo = args.ctx_min or args.ctx                       # contexts spread evenly from --ctx-min to --ctx
+                lens = [lo + (args.ctx - lo) * i // max(1, args.batch - 1) for i in range(args.batch)]
+                new = [1] * args.batch
             else:
                 lens, new = [args.start + args.tokens], [args.tokens]      # a portion that starts at --start
             pages_per = [-(-n // P) for n in lens]
@@ -151,6 +154,9 @@ def main() -> int:
                 fn = lambda: ops.silu_mul(torch.mm(x, w.t()), 8)
             elif args.impl == "tcgen05":
                 fn = lambda: ops.linear_tcgen05(x, w, tile_n=args.tile_n)
+            elif args.impl == "midrows":
+                r = torch.randn(args.m, args.n, device=dev).to(bf) if args.fused == "residual" else None
+                fn = lambda: ops.linear_midrows(x, w, swiglu=args.fused == "swiglu", residual=r)
             elif args.impl == "skinny" and args.fused == "residual":
                 r = torch.randn(args.m, args.n, device=dev).to(bf)
                 fn = lambda: ops.linear_skinny(x, w, residual=r)
