@@ -333,10 +333,15 @@ static int launch_midrows(MidParams p, cudaStream_t s) {
   int chosen = 0, smem = 0, clusters_max = 0;
   for (int c = 2, log2c = 1; c <= 8; c *= 2, ++log2c) {
     const int kbs = (KB + c - 1) / c;
-    const int clusters = clusters_at_once(c, log2c);
-    const int upc = (units + clusters - 1) / clusters;
-    const int rounds = (upc + MID_WARPS - 1) / MID_WARPS;
+    int clusters = clusters_at_once(c, log2c);
+    int upc = (units + clusters - 1) / clusters;
     const int x_bytes = 16 * MT * (kbs * 64 + 64);
+    if (upc > MID_WARPS && x_bytes + ((upc + MID_WARPS - 1) / MID_WARPS - 1) * MID_WARPS * 2 * MT * 32 * 16 > 220 * 1024) {
+      // no room to park a warp's second unit beside the token columns: a unit a warp, in more clusters than run at once
+      upc = MID_WARPS;
+      clusters = (units + upc - 1) / upc;
+    }
+    const int rounds = (upc + MID_WARPS - 1) / MID_WARPS;
     const int parked = rounds > 1 ? (rounds - 1) * MID_WARPS * 2 * MT * 32 * 16 : 0;
     const int part_bytes = upc * 2 * MT * 32 * 16;
     const int front = x_bytes > part_bytes ? x_bytes : part_bytes;
