@@ -59,17 +59,20 @@ class _BoundedPlans(dict):
 
 class _PaddedPlans(dict):
     """Attention plans of a step padded to ``rows`` rows: whatever its requests bring.  Any request may be a
-    portion of up to all the rows, or decode-like with as many rows as 16 packed rows hold."""
+    portion of up to all the rows, or decode-like with as many rows as 16 packed rows hold — unless the step's
+    key says that it has no request of one of the two kinds (then that kind's kernel is not launched)."""
 
-    def __init__(self, rows: int, max_ctx: int):
+    def __init__(self, rows: int, max_ctx: int, small: bool = True, large: bool = True):
         super().__init__()
-        self._rows, self._max_ctx = rows, max_ctx
+        self._rows, self._max_ctx, self._small, self._large = rows, max_ctx, small, large
 
     def __contains__(self, key):
         return True
 
     def __getitem__(self, group):
-        return (self._rows if self._rows * group > 16 else 0), max(1, min(self._rows, 16 // group)), self._max_ctx
+        tile_max_q = self._rows if (self._large and self._rows * group > 16) else 0
+        dec_cap = max(1, min(self._rows, 16 // group)) if (self._small or tile_max_q == 0) else 0
+        return tile_max_q, dec_cap, self._max_ctx if dec_cap else 0
 
 
 def _rows_bucket(n: int) -> int:
@@ -219,7 +222,10 @@ class ModelRunner:
             return None
         if self.pad_steps:
             requests = _requests_bucket(n)
-            return ("padded", _rows_bucket(sum(counts)), requests, requests if any(e.want for e in entries) else 0)
+            # whether a request may be decode-like (at most 16 packed rows) / a portion, for any group size of a mixer
+            small, large = any(c <= 16 for c in counts), any(c >= 2 for c in counts)
+            return ("padded", _rows_bucket(sum(counts)), requests, requests if any(e.want for e in entries) else 0,
+                    small, large)
         if sum(counts) >= self.GRAPH_MIN_ROWS:
             return ("step", counts, tuple(len(e.want) for e in entries))
         return None
@@ -242,7 +248,7 @@ class ModelRunner:
         if kind[0] == "decode":
             return _FixedPlans((0, 1, max_ctx))
         if kind[0] == "padded":
-            return _PaddedPlans(kind[1], max_ctx)
+            return _PaddedPlans(kind[1], max_ctx, kind[4], kind[5])
         return _BoundedPlans(kind[1], max_ctx)
 
     @staticmethod
