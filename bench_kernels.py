@@ -79,7 +79,7 @@ def main() -> int:
     ap.add_argument("--width", type=int, default=1024)
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--no-flush", action="store_true")
-    ap.add_argument("--impl", default="default", choices=["default", "tcgen05", "skinny", "midrows", "library"])
+    ap.add_argument("--impl", default="default", choices=["default", "tcgen05", "skinny", "library"])
     ap.add_argument("--fused", default="none", choices=["none", "norm", "addnorm", "swiglu", "residual"],
                     help="linear --impl skinny: with the RMSNorm prologue (addnorm: and the residual add before it; "
                          "swiglu: and the SwiGLU epilogue), or with the residual add in the epilogue")
@@ -154,9 +154,6 @@ def main() -> int:
                 fn = lambda: ops.silu_mul(torch.mm(x, w.t()), 8)
             elif args.impl == "tcgen05":
                 fn = lambda: ops.linear_tcgen05(x, w, tile_n=args.tile_n)
-            elif args.impl == "midrows":
-                r = torch.randn(args.m, args.n, device=dev).to(bf) if args.fused == "residual" else None
-                fn = lambda: ops.linear_midrows(x, w, swiglu=args.fused == "swiglu", residual=r)
             elif args.impl == "skinny" and args.fused == "residual":
                 r = torch.randn(args.m, args.n, device=dev).to(bf)
                 fn = lambda: ops.linear_skinny(x, w, residual=r)

@@ -99,22 +99,32 @@ def main() -> int:
                                 temperature=0.7 if sampled else 0.0, seed=7 + i)
         reqs.append(engine._live[engine.submit(prompt, params)])
 
+    import bench                                           # the clock sampler, the peaks and the weights' bytes
     torch.cuda.synchronize()
     steps = 0
-    decode_only = {"steps": 0, "tokens": 0, "seconds": 0.0}
-    t0 = time.perf_counter()
-    while engine.has_work():
-        all_decode = all(r.num_computed >= len(r.prompt) for r in reqs if r.status != "finished")
-        before = sum(len(r.outputs) for r in reqs)
-        t = time.perf_counter()
-        engine.step()
-        steps += 1
-        if all_decode:
-            decode_only["steps"] += 1
-            decode_only["tokens"] += sum(len(r.outputs) for r in reqs) - before
-            decode_only["seconds"] += time.perf_counter() - t
-    torch.cuda.synchronize()
-    dt = time.perf_counter() - t0
+    decode_only = {"steps": 0, "tokens": 0, "seconds": 0.0, "bytes": 0}
+    weights = bench.weight_bytes(model)
+    per_token = engine.cache.bytes_per_token()
+    with bench.ClockSampler() as clocks:
+        t0 = time.perf_counter()
+        while engine.has_work():
+            live = [r for r in reqs if r.status != "finished"]
+            all_decode = all(r.num_computed >= len(r.prompt) for r in live)
+            before = sum(len(r.outputs) for r in reqs)
+            # what an all-decode step has to read: every weight once and the cache of the live requests
+            need = weights + per_token * sum(r.num_computed for r in live)
+            t = time.perf_counter()
+            engine.step()
+            steps += 1
+            if all_decode:
+                decode_only["steps"] += 1
+                decode_only["tokens"] += sum(len(r.outputs) for r in reqs) - before
+                decode_only["seconds"] += time.perf_counter() - t
+                decode_only["bytes"] += need
+        torch.cuda.synchronize()
+        dt = time.perf_counter() - t0
+    hbm_gbs, _, peak_source = bench.peaks()
+    peaks = {"hbm_gbs": hbm_gbs, "source": peak_source}
     generated = sum(len(r.outputs) for r in reqs)
     assert all(r.status == "finished" and len(r.outputs) == work["new_tokens"] for r in reqs)
     line = {
@@ -122,7 +132,14 @@ def main() -> int:
         "unit": "tok/s", "seconds": round(dt, 3), "steps": steps, "generated_tokens": generated,
         "prompt_tokens": sum(lengths), "prompt_and_generated_tok_s": round((generated + sum(lengths)) / dt, 1),
         "decode_only": {"steps": decode_only["steps"],
-                        "tok_s": round(decode_only["tokens"] / decode_only["seconds"], 1) if decode_only["seconds"] else None},
+                        "tok_s": round(decode_only["tokens"] / decode_only["seconds"], 1) if decode_only["seconds"] else None,
+                        "ms_per_step": round(decode_only["seconds"] / decode_only["steps"] * 1e3, 3) if decode_only["steps"] else None,
+                        # bytes that the all-decode steps had to read / their wall time / the copy peak
+                        "roofline": ({"bound": "hbm", "achieved": round(decode_only["bytes"] / decode_only["seconds"] / 1e9, 1),
+                                      "peak": peaks["hbm_gbs"], "unit": "GB/s", "peaks": peaks["source"],
+                                      "frac": round(decode_only["bytes"] / decode_only["seconds"] / 1e9 / peaks["hbm_gbs"], 4)}
+                                     if decode_only["seconds"] else None)},
+        "clocks": clocks.summary(),
         "preemptions": sum(r.preemptions for r in reqs),
         "steps_planned_ahead": engine.steps_planned_ahead, "cache_tokens": engine.cache_tokens,
         "warm_up": None if warm is None else {"seconds": warm["seconds"], "graphs": warm["graphs"]},

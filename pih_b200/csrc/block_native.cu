@@ -53,8 +53,6 @@ int pih_qk_attention_fused(const void* qkv, int q_stride, void* out, void* cache
                            float scale, int window, int split, int max_splits, const int* max_ctx_ptr, float* scratch,
                            const void* kv_tensor_map, int norm_dtype, const void* q_norm_w, const void* k_norm_w,
                            float eps, const float* rope, int max_pos, int write_kv, uint32_t* error, void* stream);
-int pih_gemm_midrows(const void* x, const void* W, void* out, const void* residual, int M, int N, int K, long long ldx,
-                     long long ldw, long long ldo, int swiglu, void* stream);
 int pih_attention_prefill_tcgen05(const void* q, int q_stride, int rows, void* out, const int* block_table, int table_width,
                                   const int* cu_q, const int* q_start, int num_requests, int tile_max_q, int heads,
                                   int kv_heads, int head_dim, int page_size, int num_pages, float scale, int window,
@@ -76,7 +74,6 @@ struct PihStepArgs {                     // the same for every block of a step
   void* stream;
   void* library_workspace;               // for the library's products; allocated by the caller, capture-safe
   long long library_workspace_bytes;
-  int midrows;                           // products of 17 to 64 rows by the pack's cluster kernel (else the library's)
 };
 
 struct PihAttentionArgs {                // per step, cache group and attention geometry
@@ -180,10 +177,6 @@ int product(const PihStepArgs& s, const void* x, long long ldx, const void* w, l
             int M, int N, int K) {
   if (M <= 0 || N <= 0) return 0;
   if (s.dtype == PIH_F32) return pih_gemm_simt(PIH_F32, PIH_F32, x, w, out, M, N, K, ldx, ldw, ldo, s.stream);
-  if (s.midrows && M > 16 && M <= 64) {                    // a decode step of that many requests: the pack's own kernel
-    const int rc = pih_gemm_midrows(x, w, out, nullptr, M, N, K, ldx, ldw, ldo, 0, s.stream);
-    if (rc != PIH_ERR_UNSUPPORTED) return rc;
-  }
   Library* L = library();
   if (L == nullptr) return PIH_ERR_UNSUPPORTED;
   if (L->set_stream(L->handle, static_cast<cudaStream_t>(s.stream)) != 0) return PIH_ERR_UNSUPPORTED;
@@ -330,16 +323,8 @@ extern "C" int pih_prenorm_attention_swiglu_block(const PihStepArgs* sp, const P
   if (!done) {
     PIH_TRY(pih_rmsnorm(s.dtype, b->norm_w_dtype, h, pending, b->norm_post_w, b->xn, nullptr, T, H, b->norm_post_eps,
                         s.stream));
-    int rc = PIH_ERR_UNSUPPORTED;
-    if (s.midrows && s.dtype == PIH_BF16 && T > 16 && T <= 64 && b->interleave == 8)    // SiLU-mul in the product's epilogue
-      rc = pih_gemm_midrows(b->xn, b->w_gate_up, b->act, nullptr, T, 2 * I, H, H, b->ld_gate_up, I, 1, s.stream);
-    if (rc == PIH_ERR_UNSUPPORTED) {
-      PIH_TRY(product(s, b->xn, H, b->w_gate_up, b->ld_gate_up, b->gate_up, 2 * I, T, 2 * I, H));
-      PIH_TRY(pih_silu_mul(s.dtype, b->gate_up, b->act, T, I, b->interleave, s.stream));
-    } else {
-      if (rc != 0) return rc;
-      ++b->launched;
-    }
+    PIH_TRY(product(s, b->xn, H, b->w_gate_up, b->ld_gate_up, b->gate_up, 2 * I, T, 2 * I, H));
+    PIH_TRY(pih_silu_mul(s.dtype, b->gate_up, b->act, T, I, b->interleave, s.stream));
   }
 
   // ---- down product, the residual add in its epilogue for few rows

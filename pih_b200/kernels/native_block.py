@@ -22,7 +22,7 @@ class StepArgs(ctypes.Structure):
     _fields_ = [("dtype", c_int), ("rows", c_int), ("num_requests", c_int), ("skinny_max_rows", c_int),
                 ("fused_residual", c_int), ("positions", c_void_p), ("request_of_row", c_void_p), ("cu_q", c_void_p),
                 ("q_start", c_void_p), ("max_ctx_ptr", c_void_p), ("error", c_void_p), ("stream", c_void_p),
-                ("library_workspace", c_void_p), ("library_workspace_bytes", c_ll), ("midrows", c_int)]
+                ("library_workspace", c_void_p), ("library_workspace_bytes", c_ll)]
 
 
 class AttentionArgs(ctypes.Structure):
@@ -125,7 +125,6 @@ class NativeBlocks:
             a.error = ops.error_word.data_ptr()
             a.library_workspace = self._library_workspace.data_ptr()
             a.library_workspace_bytes = self.LIBRARY_WORKSPACE_BYTES
-            a.midrows = 1 if ops.midrows_product else 0
             st.args = a
             step._native = st
         return st

@@ -77,10 +77,6 @@ class CudaOps:
         self.tcgen05_swiglu_min_rows = None
         self.tcgen05_min_rows = None       # bf16 products with at least this many rows use the pack's tcgen05 kernel
         self.skinny_max_rows = 16          # bf16 products with at most this many rows use the fused few-rows kernel
-        # bf16 products of 17 to 64 rows by the pack's cluster kernel (gemm_midrows.cu).  Off: the library's products
-        # are faster on these shapes (32 rows, N x K = 4096 x 2048: 6.1 us against 8.3; 12288 x 2048: 11.9 + 2.3 of
-        # SiLU-mul against 21.3 fused; 2048 x 6144: 10.7 against 15.5).
-        self.midrows_product = False
         self.fused_residual = True         # ... and add the residual in the epilogue of output projections
         self.native_blocks = True          # blocks of the built-in parts are issued by one native call each
         self._native = None
@@ -92,7 +88,7 @@ class CudaOps:
         for name in ("pih_embedding", "pih_rmsnorm", "pih_qk_norm_rope_kv_write", "pih_silu_mul",
                      "pih_gather_rows", "pih_gemm_simt", "pih_paged_attention_generic", "pih_argmax",
                      "pih_sample", "pih_paged_attention_mma", "pih_gemm_tcgen05", "pih_make_kv_tensor_map",
-                     "pih_attention_prefill_tcgen05", "pih_gemm_skinny", "pih_gemm_midrows", "pih_set_dependent_launch", "pih_set_attention_cluster_merge",
+                     "pih_attention_prefill_tcgen05", "pih_gemm_skinny", "pih_set_dependent_launch", "pih_set_attention_cluster_merge",
                      "pih_gemm_skinny_f32out",
                      "pih_qk_attention_fused", "pih_gemm_tcgen05_swiglu"):
             getattr(lib, name).restype = c_int
@@ -196,10 +192,6 @@ class CudaOps:
             out = self.linear_skinny(x, w)
             if out is not None:
                 return out
-        if out_dtype == torch.bfloat16 and self.midrows_product and 16 < M <= 64:
-            out = self.linear_midrows(x, w)
-            if out is not None:
-                return out
         if out_dtype == torch.float32 and M <= self.skinny_max_rows and K % 32 == 0:
             out = torch.empty(M, N, dtype=torch.float32, device=x.device)
             rc = self.lib.pih_gemm_skinny_f32out(_ptr(x), _ptr(w), _ptr(out), M, N, K, c_ll(x.stride(0)),
@@ -236,23 +228,6 @@ class CudaOps:
             return None
         self._check(rc, "gemm_skinny")
         return out if delta is None else (x_out, out)
-
-    def linear_midrows(self, x: torch.Tensor, w: torch.Tensor, *, swiglu: bool = False,
-                       residual: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
-        """``x . w^T`` for 17 to 64 rows of bf16 by the cluster kernel that splits k over the blocks of a cluster
-        (``gemm_midrows.cu``), optionally with SiLU-mul (``w`` in blocks of 8 gate rows and their 8 up rows; the
-        result is ``[M, N / 2]``) or the residual add in its epilogue; None for shapes it does not take."""
-        M, K = x.shape
-        N = w.shape[0]
-        if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or x.stride(1) != 1 or w.stride(1) != 1:
-            return None
-        out = torch.empty(M, N // 2 if swiglu else N, dtype=torch.bfloat16, device=x.device)
-        rc = self.lib.pih_gemm_midrows(_ptr(x), _ptr(w), _ptr(out), _ptr(residual), M, N, K, c_ll(x.stride(0)),
-                                       c_ll(w.stride(0)), c_ll(out.stride(0)), 1 if swiglu else 0, self._stream())
-        if rc == -2:
-            return None
-        self._check(rc, "gemm_midrows")
-        return out
 
     def linear_add(self, x: torch.Tensor, w: torch.Tensor, residual: torch.Tensor):
         """``round(round(x . w^T) + residual)`` as one kernel — an output projection with the residual add that
@@ -294,10 +269,6 @@ class CudaOps:
                 if out is not None:
                     return h, out
         xn = self.rmsnorm(h, norm_weight, eps, delta=delta)
-        if swiglu_interleave == 8 and self.midrows_product and 16 < xn.shape[0] <= 64 and xn.dtype == torch.bfloat16:
-            out = self.linear_midrows(xn, w, swiglu=True)
-            if out is not None:
-                return h, out
         if (swiglu_interleave == 8 and self.tcgen05_swiglu_min_rows is not None
                 and xn.shape[0] >= self.tcgen05_swiglu_min_rows and xn.dtype == torch.bfloat16):
             out = self.linear_tcgen05_swiglu(xn, w)

@@ -212,48 +212,6 @@ def test_linear_skinny_fused_add_norm_and_swiglu(ops, M, norm_dtype):
     assert bool((err2 <= 2.1 * bound).all()), float((err2 / bound).max())
 
 
-@pytest.mark.parametrize("M", [17, 32, 33, 47, 64])
-@pytest.mark.parametrize("N,K", [(4096, 2048), (2048, 6144), (1024, 3072), (1000, 96), (40, 2048), (12288, 1024),
-                                 (2048, 12288), (24, 64)])
-def test_linear_midrows(ops, M, N, K):
-    """The product for 17 to 64 rows alone: clusters of 2, 4 and 8 blocks that split k (k parts of uneven length, a
-    block without k blocks), slices of one unit and of more units than warps, widths that are no multiple of 16."""
-    x = _rand((M, K), torch.bfloat16, 3)
-    w = _rand((N, K), torch.bfloat16, 4, 0.1)
-    out = ops.linear_midrows(x, w)
-    assert out is not None and out.shape == (M, N)
-    ref = x.cpu().double() @ w.cpu().double().T
-    torch.testing.assert_close(out.cpu().double(), ref, rtol=8e-3, atol=1e-3 * max(1.0, float(ref.abs().max()) / 4))
-    # a row gives the same bits among 17 others as among all (the same tiles of 16 rows, the same k parts)
-    if M > 17:
-        assert torch.equal(ops.linear_midrows(x[M - 17:].contiguous(), w)[-1], out[M - 1])
-    # the residual add in the epilogue: the bits of the separate add
-    h = _rand((M, N), torch.bfloat16, 5, 2.0)
-    fused = ops.linear_midrows(x, w, residual=h)
-    assert torch.equal(fused, (out.float() + h.float()).to(torch.bfloat16))
-    ops.check_errors()
-
-
-@pytest.mark.parametrize("M", [17, 40, 64])
-@pytest.mark.parametrize("K,inter", [(1024, 3072), (2048, 6144), (96, 24)])
-def test_linear_midrows_swiglu(ops, M, K, inter):
-    """SiLU-mul in the epilogue of the 17-to-64-row product: the bits of the product followed by the separate
-    SiLU-mul kernel (same sums, same rounding places)."""
-    x = _rand((M, K), torch.bfloat16, 5)
-    gate = _rand((inter, K), torch.bfloat16, 7, 0.05)
-    up = _rand((inter, K), torch.bfloat16, 8, 0.05)
-    w = torch.stack([gate.reshape(-1, 8, K), up.reshape(-1, 8, K)], dim=1).reshape(2 * inter, K).contiguous()
-    act = ops.linear_midrows(x, w, swiglu=True)
-    assert act is not None and act.shape == (M, inter)
-    gu = ops.linear_midrows(x, w)
-    g, u = gu.reshape(M, -1, 2, 8)[:, :, 0].reshape(M, inter).float(), gu.reshape(M, -1, 2, 8)[:, :, 1].reshape(M, inter).float()
-    want = ((g / (1.0 + torch.exp(-g))) * u)
-    torch.testing.assert_close(act.float(), want.to(torch.bfloat16).float(), rtol=8e-3, atol=1e-6)
-    act_ref = plain_impl.silu_mul(plain_impl.linear(x.cpu(), gate.cpu(), "bf16"), plain_impl.linear(x.cpu(), up.cpu(), "bf16"), "bf16")
-    torch.testing.assert_close(act.cpu().double(), act_ref, rtol=3e-2, atol=2e-3)
-    ops.check_errors()
-
-
 def test_silu_mul_interleaved(ops):
     for dtype in DTYPES:
         gu = _rand((5, 2 * 48), dtype, 9, 2.0)
