@@ -463,9 +463,80 @@ __global__ void argmax_final_kernel(const float* __restrict__ part_val, const in
   if (lane == 0) out_tokens[row] = best_id == 0x7fffffff ? 0 : best_id;
 }
 
+// The log-probability of the token that was chosen for a row: scaled[token] - logsumexp(scaled) over the ids that
+// are not suppressed, scaled = logit / temperature (1 when greedy), as the reference returns it with every sampled
+// token (plugins/model-qwen3/qwen3_sampler.cpp:116-126, :143).  One block a row, two passes over the row (maximum,
+// then the sum of exponentials); every sum in 32-bit with an order that depends on the block size alone.  The
+// reference adds the exponentials one after the other in float32, which over a vocabulary of 150 000 drops a few
+// thousandths of the mass; this sum does not.
+constexpr int kLogprobThreads = 256;
+constexpr int kLogprobMaxSuppressed = 17;
+__global__ void __launch_bounds__(kLogprobThreads)
+selected_logprob_kernel(const float* __restrict__ logits, int vocab, const int* __restrict__ tokens,
+                        const float* __restrict__ fparams, const int* __restrict__ iparams, int icolumns,
+                        float* __restrict__ out, uint32_t* error) {
+  wait_for_prior_kernels();
+  launch_dependents();
+  __shared__ float scratch[33];
+  __shared__ int suppressed[kLogprobMaxSuppressed];
+  const int row = blockIdx.x;
+  const float* x = logits + static_cast<size_t>(row) * vocab;
+  float temperature = fparams != nullptr ? fparams[row * 2] : 0.0f;
+  if (!(temperature > 0.0f)) temperature = 1.0f;
+  int nsup = 0;
+  if (iparams != nullptr) {
+    nsup = min(max(iparams[row * icolumns + 5], 0), kLogprobMaxSuppressed);
+    if (threadIdx.x < nsup) suppressed[threadIdx.x] = iparams[row * icolumns + 6 + threadIdx.x];
+  }
+  __syncthreads();
+  auto allowed = [&](int i) {
+    for (int k = 0; k < nsup; ++k)
+      if (suppressed[k] == i) return false;
+    return true;
+  };
+  float m = -INFINITY;
+  for (int i = threadIdx.x; i < vocab; i += kLogprobThreads)
+    if (nsup == 0 || allowed(i)) m = fmaxf(m, x[i] / temperature);
+  // block maximum
+  m = warp_max(m);
+  if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = m;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    float v = threadIdx.x < kLogprobThreads / 32 ? scratch[threadIdx.x] : -INFINITY;
+    v = warp_max(v);
+    if (threadIdx.x == 0) scratch[32] = v;
+  }
+  __syncthreads();
+  m = scratch[32];
+  float sum = 0.0f;
+  for (int i = threadIdx.x; i < vocab; i += kLogprobThreads)
+    if (nsup == 0 || allowed(i)) sum += expf(x[i] / temperature - m);
+  sum = block_sum(sum, scratch);
+  if (threadIdx.x == 0) {
+    const int tok = tokens[row];
+    float lp = -INFINITY;
+    if (tok >= 0 && tok < vocab && sum > 0.0f) lp = x[tok] / temperature - (m + logf(sum));
+    if (!isfinite(lp)) publish_error(error, kNonFiniteLogit);
+    out[row] = lp;
+  }
+}
+
 }  // namespace pih
 
 using namespace pih;
+
+// out[row] = log-probability of tokens[row] under the row's scaled logits.  fparams [rows, 2] (temperature, top_p)
+// and iparams [rows, icolumns] (column 5: the number of suppressed ids, columns 6..: the ids) as pih_sample takes
+// them, or both null: temperature 1, nothing suppressed (the greedy path).
+extern "C" int pih_selected_logprob(const float* logits, int rows, int vocab, const int* tokens, const float* fparams,
+                                    const int* iparams, int icolumns, float* out, uint32_t* error, void* stream) {
+  if (rows <= 0) return 0;
+  if (vocab <= 0 || (iparams != nullptr && icolumns < 6 + kLogprobMaxSuppressed)) return PIH_ERR_BAD_ARGUMENT;
+  launch_kernel(selected_logprob_kernel, dim3(rows), dim3(kLogprobThreads), 0, static_cast<cudaStream_t>(stream), logits,
+                vocab, tokens, fparams, iparams, icolumns, out, error);
+  PIH_LAUNCH_CHECK();
+  return 0;
+}
 
 // scratch: rows * 64 floats followed by rows * 64 ints (used when vocab is large); may be null,
 // in which case one block reduces each row.

@@ -38,11 +38,13 @@ RESULT_SCHEMA = "pih.token-generation-result.v1"
 
 
 class _Landing:
-    """Pinned host memory for what one step reports back: the ids it sampled and, behind them, the device's
-    error word as it stood after the step; with the event that says both have arrived."""
+    """Pinned host memory for what one step reports back: the ids it sampled, their log-probabilities where a
+    request asked for them, and, behind them, the device's error word as it stood after the step; with the
+    event that says all have arrived."""
 
     def __init__(self, rows: int):
-        self.buffer = torch.empty(rows + 1, dtype=torch.int32, pin_memory=True)
+        self.rows = rows
+        self.buffer = torch.empty(2 * rows + 1, dtype=torch.int32, pin_memory=True)
         self.event = torch.cuda.Event()
 
 
@@ -50,9 +52,10 @@ class _InFlight:
     """A step that has been queued on the device: its plan, the ids it samples, and the error word after it —
     both copied to pinned host memory right behind the step, before any later step."""
 
-    def __init__(self, out, tokens, error_word=None, landing: Optional[_Landing] = None):
+    def __init__(self, out, tokens, error_word=None, landing: Optional[_Landing] = None, logprobs=None):
         self.out = out
         self.tokens = tokens
+        self.logprobs = logprobs            # fp32 on the device, one per sampled id, or None
         self.landing = landing
         self.error_word = error_word
         self.rows = 0 if tokens is None else int(tokens.shape[0])
@@ -62,6 +65,8 @@ class _InFlight:
         if landing is not None:
             if tokens is not None:
                 landing.buffer[:self.rows].copy_(tokens, non_blocking=True)
+            if logprobs is not None:
+                landing.buffer[landing.rows:landing.rows + self.rows].copy_(logprobs.view(torch.int32), non_blocking=True)
             landing.buffer[-1:].copy_(error_word, non_blocking=True)
             landing.event.record()
 
@@ -86,6 +91,14 @@ class _InFlight:
             return self.tokens.tolist()
         self.wait()
         return self.landing.buffer[:self.rows].tolist()
+
+    def logprob_list(self) -> Optional[List[float]]:
+        if self.logprobs is None:
+            return None
+        if self.landing is None:
+            return self.logprobs.tolist()
+        self.wait()
+        return self.landing.buffer[self.landing.rows:self.landing.rows + self.rows].view(torch.float32).tolist()
 
 
 class Engine:
@@ -275,14 +288,17 @@ class Engine:
                    for s in out.scheduled]
         logits = self.runner.step(entries, token_feed=feed, confirm=False)
         sampling = [s.request for s in out.scheduled if s.samples]
-        tokens = None
+        tokens = logprobs = None
         if sampling:
+            wanted = any(r.params.logprobs for r in sampling)
             tokens = self.sampler.sample_on_device(
                 logits, [r.params for r in sampling], [len(r.outputs) + pending for r in sampling],
-                [self.scheduler.suppressed_ids(r, pending) for r in sampling])
+                [self.scheduler.suppressed_ids(r, pending) for r in sampling], **({"logprobs": True} if wanted else {}))
+            if wanted:
+                tokens, logprobs = tokens
         word = getattr(self.rt.ops, "error_word", None)
         on_gpu = self.device.type == "cuda" and word is not None
-        flight = _InFlight(out, tokens, word, self._landing() if on_gpu else None)
+        flight = _InFlight(out, tokens, word, self._landing() if on_gpu else None, logprobs)
         flight.holders = [(s.request.rid, self.cache.requests[s.request.rid]) for s in out.scheduled]
         self._unconfirmed.append(flight)
         return flight
@@ -338,13 +354,18 @@ class Engine:
         self._settle(flight if flight.tokens is not None else None)
         out = flight.out
         sampled: List[Optional[int]] = [None] * len(out.scheduled)
+        logprobs: List[Optional[float]] = [None] * len(out.scheduled)
         if flight.tokens is not None:
             it = iter(flight.token_list())
+            lp = flight.logprob_list()
+            lp_it = iter(lp) if lp is not None else None
             for i, s in enumerate(out.scheduled):
                 if s.samples:
                     sampled[i] = next(it)
+                    if lp_it is not None:
+                        logprobs[i] = next(lp_it)
         live = [s.request for s in out.scheduled if s.samples and s.request.status != "finished"]
-        self.scheduler.update(out, sampled)
+        self.scheduler.update(out, sampled, logprobs)
         progressed = live + list(out.failed)
         for req in progressed:
             if req.status == "finished":
@@ -386,8 +407,11 @@ class Engine:
     # -- whole generations ------------------------------------------------------------
     @staticmethod
     def _result(req: Request) -> dict:
-        return {"schema": RESULT_SCHEMA, "token_ids": list(req.outputs), "finish_reason": req.finish_reason,
-                "prompt_tokens": len(req.prompt), "completion_tokens": len(req.outputs)}
+        result = {"schema": RESULT_SCHEMA, "token_ids": list(req.outputs), "finish_reason": req.finish_reason,
+                  "prompt_tokens": len(req.prompt), "completion_tokens": len(req.outputs)}
+        if req.params.logprobs:
+            result["logprobs"] = list(req.output_logprobs)     # log-probability of each token under its scaled logits
+        return result
 
     @staticmethod
     def _params(max_tokens: int, parameters: dict) -> SamplingParams:

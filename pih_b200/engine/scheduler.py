@@ -55,6 +55,7 @@ class Request:
     params: SamplingParams
     eos_token_ids: Sequence[int] = ()
     outputs: List[int] = field(default_factory=list)
+    output_logprobs: List[float] = field(default_factory=list)     # one per output, when the request asked for them
     num_computed: int = 0
     status: str = "waiting"              # waiting | running | finished
     finish_reason: Optional[str] = None  # stop | length | capacity | cancelled | error
@@ -248,11 +249,13 @@ class Scheduler:
             self.cache.release(req.rid)
 
     # -- after the step ----------------------------------------------------------
-    def update(self, out: SchedulerOutput, sampled: Sequence[Optional[int]]) -> List[Request]:
+    def update(self, out: SchedulerOutput, sampled: Sequence[Optional[int]],
+               logprobs: Optional[Sequence[Optional[float]]] = None) -> List[Request]:
         """``sampled[i]`` is the token sampled for ``out.scheduled[i]`` (None
-        when that entry did not sample).  Returns the requests that finished."""
+        when that entry did not sample), ``logprobs[i]`` its log-probability where it was asked for.
+        Returns the requests that finished."""
         finished = []
-        for s, tok in zip(out.scheduled, sampled):
+        for i, (s, tok) in enumerate(zip(out.scheduled, sampled)):
             req = s.request
             if req.status == "finished":
                 continue                   # it ended while this step was in flight (planned ahead): dropped
@@ -262,6 +265,8 @@ class Scheduler:
             if tok is None:
                 raise ValueError(f"request {req.rid!r} reached its end but no token was sampled")
             req.outputs.append(int(tok))
+            if req.params.logprobs and logprobs is not None and logprobs[i] is not None:
+                req.output_logprobs.append(float(logprobs[i]))
             accepted = len(req.outputs)
             stops = set(req.params.stop_token_ids)
             if not req.params.ignore_eos:

@@ -87,7 +87,7 @@ class CudaOps:
         lib = self.lib
         for name in ("pih_embedding", "pih_rmsnorm", "pih_qk_norm_rope_kv_write", "pih_silu_mul",
                      "pih_gather_rows", "pih_gemm_simt", "pih_paged_attention_generic", "pih_argmax",
-                     "pih_sample", "pih_paged_attention_mma", "pih_gemm_tcgen05", "pih_make_kv_tensor_map",
+                     "pih_sample", "pih_selected_logprob", "pih_paged_attention_mma", "pih_gemm_tcgen05", "pih_make_kv_tensor_map",
                      "pih_attention_prefill_tcgen05", "pih_gemm_skinny", "pih_set_dependent_launch", "pih_set_attention_cluster_merge",
                      "pih_gemm_skinny_f32out",
                      "pih_qk_attention_fused", "pih_gemm_tcgen05_swiglu"):
@@ -499,6 +499,18 @@ class CudaOps:
         scratch = torch.empty(rows * 128, dtype=torch.float32, device=logits.device) if vocab >= 8192 else None
         rc = self.lib.pih_argmax(_ptr(logits), rows, vocab, _ptr(out), _ptr(scratch), self._err(), self._stream())
         self._check(rc, "argmax")
+        return out
+
+    def selected_logprob(self, logits: torch.Tensor, tokens: torch.Tensor, fparams: Optional[torch.Tensor] = None,
+                         iparams: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """The log-probability of ``tokens[row]`` under each row's scaled logits (fp32 ``[rows]``); the
+        parameters are those given to ``sample``, or none for greedy rows."""
+        rows, vocab = logits.shape
+        out = torch.empty(rows, dtype=torch.float32, device=logits.device)
+        rc = self.lib.pih_selected_logprob(_ptr(logits), rows, vocab, _ptr(tokens), _ptr(fparams), _ptr(iparams),
+                                           iparams.shape[1] if iparams is not None else 0, _ptr(out), self._err(),
+                                           self._stream())
+        self._check(rc, "selected_logprob")
         return out
 
     def sample(self, logits: torch.Tensor, fparams: torch.Tensor, iparams: torch.Tensor) -> torch.Tensor:

@@ -7,7 +7,10 @@ an omitted seed meaning 0 ("deliberately zero, not hidden host RNG state"),
 reference's descriptor (include/pih/model/qwen3_sampler.h:23;
 include/pih/scheduler/controller_request_arena.h:28-30) without an HTTP key;
 here they are plain options.  ``max_tokens`` defaults to 128
-(plugins/model-qwen3/entrypoint.cpp:252-254).
+(plugins/model-qwen3/entrypoint.cpp:252-254).  ``logprobs`` asks for what the
+reference's sampler returns with every token, ``selected_logprob``
+(plugins/model-qwen3/qwen3_sampler.cpp:143-149); its ``top_logprobs`` list is
+not returned.
 """
 from __future__ import annotations
 
@@ -27,6 +30,7 @@ class SamplingParams:
     minimum_new_tokens: int = 0
     ignore_eos: bool = False
     n: int = 1
+    logprobs: bool = False             # return the log-probability of every sampled token (the reference's selected_logprob)
 
     def __post_init__(self):
         if self.n != 1:

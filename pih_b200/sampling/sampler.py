@@ -68,13 +68,15 @@ class Sampler:
         return stage
 
     def sample_on_device(self, logits: torch.Tensor, params: Sequence[SamplingParams], ordinals: Sequence[int],
-                         suppressed: Sequence[Sequence[int]]) -> torch.Tensor:
-        """The sampled ids as an int32 tensor on the device, without waiting for them."""
+                         suppressed: Sequence[Sequence[int]], logprobs: bool = False):
+        """The sampled ids as an int32 tensor on the device, without waiting for them; with ``logprobs`` a pair
+        of the ids and the log-probability of each (fp32, on the device)."""
         S = logits.shape[0]
         if not (len(params) == len(ordinals) == len(suppressed) == S):
             raise ValueError("one set of sampling parameters per row of logits is needed")
         if all(p.greedy for p in params) and not any(suppressed):
-            return self.ops.argmax(logits)
+            ids = self.ops.argmax(logits)
+            return (ids, self.ops.selected_logprob(logits, ids)) if logprobs else ids
         stage = self._stage(S)
         host = stage[0][:S * (2 + _INT_COLUMNS)]
         view = host.numpy()
@@ -95,4 +97,6 @@ class Sampler:
         if stage[1] is not None:
             stage[1].record()
             stage[2] = True
-        return self.ops.sample(logits, dev[:2 * S].view(torch.float32).view(S, 2), dev[2 * S:].view(S, _INT_COLUMNS))
+        fparams, iparams = dev[:2 * S].view(torch.float32).view(S, 2), dev[2 * S:].view(S, _INT_COLUMNS)
+        ids = self.ops.sample(logits, fparams, iparams)
+        return (ids, self.ops.selected_logprob(logits, ids, fparams, iparams)) if logprobs else ids

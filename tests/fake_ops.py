@@ -119,6 +119,18 @@ class FakeOps:
     def argmax(self, logits):
         return torch.argmax(logits, dim=-1).to(torch.int32)
 
+    def selected_logprob(self, logits, tokens, fparams=None, iparams=None):
+        out = []
+        for i in range(logits.shape[0]):
+            t = float(fparams[i, 0]) if fparams is not None else 0.0
+            scaled = logits[i].double() / (t if t > 0 else 1.0)
+            keep = torch.ones(logits.shape[1], dtype=torch.bool)
+            if iparams is not None:
+                nsup = int(iparams[i, 5])
+                keep[[int(v) for v in iparams[i, 6:6 + nsup].tolist()]] = False
+            out.append(float(scaled[int(tokens[i])] - torch.logsumexp(scaled[keep], dim=0)))
+        return torch.tensor(out, dtype=torch.float32)
+
     def sample(self, logits, fparams, iparams):
         from plain_impl import sample
         out = []

@@ -149,3 +149,25 @@ def test_random_workloads_give_the_same_tokens_with_and_without_run_ahead(model_
         return {i: (r.outputs, r.finish_reason) for i, r in reqs.items() if i not in cancelled}
 
     assert run(True) == run(False)
+
+
+@pytest.mark.parametrize("temperature", [0.0, 0.9])
+def test_log_probabilities_come_back_with_the_tokens(model_dirs, tiny_configs, temperature):
+    """``logprobs=True``: one log-probability per generated token (the reference's selected_logprob), the same
+    with and without a step planned ahead, equal to the plain implementation's log-softmax of the scaled logits at
+    the token; a request that did not ask gets none."""
+    import plain_impl
+    import torch
+    from conftest import load_plain_weights
+    prompts = _prompts(tiny_configs["A"]["vocab_size"], [11, 4], seed=9)
+    per_prompt = [dict(logprobs=True), dict()]
+    kw = dict(max_tokens=7, temperature=temperature, seed=4, ignore_eos=True, parameters_per_prompt=per_prompt)
+    got = _engine(model_dirs["A"], True, page_size=16).complete_batch(prompts, **kw)
+    assert got == _engine(model_dirs["A"], False, page_size=16).complete_batch(prompts, **kw)
+    assert "logprobs" not in got[1] and len(got[0]["logprobs"]) == 7
+    cfg, w = load_plain_weights(model_dirs["A"])
+    tokens = prompts[0] + got[0]["token_ids"]
+    logits = plain_impl.forward(cfg, w, tokens)[len(prompts[0]) - 1:-1]
+    scaled = logits.double() / (temperature if temperature > 0 else 1.0)
+    want = torch.log_softmax(scaled, dim=-1)[torch.arange(7), torch.tensor(got[0]["token_ids"])]
+    torch.testing.assert_close(torch.tensor(got[0]["logprobs"], dtype=torch.float64), want, rtol=1e-4, atol=1e-4)

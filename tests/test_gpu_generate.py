@@ -268,3 +268,25 @@ def test_worker_command_line(model_dirs):
     cfg, w = load_plain_weights(model_dirs["A"])
     ref = plain_impl.generate_greedy(cfg, w, [5, 17, 3, 200], len(res["token_ids"]))
     assert res["token_ids"] == ref
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_log_probabilities_through_the_entry_point(model_dirs, tiny_configs, dtype):
+    """``logprobs=True`` on the GPU, graphs and run-ahead on: one log-probability per token, equal to the plain
+    implementation's log-softmax at the tokens that the engine chose (greedy and sampled requests in one batch)."""
+    from pih_b200.engine import Engine
+    vocab = tiny_configs["A"]["vocab_size"]
+    prompts = list(traces.make_requests(vocab, [23, 9, 40], seed=15).values())
+    e = Engine(model_dirs["A"], dtype, page_size=16, max_cache_tokens=1024, maximum_batch_sequences=4)
+    per = [dict(logprobs=True), dict(logprobs=True, temperature=0.8, seed=3), dict()]
+    got = e.complete_batch(prompts, max_tokens=9, ignore_eos=True, parameters_per_prompt=per)
+    e.drain()
+    e.rt.ops.check_errors()
+    assert "logprobs" not in got[2]
+    cfg, w = load_plain_weights(model_dirs["A"])
+    for r, prompt, temperature in ((got[0], prompts[0], 1.0), (got[1], prompts[1], 0.8)):
+        assert len(r["logprobs"]) == 9 and all(lp <= 0.0 for lp in r["logprobs"])
+        logits = plain_impl.forward(cfg, w, prompt + r["token_ids"])[len(prompt) - 1:-1].double()
+        want = torch.log_softmax(logits / temperature, dim=-1)[torch.arange(9), torch.tensor(r["token_ids"])]
+        tol = 1e-3 if dtype == "float32" else 0.25           # bf16: the logits themselves carry rounding
+        torch.testing.assert_close(torch.tensor(r["logprobs"], dtype=torch.float64), want, rtol=tol, atol=tol)

@@ -526,6 +526,43 @@ def test_sampler_matches_the_plain_definition(ops, vocab):
         assert got[i] == ref, (i, rows[i], got[i], ref)
 
 
+@pytest.mark.parametrize("vocab", [384, 5000, 151936])
+def test_selected_logprob(ops, vocab):
+    """The log-probability of the chosen token (the reference's selected_logprob): greedy rows, sampled rows at
+    several temperatures, rows with suppressed ids — against the exact value in float64 and, where the
+    reference's sequential float32 sum is still accurate, against the plain sampler."""
+    from pih_b200.sampling import Sampler, SamplingParams
+    g = torch.Generator().manual_seed(21)
+    S = 12
+    logits = torch.randn(S, vocab, generator=g) * 3.0
+    rows = []
+    for i in range(S):
+        t = [0.0, 0.7, 1.0, 2.0][i % 4]
+        sup = [] if i % 3 else [int(torch.argmax(logits[i])), 5]
+        rows.append((t, 1.0 if t == 0.0 else 0.9, None, 77 + i, 2 * i, sup))
+    sampler = Sampler(ops, vocab, torch.device(DEV))
+    params = [SamplingParams(temperature=t, top_p=p, top_k=k, seed=s) for (t, p, k, s, o, sup) in rows]
+    ids, lps = sampler.sample_on_device(logits.to(DEV), params, [r[4] for r in rows], [r[5] for r in rows], logprobs=True)
+    ids, lps = ids.tolist(), lps.tolist()
+    ops.check_errors()
+    for i, (t, p, k, seed, ordinal, sup) in enumerate(rows):
+        scaled = logits[i].double() / (t if t > 0 else 1.0)
+        keep = torch.ones(vocab, dtype=torch.bool)
+        keep[sup] = False
+        exact = float(scaled[ids[i]] - torch.logsumexp(scaled[keep], dim=0))
+        assert abs(lps[i] - exact) <= 2e-5 * max(1.0, abs(exact)), (i, lps[i], exact)
+        if vocab <= 5000:
+            tok, ref, _ = plain_impl.sample(logits[i].tolist(), temperature=t, top_p=p, top_k=k, seed=seed,
+                                            ordinal=ordinal, suppressed=sup)
+            assert tok == ids[i] and abs(lps[i] - ref) <= 2e-5 * max(1.0, abs(ref))
+    # all rows greedy and nothing suppressed: the argmax path
+    greedy = [SamplingParams()] * S
+    ids, lps = sampler.sample_on_device(logits.to(DEV), greedy, [0] * S, [[]] * S, logprobs=True)
+    want = torch.log_softmax(logits.double(), dim=-1).max(dim=-1).values
+    torch.testing.assert_close(lps.cpu().double(), want, rtol=2e-5, atol=2e-5)
+    assert ids.tolist() == torch.argmax(logits, dim=-1).tolist()
+
+
 def test_sampler_at_the_full_vocabulary(ops):
     """The vocabulary that serving samples from (151 936): the radix selection's two-level counts and the
     fixed-point mass over 150 000 terms.  Temperature alone, top-k 50, top-p 0.9, both, a suppressed arg-max,
