@@ -62,7 +62,7 @@ def step_of(lens, new, dev):
 
 def main() -> int:
     ap = argparse.ArgumentParser()
-    ap.add_argument("kernel", choices=["attn_decode", "attn_prefill", "linear", "rmsnorm", "qk", "silu", "argmax"])
+    ap.add_argument("kernel", choices=["attn_decode", "attn_prefill", "linear", "rmsnorm", "qk", "silu", "argmax", "sample"])
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--ctx", type=int, default=2048)
     ap.add_argument("--ctx-min", type=int, default=0, help="attn_decode: the shortest context (default: all --ctx)")
@@ -76,6 +76,8 @@ def main() -> int:
     ap.add_argument("--n", type=int, default=4096)
     ap.add_argument("--k", type=int, default=1024)
     ap.add_argument("--rows", type=int, default=8)
+    ap.add_argument("--top-p", type=float, default=1.0, help="sample: nucleus share")
+    ap.add_argument("--top-k", type=int, default=0, help="sample: keep this many (0: all)")
     ap.add_argument("--width", type=int, default=1024)
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--no-flush", action="store_true")
@@ -194,8 +196,14 @@ def main() -> int:
             gu = torch.randn(args.rows, 2 * 3072, device=dev).to(bf)
             rates.update(bytes=args.rows * 3072 * 2 * 3, rows=args.rows)
             return (lambda: ops.silu_mul(gu)), gu.numel() * 3
-        lg = torch.randn(args.rows, 151936, device=dev)
+        lg = torch.randn(args.rows, 151936, device=dev) * 3.0
         rates.update(bytes=args.rows * 151936 * 4, rows=args.rows)
+        if k == "sample":                               # temperature 0.7 over the whole vocabulary, top_p / top_k as given
+            from pih_b200.sampling import Sampler, SamplingParams
+            sampler = Sampler(ops, 151936, dev)
+            params = [SamplingParams(temperature=0.7, top_p=args.top_p, top_k=args.top_k or None, seed=i) for i in range(args.rows)]
+            rates.update(top_p=args.top_p, top_k=args.top_k)
+            return (lambda: sampler.sample_on_device(lg, params, list(range(args.rows)), [[]] * args.rows)), lg.numel() * 4
         return (lambda: ops.argmax(lg)), lg.numel() * 4
 
     if args.chain:

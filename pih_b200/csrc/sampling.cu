@@ -130,13 +130,33 @@ __device__ Prefix find_crossing(const RowView& rv, const Prefix& p, bool use_mas
     for (int i = threadIdx.x; i < 256; i += blockDim.x) hist[i] = 0;
     __syncthreads();
     const uint32_t want = s_prefix_val;
-    for (int id = threadIdx.x; id < rv.vocab; id += blockDim.x) {
-      if (!allowed(rv, id)) continue;
-      const float s = scaled_of(rv, id);
-      const uint32_t key = ordered_key(s);
-      if ((key & mask) != want || !member(p, key, id)) continue;
-      const unsigned long long a = use_mass ? mass_of(rv, s) : 1ull;
-      if (a) atomicAdd(&hist[(key >> shift) & 255u], a);
+    // A warp adds up what its lanes have for the same digit and sends one atomic addition per digit: a row of
+    // logits has most of its keys under two or three values of the leading digit (sign and exponent), and 150 000
+    // additions to three words of shared memory, one after the other, took 2 ms a row.  (Integer sums: the
+    // order does not matter.)
+    for (int base = 0; base < rv.vocab; base += blockDim.x) {
+      const int id = base + threadIdx.x;
+      int digit = -1;
+      unsigned long long a = 0ull;
+      if (id < rv.vocab && allowed(rv, id)) {
+        const float s = scaled_of(rv, id);
+        const uint32_t key = ordered_key(s);
+        if ((key & mask) == want && member(p, key, id)) {
+          a = use_mass ? mass_of(rv, s) : 1ull;
+          if (a) digit = static_cast<int>((key >> shift) & 255u);
+        }
+      }
+      unsigned todo = __ballot_sync(0xffffffffu, digit >= 0);
+      while (todo) {
+        const int leader = __ffs(todo) - 1;
+        const int d = __shfl_sync(0xffffffffu, digit, leader);
+        const unsigned same = __ballot_sync(0xffffffffu, digit == d);
+        unsigned long long v = digit == d ? a : 0ull;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+        if ((threadIdx.x & 31) == leader) atomicAdd(&hist[d], v);
+        todo &= ~same;
+      }
     }
     __syncthreads();
     if (threadIdx.x == 0) {
