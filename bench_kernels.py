@@ -199,11 +199,15 @@ def main() -> int:
         lg = torch.randn(args.rows, 151936, device=dev) * 3.0
         rates.update(bytes=args.rows * 151936 * 4, rows=args.rows)
         if k == "sample":                               # temperature 0.7 over the whole vocabulary, top_p / top_k as given
-            from pih_b200.sampling import Sampler, SamplingParams
-            sampler = Sampler(ops, 151936, dev)
-            params = [SamplingParams(temperature=0.7, top_p=args.top_p, top_k=args.top_k or None, seed=i) for i in range(args.rows)]
+            # the kernel alone: its per-row parameters are on the device already (temperature, top_p | top_k, seed,
+            # ordinal, no suppressed ids), as pih_b200/sampling/sampler.py lays them out
+            fparams = torch.tensor([[0.7, args.top_p]] * args.rows, dtype=torch.float32, device=dev)
+            iparams = torch.full((args.rows, 23), -1, dtype=torch.int32)
+            for i in range(args.rows):
+                iparams[i, :6] = torch.tensor([args.top_k, i, 0, i, 0, 0], dtype=torch.int32)
+            iparams = iparams.to(dev)
             rates.update(top_p=args.top_p, top_k=args.top_k)
-            return (lambda: sampler.sample_on_device(lg, params, list(range(args.rows)), [[]] * args.rows)), lg.numel() * 4
+            return (lambda: ops.sample(lg, fparams, iparams)), lg.numel() * 4
         return (lambda: ops.argmax(lg)), lg.numel() * 4
 
     if args.chain:

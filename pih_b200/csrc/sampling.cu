@@ -1,4 +1,4 @@
-// Sampling on the device: one block per row of logits.
+// Sampling on the device: a thread-block cluster per row of logits.
 //
 // The reference samples with ONE THREAD per row and an in-place heapsort of
 // the whole vocabulary (kernels/cuda/qwen_bf16_primitives.cu:894-999; CPU
@@ -52,14 +52,80 @@ __device__ uint32_t philox_word(uint32_t key0, uint32_t key1, uint64_t ordinal) 
   return w[ordinal & 3];
 }
 
+// ---- a row is sampled by a CLUSTER of blocks ---------------------------------------------------------------------
+// One block a row (what this kernel was first) made a row's eight to twenty passes over 150 000 logits the work
+// of one SM: 0.84 ms for a step's sampled rows however few, on top of a decode step of 1 ms.  Now block c of a
+// cluster of kSampleCluster takes the ids [c V/C, (c+1) V/C) of the row.  Whatever the single block summed over the
+// row — the maximum, masses, the 256 counts of a radix pass, the number of ties — each block sums over its part
+// and the blocks exchange through distributed shared memory: a block writes its words into one of two exchange
+// areas in turn, a cluster barrier follows, and every block reads all blocks' words and combines them in rank order,
+// so all blocks go on with the same values.  (Two areas: a block can only be one barrier ahead of the slowest
+// reader.)  Sums are integers, so nothing depends on how the row is cut.
+constexpr int kSampleCluster = 8;
+constexpr int kSampleBlock = 512;
+constexpr int kExchangeWords = 4;
+constexpr int kSampleCopies = 8;
+
+__device__ __forceinline__ uint32_t sample_cluster_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void sample_cluster_sync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ unsigned long long load_u64_from_block(const unsigned long long* local, uint32_t rank) {
+  const uint32_t a = static_cast<uint32_t>(__cvta_generic_to_shared(local));
+  uint32_t remote;
+  unsigned long long v;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(a), "r"(rank));
+  asm volatile("ld.shared::cluster.u64 %0, [%1];" : "=l"(v) : "r"(remote) : "memory");
+  return v;
+}
+
+__device__ __forceinline__ uint32_t load_u32_from_block(const uint32_t* local, uint32_t rank) {
+  const uint32_t a = static_cast<uint32_t>(__cvta_generic_to_shared(local));
+  uint32_t remote, v;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(a), "r"(rank));
+  asm volatile("ld.shared::cluster.u32 %0, [%1];" : "=r"(v) : "r"(remote) : "memory");
+  return v;
+}
+
+struct SampleShared {
+  // this block's counts of a radix pass, two in turn, as three limbs of 15 bits each summed in 32 bits (a block's
+  // part is at most 2^16 ids): 32-bit additions to shared memory are one instruction, 64-bit ones a loop
+  uint32_t hist[2][3][256];
+  // Copies of the counts for pairs of warps: a row's masses fall on few digits, and additions to one word of shared
+  // memory are done one after the other whichever warps they come from (measured: one copy a block 70 us a pass;
+  // adding up a warp's lanes per digit first — match.any, redux.sync — no better, because a warp's dozen distinct
+  // digits are worked off one after the other as well).
+  uint32_t priv[kSampleCopies][3][256];
+  unsigned long long ghist[256];                         // the row's
+  unsigned long long mine[2][kExchangeWords];            // this block's words of an exchange, two in turn
+  unsigned long long all[kSampleCluster][kExchangeWords];
+  unsigned long long scratch[40];
+  int iscratch[40];
+  int sup[kMaxSuppressed];
+  float val[32];
+  int idx[32];
+  uint32_t prefix_val;
+  unsigned long long acc;
+  unsigned long long a0;
+  int found;
+};
+
 struct RowView {
   const float* logits;
   int vocab;
-  float inv_unused;
+  int lo, hi;             // this block's ids
+  const float* staged;    // scaled values of this block's ids in shared memory, or null (the part does not fit)
   float temperature;      // divisor (1 when greedy)
   float max_scaled;
   int nsup;
   const int* sup;         // in shared memory
+  int phase;              // which exchange area / counts come next
+  int hphase;
+  uint32_t rank;
 };
 
 __device__ __forceinline__ bool allowed(const RowView& rv, int id) {
@@ -68,7 +134,9 @@ __device__ __forceinline__ bool allowed(const RowView& rv, int id) {
   return true;
 }
 
-__device__ __forceinline__ float scaled_of(const RowView& rv, int id) { return rv.logits[id] / rv.temperature; }
+__device__ __forceinline__ float scaled_of(const RowView& rv, int id) {
+  return rv.staged != nullptr ? rv.staged[id - rv.lo] : rv.logits[id] / rv.temperature;
+}
 
 __device__ __forceinline__ unsigned long long mass_of(const RowView& rv, float scaled) {
   return __double2ull_rd(static_cast<double>(expf(scaled - rv.max_scaled)) * kFixedOne);
@@ -100,86 +168,154 @@ __device__ unsigned long long block_sum_u64(unsigned long long v, unsigned long 
   return scratch[32];
 }
 
-// total count (use_mass = false) or mass of the members of `p`
-__device__ unsigned long long prefix_total(const RowView& rv, const Prefix& p, bool use_mass,
-                                           unsigned long long* scratch) {
+// Every block gives kExchangeWords words (thread 0's `w`) and gets all blocks' words in sm.all[rank][word].
+// Called by every thread of every block of the cluster.
+__device__ void exchange(SampleShared& sm, RowView& rv, const unsigned long long (&w)[kExchangeWords]) {
+  if (threadIdx.x == 0) {
+#pragma unroll
+    for (int k = 0; k < kExchangeWords; ++k) sm.mine[rv.phase][k] = w[k];
+  }
+  sample_cluster_sync();                               // (a block barrier too: thread 0's stores are in place)
+  if (threadIdx.x < kSampleCluster * kExchangeWords)
+    sm.all[threadIdx.x / kExchangeWords][threadIdx.x % kExchangeWords] =
+        load_u64_from_block(&sm.mine[rv.phase][threadIdx.x % kExchangeWords], threadIdx.x / kExchangeWords);
+  __syncthreads();
+  rv.phase ^= 1;
+}
+
+// total count (use_mass = false) or mass of the members of `p`, over the whole row
+__device__ unsigned long long prefix_total(SampleShared& sm, RowView& rv, const Prefix& p, bool use_mass) {
   unsigned long long local = 0;
-  for (int id = threadIdx.x; id < rv.vocab; id += blockDim.x) {
+  for (int id = rv.lo + threadIdx.x; id < rv.hi; id += blockDim.x) {
     if (!allowed(rv, id)) continue;
     const float s = scaled_of(rv, id);
     if (!member(p, ordered_key(s), id)) continue;
     local += use_mass ? mass_of(rv, s) : 1ull;
   }
-  return block_sum_u64(local, scratch);
+  const unsigned long long w[kExchangeWords] = {block_sum_u64(local, sm.scratch), 0ull, 0ull, 0ull};
+  exchange(sm, rv, w);
+  unsigned long long total = 0;
+#pragma unroll
+  for (int r = 0; r < kSampleCluster; ++r) total += sm.all[r][0];
+  __syncthreads();
+  return total;
 }
 
-// First place, in sorted order among the members of `p`, where the running total
-// (count or mass) reaches `target` (1 <= target <= total of p).
-__device__ Prefix find_crossing(const RowView& rv, const Prefix& p, bool use_mass,
-                                unsigned long long target, unsigned long long* hist /*256*/,
-                                unsigned long long* scratch /*40*/, int* iscratch /*40*/) {
-  __shared__ uint32_t s_prefix_val;
-  __shared__ unsigned long long s_acc;
+// First place, in sorted order among the members of `p`, where the running total (count or mass) reaches a target
+// (1 <= target <= total of p).  The target is `target` itself (kTargetGiven), or follows from the total of p, which
+// the first radix pass yields on the way (a pass over the row saved): the least total that is at least `share` of
+// it (kTargetShare: top_p) or the place of the draw `share` in it (kTargetDraw).
+enum TargetKind { kTargetGiven, kTargetShare, kTargetDraw };
+__device__ Prefix find_crossing(SampleShared& sm, RowView& rv, const Prefix& p, bool use_mass, TargetKind kind,
+                                unsigned long long target, double share) {
   if (threadIdx.x == 0) {
-    s_prefix_val = 0;
-    s_acc = 0;
+    sm.prefix_val = 0;
+    sm.acc = 0;
   }
   uint32_t mask = 0;
   for (int pass = 0; pass < 4; ++pass) {
     const int shift = 24 - 8 * pass;
-    for (int i = threadIdx.x; i < 256; i += blockDim.x) hist[i] = 0;
+    uint32_t (*hist)[256] = sm.hist[rv.hphase];
+    uint32_t (*mine)[256] = sm.priv[(threadIdx.x >> 5) % kSampleCopies];
+    for (int i = threadIdx.x; i < kSampleCopies * 3 * 256; i += blockDim.x) (&sm.priv[0][0][0])[i] = 0;
     __syncthreads();
-    const uint32_t want = s_prefix_val;
-    // A warp adds up what its lanes have for the same digit and sends one atomic addition per digit: a row of
-    // logits has most of its keys under two or three values of the leading digit (sign and exponent), and 150 000
-    // additions to three words of shared memory, one after the other, took 2 ms a row.  (Integer sums: the
-    // order does not matter.)
-    for (int base = 0; base < rv.vocab; base += blockDim.x) {
-      const int id = base + threadIdx.x;
-      int digit = -1;
-      unsigned long long a = 0ull;
-      if (id < rv.vocab && allowed(rv, id)) {
-        const float s = scaled_of(rv, id);
-        const uint32_t key = ordered_key(s);
-        if ((key & mask) == want && member(p, key, id)) {
-          a = use_mass ? mass_of(rv, s) : 1ull;
-          if (a) digit = static_cast<int>((key >> shift) & 255u);
-        }
-      }
-      unsigned todo = __ballot_sync(0xffffffffu, digit >= 0);
-      while (todo) {
-        const int leader = __ffs(todo) - 1;
-        const int d = __shfl_sync(0xffffffffu, digit, leader);
-        const unsigned same = __ballot_sync(0xffffffffu, digit == d);
-        unsigned long long v = digit == d ? a : 0ull;
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-        if ((threadIdx.x & 31) == leader) atomicAdd(&hist[d], v);
-        todo &= ~same;
-      }
+    const uint32_t want = sm.prefix_val;
+    for (int id = rv.lo + threadIdx.x; id < rv.hi; id += blockDim.x) {
+      if (!allowed(rv, id)) continue;
+      const float s = scaled_of(rv, id);
+      const uint32_t key = ordered_key(s);
+      if ((key & mask) != want || !member(p, key, id)) continue;
+      const unsigned long long a = use_mass ? mass_of(rv, s) : 1ull;
+      if (a == 0ull) continue;
+      const int digit = static_cast<int>((key >> shift) & 255u);
+      // a mass is at most 2^44: three limbs of 15 bits
+      const uint32_t a0 = static_cast<uint32_t>(a) & 0x7FFFu, a1 = static_cast<uint32_t>(a >> 15) & 0x7FFFu,
+                     a2 = static_cast<uint32_t>(a >> 30);
+      if (a0) atomicAdd(&mine[0][digit], a0);
+      if (a1) atomicAdd(&mine[1][digit], a1);
+      if (a2) atomicAdd(&mine[2][digit], a2);
     }
     __syncthreads();
-    if (threadIdx.x == 0) {
-      unsigned long long acc = s_acc;
-      int digit = 0;
-      for (int d = 255; d >= 0; --d) {
-        if (acc + hist[d] >= target) {
-          digit = d;
-          break;
-        }
-        acc += hist[d];
+    for (int i = threadIdx.x; i < 3 * 256; i += blockDim.x) {
+      uint32_t t = 0;
+#pragma unroll
+      for (int c = 0; c < kSampleCopies; ++c) t += (&sm.priv[c][0][0])[i];
+      (&hist[0][0])[i] = t;
+    }
+    sample_cluster_sync();                             // every block's counts are complete
+    for (int i = threadIdx.x; i < 256; i += blockDim.x) {
+      uint32_t part[kSampleCluster][3];
+#pragma unroll
+      for (int r = 0; r < kSampleCluster; ++r)                 // (all on their way at once)
+#pragma unroll
+        for (int k = 0; k < 3; ++k) part[r][k] = load_u32_from_block(&hist[k][i], r);
+      unsigned long long g = 0;
+#pragma unroll
+      for (int r = 0; r < kSampleCluster; ++r)
+        g += static_cast<unsigned long long>(part[r][0]) + (static_cast<unsigned long long>(part[r][1]) << 15) +
+             (static_cast<unsigned long long>(part[r][2]) << 30);
+      sm.ghist[i] = g;
+    }
+    rv.hphase ^= 1;
+    __syncthreads();
+    if (pass == 0 && kind != kTargetGiven) {
+      // the total of p: the sum of the first pass's counts (every block has the same counts and finds the same)
+      unsigned long long total = 0;
+      for (int i = 0; i < 256; ++i) total += sm.ghist[i];
+      if (kind == kTargetShare) target = __double2ull_ru(share * static_cast<double>(total));
+      else target = __double2ull_rd(share * static_cast<double>(total)) + 1ull;
+      target = min(max(target, 1ull), total);
+    }
+    // the digit at which the running total, from the largest digit down, reaches the target: warp 0, a lane per
+    // eight digits (lane 0 the largest), a scan over the lanes' sums, then the lane that holds the crossing walks
+    // its eight
+    if (threadIdx.x < 32) {
+      const int ln = threadIdx.x;
+      unsigned long long eight[8], sum = 0;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        eight[j] = sm.ghist[255 - (ln * 8 + j)];
+        sum += eight[j];
       }
-      s_acc = acc;
-      s_prefix_val = want | (static_cast<uint32_t>(digit) << shift);
+      unsigned long long incl = sum;
+#pragma unroll
+      for (int d = 1; d < 32; d <<= 1) {
+        const unsigned long long n = __shfl_up_sync(0xffffffffu, incl, d);
+        if (ln >= d) incl += n;
+      }
+      const unsigned long long base = sm.acc + incl - sum;      // the total before this lane's digits
+      const bool here = base < target && base + sum >= target;
+      const unsigned found = __ballot_sync(0xffffffffu, here);
+      // (a target beyond the row's total cannot happen: callers clamp it; digit 0 then)
+      if (found == 0u ? ln == 31 : ln == __ffs(found) - 1) {
+        unsigned long long acc = base;
+        int digit = 0;
+        if (found != 0u) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            if (acc + eight[j] >= target) {
+              digit = 255 - (ln * 8 + j);
+              break;
+            }
+            acc += eight[j];
+          }
+        } else {
+          acc = base + sum;
+        }
+        sm.acc = acc;
+        sm.prefix_val = want | (static_cast<uint32_t>(digit) << shift);
+      }
     }
     mask |= 255u << shift;
     __syncthreads();
   }
-  const uint32_t key_c = s_prefix_val;
-  const unsigned long long acc = s_acc;
-  // members with exactly this key share one weight; how many of them are needed
-  const int chunk = (rv.vocab + blockDim.x - 1) / blockDim.x;
-  const int lo = threadIdx.x * chunk, hi = min(rv.vocab, lo + chunk);
+  const uint32_t key_c = sm.prefix_val;
+  const unsigned long long acc = sm.acc;
+  // members with exactly this key share one weight; how many of them are needed.  Ties are counted in id order:
+  // a thread takes a run of consecutive ids of this block's part, and the blocks' parts follow one another.
+  const int span = rv.hi - rv.lo;
+  const int chunk = (span + blockDim.x - 1) / blockDim.x;
+  const int lo = rv.lo + threadIdx.x * chunk, hi = min(rv.hi, lo + chunk);
   int mine = 0;
   unsigned long long a0 = 1ull;
   for (int id = lo; id < hi; ++id) {
@@ -200,32 +336,51 @@ __device__ Prefix find_crossing(const RowView& rv, const Prefix& p, bool use_mas
     if (lane >= d) incl += n;
   }
   __syncthreads();
-  if (lane == 31) iscratch[warp] = incl;
+  if (lane == 31) sm.iscratch[warp] = incl;
+  if (threadIdx.x == 0) sm.a0 = 0ull;
   __syncthreads();
   if (warp == 0) {
-    int w = lane < (blockDim.x >> 5) ? iscratch[lane] : 0;
+    int w = lane < (blockDim.x >> 5) ? sm.iscratch[lane] : 0;
     int wi = w;
 #pragma unroll
     for (int d = 1; d < 32; d <<= 1) {
       const int n = __shfl_up_sync(0xffffffffu, wi, d);
       if (lane >= d) wi += n;
     }
-    iscratch[lane] = wi - w;          // exclusive prefix of the warp totals
-    if (lane == 31) iscratch[32] = wi;  // number of ties
+    sm.iscratch[lane] = wi - w;          // exclusive prefix of the warp totals
+    if (lane == 31) sm.iscratch[32] = wi;  // this block's ties
   }
   __syncthreads();
-  const int before = iscratch[warp] + incl - mine;
-  const int ties = iscratch[32];
-  // every tie has weight a0 (> 0 where mass is used: a zero weight cannot reach the target)
-  __shared__ unsigned long long s_a0;
-  if (mine > 0 && before == 0) s_a0 = a0;
+  const int before_in_block = sm.iscratch[warp] + incl - mine;
+  const int block_ties = sm.iscratch[32];
+  if (mine > 0 && before_in_block == 0) sm.a0 = a0;       // (every tie has the same weight)
   __syncthreads();
-  const unsigned long long w0 = use_mass ? s_a0 : 1ull;
+  {
+    const unsigned long long w[kExchangeWords] = {static_cast<unsigned long long>(block_ties), sm.a0, 0ull, 0ull};
+    exchange(sm, rv, w);
+  }
+  int ties = 0, before_block = 0;
+  unsigned long long w0 = 1ull;
+  bool have = false;
+#pragma unroll
+  for (int r = 0; r < kSampleCluster; ++r) {
+    const int t = static_cast<int>(sm.all[r][0]);
+    if (static_cast<uint32_t>(r) < rv.rank) before_block += t;
+    if (t > 0 && !have) {
+      w0 = sm.all[r][1];
+      have = true;
+    }
+    ties += t;
+  }
+  if (!use_mass) w0 = 1ull;
+  // every tie has weight w0 (> 0 where mass is used: a zero weight cannot reach the target)
   unsigned long long need = w0 ? (target - acc + w0 - 1) / w0 : 1ull;
   if (need < 1) need = 1;
   if (need > static_cast<unsigned long long>(ties)) need = ties;
   const int r = static_cast<int>(need);               // the r-th tie in id order, 1-based
-  __shared__ int s_id;
+  const int before = before_block + before_in_block;
+  if (threadIdx.x == 0) sm.found = -1;
+  __syncthreads();
   if (mine > 0 && before < r && r <= before + mine) {
     int seen = before;
     for (int id = lo; id < hi; ++id) {
@@ -233,61 +388,80 @@ __device__ Prefix find_crossing(const RowView& rv, const Prefix& p, bool use_mas
       const uint32_t key = ordered_key(scaled_of(rv, id));
       if (key == key_c && member(p, key, id)) {
         if (++seen == r) {
-          s_id = id;
+          sm.found = id;
           break;
         }
       }
     }
   }
   __syncthreads();
+  {
+    const unsigned long long w[kExchangeWords] = {static_cast<unsigned long long>(static_cast<long long>(sm.found)), 0ull, 0ull, 0ull};
+    exchange(sm, rv, w);
+  }
   Prefix out;
   out.key = key_c;
-  out.id = s_id;
+  out.id = 0;
+#pragma unroll
+  for (int q = 0; q < kSampleCluster; ++q) {
+    const long long f = static_cast<long long>(sm.all[q][0]);
+    if (f >= 0) out.id = static_cast<int>(f);
+  }
   __syncthreads();
   return out;
 }
 
-__global__ void __launch_bounds__(kSampleThreads)
+__global__ void __launch_bounds__(kSampleBlock)
 sample_kernel(const float* __restrict__ logits, int vocab, const float* __restrict__ fparams,
-              const int* __restrict__ iparams, int* __restrict__ out_tokens, uint32_t* error) {
+              const int* __restrict__ iparams, int* __restrict__ out_tokens, int staged_floats, uint32_t* error) {
   wait_for_prior_kernels();
   launch_dependents();                                   // (the next kernel's blocks may become resident and wait)
-  __shared__ int s_sup[kMaxSuppressed];
-  __shared__ unsigned long long s_hist[256];
-  __shared__ unsigned long long s_scratch[40];
-  __shared__ int s_iscratch[40];
-  __shared__ float s_val[32];
-  __shared__ int s_idx[32];
-  const int row = blockIdx.x;
+  __shared__ SampleShared sm;
+  const int row = blockIdx.x / kSampleCluster;
   const float temperature = fparams[row * 2 + 0];
   const float top_p = fparams[row * 2 + 1];
   const int* ip = iparams + static_cast<size_t>(row) * kParamInts;
   const int top_k = ip[0];
   const int nsup = min(max(ip[5], 0), kMaxSuppressed);
-  if (threadIdx.x < kMaxSuppressed) s_sup[threadIdx.x] = threadIdx.x < nsup ? ip[6 + threadIdx.x] : -1;
+  if (threadIdx.x < kMaxSuppressed) sm.sup[threadIdx.x] = threadIdx.x < nsup ? ip[6 + threadIdx.x] : -1;
   __syncthreads();
   RowView rv;
   rv.logits = logits + static_cast<size_t>(row) * vocab;
   rv.vocab = vocab;
+  rv.rank = sample_cluster_rank();
+  const int part = (vocab + kSampleCluster - 1) / kSampleCluster;
+  rv.lo = min(vocab, static_cast<int>(rv.rank) * part);
+  rv.hi = min(vocab, rv.lo + part);
   rv.temperature = temperature > 0.0f ? temperature : 1.0f;
   rv.nsup = nsup;
-  rv.sup = s_sup;
+  rv.sup = sm.sup;
   rv.max_scaled = 0.0f;
+  rv.phase = 0;
+  rv.hphase = 0;
+  rv.staged = nullptr;
 
-  // maximum and its lowest id
+  // The block's part of the row goes to shared memory once, divided by the temperature: the passes that follow read
+  // it eight to twenty times.  From global memory a pass was bound by latency (a thread had one 4-byte load in
+  // flight at a time, between the warp votes of the counting loop: 13 us a pass), and every pass paid the division
+  // again.  These loads do not depend on one another and go out back to back.
+  extern __shared__ float staged_part[];
+  bool bad = false;
+  // maximum and its lowest id, found on the way
   float best = -INFINITY;
   int best_id = 0x7fffffff;
-  bool bad = false;
-  for (int id = threadIdx.x; id < vocab; id += blockDim.x) {
+  const bool stage = staged_floats >= rv.hi - rv.lo;
+  for (int id = rv.lo + threadIdx.x; id < rv.hi; id += blockDim.x) {
     const float raw = rv.logits[id];
     if (!isfinite(raw)) bad = true;
-    if (!allowed(rv, id)) continue;
     const float s = raw / rv.temperature;
+    if (stage) staged_part[id - rv.lo] = s;
+    if (!allowed(rv, id)) continue;
     if (s > best || (s == best && id < best_id)) {
       best = s;
       best_id = id;
     }
   }
+  if (stage) rv.staged = staged_part;                    // (read only after the block barriers of the reduction below)
   if (bad) publish_error(error, kNonFiniteLogit);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
 #pragma unroll
@@ -300,13 +474,13 @@ sample_kernel(const float* __restrict__ logits, int vocab, const float* __restri
     }
   }
   if (lane == 0) {
-    s_val[warp] = best;
-    s_idx[warp] = best_id;
+    sm.val[warp] = best;
+    sm.idx[warp] = best_id;
   }
   __syncthreads();
   if (warp == 0) {
-    best = lane < (blockDim.x >> 5) ? s_val[lane] : -INFINITY;
-    best_id = lane < (blockDim.x >> 5) ? s_idx[lane] : 0x7fffffff;
+    best = lane < (blockDim.x >> 5) ? sm.val[lane] : -INFINITY;
+    best_id = lane < (blockDim.x >> 5) ? sm.idx[lane] : 0x7fffffff;
 #pragma unroll
     for (int d = 16; d > 0; d >>= 1) {
       const float ov = __shfl_xor_sync(0xffffffffu, best, d);
@@ -317,16 +491,32 @@ sample_kernel(const float* __restrict__ logits, int vocab, const float* __restri
       }
     }
     if (lane == 0) {
-      s_val[0] = best;
-      s_idx[0] = best_id;
+      sm.val[0] = best;
+      sm.idx[0] = best_id;
     }
   }
   __syncthreads();
-  best = s_val[0];
-  best_id = s_idx[0];
+  {
+    const unsigned long long w[kExchangeWords] = {static_cast<unsigned long long>(__float_as_uint(sm.val[0])),
+                                                  static_cast<unsigned long long>(static_cast<uint32_t>(sm.idx[0])), 0ull, 0ull};
+    exchange(sm, rv, w);
+  }
+  best = -INFINITY;
+  best_id = 0x7fffffff;
+#pragma unroll
+  for (int r = 0; r < kSampleCluster; ++r) {             // the blocks' ids ascend with their rank: the first maximum has the lowest id
+    const float v = __uint_as_float(static_cast<uint32_t>(sm.all[r][0]));
+    const int i = static_cast<int>(static_cast<uint32_t>(sm.all[r][1]));
+    if (v > best || (v == best && i < best_id)) {
+      best = v;
+      best_id = i;
+    }
+  }
+  __syncthreads();
   if (best_id == 0x7fffffff) best_id = 0;      // nothing finite and allowed: reported above
-  if (!(temperature > 0.0f) || !isfinite(best)) {
-    if (threadIdx.x == 0) out_tokens[row] = best_id;
+  if (!(temperature > 0.0f) || !isfinite(best)) {        // (every block of the cluster sees the same and leaves)
+    if (threadIdx.x == 0 && rv.rank == 0) out_tokens[row] = best_id;
+    sample_cluster_sync();                               // (another block may still be reading this one's words)
     return;
   }
   rv.max_scaled = best;
@@ -336,22 +526,17 @@ sample_kernel(const float* __restrict__ logits, int vocab, const float* __restri
   kept.id = 0x7fffffff;
   const int n_allowed = vocab - nsup;
   if (top_k > 0 && top_k < n_allowed)
-    kept = find_crossing(rv, kept, false, static_cast<unsigned long long>(top_k), s_hist, s_scratch, s_iscratch);
+    kept = find_crossing(sm, rv, kept, false, kTargetGiven, static_cast<unsigned long long>(top_k), 0.0);
   if (top_p < 1.0f) {
-    const unsigned long long filtered = prefix_total(rv, kept, true, s_scratch);
-    unsigned long long target = __double2ull_ru(static_cast<double>(top_p) * static_cast<double>(filtered));
-    target = min(max(target, 1ull), filtered);
-    kept = find_crossing(rv, kept, true, target, s_hist, s_scratch, s_iscratch);
+    kept = find_crossing(sm, rv, kept, true, kTargetShare, 0ull, static_cast<double>(top_p));
   }
-  const unsigned long long retained = prefix_total(rv, kept, true, s_scratch);
   const uint32_t word = philox_word(static_cast<uint32_t>(ip[1]), static_cast<uint32_t>(ip[2]),
                                     (static_cast<uint64_t>(static_cast<uint32_t>(ip[4])) << 32) |
                                         static_cast<uint32_t>(ip[3]));
   const double u = (static_cast<double>(word) + 0.5) / 4294967296.0;
-  unsigned long long target = __double2ull_rd(u * static_cast<double>(retained)) + 1ull;
-  target = min(max(target, 1ull), retained);
-  const Prefix pick = find_crossing(rv, kept, true, target, s_hist, s_scratch, s_iscratch);
-  if (threadIdx.x == 0) out_tokens[row] = pick.id;
+  const Prefix pick = find_crossing(sm, rv, kept, true, kTargetDraw, 0ull, u);
+  if (threadIdx.x == 0 && rv.rank == 0) out_tokens[row] = pick.id;
+  sample_cluster_sync();                                 // nobody leaves while another block may still read its words
 }
 
 // argmax per row, ties to the lower id (qwen_bf16_primitives.cu:761-807)
@@ -586,8 +771,20 @@ extern "C" int pih_sample(const float* logits, int rows, int vocab, const float*
                           const int* iparams, int* out_tokens, uint32_t* error, void* stream) {
   if (rows <= 0) return 0;
   if (vocab <= 0) return PIH_ERR_BAD_ARGUMENT;
-  launch_kernel(sample_kernel, dim3(rows), dim3(kSampleThreads), 0, static_cast<cudaStream_t>(stream), logits, vocab, fparams,
-                                                                                  iparams, out_tokens, error);
+  if (vocab > kSampleCluster * 65536) return PIH_ERR_UNSUPPORTED;      // (the 32-bit sums of a block's part)
+  // a block's part of a row in shared memory, if it fits beside the kernel's own (7 KB)
+  const int part = (vocab + kSampleCluster - 1) / kSampleCluster;
+  int staged_floats = part;
+  if (static_cast<long long>(part) * 4 > 200 * 1024) staged_floats = 0;
+  static int smem_set = 0;
+  if (staged_floats * 4 > 40 * 1024 && smem_set < staged_floats * 4) {
+    cudaError_t e = cudaFuncSetAttribute(sample_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, staged_floats * 4);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    smem_set = staged_floats * 4;
+  }
+  launch_kernel_clustered(sample_kernel, dim3(rows * kSampleCluster), dim3(kSampleBlock), static_cast<size_t>(staged_floats) * 4,
+                          static_cast<cudaStream_t>(stream), static_cast<unsigned>(kSampleCluster), logits, vocab, fparams,
+                          iparams, out_tokens, staged_floats, error);
   PIH_LAUNCH_CHECK();
   return 0;
 }
