@@ -45,6 +45,7 @@ def main() -> int:
     ap.add_argument("--page-size", type=int, default=64)
     ap.add_argument("--requests", type=int, default=None)
     ap.add_argument("--new-tokens", type=int, default=None)
+    ap.add_argument("--budget", type=int, default=None, help="tokens a step (default: the shape's workload)")
     ap.add_argument("--no-warm-up", action="store_true",
                     help="first request on a cold engine: what a process sets up and captures once falls into the run")
     ap.add_argument("--capture-decode-after", type=int, default=None,
@@ -70,6 +71,8 @@ def main() -> int:
         work["requests"] = args.requests
     if args.new_tokens:
         work["new_tokens"] = args.new_tokens
+    if args.budget:
+        work["budget"] = args.budget
     config = config_from_dict(dict(COMMON, **shape))
     spec = config.model_spec()
     dev = torch.device("cuda:0")
