@@ -243,3 +243,35 @@ def test_trace_run_steps_without_wanted_logits_and_pauses(model_dirs, tmp_path):
     data = torch.from_numpy(np.fromfile(os.path.join(out_dir, "2.f32"), dtype="<f4").reshape(2, 256).copy())
     assert float((data[0].double() - plain_impl.forward(cfg, w, a)[-1]).abs().max()) < TOL_F32
     assert float((data[1].double() - plain_impl.forward(cfg, w, b)[-1]).abs().max()) < TOL_F32
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_padded_step_gives_the_same_bits_run_captured_and_replayed(model_dirs, tiny_configs, dtype):
+    """A step of a shape that comes again is padded the same way whether it is run launch by launch (first
+    sighting), run and captured (second) or replayed (third and later): the same kernels on the same shapes, so
+    the logits of the same tokens are the same bits every time — and the padding's rows and requests leave no
+    trace: the cache is whole afterwards and no error is reported."""
+    from pih_b200.engine import StepEntry
+    from pih_b200.engine.factory import create_runner
+    name = "B"
+    vocab = tiny_configs[name]["vocab_size"]
+    toks = traces.make_requests(vocab, [50, 37, 9], seed=77)
+    _, model, cache, runner = create_runner(model_dirs[name], dtype, page_size=PAGE[name], max_cache_tokens=1024,
+                                            max_requests=4, cuda_graphs=True)
+    assert runner.pad_steps
+    outs = []
+    for turn in range(4):
+        rids = [f"{rid}-{turn}" for rid in toks]
+        (a, ta), (b, tb), (c, tc) = [(r, t) for r, t in zip(rids, toks.values())]
+        runner.step([StepEntry(a, ta[:30], []), StepEntry(c, tc[:8], [])])            # contexts for the mixed step
+        # 20 + 37 + 1 rows of three requests: padded to 64 rows and four requests
+        out = runner.step([StepEntry(a, ta[30:], [19]), StepEntry(b, tb, [36]), StepEntry(c, tc[8:], [0])])
+        outs.append(out.float().cpu().clone())
+        for r in rids:
+            runner.finish(r)
+    model.rt.ops.check_errors()
+    cache.check()
+    assert any(k[0] == "padded" and k[1] == 64 and k[2] == 4 for k in runner._graphs), list(runner._graphs)
+    for later in outs[1:]:
+        assert torch.equal(later, outs[0])
+    assert all(f == cache.num_pages for f in cache.num_free_pages())
