@@ -82,16 +82,21 @@ class Sampler:
         view = host.numpy()
         fl = view[:2 * S].view(np.float32).reshape(S, 2)
         it = view[2 * S:].view(np.uint32).reshape(S, _INT_COLUMNS)
-        for i, (p, o, sup) in enumerate(zip(params, ordinals, suppressed)):
-            if len(sup) > MAX_SUPPRESSED or len(sup) >= self.vocab:
-                raise ValueError("too many suppressed token ids")
-            fl[i, 0] = p.temperature
-            fl[i, 1] = p.top_p
-            k = 0 if p.top_k is None or p.top_k >= self.vocab else p.top_k
-            it[i, :6] = (k, p.seed & 0xFFFFFFFF, (p.seed >> 32) & 0xFFFFFFFF, o & 0xFFFFFFFF,
-                         (o >> 32) & 0xFFFFFFFF, len(sup))
-            it[i, 6:6 + len(sup)] = list(sup)
-            it[i, 6 + len(sup):] = 0xFFFFFFFF
+        # whole columns at a time (a row at a time cost the host 8 us a row, every step)
+        fl[:, 0] = [p.temperature for p in params]
+        fl[:, 1] = [p.top_p for p in params]
+        it[:, 0] = [0 if p.top_k is None or p.top_k >= self.vocab else p.top_k for p in params]
+        it[:, 1] = [p.seed & 0xFFFFFFFF for p in params]
+        it[:, 2] = [(p.seed >> 32) & 0xFFFFFFFF for p in params]
+        it[:, 3] = [o & 0xFFFFFFFF for o in ordinals]
+        it[:, 4] = [(o >> 32) & 0xFFFFFFFF for o in ordinals]
+        it[:, 5] = [len(sup) for sup in suppressed]
+        it[:, 6:] = 0xFFFFFFFF
+        for i, sup in enumerate(suppressed):
+            if sup:
+                if len(sup) > MAX_SUPPRESSED or len(sup) >= self.vocab:
+                    raise ValueError("too many suppressed token ids")
+                it[i, 6:6 + len(sup)] = list(sup)
         dev = torch.empty(host.numel(), dtype=torch.int32, device=self.device)
         dev.copy_(host, non_blocking=True)
         if stage[1] is not None:
