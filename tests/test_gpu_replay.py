@@ -275,3 +275,34 @@ def test_a_padded_step_gives_the_same_bits_run_captured_and_replayed(model_dirs,
     for later in outs[1:]:
         assert torch.equal(later, outs[0])
     assert all(f == cache.num_pages for f in cache.num_free_pages())
+
+
+def test_graphs_of_padded_shapes_are_dropped_and_made_again(model_dirs, tiny_configs):
+    """Only the most recently used graphs of non-decode shapes are kept; with room for two, a run over five
+    shapes, each met five times in turn, drops and recaptures graphs all the time — every logit still matches the
+    plain implementation, and the logits of a step are the same bits each time its shape comes round."""
+    from pih_b200.engine import StepEntry
+    from pih_b200.engine.factory import create_runner
+    name, dtype = "A", "float32"
+    vocab = tiny_configs[name]["vocab_size"]
+    _, model, cache, runner = create_runner(model_dirs[name], dtype, page_size=16, max_cache_tokens=2048,
+                                            max_requests=4, cuda_graphs=True)
+    runner.GRAPH_LIMIT = 2
+    lengths = [20, 40, 70, 140, 200]                                     # rows buckets 32, 64, 128, 192, 256
+    prompts = traces.make_requests(vocab, lengths, seed=91)
+    cfg, w = load_plain_weights(model_dirs[name])
+    truth = {rid: plain_impl.forward(cfg, w, toks)[[len(toks) - 1]] for rid, toks in prompts.items()}
+    seen = {}
+    captures = 0
+    for turn in range(5):
+        for rid, toks in prompts.items():
+            before = set(runner._graphs)
+            out = runner.step([StepEntry((rid, turn), toks, [len(toks) - 1])]).float().cpu().clone()
+            captures += len(set(runner._graphs) - before)
+            runner.finish((rid, turn))
+            compare({rid: out}, {rid: truth[rid]}, dtype, f"turn {turn} {rid}")
+            assert torch.equal(out, seen.setdefault(rid, out))
+            assert sum(1 for k in runner._graphs if k[0] != "decode") <= 2
+    model.rt.ops.check_errors()
+    cache.check()
+    assert captures >= 8, captures                                        # shapes were captured more than once
