@@ -378,6 +378,11 @@ qk_norm_rope_kv_wide_kernel(T* __restrict__ qkv, int row_stride, int rows, int h
   const int slot0 = static_cast<int>(item % groups) * 2 * SPW;
   const int slot_end = min(slot0 + 2 * SPW, slots);        // past the group's last live slot
   T* row = qkv + static_cast<size_t>(t) * row_stride + l16 * E2;
+  // what the row's rotation angles and cache slot depend on is asked for first: the angles' load waits for the
+  // position, and that wait then runs under the loads of the row itself
+  int pos_raw = 0, m_raw = -1;
+  if (rope != nullptr && slot0 < heads + kv_heads) pos_raw = positions[t];
+  if (slot_end > heads) m_raw = slot_mapping[t];
   VecPack<T, E2> lo[SPW], hi[SPW];
 #pragma unroll
   for (int i = 0; i < SPW; ++i) {
@@ -388,7 +393,7 @@ qk_norm_rope_kv_wide_kernel(T* __restrict__ qkv, int row_stride, int rows, int h
   int m = -1;
   size_t cache_k = 0;
   if (slot_end > heads) {
-    m = slot_mapping[t];
+    m = m_raw;
     if (m < 0 || m >= num_pages * page_size) {
       if (lane == 0 && m != kPaddingSlot) publish_error(error, kRowWithoutPage);   // (a row of padding is left alone)
       m = -1;
@@ -414,7 +419,7 @@ qk_norm_rope_kv_wide_kernel(T* __restrict__ qkv, int row_stride, int rows, int h
 #pragma unroll
   for (int j = 0; j < E2; ++j) cs.e[j] = make_float2(1.0f, 0.0f);
   if (rope != nullptr) {
-    int pos = positions[t];
+    int pos = pos_raw;
     if (pos < 0 || pos >= max_pos) {
       if (lane == 0) publish_error(error, kBadPosition);
       pos = 0;
