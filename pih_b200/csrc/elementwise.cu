@@ -544,6 +544,15 @@ __global__ void rmsnorm_vec_kernel(T* __restrict__ x, const T* __restrict__ delt
       for (int j = 0; j < VEC; ++j) ss += v[k][j] * v[k][j];
     }
   }
+  // (the weights are asked for before the block-wide sum: after it they would be one more trip to the cache on the
+  // path of every row)
+  float wv[CHUNKS][VEC];
+#pragma unroll
+  for (int k = 0; k < CHUNKS; ++k) {
+    const int i = threadIdx.x + k * blockDim.x;
+#pragma unroll
+    for (int j = 0; j < VEC; ++j) wv[k][j] = i < nvec ? to_float<W>(weight[i * VEC + j]) : 0.0f;
+  }
   ss = block_sum(ss, scratch);
   const float scale = 1.0f / sqrtf(ss / static_cast<float>(width) + eps);
   T* yr = out + static_cast<size_t>(o) * width;
@@ -554,8 +563,7 @@ __global__ void rmsnorm_vec_kernel(T* __restrict__ x, const T* __restrict__ delt
       uint4 packed;
       T* pk = reinterpret_cast<T*>(&packed);
 #pragma unroll
-      for (int j = 0; j < VEC; ++j)
-        pk[j] = from_float<T>((v[k][j] * scale) * to_float<W>(weight[i * VEC + j]));
+      for (int j = 0; j < VEC; ++j) pk[j] = from_float<T>((v[k][j] * scale) * wv[k][j]);
       reinterpret_cast<uint4*>(yr)[i] = packed;
     }
   }
@@ -582,13 +590,18 @@ rmsnorm_rows_kernel(T* __restrict__ x, const T* __restrict__ delta, const W* __r
   uint4* xr = reinterpret_cast<uint4*>(x + r * width);
   const uint4* dr = delta != nullptr ? reinterpret_cast<const uint4*>(delta + r * width) : nullptr;
   const bool write_back = delta != nullptr && rows == nullptr;
-  uint4 h[CHUNKS], d[CHUNKS];
+  uint4 h[CHUNKS], d[CHUNKS], wq[CHUNKS][WV];
 #pragma unroll
   for (int k = 0; k < CHUNKS; ++k) h[k] = xr[lane + 32 * k];
   if (dr != nullptr) {
 #pragma unroll
     for (int k = 0; k < CHUNKS; ++k) d[k] = dr[lane + 32 * k];
   }
+  // (the weights too: asked for after the sum they would be one more trip to the cache on every row's path)
+#pragma unroll
+  for (int k = 0; k < CHUNKS; ++k)
+#pragma unroll
+    for (int u = 0; u < WV; ++u) wq[k][u] = reinterpret_cast<const uint4*>(weight)[(lane + 32 * k) * WV + u];
   float ss = 0.0f;
 #pragma unroll
   for (int k = 0; k < CHUNKS; ++k) {
@@ -610,10 +623,7 @@ rmsnorm_rows_kernel(T* __restrict__ x, const T* __restrict__ delta, const W* __r
   uint4* yr = reinterpret_cast<uint4*>(out + static_cast<size_t>(o) * width);
 #pragma unroll
   for (int k = 0; k < CHUNKS; ++k) {
-    uint4 wq[WV];
-#pragma unroll
-    for (int u = 0; u < WV; ++u) wq[u] = reinterpret_cast<const uint4*>(weight)[(lane + 32 * k) * WV + u];
-    const W* we = reinterpret_cast<const W*>(wq);
+    const W* we = reinterpret_cast<const W*>(wq[k]);
     T* e = reinterpret_cast<T*>(&h[k]);
 #pragma unroll
     for (int j = 0; j < VEC; ++j) e[j] = from_float<T>((to_float<T>(e[j]) * scale) * to_float<W>(we[j]));
