@@ -71,7 +71,7 @@ def main() -> int:
     ap.add_argument("--heads", type=int, default=16)
     ap.add_argument("--kv-heads", type=int, default=8)
     ap.add_argument("--head-dim", type=int, default=128)
-    ap.add_argument("--page", type=int, default=16)
+    ap.add_argument("--page", type=int, default=64)
     ap.add_argument("--m", type=int, default=8)
     ap.add_argument("--n", type=int, default=4096)
     ap.add_argument("--k", type=int, default=1024)
