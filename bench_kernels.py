@@ -81,7 +81,7 @@ def main() -> int:
     ap.add_argument("--width", type=int, default=1024)
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--no-flush", action="store_true")
-    ap.add_argument("--impl", default="default", choices=["default", "tcgen05", "skinny", "library"])
+    ap.add_argument("--impl", default="default", choices=["default", "tcgen05", "tcgen05pair", "skinny", "library"])
     ap.add_argument("--fused", default="none", choices=["none", "norm", "addnorm", "swiglu", "residual"],
                     help="linear --impl skinny: with the RMSNorm prologue (addnorm: and the residual add before it; "
                          "swiglu: and the SwiGLU epilogue), or with the residual add in the epilogue")
@@ -94,6 +94,8 @@ def main() -> int:
     ap.add_argument("--no-tma", action="store_true", help="decode attention gathers with cp.async instead of TMA")
     ap.add_argument("--tickets", action="store_true",
                     help="decode attention merges its splits through scratch memory and tickets, not as a cluster")
+    ap.add_argument("--fetched-merge", action="store_true",
+                    help="decode attention: the cluster's blocks fetch one another's partials even where they would send them")
     ap.add_argument("--plain", action="store_true", help="the pack's plain (generic / FMA) kernel instead")
     args = ap.parse_args()
 
@@ -107,6 +109,8 @@ def main() -> int:
     ops.tma_attention = not args.no_tma
     if args.tickets:
         ops.set_attention_cluster_merge(False)
+    elif args.fetched_merge:
+        ops.set_attention_cluster_merge("fetched")
     out = {"kernel": args.kernel}
 
     scale = 1.0 / math.sqrt(D)
@@ -150,12 +154,12 @@ def main() -> int:
             w = torch.randn(args.n, args.k, device=dev).to(bf)
             rates.update(flops=2 * args.m * args.n * args.k, m=args.m, n=args.n, k=args.k,
                          bytes=2 * (args.m * args.k + args.n * args.k + args.m * args.n))
-            if args.impl == "tcgen05" and args.fused == "swiglu":
-                fn = lambda: ops.linear_tcgen05_swiglu(x, w, tile_n=args.tile_n)
+            if args.impl in ("tcgen05", "tcgen05pair") and args.fused == "swiglu":
+                fn = lambda: ops.linear_tcgen05_swiglu(x, w, tile_n=args.tile_n, pairs=args.impl == "tcgen05pair")
             elif args.impl == "library" and args.fused == "swiglu":
                 fn = lambda: ops.silu_mul(torch.mm(x, w.t()), 8)
-            elif args.impl == "tcgen05":
-                fn = lambda: ops.linear_tcgen05(x, w, tile_n=args.tile_n)
+            elif args.impl in ("tcgen05", "tcgen05pair"):
+                fn = lambda: ops.linear_tcgen05(x, w, tile_n=args.tile_n, pairs=args.impl == "tcgen05pair")
             elif args.impl == "skinny" and args.fused == "residual":
                 r = torch.randn(args.m, args.n, device=dev).to(bf)
                 fn = lambda: ops.linear_skinny(x, w, residual=r)

@@ -73,6 +73,7 @@ struct AttnParams {
   int write_kv;                        // append the new tokens' k and v to the cache (and use them)
   __nv_bfloat16* cache_w;              // the cache, writable
   int fused;                           // host: launch the FUSE variant
+  int push_merge;                      // host: the cluster's blocks send their partials to the blocks that finish them
 };
 
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem, int src_bytes) {
@@ -618,6 +619,126 @@ __device__ __forceinline__ void cluster_finish(const AttnParams& p, int g, int n
   cluster_sync();                                    // every block has read: all may go
 }
 
+// The same end with the partials SENT instead of fetched, for requests whose partial is small (at most
+// kPushRows packed rows and kPushFloats output elements: a decoded token of up to four query heads a kv
+// head): every block stores each element of its partial into the inbox of the block that finishes that
+// element, and its rows' maxima and sums into every block's inbox; after ONE cluster barrier every block
+// finishes its share from its own shared memory and leaves.  Against cluster_finish this saves the trip of
+// dependent loads through distributed shared memory after the barrier and the second barrier (nobody reads a
+// block's memory after the barrier, so a block may leave at once).  `inbox` is shared memory that nothing
+// else uses during the kernel — other blocks write it while this one is still working on its keys — of
+// kPushInboxFloats floats.  Before the first store the caller has waited for the barrier at which every block
+// of the cluster arrived when it started (cluster_started_*): a block's shared memory may be written by
+// another only once it runs.
+constexpr int kPushRows = 4;
+constexpr int kPushFloats = 512;
+constexpr int kPushInboxFloats = kPushFloats + kMaxCluster + kMaxCluster * kPushRows * 2;
+
+__device__ __forceinline__ void cluster_started_arrive() {
+  asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void cluster_started_wait() {
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void store_to_cluster_block(float* local, uint32_t rank, float v) {
+  const uint32_t a = static_cast<uint32_t>(__cvta_generic_to_shared(local));
+  uint32_t remote;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(a), "r"(rank));
+  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(v) : "memory");
+}
+
+template <int D>
+__device__ __forceinline__ void cluster_finish_push(const AttnParams& p, int g, int nsp, int packed, int G, int row0,
+                                                    float (&m)[2], float (&l)[2], float (&o)[D / 8][4],
+                                                    float* scratch, float* inbox) {
+  constexpr int THREADS = 128;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    l[h] += __shfl_xor_sync(0xffffffffu, l[h], 1);
+    l[h] += __shfl_xor_sync(0xffffffffu, l[h], 2);
+  }
+  __syncthreads();                                   // the K/V tiles are no longer needed
+  float* Ow = scratch;                               // [4][16][D]
+  float* Mw = Ow + 4 * 16 * D;                       // [4][16]
+  float* Lw = Mw + 4 * 16;                           // [4][16]
+  float* In_o = inbox;                               // [nsp][share]: block c's partial of this block's elements
+  float* In_ml = inbox + kPushFloats + kMaxCluster;  // [kMaxCluster][kPushRows][2]: block c's maximum and sum of every row
+#pragma unroll
+  for (int h = 0; h < 2 && warp < 4; ++h) {
+    const int row = (lane >> 2) + h * 8;
+    if (row >= packed) continue;
+    float* orow = Ow + (warp * 16 + row) * D;
+#pragma unroll
+    for (int n = 0; n < D / 8; ++n) {
+      const int d = n * 8 + (lane & 3) * 2;
+      *reinterpret_cast<float2*>(orow + d) = make_float2(o[n][2 * h], o[n][2 * h + 1]);
+    }
+    if ((lane & 3) == 0) {
+      Mw[warp * 16 + row] = m[h];
+      Lw[warp * 16 + row] = l[h];
+    }
+  }
+  __syncthreads();
+  const int total = packed * D;
+  const int share = (total + nsp - 1) / nsp;
+  const uint32_t me = cluster_rank();
+  cluster_started_wait();                            // every block of the cluster runs: its inbox may be written
+  for (int idx = threadIdx.x; idx < total && threadIdx.x < THREADS; idx += THREADS) {
+    const int row = idx / D, d = idx % D;
+    float mm = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) mm = fmaxf(mm, Mw[w * 16 + row]);
+    float acc = 0.0f, ll = 0.0f;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      const float mw = Mw[w * 16 + row];
+      if (mw == -INFINITY) continue;
+      const float f = exp2f(mw - mm);
+      acc += Ow[(w * 16 + row) * D + d] * f;
+      ll += Lw[w * 16 + row] * f;
+    }
+    const int owner = idx / share;
+    store_to_cluster_block(In_o + me * share + (idx - owner * share), owner, acc);
+    if (d < nsp) {                                   // thread d of a row tells block d the row's maximum and sum
+      store_to_cluster_block(In_ml + (me * kPushRows + row) * 2, d, mm);
+      store_to_cluster_block(In_ml + (me * kPushRows + row) * 2 + 1, d, ll);
+    }
+  }
+  cluster_sync();                                    // every block's stores have arrived
+  const int first = static_cast<int>(me) * share;
+  for (int idx = first + threadIdx.x; idx < min(total, first + share); idx += blockDim.x) {
+    const int row = idx / D, d = idx % D;
+    float pm[kMaxCluster], pl[kMaxCluster], po[kMaxCluster];
+#pragma unroll
+    for (int c = 0; c < kMaxCluster; ++c) {
+      pm[c] = -INFINITY;
+      pl[c] = po[c] = 0.0f;
+      if (c < nsp) {
+        pm[c] = In_ml[(c * kPushRows + row) * 2];
+        pl[c] = In_ml[(c * kPushRows + row) * 2 + 1];
+        po[c] = In_o[c * share + (idx - first)];
+      }
+    }
+    float mm = -INFINITY;
+#pragma unroll
+    for (int c = 0; c < kMaxCluster; ++c) mm = fmaxf(mm, pm[c]);
+    float acc = 0.0f, ll = 0.0f;
+#pragma unroll
+    for (int c = 0; c < kMaxCluster; ++c) {
+      if (pm[c] == -INFINITY) continue;
+      const float f = exp2f(pm[c] - mm);
+      acc += po[c] * f;
+      ll += pl[c] * f;
+    }
+    if (!(ll > 0.0f) || !isfinite(ll)) {
+      publish_error(p.error, kAttentionDenominator);
+      continue;
+    }
+    p.out[(static_cast<size_t>(row0 + row / G) * p.heads + g * G + row % G) * D + d] = __float2bfloat16_rn(acc / ll);
+  }
+}
+
 constexpr int kSplitStages = 3;        // ring of K/V tiles in the split kernel
 
 // Split kernel: 4 warps, at most 16 packed rows, grid (splits, kv_heads, R); decode-like requests.
@@ -769,6 +890,7 @@ attn_split_tma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap kv
     mbar_init_fence();
   }
   __syncthreads();                                     // barriers initialised
+  if (CLUSTER && p.push_merge) cluster_started_arrive();   // waited for before the first store into another block
 
   int row_pos[2], row_first[2];
 #pragma unroll
@@ -953,7 +1075,10 @@ attn_split_tma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap kv
     }
   }
   __syncwarp();
-  if (CLUSTER)
+  if (CLUSTER && p.push_merge)
+    cluster_finish_push<D>(p, g, static_cast<int>(gridDim.x), packed, G, row0, m, l, o, reinterpret_cast<float*>(KV),
+                           reinterpret_cast<float*>(NewV + 16 * D));
+  else if (CLUSTER)
     cluster_finish<D>(p, g, static_cast<int>(gridDim.x), packed, G, row0, m, l, o, reinterpret_cast<float*>(KV));
   else
     split_finish<D>(p, r, g, sp, s_lo, s_hi, packed, G, row0, m, l, o, reinterpret_cast<float*>(KV), &s_last);
@@ -964,13 +1089,18 @@ int g_cluster_merge = 1;
 
 
 template <int D>
-static int launch_split_tma(const AttnParams& p, int R, const CUtensorMap* kv_map, cudaStream_t s) {
+static int launch_split_tma(const AttnParams& params, int R, const CUtensorMap* kv_map, cudaStream_t s) {
   if constexpr (D % 64 == 0) {
     constexpr int LD = D + 8;
+    AttnParams p = params;
     const bool cluster = g_cluster_merge && p.max_splits >= 2 && p.max_splits <= kMaxCluster;
     int smem = 1024 + kSplitStages * 2 * BN * D * 2 + 16 * LD * 2 + 2 * kSplitStages * 8 + 2 * 16 * D * 2;
     const int merge = 1024 + (4 * 16 * D + 128 + 16 * D + 32 + 32 * p.max_splits + 16) * 4;
     if (merge > smem) smem = merge;
+    // small partials are sent to the blocks that finish them (cluster_finish_push): the inbox lies behind all else
+    const int packed_cap = p.dec_tok_cap * (p.heads / p.kv_heads);
+    p.push_merge = cluster && g_cluster_merge == 1 && packed_cap <= kPushRows && packed_cap * D <= kPushFloats;
+    if (p.push_merge) smem += kPushInboxFloats * 4;
     if (smem > 227 * 1024) return PIH_ERR_UNSUPPORTED;
     dim3 grid(p.max_splits, p.kv_heads, R);
 #define PIH_SPLIT_TMA(CLUSTER, FUSE)                                                                              \
@@ -1049,11 +1179,11 @@ static int launch_both(const AttnParams& p, int R, int tile_max_q, const CUtenso
 using namespace pih;
 
 // 1 (the default): 2 to 8 splits of one (request, kv head) run as a thread-block cluster and merge through
-// distributed shared memory; 0: every split count merges through scratch memory and tickets.  Returns the
-// previous setting.
-extern "C" int pih_set_attention_cluster_merge(int on) {
+// distributed shared memory, small partials sent and larger ones fetched; 2: always fetched; 0: every split
+// count merges through scratch memory and tickets.  Returns the previous setting.
+extern "C" int pih_set_attention_cluster_merge(int mode) {
   const int before = pih::g_cluster_merge;
-  pih::g_cluster_merge = on ? 1 : 0;
+  pih::g_cluster_merge = mode < 0 ? 0 : mode > 2 ? 2 : mode;
   return before;
 }
 

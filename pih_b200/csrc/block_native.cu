@@ -34,6 +34,9 @@ int pih_qk_norm_rope_kv_write(int dtype, int weight_dtype, void* qkv, int row_st
 int pih_silu_mul(int dtype, const void* gate_up, void* out, long long rows, int inter, int interleave, void* stream);
 int pih_gemm_simt(int in_dtype, int out_dtype, const void* A, const void* W, void* C, int M, int N, int K, long long lda,
                   long long ldw, long long ldc, void* stream);
+int pih_pair_swiglu_wanted(int rows, int n);
+int pih_gemm_tcgen05_pair(int out_dtype, const void* A, const void* W, void* C, int M, int N, int K, long long lda,
+                          long long ldw, long long ldc, int tile_n, int swiglu, uint32_t* error, void* stream);
 int pih_gemm_skinny(const void* x, const void* delta, void* x_out, int norm_dtype, const void* norm_w, float eps,
                     const void* W, void* out, const void* residual, int M, int N, int K, long long ldx, long long ldw,
                     long long ldo, int swiglu, uint32_t* error, void* stream);
@@ -323,6 +326,20 @@ extern "C" int pih_prenorm_attention_swiglu_block(const PihStepArgs* sp, const P
   if (!done) {
     PIH_TRY(pih_rmsnorm(s.dtype, b->norm_w_dtype, h, pending, b->norm_post_w, b->xn, nullptr, T, H, b->norm_post_eps,
                         s.stream));
+    // many rows: the pack's own product on pairs of SMs, SiLU-mul in its epilogue (the [T, 2 I] product never
+    // reaches memory); else the library's product and the separate kernel
+    if (s.dtype == PIH_BF16 && b->interleave == 8 && pih_pair_swiglu_wanted(T, 2 * I)) {
+      const int rc = pih_gemm_tcgen05_pair(PIH_BF16, b->xn, b->w_gate_up, b->act, T, 2 * I, H, H, b->ld_gate_up, I, 0, 1,
+                                           s.error, s.stream);
+      if (rc == 0) {
+        done = true;
+        ++b->launched;
+      } else if (rc != PIH_ERR_UNSUPPORTED) {
+        return rc;
+      }
+    }
+  }
+  if (!done) {
     PIH_TRY(product(s, b->xn, H, b->w_gate_up, b->ld_gate_up, b->gate_up, 2 * I, T, 2 * I, H));
     PIH_TRY(pih_silu_mul(s.dtype, b->gate_up, b->act, T, I, b->interleave, s.stream));
   }

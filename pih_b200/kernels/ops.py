@@ -71,16 +71,30 @@ class CudaOps:
         self.cluster_attention = True      # False: splits always merge through scratch memory and tickets
         self.attention_split = 0           # keys per split of the decode attention kernel; 0: from the context, on the device
         self.tensor_core_attention = True  # False: bf16 attention runs on the generic kernel too
-        # prompt portions of at least this many rows: gate/up product on the pack's tcgen05 kernel with SiLU-mul in its
-        # epilogue.  Off: measured against the library product followed by the SiLU-mul kernel (6144 x 1024 weights)
-        # it takes 30.9 against 29.3 us at 2048 rows, 53.6 against 52.9 at 4096 and far more below
-        self.tcgen05_swiglu_min_rows = None
+        self._tcgen05_swiglu_min_rows = 1536     # the library's default (see the property)
         self.tcgen05_min_rows = None       # bf16 products with at least this many rows use the pack's tcgen05 kernel
         self.skinny_max_rows = 16          # bf16 products with at most this many rows use the fused few-rows kernel
         self.fused_residual = True         # ... and add the residual in the epilogue of output projections
         self.native_blocks = True          # blocks of the built-in parts are issued by one native call each
         self._native = None
         self._declare()
+
+    @property
+    def tcgen05_swiglu_min_rows(self):
+        """Prompt portions of at least this many rows run their gate/up product on the pack's tcgen05 kernel on
+        pairs of SMs with SiLU-mul in its epilogue, when its tiles fill the SM pairs well (see
+        pih_pair_swiglu_wanted); None: never.  The setting is the library's: native blocks follow it."""
+        return self._tcgen05_swiglu_min_rows
+
+    @tcgen05_swiglu_min_rows.setter
+    def tcgen05_swiglu_min_rows(self, rows) -> None:
+        self.set_pair_swiglu_rule(rows)
+
+    def set_pair_swiglu_rule(self, min_rows, min_fill_percent: int = -1) -> None:
+        """``min_rows`` as ``tcgen05_swiglu_min_rows``; ``min_fill_percent``: how full the tiles must make the
+        rounds of SM pairs (80 by default; 0 sends every shape of enough rows to that kernel; -1: unchanged)."""
+        self._tcgen05_swiglu_min_rows = min_rows
+        self.lib.pih_set_pair_swiglu_rule(int(min_rows) if min_rows else 0, int(min_fill_percent))
 
     # -- plumbing ---------------------------------------------------------------
     def _declare(self) -> None:
@@ -90,7 +104,7 @@ class CudaOps:
                      "pih_sample", "pih_selected_logprob", "pih_paged_attention_mma", "pih_gemm_tcgen05", "pih_make_kv_tensor_map",
                      "pih_attention_prefill_tcgen05", "pih_gemm_skinny", "pih_set_dependent_launch", "pih_set_attention_cluster_merge",
                      "pih_gemm_skinny_f32out",
-                     "pih_qk_attention_fused", "pih_gemm_tcgen05_swiglu"):
+                     "pih_qk_attention_fused", "pih_gemm_tcgen05_swiglu", "pih_gemm_tcgen05_pair"):
             getattr(lib, name).restype = c_int
         lib.pih_attention_scratch_floats.restype = c_ll
 
@@ -114,12 +128,14 @@ class CudaOps:
         library's, not this object's; CUDA graphs keep the setting they were captured under."""
         return bool(self.lib.pih_set_dependent_launch(1 if on else 0))
 
-    def set_attention_cluster_merge(self, on: bool) -> bool:
+    def set_attention_cluster_merge(self, on):
         """Whether 2 to 8 splits of one (request, kv head) of the decode attention run as a thread-block
-        cluster that merges through distributed shared memory (the default) or through scratch memory and
-        tickets.  Returns the previous setting; the setting is the library's."""
+        cluster that merges through distributed shared memory (True, the default: small partials are sent to
+        the block that finishes them, larger ones fetched by it; "fetched": always fetched) or through scratch
+        memory and tickets (False).  Returns the previous setting; the setting is the library's."""
         self.cluster_attention = bool(on)
-        return bool(self.lib.pih_set_attention_cluster_merge(1 if on else 0))
+        before = self.lib.pih_set_attention_cluster_merge(2 if on == "fetched" else 1 if on else 0)
+        return "fetched" if before == 2 else bool(before)
 
     def _stream(self):
         # the raw handle of the current stream (torch.cuda.current_stream builds a Stream object: 8 us a call,
@@ -237,17 +253,23 @@ class CudaOps:
             return None
         return self.linear_skinny(x, w, residual=residual)
 
-    def linear_tcgen05_swiglu(self, x: torch.Tensor, w: torch.Tensor, tile_n: int = 0):
+    def linear_tcgen05_swiglu(self, x: torch.Tensor, w: torch.Tensor, tile_n: int = 0, pairs: bool = False):
         """``SwiGLU(x . w^T)`` with the pack's tcgen05 product and SiLU-mul in its epilogue: ``w`` holds blocks
         of 8 gate rows followed by their 8 up rows; returns ``[M, N / 2]`` (bf16), or None for shapes that the
-        kernel does not take."""
+        kernel does not take.  ``pairs``: the kernel that puts two SMs on a 256-row tile."""
         M, K = x.shape
         N = w.shape[0]
         if x.dtype != torch.bfloat16 or N % 16 or x.stride(1) != 1 or w.stride(1) != 1:
             return None
         out = torch.empty(M, N // 2, dtype=torch.bfloat16, device=x.device)
-        rc = self.lib.pih_gemm_tcgen05_swiglu(_ptr(x), _ptr(w), _ptr(out), M, N, K, c_ll(x.stride(0)), c_ll(w.stride(0)),
-                                              c_ll(out.stride(0)), tile_n, self._err(), self._stream())
+        if pairs:
+            rc = self.lib.pih_gemm_tcgen05_pair(_DT[torch.bfloat16], _ptr(x), _ptr(w), _ptr(out), M, N, K,
+                                                c_ll(x.stride(0)), c_ll(w.stride(0)), c_ll(out.stride(0)), tile_n, 1,
+                                                self._err(), self._stream())
+        else:
+            rc = self.lib.pih_gemm_tcgen05_swiglu(_ptr(x), _ptr(w), _ptr(out), M, N, K, c_ll(x.stride(0)),
+                                                  c_ll(w.stride(0)), c_ll(out.stride(0)), tile_n, self._err(),
+                                                  self._stream())
         if rc == -2:
             return None
         self._check(rc, "gemm_tcgen05_swiglu")
@@ -269,9 +291,9 @@ class CudaOps:
                 if out is not None:
                     return h, out
         xn = self.rmsnorm(h, norm_weight, eps, delta=delta)
-        if (swiglu_interleave == 8 and self.tcgen05_swiglu_min_rows is not None
-                and xn.shape[0] >= self.tcgen05_swiglu_min_rows and xn.dtype == torch.bfloat16):
-            out = self.linear_tcgen05_swiglu(xn, w)
+        if (swiglu_interleave == 8 and xn.dtype == torch.bfloat16
+                and self.lib.pih_pair_swiglu_wanted(xn.shape[0], w.shape[0])):
+            out = self.linear_tcgen05_swiglu(xn, w, pairs=True)
             if out is not None:
                 return h, out
         out = self.linear(xn, w)
@@ -280,15 +302,21 @@ class CudaOps:
         return h, out
 
     def linear_tcgen05(self, x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
-                       tile_n: int = 0):
+                       tile_n: int = 0, pairs: bool = False):
         """The pack's tcgen05 / TMA product (bf16 in, fp32 accumulation).  Returns None when the
-        operands cannot be described to TMA (K or a row stride not a multiple of 8)."""
+        operands cannot be described to TMA (K or a row stride not a multiple of 8).  ``pairs``: the kernel
+        that puts two SMs on a 256-row tile (``tile_n`` 128 or 256)."""
         M, K = x.shape
         N = w.shape[0]
         out_dtype = out_dtype or x.dtype
         out = torch.empty(M, N, dtype=out_dtype, device=x.device)
-        rc = self.lib.pih_gemm_tcgen05(_DT[out_dtype], _ptr(x), _ptr(w), _ptr(out), M, N, K, c_ll(x.stride(0)),
-                                       c_ll(w.stride(0)), c_ll(N), tile_n, self._err(), self._stream())
+        if pairs:
+            rc = self.lib.pih_gemm_tcgen05_pair(_DT[out_dtype], _ptr(x), _ptr(w), _ptr(out), M, N, K,
+                                                c_ll(x.stride(0)), c_ll(w.stride(0)), c_ll(N), tile_n, 0,
+                                                self._err(), self._stream())
+        else:
+            rc = self.lib.pih_gemm_tcgen05(_DT[out_dtype], _ptr(x), _ptr(w), _ptr(out), M, N, K, c_ll(x.stride(0)),
+                                           c_ll(w.stride(0)), c_ll(N), tile_n, self._err(), self._stream())
         if rc == -2:
             return None
         self._check(rc, "gemm_tcgen05")

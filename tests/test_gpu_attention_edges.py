@@ -112,7 +112,7 @@ def test_one_heavy_key_is_found_or_masked_exactly(ops, case):
             s["table"][r, :first] = -1
     scale = 1.0 / math.sqrt(D)
     decode_like = all(n * (HEADS // KV_HEADS) <= 16 for n in new)
-    kinds = ["cluster", "tickets", "fused", "cp.async"] if decode_like else ["tcgen05", "mma.sync"]
+    kinds = ["cluster", "fetched", "tickets", "fused", "cp.async"] if decode_like else ["tcgen05", "mma.sync"]
     for far in fars:
         planted = [(r,) + _plant(s, r, far, u) for r in range(len(lens)) if 0 <= far < lens[r]]
         try:
@@ -122,7 +122,7 @@ def test_one_heavy_key_is_found_or_masked_exactly(ops, case):
             for kind in kinds:
                 modern = kind not in ("cp.async", "mma.sync")
                 ops.tcgen05_attention = ops.tma_attention = modern
-                ops.set_attention_cluster_merge(kind != "tickets")
+                ops.set_attention_cluster_merge("fetched" if kind == "fetched" else kind != "tickets")
                 try:
                     out = _run(ops, kind, s, D, lens, new, window, scale)
                 finally:

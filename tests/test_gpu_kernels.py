@@ -120,6 +120,26 @@ def test_linear_tcgen05(ops, out_dtype, tile_n, M, N, K):
     torch.testing.assert_close(out.cpu().double(), ref, **tol)
 
 
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("tile_n", [0, 128, 256])
+@pytest.mark.parametrize("M,N,K", [(256, 256, 64), (1, 8, 8), (37, 130, 96), (300, 257, 1032), (2048, 1024, 3072),
+                                   (129, 1000, 72), (385, 152, 1024), (4000, 4300, 520)])
+def test_linear_tcgen05_on_pairs_of_sms(ops, out_dtype, tile_n, M, N, K):
+    """The product with two SMs on a 256-row tile (cta_group::2) against a float64 reference: tiles that overhang
+    M, N and K — a pair whose second CTA has no rows or no columns at all —, both tile widths, and enough tiles
+    that a pair walks over several (both accumulators, ring wrap-around)."""
+    x = _rand((M, K), torch.bfloat16, 3)
+    w = _rand((N, K), torch.bfloat16, 4, 0.1)
+    out = ops.linear_tcgen05(x, w, out_dtype, tile_n=tile_n, pairs=True)
+    ops.check_errors()
+    assert out is not None and out.dtype == out_dtype and out.shape == (M, N)
+    ref = x.cpu().double() @ w.cpu().double().T
+    tol = dict(rtol=1e-4, atol=1e-4)
+    if out_dtype == torch.bfloat16:
+        tol = dict(rtol=8e-3, atol=1e-3 * max(1.0, float(ref.abs().max()) / 4))
+    torch.testing.assert_close(out.cpu().double(), ref, **tol)
+
+
 def test_linear_tcgen05_takes_strided_rows_and_refuses_what_tma_cannot_describe(ops):
     x = _rand((40, 256), torch.bfloat16, 5)
     w = _rand((512, 128), torch.bfloat16, 6, 0.1)
@@ -387,15 +407,17 @@ MMA_CASES = [c for c in ATTN_CASES if c[2] != 48] + [
 ]
 
 
-@pytest.fixture(params=["tcgen05+tma", "tcgen05+tma+tickets", "mma.sync+cp.async"])
+@pytest.fixture(params=["tcgen05+tma", "tcgen05+tma+fetched", "tcgen05+tma+tickets", "mma.sync+cp.async"])
 def attention_variant(request, ops):
     """The families of tensor-core attention kernels: tcgen05 tiles with TMA-fed splits that merge as a
-    thread-block cluster; the same with the splits merged through scratch memory and tickets (what more than
-    eight splits use); and the mma.sync tile kernel with cp.async splits (which also serve the sizes the
+    thread-block cluster (small partials sent to the block that finishes them); the same with every partial
+    fetched by that block (what larger partials use); with the splits merged through scratch memory and tickets
+    (what more than eight splits use); and the mma.sync tile kernel with cp.async splits (which also serve the sizes the
     first does not take)."""
     modern = request.param != "mma.sync+cp.async"
     ops.tcgen05_attention, ops.tma_attention = modern, modern
-    ops.set_attention_cluster_merge(request.param != "tcgen05+tma+tickets")
+    ops.set_attention_cluster_merge("fetched" if request.param.endswith("fetched")
+                                    else request.param != "tcgen05+tma+tickets")
     yield request.param
     ops.tcgen05_attention, ops.tma_attention = True, True
     ops.set_attention_cluster_merge(True)
@@ -701,15 +723,16 @@ def test_qk_attention_fused_declines_what_it_does_not_take(ops):
     ops.check_errors()
 
 
+@pytest.mark.parametrize("pairs", [False, True])
 @pytest.mark.parametrize("M,I,K", [(300, 264, 200), (2048, 3072, 1024), (130, 8, 64), (129, 1000, 1032)])
-def test_linear_tcgen05_swiglu(ops, M, I, K):
+def test_linear_tcgen05_swiglu(ops, M, I, K, pairs):
     """The tcgen05 product with SiLU-mul in its epilogue against the plain parts: gate and up rounded to bf16, then
     silu(g) * u rounded — each element within what one rounding flip per stage can do (see the few-rows test)."""
     x = _rand((M, K), torch.bfloat16, 51)
     gate = _rand((I, K), torch.bfloat16, 52, 0.05)
     up = _rand((I, K), torch.bfloat16, 53, 0.05)
     w = torch.stack([gate.reshape(-1, 8, K), up.reshape(-1, 8, K)], dim=1).reshape(2 * I, K).contiguous()
-    act = ops.linear_tcgen05_swiglu(x, w)
+    act = ops.linear_tcgen05_swiglu(x, w, pairs=pairs)
     ops.check_errors()
     assert act is not None and act.shape == (M, I)
     g_ref = plain_impl.linear(x.cpu(), gate.cpu(), "bf16")

@@ -96,6 +96,30 @@ def test_replay_families(model_dirs, requests_of, name, dtype, family):
         assert all(g.pool.pages_handed_out > g.pool.num_pages for g in cache.groups)
 
 
+@pytest.mark.parametrize("name", ["A", "C", "D"])
+@pytest.mark.parametrize("family", ["whole", "mixed"])
+def test_replay_with_the_gate_up_product_on_pairs_of_sms(model_dirs, tiny_configs, requests_of, name, family):
+    """The gate/up product of large prompt portions runs on the pack's tcgen05 kernel on pairs of SMs with SiLU-mul
+    in its epilogue; the tiny models' steps never reach its row count.  With the rule opened to every step of more
+    than 16 rows, whole prompts and mixed steps still agree with the plain implementation."""
+    from pih_b200.engine.factory import create_runner
+    requests = requests_of[name]
+    steps = getattr(traces, family)(requests)
+    _, model, cache, runner = create_runner(model_dirs[name], "bfloat16", page_size=PAGE[name],
+                                            max_cache_tokens=traces.peak_tokens(steps, round_to=64), max_requests=4)
+    ops = model.rt.ops
+    rows = ops.tcgen05_swiglu_min_rows
+    ops.set_pair_swiglu_rule(17, 0)
+    try:
+        assert ops.lib.pih_pair_swiglu_wanted(17, 2 * tiny_configs[name]["intermediate_size"]) == 1
+        got = traces.replay(runner, steps)
+        ops.check_errors()
+    finally:
+        ops.set_pair_swiglu_rule(rows, 80)
+    compare_with_plain(got, model_dirs[name], name, requests, "bfloat16", f"{name} {family} on pairs")
+    cache.check()
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_32bit_and_bf16_cuttings_agree_with_each_other(model_dirs, requests_of, dtype):
     """Beyond the plain implementation: the engine's own cuttings agree among themselves.
