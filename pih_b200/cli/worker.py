@@ -12,7 +12,9 @@ command line prints the usage and exits with 2.
 
 Here the model folder stands where the lock file stood (there are no
 plugins to lock), ``--serve`` does not exist (servers are out of scope), and
-the sampling options that the reference fixes in code can be given.
+the sampling options that the reference fixes in code can be given;
+``--logprobs`` and ``--top-logprobs N`` add what its sampler returns with
+every token (plugins/model-qwen3/qwen3_sampler.cpp:132-149) to the line.
 """
 from __future__ import annotations
 
@@ -21,7 +23,7 @@ import sys
 
 USAGE = ("usage: pih-worker --model MODEL_DIR --generate-tokens ID,ID,... --max-tokens COUNT "
          "[--dtype bfloat16|float32] [--temperature T] [--top-p P] [--top-k K] [--seed S] "
-         "[--ignore-eos] [--page-size N] [--max-cache-tokens N]\n"
+         "[--ignore-eos] [--logprobs] [--top-logprobs N] [--page-size N] [--max-cache-tokens N]\n"
          "       pih-worker --random-model MODEL_DIR --config CONFIG_JSON --seed S [--sigma X] "
          "[--store bfloat16|float32]\n")
 
@@ -40,7 +42,7 @@ def _parse_tokens(text: str):
 
 
 def _options(argv):
-    opts, flags = {}, {"--ignore-eos"}
+    opts, flags = {}, {"--ignore-eos", "--logprobs"}
     i = 0
     while i < len(argv):
         a = argv[i]
@@ -59,7 +61,7 @@ def main(argv=None) -> int:
     argv = list(sys.argv[1:] if argv is None else argv)
     opts = _options(argv)
     known = {"--model", "--generate-tokens", "--max-tokens", "--dtype", "--temperature", "--top-p", "--top-k",
-             "--seed", "--ignore-eos", "--page-size", "--max-cache-tokens", "--random-model", "--config",
+             "--seed", "--ignore-eos", "--logprobs", "--top-logprobs", "--page-size", "--max-cache-tokens", "--random-model", "--config",
              "--sigma", "--store"}
     if opts is None or set(opts) - known:
         sys.stderr.write(USAGE)
@@ -93,6 +95,9 @@ def main(argv=None) -> int:
                   "seed": int(opts.get("--seed", 7)), "ignore_eos": bool(opts.get("--ignore-eos", False))}
         if "--top-k" in opts:
             params["top_k"] = int(opts["--top-k"])
+        if "--logprobs" in opts or "--top-logprobs" in opts:       # the result then carries "logprobs" (and "top_logprobs")
+            params["logprobs"] = True
+            params["top_logprobs"] = int(opts.get("--top-logprobs", 0))
         engine = Engine(opts["--model"], opts.get("--dtype", "bfloat16"),
                         page_size=int(opts.get("--page-size", DEFAULT_PAGE_SIZE)),
                         max_cache_tokens=int(opts["--max-cache-tokens"]) if "--max-cache-tokens" in opts

@@ -343,9 +343,13 @@ __device__ __forceinline__ void qk_wide_slots(const VecPack<T, EPL / 2> (&lo)[SP
       }
       continue;
     }
-    T* dst = row + static_cast<size_t>(slot) * D;
-    *reinterpret_cast<VecPack<T, E2>*>(dst) = out_lo;
-    *reinterpret_cast<VecPack<T, E2>*>(dst + HALF) = out_hi;
+    // a k head whose place is the cache goes there only: nothing reads it from the row afterwards (a ninth of
+    // the kernel's bytes with 16 + 8 + 8 heads)
+    if (is_q || dst_cache == nullptr) {
+      T* dst = row + static_cast<size_t>(slot) * D;
+      *reinterpret_cast<VecPack<T, E2>*>(dst) = out_lo;
+      *reinterpret_cast<VecPack<T, E2>*>(dst + HALF) = out_hi;
+    }
     if (dst_cache != nullptr) {
       *reinterpret_cast<VecPack<T, E2>*>(dst_cache) = out_lo;
       *reinterpret_cast<VecPack<T, E2>*>(dst_cache + HALF) = out_hi;

@@ -726,6 +726,182 @@ selected_logprob_kernel(const float* __restrict__ logits, int vocab, const int* 
   }
 }
 
+
+// ---------------------------------------------------------------------------------------------------------
+// The most probable ids of a row with their log-probabilities under the row's scaled logits
+// (plugins/model-qwen3/qwen3_sampler.cpp:118-143: logits / temperature, suppressed ids left out, ordered by
+// value, then by id; at most 20 of them; the choice of top-k / top-p plays no part).  Two kernels: a block a
+// (row, slice of the vocabulary) keeps its slice in shared memory and takes `count` maxima out of it one after
+// the other, with the slice's maximum and its sum of exponentials; a block a row then merges the slices.
+constexpr int kTopLogprobsMax = 20;
+constexpr int kTopThreads = 512;
+constexpr int kTopSliceFloats = 40 * 1024;      // 160 KB of shared memory at most
+constexpr int kTopMaxSlices = 64;
+
+// the better of two (value, id): the larger value, the smaller id among equals (-1: none)
+__device__ __forceinline__ void keep_better(float& v, int& i, float ov, int oi) {
+  if (oi >= 0 && (i < 0 || ov > v || (ov == v && oi < i))) {
+    v = ov;
+    i = oi;
+  }
+}
+// the best (value, id) of the block, to every thread; scratch_v / scratch_i hold 33 words each
+__device__ void block_best(float& v, int& i, float* scratch_v, int* scratch_i) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int warps = (blockDim.x + 31) >> 5;
+#pragma unroll
+  for (int d = 16; d > 0; d >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, v, d);
+    const int oi = __shfl_xor_sync(0xffffffffu, i, d);
+    keep_better(v, i, ov, oi);
+  }
+  __syncthreads();
+  if (lane == 0) {
+    scratch_v[warp] = v;
+    scratch_i[warp] = i;
+  }
+  __syncthreads();
+  if (warp == 0) {
+    float bv = lane < warps ? scratch_v[lane] : 0.0f;
+    int bi = lane < warps ? scratch_i[lane] : -1;
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, bv, d);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, d);
+      keep_better(bv, bi, ov, oi);
+    }
+    if (lane == 0) {
+      scratch_v[32] = bv;
+      scratch_i[32] = bi;
+    }
+  }
+  __syncthreads();
+  v = scratch_v[32];
+  i = scratch_i[32];
+}
+
+// part_v / part_i: [rows, slices, count] candidates; part_ms: [rows, slices, 2] (maximum, sum of exp(x - maximum))
+__global__ void __launch_bounds__(kTopThreads)
+top_logprobs_slices_kernel(const float* __restrict__ logits, int vocab, int count, int slice_len,
+                           const float* __restrict__ fparams, const int* __restrict__ iparams, int icolumns,
+                           float* __restrict__ part_v, int* __restrict__ part_i, float* __restrict__ part_ms,
+                           uint32_t* error) {
+  wait_for_prior_kernels();
+  launch_dependents();
+  extern __shared__ float slice[];
+  __shared__ float scratch_v[33];
+  __shared__ int scratch_i[33];
+  __shared__ int suppressed[kLogprobMaxSuppressed];
+  const int row = blockIdx.y, sl = blockIdx.x, slices = gridDim.x;
+  const int lo = sl * slice_len, n = max(0, min(vocab - lo, slice_len));
+  const float* x = logits + static_cast<size_t>(row) * vocab + lo;
+  float temperature = fparams != nullptr ? fparams[row * 2] : 0.0f;
+  if (!(temperature > 0.0f)) temperature = 1.0f;
+  int nsup = 0;
+  if (iparams != nullptr) {
+    nsup = min(max(iparams[row * icolumns + 5], 0), kLogprobMaxSuppressed);
+    if (threadIdx.x < nsup) suppressed[threadIdx.x] = iparams[row * icolumns + 6 + threadIdx.x];
+  }
+  __syncthreads();
+  // the slice, scaled; a suppressed id (and, reported, a value that is not finite) takes no part: marked by id -1 below
+  float m = -INFINITY;
+  bool bad = false;
+  for (int j = threadIdx.x; j < n; j += kTopThreads) {
+    float v = x[j] / temperature;
+    if (!isfinite(v)) {
+      bad = true;
+      v = -INFINITY;
+    }
+    for (int k = 0; k < nsup; ++k)
+      if (suppressed[k] == lo + j) v = -INFINITY;
+    slice[j] = v;
+    m = fmaxf(m, v);
+  }
+  if (bad) publish_error(error, kNonFiniteLogit);
+  int none = -1;
+  {
+    int id = m == -INFINITY ? -1 : 0;
+    block_best(m, id, scratch_v, scratch_i);             // (only the value matters here)
+    none = id;
+  }
+  float sum = 0.0f;
+  if (none >= 0)
+    for (int j = threadIdx.x; j < n; j += kTopThreads)
+      if (slice[j] != -INFINITY) sum += expf(slice[j] - m);
+  sum = block_sum(sum, scratch_v);
+  const size_t part = static_cast<size_t>(row) * slices + sl;
+  if (threadIdx.x == 0) {
+    part_ms[part * 2] = m;
+    part_ms[part * 2 + 1] = sum;
+  }
+  for (int c = 0; c < count; ++c) {
+    float bv = 0.0f;
+    int bi = -1;
+    for (int j = threadIdx.x; j < n; j += kTopThreads) {
+      const float v = slice[j];
+      if (v != -INFINITY) keep_better(bv, bi, v, lo + j);
+    }
+    block_best(bv, bi, scratch_v, scratch_i);
+    if (threadIdx.x == 0) {
+      part_v[part * count + c] = bv;
+      part_i[part * count + c] = bi;
+      if (bi >= 0) slice[bi - lo] = -INFINITY;            // taken
+    }
+    __syncthreads();
+  }
+}
+
+__global__ void __launch_bounds__(128)
+top_logprobs_merge_kernel(const float* __restrict__ part_v, const int* __restrict__ part_i,
+                          const float* __restrict__ part_ms, int slices, int count, int* __restrict__ out_ids,
+                          float* __restrict__ out_lps, uint32_t* error) {
+  wait_for_prior_kernels();
+  launch_dependents();
+  __shared__ float cand_v[kTopMaxSlices * kTopLogprobsMax];
+  __shared__ int cand_i[kTopMaxSlices * kTopLogprobsMax];
+  __shared__ float scratch_v[33];
+  __shared__ int scratch_i[33];
+  const int row = blockIdx.x;
+  const int total = slices * count;
+  for (int j = threadIdx.x; j < total; j += blockDim.x) {
+    cand_v[j] = part_v[static_cast<size_t>(row) * total + j];
+    cand_i[j] = part_i[static_cast<size_t>(row) * total + j];
+  }
+  float m = -INFINITY;
+  for (int sl = threadIdx.x; sl < slices; sl += blockDim.x) m = fmaxf(m, part_ms[(static_cast<size_t>(row) * slices + sl) * 2]);
+  {
+    int id = m == -INFINITY ? -1 : 0;
+    block_best(m, id, scratch_v, scratch_i);
+  }
+  float sum = 0.0f;
+  for (int sl = threadIdx.x; sl < slices; sl += blockDim.x) {
+    const float ms = part_ms[(static_cast<size_t>(row) * slices + sl) * 2];
+    if (ms != -INFINITY) sum += part_ms[(static_cast<size_t>(row) * slices + sl) * 2 + 1] * expf(ms - m);
+  }
+  sum = block_sum(sum, scratch_v);
+  const float logsumexp = m + logf(sum);
+  if (threadIdx.x == 0 && !(sum > 0.0f)) publish_error(error, kNonFiniteLogit);
+  for (int c = 0; c < count; ++c) {
+    float bv = 0.0f;
+    int bi = -1, bj = -1;
+    for (int j = threadIdx.x; j < total; j += blockDim.x) {
+      if (cand_i[j] < 0) continue;
+      if (bi < 0 || cand_v[j] > bv || (cand_v[j] == bv && cand_i[j] < bi)) {
+        bv = cand_v[j];
+        bi = cand_i[j];
+        bj = j;
+      }
+    }
+    block_best(bv, bi, scratch_v, scratch_i);
+    if (bj >= 0 && cand_i[bj] == bi) cand_i[bj] = -1;      // taken (ids are unique: one thread holds it)
+    if (threadIdx.x == 0) {
+      out_ids[static_cast<size_t>(row) * count + c] = bi;
+      out_lps[static_cast<size_t>(row) * count + c] = bi >= 0 ? bv - logsumexp : -INFINITY;
+    }
+    __syncthreads();
+  }
+}
+
 }  // namespace pih
 
 using namespace pih;
@@ -739,6 +915,53 @@ extern "C" int pih_selected_logprob(const float* logits, int rows, int vocab, co
   if (vocab <= 0 || (iparams != nullptr && icolumns < 6 + kLogprobMaxSuppressed)) return PIH_ERR_BAD_ARGUMENT;
   launch_kernel(selected_logprob_kernel, dim3(rows), dim3(kLogprobThreads), 0, static_cast<cudaStream_t>(stream), logits,
                 vocab, tokens, fparams, iparams, icolumns, out, error);
+  PIH_LAUNCH_CHECK();
+  return 0;
+}
+
+// How many slices pih_top_logprobs cuts a row of `vocab` logits into, and the 4-byte words of scratch it wants:
+// [rows, slices, count] values, the same of ids, [rows, slices, 2] maxima and sums.
+extern "C" int pih_top_logprobs_slices(int vocab) {
+  int slices = 8;
+  while (slices < kTopMaxSlices && (vocab + slices - 1) / slices > kTopSliceFloats) slices *= 2;
+  return (vocab + slices - 1) / slices > kTopSliceFloats ? -1 : slices;
+}
+extern "C" long long pih_top_logprobs_scratch_words(int rows, int vocab, int count) {
+  const int slices = pih_top_logprobs_slices(vocab);
+  if (slices < 0) return -1;
+  return static_cast<long long>(rows) * slices * (2 * count + 2);
+}
+
+// out_ids / out_lps [rows, count]: the `count` (1 to 20) most probable ids of every row that are not suppressed, by
+// value then id, and their log-probabilities under the row's scaled logits.  fparams / iparams as
+// pih_selected_logprob takes them.
+extern "C" int pih_top_logprobs(const float* logits, int rows, int vocab, int count, const float* fparams,
+                                const int* iparams, int icolumns, int* out_ids, float* out_lps, void* scratch,
+                                uint32_t* error, void* stream) {
+  if (rows <= 0) return 0;
+  if (vocab <= 0 || count < 1 || count > kTopLogprobsMax || scratch == nullptr ||
+      (iparams != nullptr && icolumns < 6 + kLogprobMaxSuppressed))
+    return PIH_ERR_BAD_ARGUMENT;
+  const int slices = pih_top_logprobs_slices(vocab);
+  if (slices < 0 || rows > 65535) return PIH_ERR_UNSUPPORTED;
+  const int slice_len = (vocab + slices - 1) / slices;
+  const size_t smem = static_cast<size_t>(slice_len) * sizeof(float);
+  static size_t smem_set = 0;
+  if (smem > 40 * 1024 && smem_set < smem) {
+    cudaError_t e = cudaFuncSetAttribute(top_logprobs_slices_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         static_cast<int>(smem));
+    if (e != cudaSuccess) return static_cast<int>(e);
+    smem_set = smem;
+  }
+  float* part_v = static_cast<float*>(scratch);
+  int* part_i = reinterpret_cast<int*>(part_v + static_cast<size_t>(rows) * slices * count);
+  float* part_ms = reinterpret_cast<float*>(part_i + static_cast<size_t>(rows) * slices * count);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  launch_kernel(top_logprobs_slices_kernel, dim3(slices, rows), dim3(kTopThreads), smem, s, logits, vocab, count,
+                slice_len, fparams, iparams, icolumns, part_v, part_i, part_ms, error);
+  PIH_LAUNCH_CHECK();
+  launch_kernel(top_logprobs_merge_kernel, dim3(rows), dim3(128), 0, s, part_v, part_i, part_ms, slices, count, out_ids,
+                out_lps, error);
   PIH_LAUNCH_CHECK();
   return 0;
 }
@@ -772,10 +995,17 @@ extern "C" int pih_sample(const float* logits, int rows, int vocab, const float*
   if (rows <= 0) return 0;
   if (vocab <= 0) return PIH_ERR_BAD_ARGUMENT;
   if (vocab > kSampleCluster * 65536) return PIH_ERR_UNSUPPORTED;      // (the 32-bit sums of a block's part)
-  // a block's part of a row in shared memory, if it fits beside the kernel's own (7 KB)
+  // a block's part of a row in shared memory, if it fits beside the kernel's own
   const int part = (vocab + kSampleCluster - 1) / kSampleCluster;
   int staged_floats = part;
-  if (static_cast<long long>(part) * 4 > 200 * 1024) staged_floats = 0;
+  static long long room = -1;                           // dynamic shared memory that the kernel's own leaves
+  if (room < 0) {
+    cudaFuncAttributes attr;
+    cudaError_t e = cudaFuncGetAttributes(&attr, sample_kernel);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    room = 227 * 1024 - static_cast<long long>(attr.sharedSizeBytes) - 1024;
+  }
+  if (static_cast<long long>(part) * 4 > room) staged_floats = 0;
   static int smem_set = 0;
   if (staged_floats * 4 > 40 * 1024 && smem_set < staged_floats * 4) {
     cudaError_t e = cudaFuncSetAttribute(sample_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, staged_floats * 4);

@@ -37,6 +37,9 @@ from .scheduler import Request, Scheduler
 RESULT_SCHEMA = "pih.token-generation-result.v1"
 
 
+MAX_TOP_LOGPROBS = 20
+
+
 class _Landing:
     """Pinned host memory for what one step reports back: the ids it sampled, their log-probabilities where a
     request asked for them, and, behind them, the device's error word as it stood after the step; with the
@@ -44,7 +47,8 @@ class _Landing:
 
     def __init__(self, rows: int):
         self.rows = rows
-        self.buffer = torch.empty(2 * rows + 1, dtype=torch.int32, pin_memory=True)
+        # ids [rows], log-probabilities [rows], top ids and top log-probabilities [rows, up to 20] each, the error word
+        self.buffer = torch.empty((2 + 2 * MAX_TOP_LOGPROBS) * rows + 1, dtype=torch.int32, pin_memory=True)
         self.event = torch.cuda.Event()
 
 
@@ -52,10 +56,11 @@ class _InFlight:
     """A step that has been queued on the device: its plan, the ids it samples, and the error word after it —
     both copied to pinned host memory right behind the step, before any later step."""
 
-    def __init__(self, out, tokens, error_word=None, landing: Optional[_Landing] = None, logprobs=None):
+    def __init__(self, out, tokens, error_word=None, landing: Optional[_Landing] = None, logprobs=None, top=None):
         self.out = out
         self.tokens = tokens
         self.logprobs = logprobs            # fp32 on the device, one per sampled id, or None
+        self.top = top                      # (ids [rows, n], log-probabilities [rows, n]) on the device, or None
         self.landing = landing
         self.error_word = error_word
         self.rows = 0 if tokens is None else int(tokens.shape[0])
@@ -67,6 +72,12 @@ class _InFlight:
                 landing.buffer[:self.rows].copy_(tokens, non_blocking=True)
             if logprobs is not None:
                 landing.buffer[landing.rows:landing.rows + self.rows].copy_(logprobs.view(torch.int32), non_blocking=True)
+            if top is not None:
+                n = int(top[0].shape[1])
+                base = 2 * landing.rows
+                landing.buffer[base:base + self.rows * n].copy_(top[0].reshape(-1), non_blocking=True)
+                base += MAX_TOP_LOGPROBS * landing.rows
+                landing.buffer[base:base + self.rows * n].copy_(top[1].reshape(-1).view(torch.int32), non_blocking=True)
             landing.buffer[-1:].copy_(error_word, non_blocking=True)
             landing.event.record()
 
@@ -99,6 +110,21 @@ class _InFlight:
             return self.logprobs.tolist()
         self.wait()
         return self.landing.buffer[self.landing.rows:self.landing.rows + self.rows].view(torch.float32).tolist()
+
+    def top_list(self) -> Optional[List[List[tuple]]]:
+        """Per sampled row its most probable ids with their log-probabilities, best first."""
+        if self.top is None:
+            return None
+        n = int(self.top[0].shape[1])
+        if self.landing is None:
+            ids, lps = self.top[0].tolist(), self.top[1].tolist()
+        else:
+            self.wait()
+            base = 2 * self.landing.rows
+            ids = self.landing.buffer[base:base + self.rows * n].view(self.rows, n).tolist()
+            base += MAX_TOP_LOGPROBS * self.landing.rows
+            lps = self.landing.buffer[base:base + self.rows * n].view(torch.float32).view(self.rows, n).tolist()
+        return [list(zip(i, l)) for i, l in zip(ids, lps)]
 
 
 class Engine:
@@ -298,17 +324,23 @@ class Engine:
                    for s in out.scheduled]
         logits = self.runner.step(entries, token_feed=feed, confirm=False)
         sampling = [s.request for s in out.scheduled if s.samples]
-        tokens = logprobs = None
+        tokens = logprobs = top = None
         if sampling:
             wanted = any(r.params.logprobs for r in sampling)
+            top_n = max(r.params.top_logprobs for r in sampling)
+            extra = {"logprobs": True} if wanted else {}
+            if top_n:
+                extra["top_logprobs"] = top_n
             tokens = self.sampler.sample_on_device(
                 logits, [r.params for r in sampling], [len(r.outputs) + pending for r in sampling],
-                [self.scheduler.suppressed_ids(r, pending) for r in sampling], **({"logprobs": True} if wanted else {}))
-            if wanted:
+                [self.scheduler.suppressed_ids(r, pending) for r in sampling], **extra)
+            if top_n:
+                tokens, logprobs, top = tokens
+            elif wanted:
                 tokens, logprobs = tokens
         word = getattr(self.rt.ops, "error_word", None)
         on_gpu = self.device.type == "cuda" and word is not None
-        flight = _InFlight(out, tokens, word, self._landing() if on_gpu else None, logprobs)
+        flight = _InFlight(out, tokens, word, self._landing() if on_gpu else None, logprobs, top)
         flight.holders = [(s.request.rid, self.cache.requests[s.request.rid]) for s in out.scheduled]
         self._unconfirmed.append(flight)
         return flight
@@ -365,17 +397,22 @@ class Engine:
         out = flight.out
         sampled: List[Optional[int]] = [None] * len(out.scheduled)
         logprobs: List[Optional[float]] = [None] * len(out.scheduled)
+        tops: List[Optional[list]] = [None] * len(out.scheduled)
         if flight.tokens is not None:
             it = iter(flight.token_list())
             lp = flight.logprob_list()
             lp_it = iter(lp) if lp is not None else None
+            top = flight.top_list()
+            top_it = iter(top) if top is not None else None
             for i, s in enumerate(out.scheduled):
                 if s.samples:
                     sampled[i] = next(it)
                     if lp_it is not None:
                         logprobs[i] = next(lp_it)
+                    if top_it is not None:
+                        tops[i] = next(top_it)
         live = [s.request for s in out.scheduled if s.samples and s.request.status != "finished"]
-        self.scheduler.update(out, sampled, logprobs)
+        self.scheduler.update(out, sampled, logprobs, tops)
         progressed = live + list(out.failed)
         for req in progressed:
             if req.status == "finished":
@@ -421,6 +458,10 @@ class Engine:
                   "prompt_tokens": len(req.prompt), "completion_tokens": len(req.outputs)}
         if req.params.logprobs:
             result["logprobs"] = list(req.output_logprobs)     # log-probability of each token under its scaled logits
+            if req.params.top_logprobs:
+                # per token the most probable ids, best first (plugins/surface-openai-http/entrypoint.cpp:367-382)
+                result["top_logprobs"] = [[{"token_id": int(i), "logprob": float(l)} for i, l in step]
+                                          for step in req.output_top_logprobs]
         return result
 
     @staticmethod

@@ -56,6 +56,7 @@ class Request:
     eos_token_ids: Sequence[int] = ()
     outputs: List[int] = field(default_factory=list)
     output_logprobs: List[float] = field(default_factory=list)     # one per output, when the request asked for them
+    output_top_logprobs: List[list] = field(default_factory=list)   # per output [(id, log-probability), ...], best first
     num_computed: int = 0
     status: str = "waiting"              # waiting | running | finished
     finish_reason: Optional[str] = None  # stop | length | capacity | cancelled | error
@@ -250,9 +251,11 @@ class Scheduler:
 
     # -- after the step ----------------------------------------------------------
     def update(self, out: SchedulerOutput, sampled: Sequence[Optional[int]],
-               logprobs: Optional[Sequence[Optional[float]]] = None) -> List[Request]:
+               logprobs: Optional[Sequence[Optional[float]]] = None,
+               top_logprobs: Optional[Sequence[Optional[list]]] = None) -> List[Request]:
         """``sampled[i]`` is the token sampled for ``out.scheduled[i]`` (None
-        when that entry did not sample), ``logprobs[i]`` its log-probability where it was asked for.
+        when that entry did not sample), ``logprobs[i]`` its log-probability where it was asked for,
+        ``top_logprobs[i]`` the step's most probable ids with theirs (the request keeps as many as it asked for).
         Returns the requests that finished."""
         finished = []
         for i, (s, tok) in enumerate(zip(out.scheduled, sampled)):
@@ -267,6 +270,8 @@ class Scheduler:
             req.outputs.append(int(tok))
             if req.params.logprobs and logprobs is not None and logprobs[i] is not None:
                 req.output_logprobs.append(float(logprobs[i]))
+            if req.params.top_logprobs and top_logprobs is not None and top_logprobs[i] is not None:
+                req.output_top_logprobs.append(list(top_logprobs[i][:req.params.top_logprobs]))
             accepted = len(req.outputs)
             stops = set(req.params.stop_token_ids)
             if not req.params.ignore_eos:

@@ -101,12 +101,13 @@ class CudaOps:
         lib = self.lib
         for name in ("pih_embedding", "pih_rmsnorm", "pih_qk_norm_rope_kv_write", "pih_silu_mul",
                      "pih_gather_rows", "pih_gemm_simt", "pih_paged_attention_generic", "pih_argmax",
-                     "pih_sample", "pih_selected_logprob", "pih_paged_attention_mma", "pih_gemm_tcgen05", "pih_make_kv_tensor_map",
+                     "pih_sample", "pih_selected_logprob", "pih_top_logprobs", "pih_paged_attention_mma", "pih_gemm_tcgen05", "pih_make_kv_tensor_map",
                      "pih_attention_prefill_tcgen05", "pih_gemm_skinny", "pih_set_dependent_launch", "pih_set_attention_cluster_merge",
                      "pih_gemm_skinny_f32out",
                      "pih_qk_attention_fused", "pih_gemm_tcgen05_swiglu", "pih_gemm_tcgen05_pair"):
             getattr(lib, name).restype = c_int
         lib.pih_attention_scratch_floats.restype = c_ll
+        lib.pih_top_logprobs_scratch_words.restype = c_ll
 
     def _native_supports(self, block) -> bool:
         from .native_block import NativeBlocks
@@ -335,6 +336,9 @@ class CudaOps:
 
     def qk_norm_rope_kv_write(self, qkv, *, heads, kv_heads, head_dim, q_norm, k_norm, eps, rope_table,
                               rotary_dim, positions, slot_mapping, kv_cache, write_kv) -> None:
+        """Per-head RMSNorm and rotation of the q and k heads of the rows ``[q | k | v]``; q is changed in place,
+        and with ``write_kv`` k and v go to their slots of the cache.  The k part of the rows is not to be read
+        afterwards: it holds the new k only where the kernel also wrote it there (few rows, rows without a slot)."""
         rows = qkv.shape[0]
         wd = _DT[q_norm.dtype] if q_norm is not None else _DT[qkv.dtype]
         num_pages, page_size = kv_cache.shape[0], kv_cache.shape[3]
@@ -540,6 +544,24 @@ class CudaOps:
                                            self._stream())
         self._check(rc, "selected_logprob")
         return out
+
+    def top_logprobs(self, logits: torch.Tensor, count: int, fparams: Optional[torch.Tensor] = None,
+                     iparams: Optional[torch.Tensor] = None):
+        """The ``count`` (1 to 20) most probable ids of every row that are not suppressed — by value, then by id —
+        and their log-probabilities under the row's scaled logits: ``(int32 [rows, count], fp32 [rows, count])``;
+        the parameters are those given to ``sample``, or none for greedy rows."""
+        rows, vocab = logits.shape
+        words = self.lib.pih_top_logprobs_scratch_words(rows, vocab, count)
+        if words < 0:
+            raise ValueError(f"top_logprobs takes no vocabulary of {vocab}")
+        scratch = torch.empty(max(int(words), 1), dtype=torch.float32, device=logits.device)
+        ids = torch.empty(rows, count, dtype=torch.int32, device=logits.device)
+        lps = torch.empty(rows, count, dtype=torch.float32, device=logits.device)
+        rc = self.lib.pih_top_logprobs(_ptr(logits), rows, vocab, count, _ptr(fparams), _ptr(iparams),
+                                       iparams.shape[1] if iparams is not None else 0, _ptr(ids), _ptr(lps),
+                                       _ptr(scratch), self._err(), self._stream())
+        self._check(rc, "top_logprobs")
+        return ids, lps
 
     def sample(self, logits: torch.Tensor, fparams: torch.Tensor, iparams: torch.Tensor) -> torch.Tensor:
         rows, vocab = logits.shape

@@ -9,8 +9,11 @@ include/pih/scheduler/controller_request_arena.h:28-30) without an HTTP key;
 here they are plain options.  ``max_tokens`` defaults to 128
 (plugins/model-qwen3/entrypoint.cpp:252-254).  ``logprobs`` asks for what the
 reference's sampler returns with every token, ``selected_logprob``
-(plugins/model-qwen3/qwen3_sampler.cpp:143-149); its ``top_logprobs`` list is
-not returned.
+(plugins/model-qwen3/qwen3_sampler.cpp:143-149); ``top_logprobs`` = n (at most
+20, qwen3_sampler.cpp:23, and only with ``logprobs``:
+plugins/model-qwen3/controller_packed_driver.cpp:125-126) adds the n most
+probable ids of every step with their log-probabilities
+(qwen3_sampler.cpp:132-143).
 """
 from __future__ import annotations
 
@@ -31,6 +34,7 @@ class SamplingParams:
     ignore_eos: bool = False
     n: int = 1
     logprobs: bool = False             # return the log-probability of every sampled token (the reference's selected_logprob)
+    top_logprobs: int = 0              # ... and the ids and log-probabilities of this many most probable tokens (at most 20)
 
     def __post_init__(self):
         if self.n != 1:
@@ -52,6 +56,11 @@ class SamplingParams:
             raise ValueError("seed must be an integer in 0..INT64_MAX")
         if isinstance(self.max_tokens, bool) or not isinstance(self.max_tokens, int) or self.max_tokens < 1:
             raise ValueError("max_tokens must be a positive integer")
+        if isinstance(self.top_logprobs, bool) or not isinstance(self.top_logprobs, int) \
+                or not 0 <= self.top_logprobs <= 20:
+            raise ValueError("top_logprobs must be an integer in 0..20")
+        if self.top_logprobs and not self.logprobs:
+            raise ValueError("top_logprobs needs logprobs")
         if self.minimum_new_tokens < 0:
             raise ValueError("minimum_new_tokens must be >= 0")
 

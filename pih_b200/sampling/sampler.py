@@ -68,14 +68,17 @@ class Sampler:
         return stage
 
     def sample_on_device(self, logits: torch.Tensor, params: Sequence[SamplingParams], ordinals: Sequence[int],
-                         suppressed: Sequence[Sequence[int]], logprobs: bool = False):
+                         suppressed: Sequence[Sequence[int]], logprobs: bool = False, top_logprobs: int = 0):
         """The sampled ids as an int32 tensor on the device, without waiting for them; with ``logprobs`` a pair
-        of the ids and the log-probability of each (fp32, on the device)."""
+        of the ids and the log-probability of each (fp32, on the device); with ``top_logprobs`` = n > 0 a triple
+        whose third member is ``(ids [rows, n], log-probabilities [rows, n])`` of every row's n most probable ids."""
         S = logits.shape[0]
         if not (len(params) == len(ordinals) == len(suppressed) == S):
             raise ValueError("one set of sampling parameters per row of logits is needed")
         if all(p.greedy for p in params) and not any(suppressed):
             ids = self.ops.argmax(logits)
+            if top_logprobs > 0:
+                return ids, self.ops.selected_logprob(logits, ids), self.ops.top_logprobs(logits, top_logprobs)
             return (ids, self.ops.selected_logprob(logits, ids)) if logprobs else ids
         stage = self._stage(S)
         host = stage[0][:S * (2 + _INT_COLUMNS)]
@@ -104,4 +107,7 @@ class Sampler:
             stage[2] = True
         fparams, iparams = dev[:2 * S].view(torch.float32).view(S, 2), dev[2 * S:].view(S, _INT_COLUMNS)
         ids = self.ops.sample(logits, fparams, iparams)
+        if top_logprobs > 0:
+            return (ids, self.ops.selected_logprob(logits, ids, fparams, iparams),
+                    self.ops.top_logprobs(logits, top_logprobs, fparams, iparams))
         return (ids, self.ops.selected_logprob(logits, ids, fparams, iparams)) if logprobs else ids

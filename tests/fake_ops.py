@@ -131,6 +131,18 @@ class FakeOps:
             out.append(float(scaled[int(tokens[i])] - torch.logsumexp(scaled[keep], dim=0)))
         return torch.tensor(out, dtype=torch.float32)
 
+    def top_logprobs(self, logits, count, fparams=None, iparams=None):
+        from plain_impl import top_logprobs
+        ids, lps = [], []
+        for i in range(logits.shape[0]):
+            t = float(fparams[i, 0]) if fparams is not None else 0.0
+            nsup = int(iparams[i, 5]) if iparams is not None else 0
+            sup = [int(v) for v in iparams[i, 6:6 + nsup].tolist()] if nsup else []
+            top = top_logprobs(logits[i].tolist(), count, temperature=t, suppressed=sup)
+            ids.append([a for a, _ in top])
+            lps.append([b for _, b in top])
+        return torch.tensor(ids, dtype=torch.int32), torch.tensor(lps, dtype=torch.float32)
+
     def sample(self, logits, fparams, iparams):
         from plain_impl import sample
         out = []

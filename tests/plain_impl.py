@@ -357,6 +357,24 @@ def sample(logits, temperature: float = 0.0, top_p: float = 1.0, top_k: int | No
     return tok, float(scaled[tok] - lse), word
 
 
+def top_logprobs(logits, count: int, temperature: float = 0.0, suppressed=()):
+    """The ``count`` most probable ids of one row with their log-probabilities, best first.
+
+    plugins/model-qwen3/qwen3_sampler.cpp:118-143: scaled = logit / T (T = 1 when greedy); suppressed ids are
+    left out; order by scaled value descending, ties to the lower id; the first ``count`` with
+    scaled - logsumexp (here in float64: the reference's own float32 sum runs one after the other).
+    """
+    import numpy as np
+    lg = np.asarray(logits, dtype=np.float32)
+    scaled = (lg / np.float32(1.0 if temperature == 0.0 else temperature)).astype(np.float32)
+    sup = set(suppressed)
+    allowed = [i for i in range(lg.shape[0]) if i not in sup]
+    vals = scaled[allowed].astype(np.float64)
+    lse = float(vals.max() + np.log(np.exp(vals - vals.max()).sum()))
+    order = sorted(allowed, key=lambda i: (-float(scaled[i]), i))[:count]
+    return [(i, float(scaled[i]) - lse) for i in order]
+
+
 def generate_greedy(cfg: dict, w: dict, prompt, max_new: int, rounding="none"):
     """Greedy generation by re-running the whole sequence for every token."""
     ids = list(prompt)

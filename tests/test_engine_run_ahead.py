@@ -171,3 +171,35 @@ def test_log_probabilities_come_back_with_the_tokens(model_dirs, tiny_configs, t
     scaled = logits.double() / (temperature if temperature > 0 else 1.0)
     want = torch.log_softmax(scaled, dim=-1)[torch.arange(7), torch.tensor(got[0]["token_ids"])]
     torch.testing.assert_close(torch.tensor(got[0]["logprobs"], dtype=torch.float64), want, rtol=1e-4, atol=1e-4)
+
+
+def test_the_most_probable_ids_come_back_with_the_tokens(model_dirs, tiny_configs):
+    """``top_logprobs=n`` (with ``logprobs``): per generated token the n most probable ids with their
+    log-probabilities, best first — the plain implementation's ordering of the scaled logits; each request gets as
+    many as it asked for, one that did not ask gets none; and the option needs ``logprobs`` and stays within 20."""
+    import plain_impl
+    from conftest import load_plain_weights
+    from pih_b200.sampling import SamplingParams
+    prompts = _prompts(tiny_configs["A"]["vocab_size"], [9, 5, 6], seed=10)
+    per_prompt = [dict(logprobs=True, top_logprobs=5), dict(logprobs=True, top_logprobs=2, temperature=0.7, seed=2),
+                  dict(logprobs=True)]
+    kw = dict(max_tokens=6, ignore_eos=True, parameters_per_prompt=per_prompt)
+    got = _engine(model_dirs["A"], True, page_size=16).complete_batch(prompts, **kw)
+    assert got == _engine(model_dirs["A"], False, page_size=16).complete_batch(prompts, **kw)
+    assert "top_logprobs" not in got[2]
+    cfg, w = load_plain_weights(model_dirs["A"])
+    for r, prompt, n, temperature in ((got[0], prompts[0], 5, 0.0), (got[1], prompts[1], 2, 0.7)):
+        assert len(r["top_logprobs"]) == 6
+        logits = plain_impl.forward(cfg, w, prompt + r["token_ids"])[len(prompt) - 1:-1]
+        for step, row in enumerate(r["top_logprobs"]):
+            want = plain_impl.top_logprobs(logits[step].tolist(), n, temperature=temperature)
+            assert [e["token_id"] for e in row] == [i for i, _ in want]
+            assert all(abs(e["logprob"] - lp) < 1e-4 for e, (_, lp) in zip(row, want))
+            if temperature == 0.0:                              # greedy: the first of them is the token, with its logprob
+                assert row[0]["token_id"] == r["token_ids"][step]
+                assert abs(row[0]["logprob"] - r["logprobs"][step]) < 1e-5
+    with pytest.raises(ValueError):
+        SamplingParams(top_logprobs=3)
+    with pytest.raises(ValueError):
+        SamplingParams(logprobs=True, top_logprobs=21)
+

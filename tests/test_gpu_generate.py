@@ -278,11 +278,16 @@ def test_log_probabilities_through_the_entry_point(model_dirs, tiny_configs, dty
     vocab = tiny_configs["A"]["vocab_size"]
     prompts = list(traces.make_requests(vocab, [23, 9, 40], seed=15).values())
     e = Engine(model_dirs["A"], dtype, page_size=16, max_cache_tokens=1024, maximum_batch_sequences=4)
-    per = [dict(logprobs=True), dict(logprobs=True, temperature=0.8, seed=3), dict()]
+    per = [dict(logprobs=True, top_logprobs=4), dict(logprobs=True, temperature=0.8, seed=3), dict()]
     got = e.complete_batch(prompts, max_tokens=9, ignore_eos=True, parameters_per_prompt=per)
     e.drain()
     e.rt.ops.check_errors()
-    assert "logprobs" not in got[2]
+    assert "logprobs" not in got[2] and "top_logprobs" not in got[1]
+    # the greedy request's list of the most probable ids opens with its token and that token's log-probability
+    assert len(got[0]["top_logprobs"]) == 9
+    for tok, lp, row in zip(got[0]["token_ids"], got[0]["logprobs"], got[0]["top_logprobs"]):
+        assert len(row) == 4 and row[0]["token_id"] == tok and abs(row[0]["logprob"] - lp) < 1e-5
+        assert all(a["logprob"] >= b["logprob"] for a, b in zip(row, row[1:]))
     cfg, w = load_plain_weights(model_dirs["A"])
     for r, prompt, temperature in ((got[0], prompts[0], 1.0), (got[1], prompts[1], 0.8)):
         assert len(r["logprobs"]) == 9 and all(lp <= 0.0 for lp in r["logprobs"])

@@ -585,6 +585,41 @@ def test_selected_logprob(ops, vocab):
     assert ids.tolist() == torch.argmax(logits, dim=-1).tolist()
 
 
+@pytest.mark.parametrize("vocab,count", [(384, 20), (5000, 7), (151936, 20), (151936, 1), (400001, 3)])
+def test_top_logprobs(ops, vocab, count):
+    """The most probable ids with their log-probabilities (the reference's top_logprobs): greedy and scaled rows,
+    rows whose best ids are suppressed, a plateau of equal logits (ties go to the lower id) that spans slices of the
+    vocabulary — against the plain ordering and the exact log-probabilities in float64."""
+    from pih_b200.sampling import Sampler, SamplingParams
+    g = torch.Generator().manual_seed(23)
+    S = 6
+    logits = torch.randn(S, vocab, generator=g) * 3.0
+    logits[1, torch.randperm(vocab, generator=g)[:40]] = 9.5           # a plateau above everything else
+    logits[2, vocab - 1] = 20.0                                          # the last id of the last slice
+    rows = []
+    for i in range(S):
+        t = [0.0, 0.7, 1.0, 2.0][i % 4]
+        sup = [] if i % 3 else sorted(set(torch.topk(logits[i], 3).indices.tolist() + [5]))
+        rows.append((t, sup))
+    sampler = Sampler(ops, vocab, torch.device(DEV))
+    params = [SamplingParams(temperature=t, seed=i, logprobs=True, top_logprobs=count) for i, (t, _) in enumerate(rows)]
+    ids, lps, (top_ids, top_lps) = sampler.sample_on_device(logits.to(DEV), params, [0] * S, [sup for _, sup in rows],
+                                                            logprobs=True, top_logprobs=count)
+    ops.check_errors()
+    top_ids, top_lps = top_ids.tolist(), top_lps.tolist()
+    for i, (t, sup) in enumerate(rows):
+        want = plain_impl.top_logprobs(logits[i].numpy(), count, temperature=t, suppressed=sup)
+        assert top_ids[i] == [a for a, _ in want], (i, top_ids[i], want)
+        for got, (_, lp) in zip(top_lps[i], want):
+            assert abs(got - lp) <= 2e-5 * max(1.0, abs(lp)), (i, got, lp)
+    # all rows greedy and nothing suppressed: the argmax path; the first of the list is the chosen token
+    greedy = [SamplingParams(logprobs=True, top_logprobs=count)] * S
+    ids, lps, (top_ids, top_lps) = sampler.sample_on_device(logits.to(DEV), greedy, [0] * S, [[]] * S, logprobs=True,
+                                                            top_logprobs=count)
+    assert top_ids[:, 0].tolist() == ids.tolist()
+    torch.testing.assert_close(top_lps[:, 0], lps, rtol=1e-6, atol=1e-6)
+
+
 def test_sampler_at_the_full_vocabulary(ops):
     """The vocabulary that serving samples from (151 936): the radix selection's two-level counts and the
     fixed-point mass over 150 000 terms.  Temperature alone, top-k 50, top-p 0.9, both, a suppressed arg-max,
