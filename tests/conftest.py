@@ -63,7 +63,7 @@ TINY_D = {
     "max_position_embeddings": 1024, "rope_theta": 1000000.0, "rms_norm_eps": 1e-6,
     "bos_token_id": 0, "eos_token_id": 1, "attention_bias": False, "use_sliding_window": False,
 }
-# sigma and seed of the random weights (BASELINE configs: 0.02 / seed 0 and 0.05 / seed 1)
+# sigma and seed of the random weights (the benchmark definition's tiny configurations: 0.02 / seed 0 and 0.05 / seed 1)
 TINY_INIT = {"A": (0.02, 0), "B": (0.05, 1), "C": (0.06, 2), "D": (0.08, 3)}
 TINY = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D}
 

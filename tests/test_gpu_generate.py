@@ -19,7 +19,7 @@ DEV = "cuda:0"
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("name", ["A", "B"])
 def test_greedy_generation_through_the_entry_point(model_dirs, tiny_configs, name, dtype):
-    """BASELINE workload of tiny A: 3 requests, prompts 5/11/17, 8 greedy tokens, page 16 — and B's."""
+    """The benchmark definition's workload of tiny A: 3 requests, prompts 5/11/17, 8 greedy tokens, page 16 — and B's."""
     from pih_b200.engine import Engine
     lengths = [5, 11, 17] if name == "A" else [1, 9, 33, 64]
     new = 8 if name == "A" else 12
@@ -48,7 +48,7 @@ def test_greedy_generation_through_the_entry_point(model_dirs, tiny_configs, nam
 
 
 def test_temperature_sampling_is_independent_of_batching(model_dirs, tiny_configs):
-    """BASELINE workload of tiny B: chunked prefill (8) mixed with decode, temperature 0.8, seed 7."""
+    """The benchmark definition's workload of tiny B: chunked prefill (8) mixed with decode, temperature 0.8, seed 7."""
     from pih_b200.engine import Engine
     prompts = list(traces.make_requests(384, [1, 9, 33, 64], seed=22).values())
     kw = dict(max_tokens=12, temperature=0.8, seed=7, ignore_eos=True)
