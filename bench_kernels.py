@@ -155,7 +155,7 @@ def main() -> int:
             rates.update(flops=2 * args.m * args.n * args.k, m=args.m, n=args.n, k=args.k,
                          bytes=2 * (args.m * args.k + args.n * args.k + args.m * args.n))
             if args.impl in ("tcgen05", "tcgen05pair") and args.fused == "swiglu":
-                fn = lambda: ops.linear_tcgen05_swiglu(x, w, tile_n=args.tile_n, pairs=args.impl == "tcgen05pair")
+                fn = lambda: ops.linear_tcgen05_swiglu(x, w)             # (on pairs of SMs whichever of the two is named)
             elif args.impl == "library" and args.fused == "swiglu":
                 fn = lambda: ops.silu_mul(torch.mm(x, w.t()), 8)
             elif args.impl in ("tcgen05", "tcgen05pair"):

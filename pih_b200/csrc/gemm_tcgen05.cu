@@ -148,11 +148,7 @@ __device__ __forceinline__ void store_chunk(const uint32_t (&v)[32], TC* __restr
 // Persistent: CTA b computes tiles b, b + gridDim.x, ... (tile t = (t % tiles_m, t / tiles_m), so that the
 // CTAs that run together share a panel of W in L2).  Two accumulators in tensor memory alternate, so the
 // epilogue of one tile overlaps the products of the next.
-// SWIGLU: the rows of W (columns of the product) come in blocks of 16 = 8 gate columns + their 8 up columns, and
-// the epilogue writes out[m, 8 b + i] = round(silu(round(g)) * round(u)) for block b — C is [M, N / 2] — with the
-// roundings of the separate kernels (the product's bf16 output, then SiLU-mul): the gate/up product of a prompt
-// portion never writes its [M, 2 I] result to memory.
-template <typename TC, int BN, int NSTAGES, bool SWIGLU>
+template <typename TC, int BN, int NSTAGES>
 __global__ void __launch_bounds__(192)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                     TC* __restrict__ C, int M, int N, int K, long long ldc, uint32_t* error) {
@@ -263,7 +259,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         uint32_t v[32];
         const uint32_t taddr = tmem_base + buf * BN + (static_cast<uint32_t>(quarter * 32) << 16) + c0;
         tmem_load_32_columns(taddr, v);
-        store_chunk<TC, SWIGLU>(v, C, row, M, N, n0 + c0, ldc);
+        store_chunk<TC, false>(v, C, row, M, N, n0 + c0, ldc);
       }
       // the accumulator may be overwritten once all four epilogue warps have read it
       asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
@@ -294,6 +290,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 //       barrier (16 arrivals) when it has read it.
 // A cluster barrier after the set-up (no CTA signals a barrier that is not initialised) and one before the
 // tensor memory is freed (no CTA leaves while the other may still read its shared memory or signal it).
+// SWIGLU: the rows of W (columns of the product) come in blocks of 16 = 8 gate columns + their 8 up columns, and
+// the epilogue writes out[m, 8 b + i] = round(silu(round(g)) * round(u)) for block b — C is [M, N / 2] — with the
+// roundings of the separate kernels (the product's bf16 output, then SiLU-mul): the gate/up product of a prompt
+// portion never writes its [M, 2 I] result to memory.
 template <int BN, int NSTAGES>
 struct PairSmem {
   alignas(1024) __nv_bfloat16 a[NSTAGES][GM * GK];          // this CTA's 128 rows of A
@@ -594,20 +594,20 @@ using namespace pih;
 // out_dtype: PIH_BF16 or PIH_F32.  Returns PIH_ERR_UNSUPPORTED when the operands cannot be described
 // to TMA (K or a row stride not a multiple of 8 elements, a base not 16-byte aligned): the caller then
 // uses another product.
-template <typename TC, int BN, int NSTAGES, bool SWIGLU = false>
+template <typename TC, int BN, int NSTAGES>
 static int launch_gemm(const CUtensorMap& map_a, const CUtensorMap& map_w, void* C, int M, int N, int K,
                        long long ldc, uint32_t* error, int sms, cudaStream_t s) {
   const int smem = static_cast<int>(sizeof(GemmSmem<BN, NSTAGES>)) + 1024;
   static bool configured = false;                     // per instance
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<TC, BN, NSTAGES, SWIGLU>,
+    cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<TC, BN, NSTAGES>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return static_cast<int>(e);
     configured = true;
   }
   const long long tiles = static_cast<long long>((M + GM - 1) / GM) * ((N + BN - 1) / BN);
   const int grid = static_cast<int>(tiles < sms ? tiles : sms);
-  launch_kernel(gemm_tcgen05_kernel<TC, BN, NSTAGES, SWIGLU>, dim3(grid), dim3(192), smem, s, map_a, map_w, static_cast<TC*>(C), M, N, K, ldc, error);
+  launch_kernel(gemm_tcgen05_kernel<TC, BN, NSTAGES>, dim3(grid), dim3(192), smem, s, map_a, map_w, static_cast<TC*>(C), M, N, K, ldc, error);
   PIH_LAUNCH_CHECK();
   return 0;
 }
@@ -660,30 +660,6 @@ extern "C" int pih_gemm_tcgen05(int out_dtype, const void* A, const void* W, voi
   return PIH_ERR_BAD_ARGUMENT;
 }
 
-// The gate/up product of a SwiGLU feed-forward with SiLU-mul in its epilogue (bf16): W [N, K] holds blocks of 8
-// gate rows followed by their 8 up rows (N a multiple of 16), C is [M, N / 2] with row stride ldc.
-extern "C" int pih_gemm_tcgen05_swiglu(const void* A, const void* W, void* C, int M, int N, int K, long long lda,
-                                       long long ldw, long long ldc, int tile_n, uint32_t* error, void* stream) {
-  if (M <= 0 || N <= 0) return 0;
-  if (K <= 0 || (tile_n != 0 && tile_n != 128 && tile_n != 256)) return PIH_ERR_BAD_ARGUMENT;
-  if (N % 16 || K % 8 || lda % 8 || ldw % 8 || (reinterpret_cast<uintptr_t>(A) & 15) ||
-      (reinterpret_cast<uintptr_t>(W) & 15) || (reinterpret_cast<uintptr_t>(C) & 3) || ldc % 2)
-    return PIH_ERR_UNSUPPORTED;
-  static int sms = 0;
-  if (sms == 0) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    if (sms <= 0) sms = 148;
-  }
-  const int bn = tile_n != 0 ? tile_n : 256;
-  CUtensorMap map_a, map_w;
-  if (!make_map(&map_a, A, M, K, lda, GM) || !make_map(&map_w, W, N, K, ldw, bn)) return PIH_ERR_UNSUPPORTED;
-  cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (bn == 256) return launch_gemm<__nv_bfloat16, 256, 4, true>(map_a, map_w, C, M, N, K, ldc, error, sms, s);
-  return launch_gemm<__nv_bfloat16, 128, 6, true>(map_a, map_w, C, M, N, K, ldc, error, sms, s);
-}
-
 template <typename TC, int BN, int NSTAGES, bool SWIGLU>
 static int launch_pair(const CUtensorMap& map_a, const CUtensorMap& map_w, const CUtensorMap& map_c, int store_by_tma,
                        void* C, int M, int N, int K, long long ldc, uint32_t* error, cudaStream_t s) {
@@ -718,7 +694,7 @@ static int launch_pair(const CUtensorMap& map_a, const CUtensorMap& map_w, const
 }
 
 // The product on pairs of SMs (256 x tile_n tiles, tile_n 128 or 256; 0: 256).  swiglu != 0: W holds blocks of
-// 8 gate rows followed by their 8 up rows, C is [M, N / 2] and bf16 (as pih_gemm_tcgen05_swiglu).
+// 8 gate rows followed by their 8 up rows (N a multiple of 16), C is [M, N / 2] and bf16, the tile 256 wide.
 extern "C" int pih_gemm_tcgen05_pair(int out_dtype, const void* A, const void* W, void* C, int M, int N, int K,
                                      long long lda, long long ldw, long long ldc, int tile_n, int swiglu,
                                      uint32_t* error, void* stream) {

@@ -104,7 +104,7 @@ class CudaOps:
                      "pih_sample", "pih_selected_logprob", "pih_top_logprobs", "pih_paged_attention_mma", "pih_gemm_tcgen05", "pih_make_kv_tensor_map",
                      "pih_attention_prefill_tcgen05", "pih_gemm_skinny", "pih_set_dependent_launch", "pih_set_attention_cluster_merge",
                      "pih_gemm_skinny_f32out",
-                     "pih_qk_attention_fused", "pih_gemm_tcgen05_swiglu", "pih_gemm_tcgen05_pair"):
+                     "pih_qk_attention_fused", "pih_gemm_tcgen05_pair"):
             getattr(lib, name).restype = c_int
         lib.pih_attention_scratch_floats.restype = c_ll
         lib.pih_top_logprobs_scratch_words.restype = c_ll
@@ -254,26 +254,21 @@ class CudaOps:
             return None
         return self.linear_skinny(x, w, residual=residual)
 
-    def linear_tcgen05_swiglu(self, x: torch.Tensor, w: torch.Tensor, tile_n: int = 0, pairs: bool = False):
-        """``SwiGLU(x . w^T)`` with the pack's tcgen05 product and SiLU-mul in its epilogue: ``w`` holds blocks
-        of 8 gate rows followed by their 8 up rows; returns ``[M, N / 2]`` (bf16), or None for shapes that the
-        kernel does not take.  ``pairs``: the kernel that puts two SMs on a 256-row tile."""
+    def linear_tcgen05_swiglu(self, x: torch.Tensor, w: torch.Tensor):
+        """``SwiGLU(x . w^T)`` with the pack's tcgen05 product on pairs of SMs and SiLU-mul in its epilogue: ``w``
+        holds blocks of 8 gate rows followed by their 8 up rows; returns ``[M, N / 2]`` (bf16), or None for shapes
+        that the kernel does not take."""
         M, K = x.shape
         N = w.shape[0]
         if x.dtype != torch.bfloat16 or N % 16 or x.stride(1) != 1 or w.stride(1) != 1:
             return None
         out = torch.empty(M, N // 2, dtype=torch.bfloat16, device=x.device)
-        if pairs:
-            rc = self.lib.pih_gemm_tcgen05_pair(_DT[torch.bfloat16], _ptr(x), _ptr(w), _ptr(out), M, N, K,
-                                                c_ll(x.stride(0)), c_ll(w.stride(0)), c_ll(out.stride(0)), tile_n, 1,
-                                                self._err(), self._stream())
-        else:
-            rc = self.lib.pih_gemm_tcgen05_swiglu(_ptr(x), _ptr(w), _ptr(out), M, N, K, c_ll(x.stride(0)),
-                                                  c_ll(w.stride(0)), c_ll(out.stride(0)), tile_n, self._err(),
-                                                  self._stream())
+        rc = self.lib.pih_gemm_tcgen05_pair(_DT[torch.bfloat16], _ptr(x), _ptr(w), _ptr(out), M, N, K,
+                                            c_ll(x.stride(0)), c_ll(w.stride(0)), c_ll(out.stride(0)), 0, 1,
+                                            self._err(), self._stream())
         if rc == -2:
             return None
-        self._check(rc, "gemm_tcgen05_swiglu")
+        self._check(rc, "gemm_tcgen05_pair")
         return out
 
     def norm_linear(self, h: torch.Tensor, delta: Optional[torch.Tensor], norm_weight: torch.Tensor, eps: float,
@@ -294,7 +289,7 @@ class CudaOps:
         xn = self.rmsnorm(h, norm_weight, eps, delta=delta)
         if (swiglu_interleave == 8 and xn.dtype == torch.bfloat16
                 and self.lib.pih_pair_swiglu_wanted(xn.shape[0], w.shape[0])):
-            out = self.linear_tcgen05_swiglu(xn, w, pairs=True)
+            out = self.linear_tcgen05_swiglu(xn, w)
             if out is not None:
                 return h, out
         out = self.linear(xn, w)
