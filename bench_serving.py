@@ -48,6 +48,8 @@ def main() -> int:
     ap.add_argument("--budget", type=int, default=None, help="tokens a step (default: the shape's workload)")
     ap.add_argument("--no-warm-up", action="store_true",
                     help="first request on a cold engine: what a process sets up and captures once falls into the run")
+    ap.add_argument("--attention-in-turn", action="store_true",
+                    help="a mixed step's two attention kernels one after the other instead of side by side")
     ap.add_argument("--capture-decode-after", type=int, default=None,
                     help="uncaptured runs of a decode shape before it is captured into a CUDA graph")
     args = ap.parse_args()
@@ -93,6 +95,8 @@ def main() -> int:
                     maximum_context_tokens=hi + work["new_tokens"] + 32)
     if args.capture_decode_after is not None:
         engine.runner.capture_decode_after = args.capture_decode_after
+    if args.attention_in_turn:
+        engine.rt.ops.set_attention_side_by_side(False)
     # as a server does before it opens: the shapes that its limits make likely are run and captured once
     warm = None if args.no_warm_up else engine.warm_up()
     reqs = []

@@ -194,6 +194,30 @@ int product(const PihStepArgs& s, const void* x, long long ldx, const void* w, l
   return rc == 0 ? 0 : 1000 + rc;
 }
 
+// A second stream with the two events of a fork and a join, one set a device, made at the first use (which is not
+// inside a graph capture: a step of a new shape runs uncaptured first).
+struct Fork {
+  cudaStream_t stream = nullptr;
+  cudaEvent_t forked = nullptr, joined = nullptr;
+  int state = 0;                         // 0 not tried, 1 ready, -1 unavailable
+};
+Fork g_fork[64];
+int g_attention_side_by_side = 1;
+
+Fork* side_stream() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  Fork& f = g_fork[dev];
+  if (f.state == 0) {
+    f.state = -1;
+    if (cudaStreamCreateWithFlags(&f.stream, cudaStreamNonBlocking) == cudaSuccess &&
+        cudaEventCreateWithFlags(&f.forked, cudaEventDisableTiming) == cudaSuccess &&
+        cudaEventCreateWithFlags(&f.joined, cudaEventDisableTiming) == cudaSuccess)
+      f.state = 1;
+  }
+  return f.state == 1 ? &f : nullptr;
+}
+
 bool few_rows(const PihStepArgs& s) { return s.dtype == PIH_BF16 && s.rows <= s.skinny_max_rows && s.rows <= 16; }
 
 #define PIH_TRY(call)            \
@@ -204,6 +228,14 @@ bool few_rows(const PihStepArgs& s) { return s.dtype == PIH_BF16 && s.rows <= s.
   } while (0)
 
 }  // namespace
+
+// 1 (the default): in a step with prompt portions and decoding requests the two attention kernels run side by side;
+// 0: one after the other in the step's stream.  Returns the previous setting.
+extern "C" int pih_set_attention_side_by_side(int on) {
+  const int before = g_attention_side_by_side;
+  g_attention_side_by_side = on ? 1 : 0;
+  return before;
+}
 
 // Returns 0, or the first failing kernel's code (PIH_ERR_* or a cudaError_t; 1000 + n: the library product failed
 // with status n), with whatever was launched before it left queued.
@@ -262,17 +294,37 @@ extern "C" int pih_prenorm_attention_swiglu_block(const PihStepArgs* sp, const P
     if (a.tensor_cores) {
       int tile_max_q = a.tile_max_q;
       if (tile_max_q > 0 && a.tcgen05_prefill && b->kv_map != nullptr) {
+        if (a.dec_cap > 0 && g_attention_side_by_side) {       // the fork for the decoding requests' kernel (below)
+          Fork* fork = side_stream();
+          if (fork != nullptr && cudaEventRecord(fork->forked, static_cast<cudaStream_t>(s.stream)) != cudaSuccess)
+            return PIH_ERR_UNSUPPORTED;
+        }
         PIH_TRY(pih_attention_prefill_tcgen05(b->qkv, b->qkv_cols, T, b->attn, a.block_table, a.table_width, s.cu_q, s.q_start,
                                               s.num_requests, tile_max_q, b->heads, b->kv_heads, D, a.page_size,
                                               a.num_pages, b->scale, b->window, b->kv_map, s.error, s.stream));
         tile_max_q = 0;
       }
-      if (tile_max_q > 0 || a.dec_cap > 0)
+      if (tile_max_q > 0 || a.dec_cap > 0) {
+        // A mixed step's decoding requests are other requests than its prompt portions, and their kernel other SMs'
+        // work (a block of the prompt kernel fills an SM's shared memory): it runs beside the prompt kernel, in a
+        // stream that forks from this one behind the q/k kernel and joins it again before the output projection.
+        Fork* fork = (a.tile_max_q > 0 && tile_max_q == 0 && a.dec_cap > 0 && g_attention_side_by_side) ? side_stream() : nullptr;
+        void* stream = s.stream;
+        if (fork != nullptr) {
+          if (cudaStreamWaitEvent(fork->stream, fork->forked, 0) != cudaSuccess) return PIH_ERR_UNSUPPORTED;
+          stream = fork->stream;
+        }
         PIH_TRY(pih_paged_attention_mma(b->qkv, b->qkv_cols, b->attn, b->kv_cache, a.block_table, a.table_width, s.cu_q,
                                         s.q_start, T, s.num_requests, tile_max_q, a.dec_cap, a.dec_ctx, b->heads,
                                         b->kv_heads, D, a.page_size, a.num_pages, b->scale, b->window, a.split, a.nsplits,
                                         s.max_ctx_ptr, a.dec_cap > 0 ? a.scratch : nullptr,
-                                        (a.tma_split && a.dec_cap > 0) ? b->kv_map : nullptr, s.error, s.stream));
+                                        (a.tma_split && a.dec_cap > 0) ? b->kv_map : nullptr, s.error, stream));
+        if (fork != nullptr) {
+          if (cudaEventRecord(fork->joined, fork->stream) != cudaSuccess ||
+              cudaStreamWaitEvent(static_cast<cudaStream_t>(s.stream), fork->joined, 0) != cudaSuccess)
+            return PIH_ERR_UNSUPPORTED;
+        }
+      }
     } else {
       PIH_TRY(pih_paged_attention_generic(s.dtype, b->qkv, b->qkv_cols, b->attn, b->kv_cache, a.block_table, a.table_width,
                                           s.request_of_row, s.positions, T, b->heads, b->kv_heads, D, a.page_size,
