@@ -169,6 +169,9 @@ def main() -> int:
                 fn = lambda: ops.linear_skinny(x, w, delta=d, norm_weight=nw, eps=1e-6, swiglu=args.fused == "swiglu")
             elif args.impl == "skinny":
                 fn = lambda: ops.linear_skinny(x, w)
+            elif args.impl == "library" and args.out_f32:
+                rates["bytes"] += 2 * args.m * args.n
+                fn = lambda: torch.mm(x, w.t(), out_dtype=torch.float32)
             elif args.impl == "library":
                 fn = lambda: torch.mm(x, w.t())
             elif args.out_f32:

@@ -167,6 +167,24 @@ def test_linear_skinny(ops, M, N, K):
     assert torch.equal(ops.linear_skinny(few.contiguous(), w)[-1], out[M - 1])
 
 
+@pytest.mark.parametrize("M", [1, 5, 8, 11, 16, 17])
+@pytest.mark.parametrize("N,K", [(151936, 1024), (100003, 2048), (80000, 96)])
+def test_the_head_of_a_decode_step(ops, M, N, K):
+    """The product with a vocabulary of weight rows and a 32-bit result against float64: up to 8 token rows by the
+    kernel that streams the weights straight into MMA operands (a last granule that is not full), more rows by the
+    library (faster there); among up to 8 rows a row gives the same bits as alone."""
+    x = _rand((M, K), torch.bfloat16, 3)
+    w = _rand((N, K), torch.bfloat16, 4, 0.1)
+    out = ops.linear(x, w, out_dtype=torch.float32)
+    ops.check_errors()
+    assert out.dtype == torch.float32 and out.shape == (M, N)
+    ref = x.cpu().double() @ w.cpu().double().T
+    torch.testing.assert_close(out.cpu().double(), ref, rtol=1e-4, atol=2e-5 * max(1.0, float(ref.abs().max())))
+    if M <= 8:
+        alone = ops.linear(x[M - 1:].contiguous(), w, out_dtype=torch.float32)
+        assert torch.equal(alone[0], out[M - 1])
+
+
 @pytest.mark.parametrize("M", [1, 8, 13])
 @pytest.mark.parametrize("N,K", [(1024, 2048), (1024, 3072), (151, 96), (1000, 1024)])
 def test_linear_skinny_adds_the_residual_in_its_epilogue(ops, M, N, K):
