@@ -107,6 +107,8 @@ def main() -> int:
     H, KV, D, P = args.heads, args.kv_heads, args.head_dim, args.page
     ops.attention_split = args.split
     ops.tma_attention = not args.no_tma
+    if args.impl == "skinny":
+        ops.set_skinny_rule(False)                    # the kernel itself, also where the engine would not use it
     if args.tickets:
         ops.set_attention_cluster_merge(False)
     elif args.fetched_merge:

@@ -571,9 +571,19 @@ static bool skinny_takes(const void* x, const void* W, int M, int K, long long l
          (reinterpret_cast<uintptr_t>(x) & 15) == 0 && (reinterpret_cast<uintptr_t>(W) & 15) == 0;
 }
 
+int g_skinny_rule = 1;
+
 }  // namespace pih
 
 using namespace pih;
+
+// 1 (the default): pih_gemm_skinny declines the shapes for which the library's product is the faster way; 0: it takes
+// every shape it can (for measurements of the kernel itself).  Returns the previous setting.
+extern "C" int pih_set_skinny_rule(int on) {
+  const int before = pih::g_skinny_rule;
+  pih::g_skinny_rule = on ? 1 : 0;
+  return before;
+}
 
 // bf16 only.  M <= 16 rows; K a multiple of 32; x rows, W rows and out rows 16-byte aligned.
 //   delta      nullable: the rows are round(x + delta), as the fused add of a pre-norm block; the sums are also
@@ -592,6 +602,18 @@ extern "C" int pih_gemm_skinny(const void* x, const void* delta, void* x_out, in
       (reinterpret_cast<uintptr_t>(norm_w) & 15) || residual == out || (norm_w != nullptr && K % 8) ||
       (delta != nullptr && ((reinterpret_cast<uintptr_t>(delta) & 15) || x_out == nullptr || x_out == x)))
     return PIH_ERR_UNSUPPORTED;
+  // Where the library's product with the separate norm, SiLU-mul and add kernels is the faster way (measured at the
+  // Qwen3-0.6B, 1.7B and 8B layer sizes, 8 and 16 rows, weights larger than L2 between calls), the caller is sent there:
+  // up to 8 rows this kernel wins until a block's share of the weights passes what shared memory holds several times
+  // (gate/up 24576 x 4096: 46 against 36 + 5 us) or the norm of rows of 4096 is repeated by every block (q/k/v 6144 x
+  // 4096: 16.4 against 11.8 + 3); with 9 to 16 rows only at the smallest sizes (6144 x 1024: 7.2 against 5.8 + 5;
+  // 12288 x 2048: 21.9 against 11.7 + 5; 6144 x 4096: 26.5 against 12.8 + 3).
+  if (g_skinny_rule) {
+    const long long weight_bytes = static_cast<long long>(N) * K * 2;
+    const bool slower = M <= 8 ? (weight_bytes > (64ll << 20) || (norm_w != nullptr && K >= 4096))
+                               : weight_bytes > (13ll << 20);
+    if (slower) return PIH_ERR_UNSUPPORTED;
+  }
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   SkinnyParams p = {};
   p.x = static_cast<const __nv_bfloat16*>(x);

@@ -104,7 +104,7 @@ class CudaOps:
                      "pih_sample", "pih_selected_logprob", "pih_top_logprobs", "pih_paged_attention_mma", "pih_gemm_tcgen05", "pih_make_kv_tensor_map",
                      "pih_attention_prefill_tcgen05", "pih_gemm_skinny", "pih_set_dependent_launch", "pih_set_attention_cluster_merge",
                      "pih_gemm_skinny_f32out",
-                     "pih_qk_attention_fused", "pih_gemm_tcgen05_pair", "pih_set_attention_side_by_side"):
+                     "pih_qk_attention_fused", "pih_gemm_tcgen05_pair", "pih_set_attention_side_by_side", "pih_set_skinny_rule"):
             getattr(lib, name).restype = c_int
         lib.pih_attention_scratch_floats.restype = c_ll
         lib.pih_top_logprobs_scratch_words.restype = c_ll
@@ -128,6 +128,11 @@ class CudaOps:
         (programmatic dependent launch; the default).  Returns the previous setting.  The setting is the
         library's, not this object's; CUDA graphs keep the setting they were captured under."""
         return bool(self.lib.pih_set_dependent_launch(1 if on else 0))
+
+    def set_skinny_rule(self, on: bool) -> bool:
+        """Whether the few-rows product declines the shapes for which the library's product with the separate
+        kernels is faster (the default) or takes every shape it can.  Returns the previous setting (the library's)."""
+        return bool(self.lib.pih_set_skinny_rule(1 if on else 0))
 
     def set_attention_side_by_side(self, on: bool) -> bool:
         """Whether, in a step with prompt portions and decoding requests, native blocks run the two attention
