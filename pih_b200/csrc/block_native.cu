@@ -296,8 +296,10 @@ extern "C" int pih_prenorm_attention_swiglu_block(const PihStepArgs* sp, const P
       if (tile_max_q > 0 && a.tcgen05_prefill && b->kv_map != nullptr) {
         if (a.dec_cap > 0 && g_attention_side_by_side) {       // the fork for the decoding requests' kernel (below)
           Fork* fork = side_stream();
-          if (fork != nullptr && cudaEventRecord(fork->forked, static_cast<cudaStream_t>(s.stream)) != cudaSuccess)
-            return PIH_ERR_UNSUPPORTED;
+          if (fork != nullptr) {
+            const cudaError_t e = cudaEventRecord(fork->forked, static_cast<cudaStream_t>(s.stream));
+            if (e != cudaSuccess) return static_cast<int>(e);
+          }
         }
         PIH_TRY(pih_attention_prefill_tcgen05(b->qkv, b->qkv_cols, T, b->attn, a.block_table, a.table_width, s.cu_q, s.q_start,
                                               s.num_requests, tile_max_q, b->heads, b->kv_heads, D, a.page_size,
@@ -311,7 +313,8 @@ extern "C" int pih_prenorm_attention_swiglu_block(const PihStepArgs* sp, const P
         Fork* fork = (a.tile_max_q > 0 && tile_max_q == 0 && a.dec_cap > 0 && g_attention_side_by_side) ? side_stream() : nullptr;
         void* stream = s.stream;
         if (fork != nullptr) {
-          if (cudaStreamWaitEvent(fork->stream, fork->forked, 0) != cudaSuccess) return PIH_ERR_UNSUPPORTED;
+          const cudaError_t e = cudaStreamWaitEvent(fork->stream, fork->forked, 0);
+          if (e != cudaSuccess) return static_cast<int>(e);
           stream = fork->stream;
         }
         PIH_TRY(pih_paged_attention_mma(b->qkv, b->qkv_cols, b->attn, b->kv_cache, a.block_table, a.table_width, s.cu_q,
@@ -320,9 +323,9 @@ extern "C" int pih_prenorm_attention_swiglu_block(const PihStepArgs* sp, const P
                                         s.max_ctx_ptr, a.dec_cap > 0 ? a.scratch : nullptr,
                                         (a.tma_split && a.dec_cap > 0) ? b->kv_map : nullptr, s.error, stream));
         if (fork != nullptr) {
-          if (cudaEventRecord(fork->joined, fork->stream) != cudaSuccess ||
-              cudaStreamWaitEvent(static_cast<cudaStream_t>(s.stream), fork->joined, 0) != cudaSuccess)
-            return PIH_ERR_UNSUPPORTED;
+          cudaError_t e = cudaEventRecord(fork->joined, fork->stream);
+          if (e == cudaSuccess) e = cudaStreamWaitEvent(static_cast<cudaStream_t>(s.stream), fork->joined, 0);
+          if (e != cudaSuccess) return static_cast<int>(e);
         }
       }
     } else {
