@@ -204,6 +204,11 @@ class Engine:
         for t in prompt:
             if not 0 <= t < vocab:
                 raise ValueError(f"token id {t} is outside the vocabulary of {vocab}")
+        # as many ids as are asked for must be left beside the suppressed ones (plugins/model-qwen3/qwen3_sampler.cpp:46-49)
+        stops = len(set(params.stop_token_ids) | set(self.model.spec.eos_token_ids))
+        if params.top_logprobs > vocab - stops:
+            raise ValueError(f"top_logprobs of {params.top_logprobs} is more than a vocabulary of {vocab} leaves "
+                             f"beside {stops} ids that may be suppressed")
         rid = next(self._ids) if rid is None else rid
         if rid in self._live:
             raise ValueError(f"request {rid!r} is already live")

@@ -202,4 +202,11 @@ def test_the_most_probable_ids_come_back_with_the_tokens(model_dirs, tiny_config
         SamplingParams(top_logprobs=3)
     with pytest.raises(ValueError):
         SamplingParams(logprobs=True, top_logprobs=21)
+    # more ids than the vocabulary leaves beside those that may be suppressed: refused when the request is handed in
+    tiny = _engine(model_dirs["A"], False, page_size=16)
+    import dataclasses
+    tiny.model.spec = dataclasses.replace(tiny.model.spec, vocab=12)       # (only what submit looks at)
+    with pytest.raises(ValueError, match="top_logprobs"):
+        tiny.submit([1, 2, 3], SamplingParams(logprobs=True, top_logprobs=12))
+    assert not tiny.has_work()
 
