@@ -44,7 +44,6 @@ def main(argv=None) -> int:
     if args.max_tokens < 1:
         ap.error("--max-tokens must be >= 1")
 
-    import numpy as np
     import torch
     from ..engine.batch import StepEntry
     from ..engine.factory import create_runner

@@ -3,7 +3,6 @@ vocabulary of 151 936; two layers, random weights): the shapes that the benchmar
 configurations never reach — the few-rows products with their fused prologues, the 32-bit-output head, the
 decode attention that norms and rotates for itself and merges as a cluster, the tcgen05 prompt attention."""
 import pytest
-import torch
 
 import plain_impl
 import traces

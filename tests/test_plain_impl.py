@@ -1,7 +1,6 @@
 """The plain implementation checked against hand-derived values and the reference's known answers."""
 import math
 
-import pytest
 import torch
 
 import plain_impl as P
