@@ -6,8 +6,8 @@
 // The reference runs every product through cuBLASLt
 // (src/backend/cuda/gemm_plan.cpp:83-199) and has no kernel of its own.
 //
-// A tile of C is 128 x BN (BN = 64, 128 or 256); the kernel is persistent, one CTA per SM
-// walking over tiles, with two accumulators in tensor memory so that the epilogue of one
+// Two kernels.  gemm_tcgen05_kernel, described here: a tile of C is 128 x BN (BN = 64, 128 or 256); the kernel is
+// persistent, one CTA per SM walking over tiles, with two accumulators in tensor memory so that the epilogue of one
 // tile overlaps the products of the next.  Warp roles:
 //   warp 0      TMA producer: one thread issues the two tile loads of a k-block
 //               (A 128 x 64, W BN x 64) into a ring of STAGES buffers;
@@ -23,7 +23,9 @@
 //
 // Every wait on an mbarrier is bounded; when a bound is hit the kernel records
 // kWaitTimedOut, stops waiting, still frees its tensor memory and returns.
-// No cluster launch and no multicast are used.
+// gemm_tcgen05_pair_kernel, described further down: two CTAs of a cluster on one 256 x BN tile (cta_group::2), the
+// output through TMA stores; it is the one that the engine uses (gate/up of large prompt portions, SiLU-mul fused).
+// Every load of both kernels goes to the shared memory of the CTA that issues it.
 #include "ptx.cuh"
 
 namespace pih {
@@ -280,7 +282,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 // the tensor cores of both SMs read both halves of W: a CTA brings 32 KB per k-block into its shared memory
 // for 256 x 256 x 64 of product per pair, where a single CTA on a 128 x 256 tile brings 48 KB for half of
 // that — the shared-memory port, which carries the TMA writes and the operand reads, is what bounded the
-// single-CTA kernel (tensor pipe 52 % busy).  No load is multicast.
+// single-CTA kernel (tensor pipe 52 % busy).  Every load goes to the shared memory of the CTA that issues it.
 //   CTA 0 of the pair (the leader): its MMA thread issues every tcgen05.mma for both SMs, and commits them
 //       to the "empty" barrier of the stage and to the "accumulator full" barrier in BOTH CTAs;
 //   both CTAs: the producer thread loads the CTA's own halves into its own ring; the loads of both CTAs
