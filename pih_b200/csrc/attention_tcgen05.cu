@@ -237,8 +237,6 @@ template <int THREADS> __device__ __forceinline__ void first_set_sync() {
 template <int D, int SPLIT>
 __global__ void __launch_bounds__(256 * SPLIT + 128)
 attn_prefill_tcgen05_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap kv_map) {
-  wait_for_prior_kernels();
-  launch_dependents();                                   // (the next kernel's blocks may become resident and wait)
   using Smem = PrefillSmem<D, SPLIT>;
   constexpr int kSetThreads = 128 * SPLIT;                        // softmax threads of a set
   constexpr int kSetWarps = 4 * SPLIT;
@@ -296,6 +294,11 @@ attn_prefill_tcgen05_kernel(const PrefillParams p, const __grid_constant__ CUten
                  "r"(512));
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::);
   }
+  // Up to here the block has read only what the step's set-up wrote (row ranges, starts: kernels before the one
+  // before this, which has waited for them itself) and taken its tensor memory: that ran beside the end of the
+  // q/k kernel.  Its q rows and the cache are read from here on.
+  wait_for_prior_kernels();
+  launch_dependents();                                   // (the next kernel's blocks may become resident and wait)
 
   for (int item = 0; item < items; ++item) {
     const int qt = item == 0 ? tiles_q - 1 - bx : bx;
